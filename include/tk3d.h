@@ -1,0 +1,173 @@
+/*
+ * tk3d.h -- C ABI of libtk3d_b200.so: the torkit3d neighbour-search / sampling operators,
+ * hand-written for NVIDIA B200 (sm_100a).
+ *
+ * These entry points are what the reference's Python operators bind instead of the nine functions
+ * of its pybind11 module `torkit3d._C` (torkit3d/csrc/torkit3d.cpp:13-21).  Each declaration names
+ * the reference prototype it replaces.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer into the current CUDA device's memory unless stated;
+ *     tensors are dense, row-major ("contiguous") in the shapes written beside them;
+ *   - `dtype` is TK3D_F32 or TK3D_F64 and applies to every `void*` floating-point tensor;
+ *     indices are always int64;
+ *   - the caller allocates and owns every output and scratch buffer; the library allocates no
+ *     device memory, keeps no state between calls and never synchronises the host;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default
+ *     stream) of the device that is current on the calling thread;
+ *   - every output element is written by the call (no pre-zeroing needed);
+ *   - the return value is TK3D_OK or an error code; argument errors are detected before anything
+ *     is launched.  Nothing throws.  tk3d_strerror() names a code, tk3d_last_error() gives the
+ *     calling thread's most recent detailed message (including the CUDA error text for
+ *     TK3D_ERR_CUDA);
+ *   - the squared distance is ((dx*dx + dy*dy) + dz*dz) with dx = ref.x - query.x, every
+ *     operation rounded on its own (no fused multiply-add), so indices are reproducible bit for
+ *     bit; ties always go to the lowest index.
+ */
+#ifndef TK3D_H_
+#define TK3D_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TK3D_F32 0
+#define TK3D_F64 1
+
+#define TK3D_OK 0
+#define TK3D_ERR_NULL 1        /* a required pointer is NULL */
+#define TK3D_ERR_SHAPE 2       /* a size is negative, or too large for the implementation */
+#define TK3D_ERR_K 3           /* k / num_samples out of range for the given cloud */
+#define TK3D_ERR_DTYPE 4       /* dtype is neither TK3D_F32 nor TK3D_F64 */
+#define TK3D_ERR_CUDA 5        /* a CUDA runtime call or kernel launch failed */
+#define TK3D_ERR_SCRATCH 6     /* scratch buffer missing or too small */
+#define TK3D_ERR_UNSUPPORTED 7 /* valid request the library does not implement */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int tk3d_version(void);
+/* Static description of an error code. */
+const char *tk3d_strerror(int code);
+/* Detailed message of the calling thread's last failing call ("" if none). */
+const char *tk3d_last_error(void);
+
+/*
+ * Chamfer forward, both directions in one call.
+ * Replaces chamfer_distance_forward_cuda (torkit3d/csrc/include/chamfer_distance.h:6-8,
+ * torkit3d/csrc/cuda/chamfer_distance_kernel.cu:91-151).
+ *   xyz1 [B,N1,3], xyz2 [B,N2,3]                          in
+ *   dist1 [B,N1], idx1 [B,N1], dist2 [B,N2], idx2 [B,N2]  out (squared distance, arg-min; an empty
+ *                                                         partner cloud gives +inf / -1)
+ *   sums  [2] float64, optional (NULL to skip)            out: sum(dist1), sum(dist2) over the call,
+ *         accumulated in the kernel epilogue so a loss needs no further reduction pass.
+ */
+int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, void *dist1,
+                     int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype, void *stream);
+
+/*
+ * Chamfer backward: gradients w.r.t. both clouds.
+ * Replaces chamfer_distance_backward_cuda (torkit3d/csrc/include/chamfer_distance.h:10-16,
+ * torkit3d/csrc/cuda/chamfer_distance_kernel.cu:200-274).
+ *   grad_dist1 [B,N1], grad_dist2 [B,N2], xyz1, xyz2, idx1, idx2   in
+ *   grad_xyz1 [B,N1,3], grad_xyz2 [B,N2,3]                         out
+ * grad_xyz1[i] = 2 g1[i] (p1_i - p2_idx1[i]) - sum_{j: idx2[j]=i} 2 g2[j] (p2_j - p1_i), and the
+ * mirror image for grad_xyz2.  The scattered terms use floating-point atomics.  Indices outside
+ * [0, partner size) contribute nothing.
+ */
+int tk3d_chamfer_bwd(const void *grad_dist1, const void *grad_dist2, const void *xyz1, const void *xyz2,
+                     const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
+                     void *grad_xyz1, void *grad_xyz2, int dtype, void *stream);
+
+/*
+ * Brute-force k nearest neighbours.
+ * Replaces knn_distance_cuda (torkit3d/csrc/include/knn_distance.h:7-11,
+ * torkit3d/csrc/cuda/knn_distance_kernel.cu:187-298), both of its `version`s.
+ *   query [B,N1,3], key [B,N2,3]                in;  requires 1 <= k <= N2
+ *   distance [B,N1,k] (squared), index [B,N1,k]  out; each row is sorted ascending by
+ *                                                (distance, index).  (The reference leaves rows in
+ *                                                an unspecified order; the retained set is equal.)
+ */
+int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k, void *distance,
+             int64_t *index, int dtype, void *stream);
+
+/*
+ * Farthest point sampling, first sample = point 0, lowest index among exact maxima.
+ * Replaces sample_farthest_points_cuda (torkit3d/csrc/include/sample_farthest_points.h:6-8,
+ * torkit3d/csrc/cuda/sample_farthest_points_kernel.cu:106-165).
+ *   points [B,N,3]   in;  requires 1 <= num_samples <= N
+ *   index  [B,S]     out
+ *   scratch          device buffer of at least tk3d_fps_scratch_bytes(B,N,dtype) bytes (the running
+ *                    minimum distance of clouds too large to keep on chip); may be NULL when that
+ *                    function returns 0.  Contents on entry are ignored.
+ */
+size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype);
+int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t num_samples, int64_t *index, void *scratch,
+             size_t scratch_bytes, int dtype, void *stream);
+
+/*
+ * Ball query: the first k key indices (ascending) with squared distance < radius*radius (radius is
+ * squared in `dtype` after conversion from float); short rows are padded with their first hit, rows
+ * without a hit are all -1.
+ * Replaces ball_query_cuda (torkit3d/csrc/include/ball_query.h:6-10,
+ * torkit3d/csrc/cuda/ball_query_kernel.cu:105-173).
+ *   query [B,N1,3], key [B,N2,3]   in;  k >= 1
+ *   index [B,N1,k]                 out
+ */
+int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
+                    int64_t k, int64_t *index, int dtype, void *stream);
+
+/*
+ * group_points forward: out[b,c,m,j] = in[b,c,index[b,m,j]].
+ * Replaces group_points_forward_cuda (torkit3d/csrc/include/group_points.h:6-8,
+ * torkit3d/csrc/cuda/group_points_kernel.cu:8-31).
+ *   in [B,C,N1], index [B,N2,K]   in
+ *   out [B,C,N2,K]                out
+ * An index outside [0,N1) yields 0 (the reference faults the device instead); when `status` is not
+ * NULL, bit 0 of *status (a device int32 the caller zeroed) is set if any such index was seen.
+ */
+int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K,
+                   void *out, int32_t *status, int dtype, void *stream);
+
+/*
+ * group_points backward: grad_in[b,c,index[b,m,j]] += grad_out[b,c,m,j] (grad_in is zeroed first).
+ * Replaces group_points_backward_cuda (torkit3d/csrc/include/group_points.h:10-13,
+ * torkit3d/csrc/cuda/group_points_kernel.cu:67-114).  Out-of-range indices are skipped and
+ * reported through `status` as above.
+ */
+int tk3d_group_bwd(const void *grad_out, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
+                   int64_t K, void *grad_in, int32_t *status, int dtype, void *stream);
+
+/*
+ * Feature interpolation forward: out[b,c,m] = sum_{i<K} in[b,c,index[b,m,i]] * weight[b,m,i].
+ * Replaces interpolate_forward_cuda (torkit3d/csrc/include/interpolate.h:7-10,
+ * torkit3d/csrc/cuda/interpolate_kernel.cu:49-103).  K must be 3, as in the reference.
+ *   in [B,C,N1], index [B,N2,3], weight [B,N2,3]   in
+ *   out [B,C,N2]                                   out
+ */
+int tk3d_interp_fwd(const void *in, const int64_t *index, const void *weight, int64_t B, int64_t C, int64_t N1,
+                    int64_t N2, int64_t K, void *out, int32_t *status, int dtype, void *stream);
+
+/*
+ * Feature interpolation backward (w.r.t. the features only):
+ * grad_in[b,c,index[b,m,i]] += grad_out[b,c,m] * weight[b,m,i] (grad_in is zeroed first).
+ * Replaces interpolate_backward_cuda (torkit3d/csrc/include/interpolate.h:12-16,
+ * torkit3d/csrc/cuda/interpolate_kernel.cu:147-201).
+ */
+int tk3d_interp_bwd(const void *grad_out, const int64_t *index, const void *weight, int64_t B, int64_t C,
+                    int64_t N1, int64_t N2, int64_t K, void *grad_in, int32_t *status, int dtype, void *stream);
+
+/*
+ * Inverse squared-distance weights of the k nearest neighbours:
+ * inv = 1 / max(d, 1e-10), weight = inv / sum(inv) over the last axis.
+ * Replaces the element-wise PyTorch expressions of FeatureInterpolator.forward
+ * (torkit3d/layers/pointnet2.py:128-130).
+ *   distance [rows,k] (squared) in;  weight [rows,k] out;  1 <= k <= 8
+ */
+int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t k, void *weight, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TK3D_H_ */

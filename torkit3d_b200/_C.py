@@ -1,0 +1,285 @@
+"""Drop-in for the reference's extension module ``torkit3d._C``.
+
+Same nine functions, same argument order, same checks and the same ownership rule (the callee
+allocates the outputs on the inputs' device) as ``torkit3d/csrc/torkit3d.cpp:13-21``; underneath,
+each call goes through the C ABI of libtk3d_b200.so on the current CUDA stream of the tensors'
+device.  float32 and float64 tensors are accepted, indices are int64.
+
+Differences a caller can observe, all deliberate:
+  * ``knn_distance_cuda`` returns every row sorted ascending by (distance, index); the reference
+    leaves the row order unspecified.  ``version`` is validated (0 or 1) and otherwise ignored.
+  * kernels are launched on the current stream of the tensors' device, not on the legacy default
+    stream of whatever device happens to be current.
+  * an out-of-range index in ``group_points`` / ``interpolate`` reads as 0 (forward) or is skipped
+    (backward) instead of aborting the CUDA context with a device-side assert.
+"""
+import torch
+
+from . import _lib
+from ._lib import check, load
+
+
+def _dtype(t):
+    if t.dtype == torch.float32:
+        return _lib.F32
+    if t.dtype == torch.float64:
+        return _lib.F64
+    raise RuntimeError("tk3d: expected a float32 or float64 tensor, got %s" % t.dtype)
+
+
+def _check_cuda_contig(**tensors):
+    for name, t in tensors.items():
+        if not t.is_cuda:
+            raise RuntimeError("%s must be a CUDA tensor." % name)
+        if not t.is_contiguous():
+            raise RuntimeError("%s must be contiguous." % name)
+
+
+def _check_cuda(**tensors):
+    for name, t in tensors.items():
+        if not t.is_cuda:
+            raise RuntimeError("%s must be a CUDA tensor." % name)
+
+
+def _check_eq(a, b, what):
+    if a != b:
+        raise RuntimeError("Check failed: %s (%d vs. %d)" % (what, a, b))
+
+
+def _same_device_dtype(first, *rest, floats=()):
+    for t in rest:
+        if t.device != first.device:
+            raise RuntimeError("tk3d: all tensors must be on the same device")
+    for t in floats:
+        if t.dtype != first.dtype:
+            raise RuntimeError("tk3d: floating-point tensors must share one dtype")
+
+
+def _index(t, name):
+    if t.dtype != torch.int64:
+        raise RuntimeError("%s must be an int64 tensor." % name)
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t):
+    return t.data_ptr() if t.numel() > 0 else (t.data_ptr() or 0)
+
+
+def sample_farthest_points_cuda(points, num_samples):
+    """points [B,N,3] -> index [B,num_samples] int64 (first sample is point 0)."""
+    _check_cuda_contig(points=points)
+    _check_eq(points.dim(), 3, "points.dim() == 3")
+    _check_eq(points.size(2), 3, "points.size(2) == 3")
+    num_samples = int(num_samples)
+    if not num_samples > 0:
+        raise RuntimeError("Check failed: num_samples > 0 (%d vs. 0)" % num_samples)
+    if not points.size(1) >= num_samples:
+        raise RuntimeError("Check failed: points.size(1) >= num_samples (%d vs. %d)" % (points.size(1), num_samples))
+    lib = load()
+    B, N = points.size(0), points.size(1)
+    dt = _dtype(points)
+    with torch.cuda.device(points.device):
+        index = torch.empty((B, num_samples), dtype=torch.int64, device=points.device)
+        need = lib.tk3d_fps_scratch_bytes(B, N, dt)
+        scratch = torch.empty((need,), dtype=torch.uint8, device=points.device) if need else None
+        check(lib.tk3d_fps(_ptr(points), B, N, num_samples, _ptr(index), _ptr(scratch) if need else None, need, dt,
+                           _stream(points)))
+    return index
+
+
+def ball_query_cuda(query, key, radius, max_neighbors):
+    """query [B,N1,3], key [B,N2,3] -> index [B,N1,max_neighbors] int64."""
+    _check_cuda_contig(query=query, key=key)
+    _check_eq(query.dim(), 3, "query.dim() == 3")
+    _check_eq(key.dim(), 3, "key.dim() == 3")
+    _check_eq(query.size(0), key.size(0), "query.size(0) == key.size(0)")
+    _check_eq(query.size(2), 3, "query.size(2) == 3")
+    _check_eq(key.size(2), 3, "key.size(2) == 3")
+    _same_device_dtype(query, key, floats=(key,))
+    lib = load()
+    B, N1, N2 = query.size(0), query.size(1), key.size(1)
+    k = int(max_neighbors)
+    with torch.cuda.device(query.device):
+        index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
+        check(lib.tk3d_ball_query(_ptr(query), _ptr(key), B, N1, N2, float(radius), k, _ptr(index), _dtype(query),
+                                  _stream(query)))
+    return index
+
+
+def group_points_forward_cuda(input, index):
+    """input [B,C,N1], index [B,N2,K] -> [B,C,N2,K]."""
+    _check_cuda(input=input, index=index)
+    _check_eq(input.dim(), 3, "input.dim() == 3")
+    _check_eq(index.dim(), 3, "index.dim() == 3")
+    _check_eq(input.size(0), index.size(0), "input.size(0) == index.size(0)")
+    _index(index, "index")
+    _same_device_dtype(input, index)
+    input, index = input.contiguous(), index.contiguous()
+    lib = load()
+    B, C, N1 = input.shape
+    _, N2, K = index.shape
+    with torch.cuda.device(input.device):
+        out = torch.empty((B, C, N2, K), dtype=input.dtype, device=input.device)
+        check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None, _dtype(input),
+                                 _stream(input)))
+    return out
+
+
+def group_points_backward_cuda(grad_output, index, n1):
+    """grad_output [B,C,N2,K], index [B,N2,K] -> grad_input [B,C,n1]."""
+    _check_cuda_contig(grad_output=grad_output, index=index)
+    _check_eq(grad_output.dim(), 4, "grad_output.dim() == 4")
+    _check_eq(index.dim(), 3, "index.dim() == 3")
+    _check_eq(index.size(0), grad_output.size(0), "index.size(0) == grad_output.size(0)")
+    _check_eq(index.size(1), grad_output.size(2), "index.size(1) == grad_output.size(2)")
+    _check_eq(index.size(2), grad_output.size(3), "index.size(2) == grad_output.size(3)")
+    _index(index, "index")
+    _same_device_dtype(grad_output, index)
+    lib = load()
+    B, C, N2, K = grad_output.shape
+    n1 = int(n1)
+    with torch.cuda.device(grad_output.device):
+        gin = torch.empty((B, C, n1), dtype=grad_output.dtype, device=grad_output.device)
+        check(lib.tk3d_group_bwd(_ptr(grad_output), _ptr(index), B, C, n1, N2, K, _ptr(gin), None,
+                                 _dtype(grad_output), _stream(grad_output)))
+    return gin
+
+
+def _check_interp(a, index, weight, aname):
+    _check_cuda_contig(**{aname: a, "index": index, "weight": weight})
+    _check_eq(a.dim(), 3, aname + ".dim() == 3")
+    _check_eq(index.dim(), 3, "index.dim() == 3")
+    _check_eq(weight.dim(), 3, "weight.dim() == 3")
+    _check_eq(a.size(0), index.size(0), aname + ".size(0) == index.size(0)")
+    _check_eq(a.size(0), weight.size(0), aname + ".size(0) == weight.size(0)")
+    _check_eq(index.size(1), weight.size(1), "index.size(1) == weight.size(1)")
+    _check_eq(index.size(2), weight.size(2), "index.size(2) == weight.size(2)")
+    if index.size(2) != 3:
+        raise RuntimeError("Only support k=3.")
+    _index(index, "index")
+    _same_device_dtype(a, index, weight, floats=(weight,))
+
+
+def interpolate_forward_cuda(input, index, weight):
+    """input [B,C,N1], index/weight [B,N2,3] -> [B,C,N2]."""
+    _check_interp(input, index, weight, "input")
+    lib = load()
+    B, C, N1 = input.shape
+    N2 = index.size(1)
+    with torch.cuda.device(input.device):
+        out = torch.empty((B, C, N2), dtype=input.dtype, device=input.device)
+        check(lib.tk3d_interp_fwd(_ptr(input), _ptr(index), _ptr(weight), B, C, N1, N2, 3, _ptr(out), None,
+                                  _dtype(input), _stream(input)))
+    return out
+
+
+def interpolate_backward_cuda(grad_output, index, weight, n1):
+    """grad_output [B,C,N2], index/weight [B,N2,3] -> grad_input [B,C,n1]."""
+    _check_interp(grad_output, index, weight, "grad_output")
+    _check_eq(grad_output.size(2), index.size(1), "grad_output.size(2) == index.size(1)")
+    lib = load()
+    B, C, N2 = grad_output.shape
+    n1 = int(n1)
+    with torch.cuda.device(grad_output.device):
+        gin = torch.empty((B, C, n1), dtype=grad_output.dtype, device=grad_output.device)
+        check(lib.tk3d_interp_bwd(_ptr(grad_output), _ptr(index), _ptr(weight), B, C, n1, N2, 3, _ptr(gin), None,
+                                  _dtype(grad_output), _stream(grad_output)))
+    return gin
+
+
+def knn_distance_cuda(query, key, k, version=0):
+    """query [B,N1,3], key [B,N2,3] -> [distance [B,N1,k] (squared), index [B,N1,k] int64]."""
+    _check_cuda_contig(query=query, key=key)
+    _check_eq(query.dim(), 3, "query.dim() == 3")
+    _check_eq(query.size(2), 3, "query.size(2) == 3")
+    _check_eq(key.dim(), 3, "key.dim() == 3")
+    _check_eq(key.size(0), query.size(0), "key.size(0) == query.size(0)")
+    k = int(k)
+    if not key.size(1) >= k:
+        raise RuntimeError("Check failed: key.size(1) >= k (%d vs. %d)" % (key.size(1), k))
+    _check_eq(key.size(2), 3, "key.size(2) == 3")
+    if version not in (0, 1):
+        raise RuntimeError("Invalid version")
+    _same_device_dtype(query, key, floats=(key,))
+    lib = load()
+    B, N1, N2 = query.size(0), query.size(1), key.size(1)
+    with torch.cuda.device(query.device):
+        distance = torch.empty((B, N1, k), dtype=query.dtype, device=query.device)
+        index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
+        check(lib.tk3d_knn(_ptr(query), _ptr(key), B, N1, N2, k, _ptr(distance), _ptr(index), _dtype(query),
+                           _stream(query)))
+    return [distance, index]
+
+
+def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None):
+    """xyz1 [B,N1,3], xyz2 [B,N2,3] -> [dist1, idx1, dist2, idx2].
+
+    ``sums`` (optional, a float64 CUDA tensor of 2 elements) receives sum(dist1), sum(dist2); it has
+    no counterpart in the reference and is what the multi-GPU loss helper reduces.
+    """
+    _check_cuda_contig(xyz1=xyz1, xyz2=xyz2)
+    _check_eq(xyz1.dim(), 3, "xyz1.dim() == 3")
+    _check_eq(xyz2.dim(), 3, "xyz2.dim() == 3")
+    _check_eq(xyz1.size(0), xyz2.size(0), "xyz1.size(0) == xyz2.size(0)")
+    _check_eq(xyz1.size(2), 3, "xyz1.size(2) == 3")
+    _check_eq(xyz2.size(2), 3, "xyz2.size(2) == 3")
+    _same_device_dtype(xyz1, xyz2, floats=(xyz2,))
+    lib = load()
+    B, N1, N2 = xyz1.size(0), xyz1.size(1), xyz2.size(1)
+    dev = xyz1.device
+    with torch.cuda.device(dev):
+        dist1 = torch.empty((B, N1), dtype=xyz1.dtype, device=dev)
+        idx1 = torch.empty((B, N1), dtype=torch.int64, device=dev)
+        dist2 = torch.empty((B, N2), dtype=xyz1.dtype, device=dev)
+        idx2 = torch.empty((B, N2), dtype=torch.int64, device=dev)
+        if sums is not None:
+            if not (sums.is_cuda and sums.dtype == torch.float64 and sums.numel() == 2 and sums.is_contiguous()):
+                raise RuntimeError("sums must be a contiguous float64 CUDA tensor with 2 elements")
+        check(lib.tk3d_chamfer_fwd(_ptr(xyz1), _ptr(xyz2), B, N1, N2, _ptr(dist1), _ptr(idx1), _ptr(dist2),
+                                   _ptr(idx2), _ptr(sums) if sums is not None else None, _dtype(xyz1),
+                                   _stream(xyz1)))
+    return [dist1, idx1, dist2, idx2]
+
+
+def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2):
+    """-> [grad_xyz1 [B,N1,3], grad_xyz2 [B,N2,3]]."""
+    _check_cuda_contig(grad_dist1=grad_dist1, grad_dist2=grad_dist2, xyz1=xyz1, xyz2=xyz2, idx1=idx1, idx2=idx2)
+    bs, n1, n2 = grad_dist1.size(0), grad_dist1.size(1), grad_dist2.size(1)
+    _check_eq(grad_dist2.size(0), bs, "grad_dist2.size(0) == bs")
+    _check_eq(xyz1.size(0), bs, "xyz1.size(0) == bs")
+    _check_eq(xyz2.size(0), bs, "xyz2.size(0) == bs")
+    _check_eq(xyz1.size(1), n1, "xyz1.size(1) == n1")
+    _check_eq(xyz2.size(1), n2, "xyz2.size(1) == n2")
+    _check_eq(xyz1.size(2), 3, "xyz1.size(2) == 3")
+    _check_eq(xyz2.size(2), 3, "xyz2.size(2) == 3")
+    _check_eq(idx1.size(0), bs, "idx1.size(0) == bs")
+    _check_eq(idx2.size(0), bs, "idx2.size(0) == bs")
+    _check_eq(idx1.size(1), n1, "idx1.size(1) == n1")
+    _check_eq(idx2.size(1), n2, "idx2.size(1) == n2")
+    _index(idx1, "idx1")
+    _index(idx2, "idx2")
+    _same_device_dtype(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, floats=(grad_dist2, xyz1, xyz2))
+    lib = load()
+    dev = grad_dist1.device
+    with torch.cuda.device(dev):
+        g1 = torch.empty((bs, n1, 3), dtype=grad_dist1.dtype, device=dev)
+        g2 = torch.empty((bs, n2, 3), dtype=grad_dist1.dtype, device=dev)
+        check(lib.tk3d_chamfer_bwd(_ptr(grad_dist1), _ptr(grad_dist2), _ptr(xyz1), _ptr(xyz2), _ptr(idx1),
+                                   _ptr(idx2), bs, n1, n2, _ptr(g1), _ptr(g2), _dtype(grad_dist1),
+                                   _stream(grad_dist1)))
+    return [g1, g2]
+
+
+def three_nn_weight_cuda(distance):
+    """Inverse squared-distance weights over the last axis; [.., k] -> [.., k] (k <= 8)."""
+    _check_cuda_contig(distance=distance)
+    lib = load()
+    k = distance.size(-1)
+    with torch.cuda.device(distance.device):
+        w = torch.empty_like(distance)
+        check(lib.tk3d_three_nn_weight(_ptr(distance), distance.numel() // max(k, 1), k, _ptr(w), _dtype(distance),
+                                       _stream(distance)))
+    return w

@@ -1,0 +1,62 @@
+"""ctypes binding of libtk3d_b200.so (the C ABI declared in include/tk3d.h).
+
+The library is the product: there is no fallback.  If it is missing, or a call is made without a
+CUDA device, the operators raise instead of computing anything on the CPU.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libtk3d_b200.so")
+
+F32, F64 = 0, 1
+
+_i64 = ctypes.c_int64
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+
+# name -> (restype, argtypes); mirrors include/tk3d.h one to one
+SIGNATURES = {
+    "tk3d_version": (_int, []),
+    "tk3d_strerror": (ctypes.c_char_p, [_int]),
+    "tk3d_last_error": (ctypes.c_char_p, []),
+    "tk3d_chamfer_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
+    "tk3d_chamfer_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_knn": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_fps_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _int]),
+    "tk3d_fps": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, ctypes.c_size_t, _int, _vp]),
+    "tk3d_ball_query": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _i64, _vp, _int, _vp]),
+    "tk3d_group_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_group_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_interp_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_three_nn_weight": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library (once) and attach the prototypes.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "libtk3d_b200.so is not built (expected at %s). Run `python -m torkit3d_b200.build`; "
+            "there is no CPU or PyTorch fallback." % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(rc):
+    """Turn a non-zero status into RuntimeError (what TORCH_CHECK raises in the reference)."""
+    if rc != 0:
+        lib = load()
+        detail = lib.tk3d_last_error().decode()
+        raise RuntimeError("tk3d: %s%s" % (lib.tk3d_strerror(rc).decode(), (": " + detail) if detail else ""))

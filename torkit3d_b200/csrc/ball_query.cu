@@ -1,0 +1,183 @@
+// Ball query: first k key indices (ascending) whose squared distance is < radius^2.
+//
+// fp32 fast path: the filter-then-verify sweep of sweep.cuh with a constant bound (radius^2).  A
+// verified hit is written straight to the output row; a query stops testing once it has k hits
+// (its threshold becomes -inf) and the block leaves the key loop as soon as all its queries are
+// full -- the reference keeps scanning to the end of the cloud.  Short rows are padded with the
+// first hit, rows without a hit are filled with -1, so every output element is written here.
+#include "sweep.cuh"
+
+namespace tk3d {
+
+namespace {
+
+constexpr int BQ_THREADS = 128;
+constexpr int BQ_TILE = 512;
+
+__global__ void __launch_bounds__(BQ_THREADS)
+ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
+                       float r2, int k, int64_t *__restrict__ index, int64_t blocks_total) {
+  constexpr int PER = BQ_TILE / BQ_THREADS;
+  __shared__ float4 tile[2][BQ_TILE];
+  const int tid = threadIdx.x;
+  const int chunks = (N1 + BQ_THREADS - 1) / BQ_THREADS;
+
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int64_t b = blk / chunks;
+    const int i = (int)(blk % chunks) * BQ_THREADS + tid;
+    const bool valid = i < N1;
+    float qx = 0.f, qy = 0.f, qz = 0.f;
+    if (valid) {
+      const float *q = query + (b * N1 + i) * 3;
+      qx = q[0];
+      qy = q[1];
+      qz = q[2];
+    }
+    const float mx = -2.f * qx, my = -2.f * qy, mz = -2.f * qz;
+    const float never = __int_as_float(0xff800000);
+    float thr = valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never;
+    int cnt = 0;
+    int64_t first = -1;
+    int64_t *row = index + (b * N1 + (valid ? i : 0)) * (int64_t)k;
+
+    const float *rb = key + b * (int64_t)N2 * 3;
+    const int ntiles = (N2 + BQ_TILE - 1) / BQ_TILE;
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+      const int u = tid + p * BQ_THREADS;
+      float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
+      if (u < N2) {
+        const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
+        v = make_float4(x, y, z, sweep_key_w(x, y, z));
+      }
+      tile[0][u] = v;
+    }
+    __syncthreads();
+
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = t * BQ_TILE;
+      const float4 *tl = tile[t & 1];
+      const bool more = t + 1 < ntiles;
+      float4 nxt[PER];
+      if (more) {
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+          const int j = t0 + BQ_TILE + tid + p * BQ_THREADS;
+          float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
+          if (j < N2) {
+            const float x = rb[(int64_t)j * 3 + 0], y = rb[(int64_t)j * 3 + 1], z = rb[(int64_t)j * 3 + 2];
+            v = make_float4(x, y, z, sweep_key_w(x, y, z));
+          }
+          nxt[p] = v;
+        }
+      }
+      const int lim = (min(BQ_TILE, N2 - t0) + 3) & ~3;
+#pragma unroll 4
+      for (int u = 0; u < lim; ++u) {
+        const float4 r = tl[u];
+        const float a = fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
+        if (__builtin_expect(!(a >= thr), 0)) {
+          const int j = t0 + u;
+          if (j < N2 && cnt < k && thr != never) {
+            const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
+            if (d < r2) {
+              row[cnt] = j;
+              if (cnt == 0) first = j;
+              if (++cnt == k) thr = never;
+            }
+          }
+        }
+      }
+      if (more) {
+        float4 *nx = tile[(t + 1) & 1];
+#pragma unroll
+        for (int p = 0; p < PER; ++p) nx[tid + p * BQ_THREADS] = nxt[p];
+      }
+      // One barrier per tile; it also votes on "every query of this block is complete".
+      if (__syncthreads_and(!valid || cnt == k)) break;
+    }
+    if (valid)
+      for (int c = cnt; c < k; ++c) row[c] = first;
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
+                          T r2, int64_t k, int64_t *__restrict__ index, int64_t blocks_total) {
+  constexpr int TILE = 256;
+  __shared__ T sx[TILE], sy[TILE], sz[TILE];
+  const int tid = threadIdx.x;
+  const int64_t chunks = (N1 + TILE - 1) / TILE;
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int64_t b = blk / chunks;
+    const int64_t i = (blk % chunks) * TILE + tid;
+    const bool valid = i < N1;
+    T qx = 0, qy = 0, qz = 0;
+    if (valid) {
+      const T *q = query + (b * N1 + i) * 3;
+      qx = q[0];
+      qy = q[1];
+      qz = q[2];
+    }
+    int64_t *row = index + (b * N1 + (valid ? i : 0)) * k;
+    int64_t cnt = 0, first = -1;
+    const T *rb = key + b * N2 * 3;
+    for (int64_t t0 = 0; t0 < N2; t0 += TILE) {
+      const int64_t jl = t0 + tid;
+      if (jl < N2) {
+        sx[tid] = rb[jl * 3 + 0];
+        sy[tid] = rb[jl * 3 + 1];
+        sz[tid] = rb[jl * 3 + 2];
+      }
+      __syncthreads();
+      const int lim = (int)((N2 - t0) < TILE ? (N2 - t0) : TILE);
+      if (valid && cnt < k) {
+        for (int u = 0; u < lim && cnt < k; ++u) {
+          const T d = sqdist<T>(sx[u], sy[u], sz[u], qx, qy, qz);
+          if (d < r2) {
+            row[cnt] = t0 + u;
+            if (cnt == 0) first = t0 + u;
+            ++cnt;
+          }
+        }
+      }
+      if (__syncthreads_and(!valid || cnt == k)) break;
+    }
+    if (valid)
+      for (int64_t c = cnt; c < k; ++c) row[c] = first;
+    __syncthreads();
+  }
+}
+
+}  // namespace
+}  // namespace tk3d
+
+using namespace tk3d;
+
+extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
+                               int64_t k, int64_t *index, int dtype, void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "ball_query: dtype %d", dtype);
+  TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "ball_query: negative size");
+  TK3D_REQUIRE(k >= 1 && k < (1LL << 31), TK3D_ERR_K, "ball_query: max_neighbors must be >= 1 (got %lld)",
+               (long long)k);
+  TK3D_REQUIRE(N1 < (1LL << 30) && N2 < (1LL << 30), TK3D_ERR_SHAPE, "ball_query: clouds limited to 2^30 points");
+  if (B * N1 == 0) return TK3D_OK;
+  TK3D_REQUIRE(query && index && (key || N2 == 0), TK3D_ERR_NULL, "ball_query: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == TK3D_F32) {
+    const float r2 = radius * radius;  // squared in fp32, as the reference does for float tensors
+    const int64_t total = B * ((N1 + BQ_THREADS - 1) / BQ_THREADS);
+    const int64_t cap = (int64_t)sm_count() * 256;
+    ball_query_fast_kernel<<<(unsigned)(total < cap ? total : cap), BQ_THREADS, 0, st>>>(
+        (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, index, total);
+    return check_launch("ball_query_fast_kernel");
+  }
+  const double r = (double)radius;
+  const int64_t total = B * ((N1 + 255) / 256);
+  const int64_t cap = (int64_t)sm_count() * 64;
+  ball_query_generic_kernel<double><<<(unsigned)(total < cap ? total : cap), 256, 0, st>>>(
+      (const double *)query, (const double *)key, B, N1, N2, r * r, k, index, total);
+  return check_launch("ball_query_generic_kernel");
+}

@@ -1,0 +1,205 @@
+// Chamfer forward, fp32 fast path: register-tiled filter-then-verify sweep (see sweep.cuh).
+//
+// A block of 128 threads owns 128*Q query points (Q per thread, 128 apart so loads and stores
+// coalesce) of one cloud and sweeps the whole partner cloud in 512-point tiles.  A tile is staged
+// in shared memory as float4 (x, y, z, w): every lane reads the same 16 bytes (one broadcast
+// LDS.128 per key point serves Q pairs).  The next tile's coordinates are fetched into registers
+// before the current tile is processed and written to the other buffer afterwards, so global
+// latency hides behind the arithmetic with a single barrier per tile.
+//
+// Per pair the hot loop issues 3 FFMA + 1 FSETP; the exactly rounded distance is recomputed only
+// for pairs that pass the filter (about ln(M) + a few per query), and the running minimum is
+// updated with a strict "<" in ascending key order, so the lowest index wins ties.
+//
+// Both directions run in one launch; each block adds its partial sum of distances to `sums`.
+#include "sweep.cuh"
+
+namespace tk3d {
+
+namespace {
+
+constexpr int CF_THREADS = 128;
+constexpr int CF_TILE = 512;
+
+template <int Q>
+__global__ void __launch_bounds__(CF_THREADS)
+chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int64_t B, int N1, int N2,
+                        float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
+                        int64_t *__restrict__ idx2, double *__restrict__ sums, int64_t blocks1,
+                        int64_t blocks_total) {
+  constexpr int PER = CF_TILE / CF_THREADS;
+  __shared__ float4 tile[2][CF_TILE];
+  __shared__ double ssum[CF_THREADS / 32];
+  const int tid = threadIdx.x;
+
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int dir = blk >= blocks1;
+    const int64_t id = dir ? blk - blocks1 : blk;
+    const float *qpts = dir ? xyz2 : xyz1;
+    const float *rpts = dir ? xyz1 : xyz2;
+    const int nq = dir ? N2 : N1;
+    const int nr = dir ? N1 : N2;
+    const int chunks = (nq + CF_THREADS * Q - 1) / (CF_THREADS * Q);
+    const int64_t b = id / chunks;
+    const int i0 = (int)(id % chunks) * (CF_THREADS * Q) + tid;
+
+    float qx[Q], qy[Q], qz[Q], mx[Q], my[Q], mz[Q], thr[Q], best[Q];
+    int arg[Q];
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      const int i = i0 + s * CF_THREADS;
+      best[s] = __int_as_float(0x7f800000);
+      arg[s] = -1;
+      if (i < nq) {
+        const float *q = qpts + (b * nq + i) * 3;
+        qx[s] = q[0];
+        qy[s] = q[1];
+        qz[s] = q[2];
+        thr[s] = best[s];  // +inf: everything passes until a first candidate is verified
+      } else {
+        qx[s] = qy[s] = qz[s] = 0.f;
+        thr[s] = __int_as_float(0xff800000);  // -inf: never passes
+      }
+      mx[s] = -2.f * qx[s];
+      my[s] = -2.f * qy[s];
+      mz[s] = -2.f * qz[s];
+    }
+
+    const float *rb = rpts + b * (int64_t)nr * 3;
+    const int ntiles = (nr + CF_TILE - 1) / CF_TILE;
+
+    // Prologue: stage tile 0 (padded to the full tile with points that cannot pass).
+    if (ntiles > 0) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        const int u = tid + p * CF_THREADS;
+        float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
+        if (u < nr) {
+          const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
+          v = make_float4(x, y, z, sweep_key_w(x, y, z));
+        }
+        tile[0][u] = v;
+      }
+    }
+    __syncthreads();
+
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = t * CF_TILE;
+      const int cnt = min(CF_TILE, nr - t0);
+      const float4 *tl = tile[t & 1];
+
+      // Fetch the next tile's coordinates into registers.
+      float px[PER], py[PER], pz[PER];
+      const bool more = t + 1 < ntiles;
+      if (more) {
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+          const int j = t0 + CF_TILE + tid + p * CF_THREADS;
+          if (j < nr) {
+            px[p] = rb[(int64_t)j * 3 + 0];
+            py[p] = rb[(int64_t)j * 3 + 1];
+            pz[p] = rb[(int64_t)j * 3 + 2];
+          } else {
+            px[p] = py[p] = pz[p] = __int_as_float(0x7fc00000);  // marks "no point"
+          }
+        }
+      }
+
+      const int lim = (cnt + 3) & ~3;
+#pragma unroll 4
+      for (int u = 0; u < lim; ++u) {
+        const float4 r = tl[u];
+        bool pass = false;
+#pragma unroll
+        for (int s = 0; s < Q; ++s) {
+          const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
+          pass |= !(a >= thr[s]);
+        }
+        if (__builtin_expect(pass, 0)) {
+          const int j = t0 + u;
+          if (j < nr) {
+#pragma unroll
+            for (int s = 0; s < Q; ++s) {
+              const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
+              if (!(a >= thr[s])) {
+                const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
+                if (d < best[s]) {
+                  best[s] = d;
+                  arg[s] = j;
+                  thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
+                }
+              }
+            }
+          }
+        }
+      }
+
+      if (more) {
+        float4 *nx = tile[(t + 1) & 1];
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+          const int u = tid + p * CF_THREADS;
+          float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
+          if (t0 + CF_TILE + u < nr) v = make_float4(px[p], py[p], pz[p], sweep_key_w(px[p], py[p], pz[p]));
+          nx[u] = v;
+        }
+      }
+      __syncthreads();
+    }
+
+    float *dist = dir ? dist2 : dist1;
+    int64_t *idx = dir ? idx2 : idx1;
+    double part = 0.0;
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      const int i = i0 + s * CF_THREADS;
+      if (i < nq) {
+        dist[b * nq + i] = best[s];
+        idx[b * nq + i] = (int64_t)arg[s];
+        part += (double)best[s];
+      }
+    }
+    if (sums != nullptr) {
+      part = warp_sum(part);
+      if ((tid & 31) == 0) ssum[tid >> 5] = part;
+      __syncthreads();
+      if (tid == 0) {
+        double tot = 0;
+#pragma unroll
+        for (int w = 0; w < CF_THREADS / 32; ++w) tot += ssum[w];
+        atomicAdd(sums + dir, tot);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <int Q>
+int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
+           float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+  const int64_t per = CF_THREADS * Q;
+  const int64_t blocks1 = B * ((N1 + per - 1) / per), blocks2 = B * ((N2 + per - 1) / per);
+  const int64_t total = blocks1 + blocks2;
+  if (total == 0) return TK3D_OK;
+  const int64_t cap = (int64_t)sm_count() * 256;
+  const unsigned grid = (unsigned)(total < cap ? total : cap);
+  chamfer_fwd_fast_kernel<Q><<<grid, CF_THREADS, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
+                                                           blocks1, total);
+  return check_launch("chamfer_fwd_fast_kernel");
+}
+
+}  // namespace
+
+int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_t N1, int64_t N2, float *dist1,
+                         int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+  // Queries per thread: more register tiling when there is enough work to fill the GPU with it.
+  const int64_t queries = B * (N1 + N2);
+  const int64_t sms = sm_count();
+  if (queries >= sms * 4 * CF_THREADS * 4)
+    return launch<4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+  if (queries >= sms * 2 * CF_THREADS * 2)
+    return launch<2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+  return launch<1>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+}
+
+}  // namespace tk3d

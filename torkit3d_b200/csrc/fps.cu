@@ -1,0 +1,238 @@
+// Farthest point sampling.
+//
+// The algorithm is a chain of S-1 dependent steps per cloud (update every point's distance to the
+// selected set, pick the arg-max), so the design goal is latency per step, not bandwidth:
+//
+//  * fp32, N <= 8192 ("resident" kernel): one persistent CTA per cloud keeps every point and its
+//    running minimum distance in REGISTERS for the whole call (up to 8 points per thread), plus a
+//    copy of the coordinates in shared memory from which the newly selected point is broadcast.
+//    A step is: P exact distance updates per thread, a warp arg-max with two REDUX instructions,
+//    one shared-memory exchange between warps (double-buffered slots, a single __syncthreads),
+//    and the same two REDUX again so every warp learns the winner without a second barrier.
+//  * any other case ("streaming" kernel, also fp64): points are re-read from global memory (L1/L2
+//    resident) and the running minimum lives in a caller-provided global scratch array.
+//
+// Arg-max rule: highest running minimum distance, lowest index among exact ties.  Distances are
+// non-negative, so their IEEE bit patterns order like unsigned integers and the pair
+// (distance bits, ~index) can be maximised with integer reductions.
+#include "tk3d_common.cuh"
+
+namespace tk3d {
+
+namespace {
+
+constexpr int FPS_MAX_THREADS = 1024;
+
+// Block-wide arg-max of (bits, inv) pairs, lexicographic.  `slots` points at 2*32 uint32 words
+// that are not reused until the next-but-one call (callers alternate two slot sets).
+__device__ __forceinline__ void block_argmax(unsigned &bits, unsigned &inv, unsigned *slots, int nwarps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned hb = __reduce_max_sync(0xffffffffu, bits);
+  unsigned hi = __reduce_max_sync(0xffffffffu, bits == hb ? inv : 0u);
+  if (nwarps > 1) {
+    if (lane == 0) {
+      slots[warp] = hb;
+      slots[32 + warp] = hi;
+    }
+    __syncthreads();
+    const unsigned b2 = lane < nwarps ? slots[lane] : 0u;
+    const unsigned i2 = lane < nwarps ? slots[32 + lane] : 0u;
+    hb = __reduce_max_sync(0xffffffffu, b2);
+    hi = __reduce_max_sync(0xffffffffu, b2 == hb ? i2 : 0u);
+  }
+  bits = hb;
+  inv = hi;
+}
+
+// ---- resident kernel (fp32) ------------------------------------------------------------------
+template <int P>
+__global__ void __launch_bounds__(FPS_MAX_THREADS)
+fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__restrict__ index) {
+  extern __shared__ float sxyz[];  // [3*N] copy of the cloud, array-of-structures
+  __shared__ unsigned slots[2][64];
+  const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+  const float *pts = points + (int64_t)blockIdx.x * N * 3;
+  int64_t *out = index + (int64_t)blockIdx.x * S;
+
+  for (int e = tid; e < 3 * N; e += T) sxyz[e] = pts[e];
+  __syncthreads();
+
+  float px[P], py[P], pz[P], md[P];
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const int j = p * T + tid;
+    if (j < N) {
+      px[p] = sxyz[3 * j + 0];
+      py[p] = sxyz[3 * j + 1];
+      pz[p] = sxyz[3 * j + 2];
+      md[p] = __int_as_float(0x7f800000);
+    } else {
+      // Padding never wins: distance 0 and the largest possible index; NaN coordinates keep it 0.
+      px[p] = py[p] = pz[p] = __int_as_float(0x7fc00000);
+      md[p] = 0.f;
+    }
+  }
+
+  int cur = 0;
+  if (tid == 0) out[0] = 0;
+  for (int it = 1; it < S; ++it) {
+    const float cx = sxyz[3 * cur + 0], cy = sxyz[3 * cur + 1], cz = sxyz[3 * cur + 2];
+    float bm = -1.f;
+    int bi = 0;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const float d = sqdist<float>(px[p], py[p], pz[p], cx, cy, cz);
+      md[p] = fminf(md[p], d);
+      if (md[p] > bm) {  // ascending index within the thread: strict ">" keeps the lowest
+        bm = md[p];
+        bi = p * T + tid;
+      }
+    }
+    unsigned bits = __float_as_uint(bm), inv = 0xffffffffu - (unsigned)bi;
+    block_argmax(bits, inv, slots[it & 1], nwarps);
+    cur = (int)(0xffffffffu - inv);
+    if (tid == 0) out[it] = cur;
+  }
+}
+
+// ---- streaming kernel (any type, any N) ------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ unsigned long long dist_key(T v);
+template <>
+__device__ __forceinline__ unsigned long long dist_key<float>(float v) {
+  return (unsigned long long)__float_as_uint(v) << 32;
+}
+template <>
+__device__ __forceinline__ unsigned long long dist_key<double>(double v) {
+  return (unsigned long long)__double_as_longlong(v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(FPS_MAX_THREADS)
+fps_streaming_kernel(const T *__restrict__ points, int64_t N, int64_t S, int64_t *__restrict__ index,
+                     T *__restrict__ min_dist) {
+  // Arg-max over (distance key, ~index) with 64-bit keys for the distance and a separate 64-bit
+  // word for the index, reduced through shared memory.
+  __shared__ unsigned long long skey[2][32];
+  __shared__ unsigned long long sidx[2][32];
+  const int tid = threadIdx.x, Tn = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = Tn >> 5;
+  const T *pts = points + (int64_t)blockIdx.x * N * 3;
+  T *md = min_dist + (int64_t)blockIdx.x * N;
+  int64_t *out = index + (int64_t)blockIdx.x * S;
+
+  int64_t cur = 0;
+  if (tid == 0) out[0] = 0;
+  for (int64_t it = 1; it < S; ++it) {
+    const T cx = pts[3 * cur + 0], cy = pts[3 * cur + 1], cz = pts[3 * cur + 2];
+    unsigned long long bk = 0;
+    unsigned long long bi = ~0ull;  // holds ~index so that max() prefers the lowest index
+    bool any = false;
+    for (int64_t j = tid; j < N; j += Tn) {
+      const T d = sqdist<T>(pts[3 * j + 0], pts[3 * j + 1], pts[3 * j + 2], cx, cy, cz);
+      T m = (it == 1) ? Exact<T>::inf() : md[j];
+      if (d < m) m = d;
+      md[j] = m;
+      const unsigned long long k = dist_key<T>(m);
+      if (!any || k > bk) {
+        bk = k;
+        bi = ~(unsigned long long)j;
+        any = true;
+      }
+    }
+    if (!any) {
+      bk = 0;
+      bi = 0;  // loses every tie against a real point
+    }
+    // warp reduce (lexicographic max on (bk, bi))
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long ok = __shfl_xor_sync(0xffffffffu, bk, o);
+      const unsigned long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ok > bk || (ok == bk && oi > bi)) {
+        bk = ok;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      skey[it & 1][warp] = bk;
+      sidx[it & 1][warp] = bi;
+    }
+    __syncthreads();
+    bk = lane < nwarps ? skey[it & 1][lane] : 0ull;
+    bi = lane < nwarps ? sidx[it & 1][lane] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long ok = __shfl_xor_sync(0xffffffffu, bk, o);
+      const unsigned long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ok > bk || (ok == bk && oi > bi)) {
+        bk = ok;
+        bi = oi;
+      }
+    }
+    cur = (int64_t)(~bi);
+    if (tid == 0) out[it] = cur;
+  }
+}
+
+constexpr int64_t FPS_RESIDENT_MAX_N = 8192;
+
+int threads_for(int64_t N) {
+  int t = 32;
+  while (t < FPS_MAX_THREADS && t < N) t <<= 1;
+  return t;
+}
+
+}  // namespace
+
+}  // namespace tk3d
+
+using namespace tk3d;
+
+extern "C" size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype) {
+  if (B <= 0 || N <= 0) return 0;
+  if (dtype == TK3D_F32 && N <= FPS_RESIDENT_MAX_N) return 0;
+  return (size_t)B * (size_t)N * (dtype == TK3D_F64 ? 8 : 4);
+}
+
+extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index, void *scratch,
+                        size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "fps: dtype %d", dtype);
+  TK3D_REQUIRE(B >= 0 && N >= 0, TK3D_ERR_SHAPE, "fps: negative size");
+  TK3D_REQUIRE(S > 0, TK3D_ERR_K, "fps: num_samples must be positive (got %lld)", (long long)S);
+  TK3D_REQUIRE(N >= S, TK3D_ERR_K, "fps: num_samples %lld exceeds the %lld points of a cloud", (long long)S,
+               (long long)N);
+  TK3D_REQUIRE(N < (1LL << 31), TK3D_ERR_SHAPE, "fps: clouds limited to 2^31-1 points");
+  TK3D_REQUIRE(B < (1LL << 31), TK3D_ERR_SHAPE, "fps: batch too large");
+  if (B == 0) return TK3D_OK;
+  TK3D_REQUIRE(points && index, TK3D_ERR_NULL, "fps: points/index is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t need = tk3d_fps_scratch_bytes(B, N, dtype);
+  if (need == 0) {
+    // Up to 8 points per thread; at least 4 warps so that every SM sub-partition has work.
+    int threads = threads_for((N + 7) / 8);
+    if (threads < 128) threads = 128;
+    const int P = (int)((N + threads - 1) / threads);
+    const size_t smem = (size_t)N * 12;
+    const float *p = (const float *)points;
+#define TK3D_FPS_CASE(PP)                                                                                         \
+  {                                                                                                               \
+    TK3D_CUDA(cudaFuncSetAttribute(fps_resident_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)); \
+    fps_resident_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index);                        \
+  }
+    if (P <= 1) TK3D_FPS_CASE(1)
+    else if (P <= 2) TK3D_FPS_CASE(2)
+    else if (P <= 4) TK3D_FPS_CASE(4)
+    else TK3D_FPS_CASE(8)
+#undef TK3D_FPS_CASE
+    return check_launch("fps_resident_kernel");
+  }
+  TK3D_REQUIRE(scratch != nullptr && scratch_bytes >= need, TK3D_ERR_SCRATCH,
+               "fps: scratch of %zu bytes required, %zu given", need, scratch ? scratch_bytes : (size_t)0);
+  const int threads = threads_for(N);
+  if (dtype == TK3D_F32)
+    fps_streaming_kernel<float><<<(unsigned)B, threads, 0, st>>>((const float *)points, N, S, index, (float *)scratch);
+  else
+    fps_streaming_kernel<double><<<(unsigned)B, threads, 0, st>>>((const double *)points, N, S, index,
+                                                                 (double *)scratch);
+  return check_launch("fps_streaming_kernel");
+}

@@ -1,0 +1,196 @@
+// Three-neighbour feature interpolation (forward / backward) and the inverse-distance weights.
+//
+//   out[b,c,m] = (in[b,c,i0]*w0 + in[b,c,i1]*w1) + in[b,c,i2]*w2,   (i*, w*) = index/weight[b,m,:]
+//
+// Memory-bound: the [B,C,N2] output dominates.  A thread owns one query m, loads its three indices
+// and weights once (the reference re-reads them for every channel) and walks the channels; lanes
+// of a warp hold consecutive m, so stores coalesce along N2.
+#include "tk3d_common.cuh"
+
+namespace tk3d {
+
+namespace {
+
+constexpr int IP_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(IP_THREADS)
+interp_fwd_direct_kernel(const T *__restrict__ in, const int64_t *__restrict__ index, const T *__restrict__ weight,
+                         int64_t C, int64_t N1, int64_t N2, int64_t c_per_block, T *__restrict__ out,
+                         int32_t *__restrict__ status) {
+  const int64_t b = blockIdx.z;
+  const int64_t m = (int64_t)blockIdx.x * IP_THREADS + threadIdx.x;
+  if (m >= N2) return;
+  const int64_t c0 = (int64_t)blockIdx.y * c_per_block;
+  const int64_t c1 = (c0 + c_per_block < C) ? c0 + c_per_block : C;
+  int64_t id[3];
+  T w[3];
+  bool bad = false;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    id[i] = index[(b * N2 + m) * 3 + i];
+    w[i] = weight[(b * N2 + m) * 3 + i];
+    if (id[i] < 0 || id[i] >= N1) {
+      id[i] = 0;
+      w[i] = (T)0;
+      bad = true;
+    }
+  }
+  if (bad && status) atomicOr(status, 1);
+  if (N1 == 0) {
+    for (int64_t c = c0; c < c1; ++c) out[(b * C + c) * N2 + m] = (T)0;
+    return;
+  }
+  const T *src = in + (b * C + c0) * N1;
+  T *dst = out + (b * C + c0) * N2 + m;
+#pragma unroll 4
+  for (int64_t c = c0; c < c1; ++c, src += N1, dst += N2) {
+    T acc = __ldg(src + id[0]) * w[0];
+    acc += __ldg(src + id[1]) * w[1];
+    acc += __ldg(src + id[2]) * w[2];
+    __stcs(dst, acc);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(IP_THREADS)
+interp_bwd_kernel(const T *__restrict__ gout, const int64_t *__restrict__ index, const T *__restrict__ weight,
+                  int64_t C, int64_t N1, int64_t N2, int64_t c_per_block, T *__restrict__ gin,
+                  int32_t *__restrict__ status) {
+  const int64_t b = blockIdx.z;
+  const int64_t m = (int64_t)blockIdx.x * IP_THREADS + threadIdx.x;
+  if (m >= N2) return;
+  const int64_t c0 = (int64_t)blockIdx.y * c_per_block;
+  const int64_t c1 = (c0 + c_per_block < C) ? c0 + c_per_block : C;
+  int64_t id[3];
+  T w[3];
+  bool bad = false;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    id[i] = index[(b * N2 + m) * 3 + i];
+    w[i] = weight[(b * N2 + m) * 3 + i];
+    if (id[i] < 0 || id[i] >= N1) {
+      id[i] = -1;
+      bad = true;
+    }
+  }
+  if (bad && status) atomicOr(status, 1);
+  const T *src = gout + (b * C + c0) * N2 + m;
+  T *dst = gin + (b * C + c0) * N1;
+#pragma unroll 4
+  for (int64_t c = c0; c < c1; ++c, src += N2, dst += N1) {
+    const T g = __ldcs(src);
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      if (id[i] >= 0) atomicAdd(dst + id[i], g * w[i]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+three_nn_weight_kernel(const T *__restrict__ dist, int64_t rows, int k, T *__restrict__ weight) {
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r < rows; r += (int64_t)gridDim.x * blockDim.x) {
+    T inv[8];
+    T sum = (T)0;
+    for (int i = 0; i < k; ++i) {
+      T d = dist[r * k + i];
+      if (d < (T)1e-10) d = (T)1e-10;
+      inv[i] = (T)1 / d;
+      sum += inv[i];
+    }
+    for (int i = 0; i < k; ++i) weight[r * k + i] = inv[i] / sum;
+  }
+}
+
+int64_t channels_per_block(int64_t tiles, int64_t B, int64_t C) {
+  const int64_t want = (int64_t)sm_count() * 8;
+  int64_t groups = (want + tiles * B - 1) / (tiles * B);
+  if (groups < 1) groups = 1;
+  if (groups > C) groups = C;
+  return (C + groups - 1) / groups;
+}
+
+template <typename T>
+int interp_fwd_t(const T *in, const int64_t *index, const T *weight, int64_t B, int64_t C, int64_t N1, int64_t N2,
+                 T *out, int32_t *status, cudaStream_t st) {
+  const int64_t tiles = (N2 + IP_THREADS - 1) / IP_THREADS;
+  const int64_t cpb = channels_per_block(tiles, B, C);
+  const int64_t groups = (C + cpb - 1) / cpb;
+  TK3D_REQUIRE(tiles < (1LL << 31) && groups <= 65535 && B <= 65535, TK3D_ERR_SHAPE, "interpolate: grid too large");
+  dim3 grid((unsigned)tiles, (unsigned)groups, (unsigned)B);
+  interp_fwd_direct_kernel<T><<<grid, IP_THREADS, 0, st>>>(in, index, weight, C, N1, N2, cpb, out, status);
+  return check_launch("interp_fwd_direct_kernel");
+}
+
+template <typename T>
+int interp_bwd_t(const T *gout, const int64_t *index, const T *weight, int64_t B, int64_t C, int64_t N1, int64_t N2,
+                 T *gin, int32_t *status, cudaStream_t st) {
+  TK3D_CUDA(cudaMemsetAsync(gin, 0, sizeof(T) * (size_t)(B * C * N1), st));
+  if (N2 == 0) return TK3D_OK;
+  const int64_t tiles = (N2 + IP_THREADS - 1) / IP_THREADS;
+  const int64_t cpb = channels_per_block(tiles, B, C);
+  const int64_t groups = (C + cpb - 1) / cpb;
+  TK3D_REQUIRE(tiles < (1LL << 31) && groups <= 65535 && B <= 65535, TK3D_ERR_SHAPE, "interpolate: grid too large");
+  dim3 grid((unsigned)tiles, (unsigned)groups, (unsigned)B);
+  interp_bwd_kernel<T><<<grid, IP_THREADS, 0, st>>>(gout, index, weight, C, N1, N2, cpb, gin, status);
+  return check_launch("interp_bwd_kernel");
+}
+
+int check_interp_args(const char *what, int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "%s: dtype %d", what, dtype);
+  TK3D_REQUIRE(B >= 0 && C >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "%s: negative size", what);
+  TK3D_REQUIRE(K == 3, TK3D_ERR_K, "%s: only k=3 is supported (got %lld)", what, (long long)K);
+  TK3D_REQUIRE(N1 < (1LL << 31), TK3D_ERR_SHAPE, "%s: N1 limited to 2^31-1", what);
+  return TK3D_OK;
+}
+
+}  // namespace
+}  // namespace tk3d
+
+using namespace tk3d;
+
+extern "C" int tk3d_interp_fwd(const void *in, const int64_t *index, const void *weight, int64_t B, int64_t C,
+                               int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, int dtype,
+                               void *stream) {
+  int rc = check_interp_args("interp_fwd", B, C, N1, N2, K, dtype);
+  if (rc) return rc;
+  if (B * C * N2 == 0) return TK3D_OK;
+  TK3D_REQUIRE(index && weight && out && (in || N1 == 0), TK3D_ERR_NULL, "interp_fwd: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == TK3D_F32)
+    return interp_fwd_t<float>((const float *)in, index, (const float *)weight, B, C, N1, N2, (float *)out, status, st);
+  return interp_fwd_t<double>((const double *)in, index, (const double *)weight, B, C, N1, N2, (double *)out, status,
+                              st);
+}
+
+extern "C" int tk3d_interp_bwd(const void *gout, const int64_t *index, const void *weight, int64_t B, int64_t C,
+                               int64_t N1, int64_t N2, int64_t K, void *gin, int32_t *status, int dtype,
+                               void *stream) {
+  int rc = check_interp_args("interp_bwd", B, C, N1, N2, K, dtype);
+  if (rc) return rc;
+  if (B * C * N1 == 0) return TK3D_OK;
+  TK3D_REQUIRE(gin && (N2 == 0 || (index && weight && gout)), TK3D_ERR_NULL, "interp_bwd: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == TK3D_F32)
+    return interp_bwd_t<float>((const float *)gout, index, (const float *)weight, B, C, N1, N2, (float *)gin, status,
+                               st);
+  return interp_bwd_t<double>((const double *)gout, index, (const double *)weight, B, C, N1, N2, (double *)gin,
+                              status, st);
+}
+
+extern "C" int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t k, void *weight, int dtype,
+                                    void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "three_nn_weight: dtype %d", dtype);
+  TK3D_REQUIRE(rows >= 0, TK3D_ERR_SHAPE, "three_nn_weight: negative size");
+  TK3D_REQUIRE(k >= 1 && k <= 8, TK3D_ERR_K, "three_nn_weight: k must be in [1,8] (got %lld)", (long long)k);
+  if (rows == 0) return TK3D_OK;
+  TK3D_REQUIRE(distance && weight, TK3D_ERR_NULL, "three_nn_weight: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t want = (rows + 255) / 256, cap = (int64_t)sm_count() * 16;
+  const unsigned grid = (unsigned)(want < cap ? want : cap);
+  if (dtype == TK3D_F32)
+    three_nn_weight_kernel<float><<<grid, 256, 0, st>>>((const float *)distance, rows, (int)k, (float *)weight);
+  else
+    three_nn_weight_kernel<double><<<grid, 256, 0, st>>>((const double *)distance, rows, (int)k, (double *)weight);
+  return check_launch("three_nn_weight_kernel");
+}
