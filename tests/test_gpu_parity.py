@@ -1,0 +1,399 @@
+"""GPU parity: the CUDA library (through the operator layer and the C ABI) against the CPU oracle
+and the golden fixtures.  Indices and forward distances must be bit-exact; gradients and
+interpolated features within rel 1e-5 / abs 1e-6 (fp32)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+GRAD_TOL = dict(rtol=1e-5, atol=1e-6)
+
+
+def T(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.to(DEV)
+
+
+def N(t):
+    return t.detach().cpu().numpy()
+
+
+def grid_cloud(rng, B, n, dtype=np.float32):
+    """Coarse grid with duplicates: many exactly tied distances."""
+    return (rng.integers(-3, 4, size=(B, n, 3)) * 0.25).astype(dtype)
+
+
+# ------------------------------------------------------------------------------------------- chamfer
+CHAMFER_SHAPES = [(1, 1, 1), (2, 31, 33), (3, 127, 129), (2, 128, 512), (1, 513, 1000), (2, 1024, 1024),
+                  (5, 700, 64), (64, 600, 601), (8, 2100, 2050)]
+
+
+@pytest.mark.parametrize("B,n1,n2", CHAMFER_SHAPES)
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_chamfer_forward_bit_exact(oracle, B, n1, n2, dtype):
+    from torkit3d_b200.ops import nn_distance
+
+    if dtype == np.float64 and B * n1 * n2 > 5_000_000:
+        pytest.skip("fp64 generic path covered by the smaller shapes")
+    rng = np.random.default_rng(B * 1000 + n1)
+    a = rng.standard_normal((B, n1, 3)).astype(dtype)
+    b = rng.standard_normal((B, n2, 3)).astype(dtype)
+    d1, i1, d2, i2 = [N(t) for t in nn_distance(T(a), T(b))]
+    e1, j1, e2, j2 = oracle.chamfer_fwd(a, b)
+    np.testing.assert_array_equal(i1, j1)
+    np.testing.assert_array_equal(i2, j2)
+    np.testing.assert_array_equal(d1, e1)
+    np.testing.assert_array_equal(d2, e2)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_chamfer_ties_go_to_lowest_index(oracle, dtype):
+    from torkit3d_b200.ops import nn_distance
+
+    rng = np.random.default_rng(3)
+    a, b = grid_cloud(rng, 4, 777, dtype), grid_cloud(rng, 4, 1500, dtype)
+    d1, i1, d2, i2 = [N(t) for t in nn_distance(T(a), T(b))]
+    e1, j1, e2, j2 = oracle.chamfer_fwd(a, b)
+    np.testing.assert_array_equal(i1, j1)
+    np.testing.assert_array_equal(i2, j2)
+    np.testing.assert_array_equal(d1, e1)
+
+
+def test_chamfer_far_from_origin_and_huge_values(oracle):
+    """The fp32 filter must stay conservative where its cheap estimate is useless."""
+    from torkit3d_b200.ops import nn_distance
+
+    rng = np.random.default_rng(4)
+    for offset, scale in ((1000.0, 1.0), (-3.0e4, 10.0), (0.0, 1e-20), (0.0, 1e18), (5e18, 1e18)):
+        a = (rng.standard_normal((2, 300, 3)) * scale + offset).astype(np.float32)
+        b = (rng.standard_normal((2, 700, 3)) * scale + offset).astype(np.float32)
+        d1, i1, d2, i2 = [N(t) for t in nn_distance(T(a), T(b))]
+        e1, j1, e2, j2 = oracle.chamfer_fwd(a, b)
+        np.testing.assert_array_equal(i1, j1)
+        np.testing.assert_array_equal(i2, j2)
+        np.testing.assert_array_equal(d1, e1)
+        np.testing.assert_array_equal(d2, e2)
+
+
+def test_chamfer_empty_partner_and_empty_batch():
+    from torkit3d_b200.ops import nn_distance
+
+    a = torch.randn(2, 5, 3, device=DEV)
+    b = torch.zeros(2, 0, 3, device=DEV)
+    d1, i1, d2, i2 = nn_distance(a, b)
+    assert torch.isinf(d1).all() and (i1 == -1).all() and d2.shape == (2, 0) and i2.shape == (2, 0)
+    d1, i1, d2, i2 = nn_distance(torch.zeros(0, 5, 3, device=DEV), torch.zeros(0, 7, 3, device=DEV))
+    assert d1.shape == (0, 5) and d2.shape == (0, 7)
+
+
+def test_chamfer_golden_and_layouts(golden):
+    from torkit3d_b200.ops import chamfer_distance
+
+    g = golden("chamfer")
+    for tag in ("f32", "f64"):
+        x1 = T(g[tag + "_xyz1"]).requires_grad_(True)
+        x2 = T(g[tag + "_xyz2"]).requires_grad_(True)
+        d1, d2 = chamfer_distance(x1, x2)
+        np.testing.assert_array_equal(N(d1), g[tag + "_dist1"])
+        np.testing.assert_array_equal(N(d2), g[tag + "_dist2"])
+        (d1.mean() + d2.mean()).backward()
+        tol = GRAD_TOL if tag == "f32" else dict(rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(N(x1.grad), g[tag + "_grad1"], **tol)
+        np.testing.assert_allclose(N(x2.grad), g[tag + "_grad2"], **tol)
+        # channel-first inputs and the 2-D (unbatched) form
+        t1, t2 = chamfer_distance(x1.detach().transpose(1, 2), x2.detach().transpose(1, 2), transpose=True)
+        assert torch.equal(t1, d1) and torch.equal(t2, d2)
+        u1, u2 = chamfer_distance(x1.detach()[0], x2.detach()[0])
+        assert torch.equal(u1[0], d1[0]) and torch.equal(u2[0], d2[0])
+        s1, _ = chamfer_distance(x1.detach(), x2.detach(), sqrt=True)
+        np.testing.assert_allclose(N(s1), np.sqrt(np.maximum(g[tag + "_dist1"], 1e-12)), rtol=1e-6)
+
+
+@pytest.mark.parametrize("B,n1,n2", [(2, 100, 130), (3, 1024, 1024), (2, 3000, 500)])
+def test_chamfer_backward_vs_oracle(oracle, B, n1, n2):
+    from torkit3d_b200 import _C
+
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((B, n1, 3)).astype(np.float32)
+    b = rng.standard_normal((B, n2, 3)).astype(np.float32)
+    g1 = rng.standard_normal((B, n1)).astype(np.float32)
+    g2 = rng.standard_normal((B, n2)).astype(np.float32)
+    _, i1, _, i2 = oracle.chamfer_fwd(a, b)
+    ga, gb = _C.chamfer_distance_backward_cuda(T(g1), T(g2), T(a), T(b), T(i1), T(i2))
+    ea, eb = oracle.chamfer_bwd(g1.astype(np.float64), g2.astype(np.float64), a.astype(np.float64),
+                                b.astype(np.float64), i1, i2)
+    np.testing.assert_allclose(N(ga), ea, rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(N(gb), eb, rtol=1e-5, atol=2e-6)
+
+
+def test_chamfer_gradcheck_fp64():
+    from torkit3d_b200.ops import chamfer_distance
+
+    torch.manual_seed(0)
+    x1 = torch.rand(2, 64, 3, dtype=torch.float64, device=DEV, requires_grad=True)
+    x2 = torch.rand(2, 50, 3, dtype=torch.float64, device=DEV, requires_grad=True)
+    assert torch.autograd.gradcheck(lambda a, b: chamfer_distance(a, b), (x1, x2), eps=1e-6, atol=1e-4,
+                                    nondet_tol=1e-9)
+
+
+def test_chamfer_partial_sums():
+    from torkit3d_b200 import _C
+
+    a = torch.randn(7, 1500, 3, device=DEV)
+    b = torch.randn(7, 900, 3, device=DEV)
+    sums = torch.full((2,), 123.0, dtype=torch.float64, device=DEV)
+    d1, _, d2, _ = _C.chamfer_distance_forward_cuda(a, b, sums=sums)
+    np.testing.assert_allclose(N(sums), [N(d1).astype(np.float64).sum(), N(d2).astype(np.float64).sum()], rtol=1e-12)
+
+
+# ----------------------------------------------------------------------------------------------- knn
+KNN_CASES = [(1, 1, 1, 1), (2, 33, 64, 1), (2, 100, 300, 3), (3, 511, 1025, 31), (2, 512, 1024, 32), (1, 700, 2000, 4),
+             (2, 257, 900, 5), (4, 1000, 1111, 16), (2, 300, 1300, 64), (1, 200, 700, 100), (1, 130, 400, 128),
+             (1, 64, 300, 200), (2, 50, 16, 16), (40, 600, 700, 16), (40, 600, 700, 3)]
+
+
+@pytest.mark.parametrize("B,n1,n2,k", KNN_CASES)
+def test_knn_bit_exact(oracle, B, n1, n2, k):
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(n1 * 7 + k)
+    q = rng.standard_normal((B, n1, 3)).astype(np.float32)
+    r = rng.standard_normal((B, n2, 3)).astype(np.float32)
+    d, i = knn_points(T(q), T(r), k)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
+@pytest.mark.parametrize("k", [1, 3, 4, 8, 16, 50, 150])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_knn_ties(oracle, k, dtype):
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(k)
+    q, r = grid_cloud(rng, 2, 300, dtype), grid_cloud(rng, 2, 900, dtype)
+    d, i = knn_points(T(q), T(r), k, sorted=True)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
+def test_knn_golden_fp64_and_options(golden):
+    from torkit3d_b200.ops import knn_points
+
+    g = golden("knn")
+    for tag in "abc":
+        k = int(g[tag + "_k"])
+        q, r = T(g[tag + "_query"]), T(g[tag + "_key"])
+        d, i = knn_points(q, r, k, sorted=True, sqrt_distance=True)
+        np.testing.assert_array_equal(N(i), g[tag + "_idx"])
+        np.testing.assert_allclose(N(d), g[tag + "_dist"], rtol=1e-4, atol=5e-5)
+        for version in (0, 1):
+            d2, i2 = knn_points(q.transpose(1, 2), r.transpose(1, 2), k, transpose=True, version=version)
+            assert torch.equal(i2, i)
+    with pytest.raises(RuntimeError):
+        knn_points(q, r[:, :5], 31)
+    with pytest.raises(RuntimeError, match="Invalid version"):
+        knn_points(q, r, 3, version=2)
+
+
+def test_knn_far_from_origin(oracle):
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(2)
+    for k in (3, 16):
+        q = (rng.standard_normal((2, 200, 3)) + 500.0).astype(np.float32)
+        r = (rng.standard_normal((2, 800, 3)) + 500.0).astype(np.float32)
+        d, i = knn_points(T(q), T(r), k)
+        e, j = oracle.knn(q, r, k)
+        np.testing.assert_array_equal(N(i), j)
+        np.testing.assert_array_equal(N(d), e)
+
+
+# ----------------------------------------------------------------------------------------------- fps
+FPS_CASES = [(1, 31, 2), (2, 1024, 128), (3, 1025, 129), (16, 1024, 512), (4, 4096, 300), (2, 8192, 1024),
+             (2, 100, 100), (1, 1, 1), (3, 33, 33), (2, 8193, 200), (1, 20000, 64)]
+
+
+@pytest.mark.parametrize("B,n,s", FPS_CASES)
+def test_fps_bit_exact(oracle, B, n, s):
+    from torkit3d_b200.ops import sample_farthest_points
+
+    rng = np.random.default_rng(n + s)
+    p = rng.random((B, n, 3)).astype(np.float32)
+    got = N(sample_farthest_points(T(p), s))
+    np.testing.assert_array_equal(got, oracle.fps(p, s))
+    got_t = N(sample_farthest_points(T(p).transpose(1, 2), s, transpose=True))
+    np.testing.assert_array_equal(got_t, got)
+
+
+def test_fps_golden_fp64_and_duplicates(oracle, golden):
+    from torkit3d_b200.ops import sample_farthest_points
+
+    g = golden("fps")
+    for tag in "abcd":
+        got = N(sample_farthest_points(T(g[tag + "_points"]), int(g[tag + "_s"])))
+        np.testing.assert_array_equal(got, g[tag + "_idx"])
+    rng = np.random.default_rng(0)
+    p = rng.random((2, 600, 3)).astype(np.float32)
+    p = np.concatenate([p, p, p[:, :100]], axis=1)  # exact duplicates -> tied maxima
+    for dtype in (np.float32, np.float64):
+        np.testing.assert_array_equal(N(sample_farthest_points(T(p.astype(dtype)), 1300)), oracle.fps(p.astype(dtype), 1300))
+    ones = torch.ones(2, 50, 3, device=DEV)
+    assert (sample_farthest_points(ones, 20) == 0).all()
+    with pytest.raises(RuntimeError):
+        sample_farthest_points(ones, 51)
+    with pytest.raises(RuntimeError):
+        sample_farthest_points(ones, 0)
+
+
+# ---------------------------------------------------------------------------------------- ball query
+@pytest.mark.parametrize("B,n1,n2,r,k", [(2, 64, 128, 0.1, 32), (3, 65, 129, 10.0, 32), (4, 513, 2000, 0.3, 16),
+                                        (2, 1000, 5000, 0.2, 64), (1, 1, 1, 1.0, 4), (2, 100, 700, 0.05, 1),
+                                        (30, 300, 600, 0.4, 8)])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_ball_query_bit_exact(oracle, B, n1, n2, r, k, dtype):
+    from torkit3d_b200.ops import ball_query
+
+    rng = np.random.default_rng(n1 + k)
+    key = rng.standard_normal((B, n2, 3)).astype(dtype)
+    query = rng.standard_normal((B, n1, 3)).astype(dtype)
+    query[:, : n1 // 2] = key[:, : n1 // 2]  # half of the queries coincide with keys
+    got = N(ball_query(T(query), T(key), r, k, transpose=False))
+    np.testing.assert_array_equal(got, oracle.ball_query(query, key, r, k))
+    got_t = N(ball_query(T(query).transpose(1, 2), T(key).transpose(1, 2), r, k))  # default: channel-first
+    np.testing.assert_array_equal(got_t, got)
+
+
+def test_ball_query_golden_and_boundary(oracle, golden):
+    from torkit3d_b200.ops import ball_query
+
+    g = golden("ball_query")
+    for tag in "abcd":
+        got = N(ball_query(T(g[tag + "_query"]), T(g[tag + "_key"]), float(g[tag + "_r"]), int(g[tag + "_k"]),
+                           transpose=False))
+        np.testing.assert_array_equal(got, g[tag + "_idx"])
+    # points exactly on the sphere are outside (strict "<"); grid data gives many such cases
+    rng = np.random.default_rng(1)
+    q, r = grid_cloud(rng, 2, 200), grid_cloud(rng, 2, 900)
+    for radius in (0.25, 0.5, 0.75):
+        got = N(ball_query(T(q), T(r), radius, 12, transpose=False))
+        np.testing.assert_array_equal(got, oracle.ball_query(q, r, radius, 12))
+
+
+# ------------------------------------------------------------------------------- group / interpolate
+@pytest.mark.parametrize("B,C,n1,n2,k", [(2, 3, 512, 128, 32), (5, 64, 513, 129, 33), (1, 1, 1, 1, 1), (3, 7, 100, 50, 5),
+                                        (4, 32, 2048, 512, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_group_points(oracle, B, C, n1, n2, k, dtype):
+    from torkit3d_b200.ops import group_points
+
+    torch.manual_seed(0)
+    f = torch.randn(B, C, n1, dtype=dtype, device=DEV, requires_grad=True)
+    idx = torch.randint(0, n1, (B, n2, k), device=DEV)
+    idx[:, :, k // 2:] = idx[:, :, :1]  # padded rows, as ball query produces them
+    out = group_points(f, idx)
+    np.testing.assert_array_equal(N(out), oracle.group_fwd(N(f), N(idx)))
+    go = torch.randn_like(out)
+    out.backward(go)
+    ref = oracle.group_bwd(N(go).astype(np.float64), N(idx), n1)
+    np.testing.assert_allclose(N(f.grad), ref, rtol=1e-5, atol=2e-5 if dtype == torch.float32 else 1e-12)
+
+
+def test_group_golden_and_bad_index(golden):
+    from torkit3d_b200 import _C, _lib
+    from torkit3d_b200.ops import group_points
+
+    g = golden("group_points")
+    for tag in "ab":
+        f = T(g[tag + "_feature"]).requires_grad_(True)
+        out = group_points(f, T(g[tag + "_index"]))
+        np.testing.assert_array_equal(N(out), g[tag + "_out"])
+        out.backward(torch.ones_like(out))
+        np.testing.assert_allclose(N(f.grad), g[tag + "_grad"], rtol=1e-6, atol=1e-6)
+    # an index of -1 (ball query row without a hit) reads as zero and raises the status bit
+    f = torch.randn(1, 2, 10, device=DEV)
+    idx = torch.tensor([[[0, -1, 9, 10]]], device=DEV)
+    out = _C.group_points_forward_cuda(f, idx)
+    assert torch.equal(out[0, :, 0, 1], torch.zeros(2, device=DEV)) and torch.equal(out[0, :, 0, 3], torch.zeros(2, device=DEV))
+    assert torch.equal(out[0, :, 0, 0], f[0, :, 0]) and torch.equal(out[0, :, 0, 2], f[0, :, 9])
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    lib = _lib.load()
+    o2 = torch.empty_like(out)
+    assert lib.tk3d_group_fwd(f.data_ptr(), idx.data_ptr(), 1, 2, 10, 1, 4, o2.data_ptr(), status.data_ptr(), 0,
+                              torch.cuda.current_stream().cuda_stream) == 0
+    assert int(status.item()) == 1 and torch.equal(o2, out)
+
+
+@pytest.mark.parametrize("B,C,n1,n2", [(2, 64, 128, 512), (3, 65, 129, 513), (1, 1, 3, 1), (4, 128, 1000, 3000)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_interpolate(oracle, B, C, n1, n2, dtype):
+    from torkit3d_b200.ops import interpolate_feature
+
+    torch.manual_seed(1)
+    f = torch.randn(B, C, n1, dtype=dtype, device=DEV, requires_grad=True)
+    idx = torch.randint(0, n1, (B, n2, 3), device=DEV)
+    w = torch.rand(B, n2, 3, dtype=dtype, device=DEV)
+    w = w / w.sum(2, keepdim=True)
+    out = interpolate_feature(f, idx, w)
+    tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=1e-12, atol=1e-14)
+    np.testing.assert_allclose(N(out), oracle.interp_fwd(N(f).astype(np.float64), N(idx), N(w).astype(np.float64)), **tol)
+    go = torch.randn_like(out)
+    out.backward(go)
+    ref = oracle.interp_bwd(N(go).astype(np.float64), N(idx), N(w).astype(np.float64), n1)
+    np.testing.assert_allclose(N(f.grad), ref, rtol=1e-5, atol=2e-5 if dtype == torch.float32 else 1e-12)
+
+
+def test_interpolate_golden_weights_and_errors(oracle, golden):
+    from torkit3d_b200.ops import interpolate_feature, knn_points, three_nn_weight
+
+    g = golden("interpolate")
+    for tag in "ab":
+        f = T(g[tag + "_feature"]).requires_grad_(True)
+        out = interpolate_feature(f, T(g[tag + "_index"]), T(g[tag + "_weight"]))
+        np.testing.assert_allclose(N(out), g[tag + "_out"], rtol=1e-12, atol=1e-14)
+        out.backward(torch.ones_like(out))
+        np.testing.assert_allclose(N(f.grad), g[tag + "_grad"], rtol=1e-10, atol=1e-12)
+    with pytest.raises(RuntimeError, match="k=3"):
+        interpolate_feature(torch.randn(1, 2, 8, device=DEV), torch.zeros(1, 4, 2, dtype=torch.long, device=DEV),
+                            torch.ones(1, 4, 2, device=DEV))
+    # three-NN chain: knn (k=3) -> weights -> interpolate, against the oracle chain
+    rng = np.random.default_rng(5)
+    q = rng.random((2, 700, 3)).astype(np.float32)
+    r = rng.random((2, 300, 3)).astype(np.float32)
+    r[0, 0] = q[0, 0]  # a zero distance exercises the clamp
+    feat = rng.standard_normal((2, 16, 300)).astype(np.float32)
+    d, i = knn_points(T(q), T(r), 3)
+    w = three_nn_weight(d)
+    ed, ei = oracle.knn(q, r, 3)
+    ew = oracle.three_nn_weight(ed)
+    np.testing.assert_array_equal(N(i), ei)
+    np.testing.assert_allclose(N(w), ew, rtol=1e-6)
+    out = interpolate_feature(T(feat), i, w)
+    np.testing.assert_allclose(N(out), oracle.interp_fwd(feat, ei, ew), rtol=1e-5, atol=1e-6)
+
+
+def test_non_default_stream_and_determinism():
+    """Index results are identical run to run and on a side stream."""
+    from torkit3d_b200.ops import knn_points, nn_distance, sample_farthest_points
+
+    torch.manual_seed(0)
+    a = torch.randn(4, 2000, 3, device=DEV)
+    b = torch.randn(4, 1500, 3, device=DEV)
+    base = nn_distance(a, b)
+    kb = knn_points(a, b, 16)
+    fb = sample_farthest_points(a, 256)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        again = nn_distance(a, b)
+        ka = knn_points(a, b, 16)
+        fa = sample_farthest_points(a, 256)
+    s.synchronize()
+    for x, y in zip(base, again):
+        assert torch.equal(x, y)
+    assert torch.equal(kb[0], ka[0]) and torch.equal(kb[1], ka[1]) and torch.equal(fa, fb)

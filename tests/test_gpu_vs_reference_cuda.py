@@ -1,0 +1,112 @@
+"""Parity against the REFERENCE's own CUDA extension, compiled unmodified with -fmad=false
+(oracle/build_ref.py -> oracle/_ref/nofma/_C.so).  Skipped when that build is not present.
+
+KNN rows of the reference come in an unspecified slot order and are canonicalised by sorting on
+(distance, index) before the bit-exact comparison."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "nofma", "_C.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF_SO):
+        pytest.skip("reference CUDA extension not built (python oracle/build_ref.py --ref <checkout>)")
+    spec = importlib.util.spec_from_file_location("_C", REF_SO)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def canon(dist, idx):
+    d, i = dist.cpu().numpy(), idx.cpu().numpy()
+    order = np.lexsort((i, d), axis=-1)
+    return np.take_along_axis(d, order, -1), np.take_along_axis(i, order, -1)
+
+
+def test_chamfer(ref):
+    from torkit3d_b200 import _C, workloads
+
+    for x1, x2 in (workloads.c1_chamfer_small(), workloads.c4_chamfer_large(num_clouds=4),
+                   (torch.randn(3, 1000, 3), torch.randn(3, 777, 3))):
+        a, b = x1.to(DEV), x2.to(DEV)
+        mine = _C.chamfer_distance_forward_cuda(a, b)
+        theirs = ref.chamfer_distance_forward_cuda(a, b)
+        for m, t in zip(mine, theirs):
+            assert torch.equal(m, t)
+        g1, g2 = torch.randn_like(mine[0]), torch.randn_like(mine[2])
+        gm = _C.chamfer_distance_backward_cuda(g1, g2, a, b, mine[1], mine[3])
+        gt = ref.chamfer_distance_backward_cuda(g1, g2, a, b, theirs[1], theirs[3])
+        for m, t in zip(gm, gt):
+            torch.testing.assert_close(m, t, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("k,version", [(3, 1), (16, 1), (32, 1), (64, 1), (31, 0), (5, 0), (130, 0)])
+def test_knn(ref, k, version):
+    from torkit3d_b200 import _C, workloads
+
+    q, r = workloads.c2_knn(B=4, N1=1500, N2=2500)
+    q, r = q.to(DEV), r.to(DEV)
+    md, mi = _C.knn_distance_cuda(q, r, k, version)
+    td, ti = ref.knn_distance_cuda(q, r, k, version)
+    cd, ci = canon(td, ti)
+    np.testing.assert_array_equal(mi.cpu().numpy(), ci)
+    np.testing.assert_array_equal(md.cpu().numpy(), cd)
+
+
+def test_fps_ball_group(ref):
+    from torkit3d_b200 import _C, workloads
+
+    p, feat = workloads.c3_set_abstraction(B=8)
+    p, feat = p.to(DEV), feat.to(DEV)
+    mi = _C.sample_farthest_points_cuda(p, 1024)
+    ti = ref.sample_farthest_points_cuda(p, 1024)
+    assert torch.equal(mi, ti)
+    cent = torch.gather(p, 1, mi.unsqueeze(2).expand(-1, -1, 3)).contiguous()
+    mb = _C.ball_query_cuda(cent, p, 0.1, 32)
+    tb = ref.ball_query_cuda(cent, p, 0.1, 32)
+    assert torch.equal(mb, tb)
+    mg = _C.group_points_forward_cuda(feat, mb)
+    tg = ref.group_points_forward_cuda(feat, tb)
+    assert torch.equal(mg, tg)
+    go = torch.randn_like(mg)
+    torch.testing.assert_close(_C.group_points_backward_cuda(go, mb, 8192), ref.group_points_backward_cuda(go, tb, 8192),
+                               rtol=1e-5, atol=2e-5)
+
+
+def test_fps_double_and_odd_sizes(ref):
+    from torkit3d_b200 import _C
+
+    torch.manual_seed(0)
+    for B, n, s, dt in ((3, 1025, 129, torch.float64), (2, 5000, 300, torch.float32), (2, 9000, 100, torch.float32)):
+        p = torch.rand(B, n, 3, dtype=dt, device=DEV)
+        assert torch.equal(_C.sample_farthest_points_cuda(p, s), ref.sample_farthest_points_cuda(p, s))
+
+
+def test_interpolate(ref):
+    from torkit3d_b200 import _C, workloads
+
+    q, r, feat = workloads.c5_scene_interp(B=2, NQ=20000, NR=5000, C=32)
+    q, r, feat = q.to(DEV), r.to(DEV), feat.to(DEV)
+    md, mi = _C.knn_distance_cuda(q, r, 3, 1)
+    td, ti = ref.knn_distance_cuda(q, r, 3, 1)
+    cd, ci = canon(td, ti)
+    np.testing.assert_array_equal(mi.cpu().numpy(), ci)
+    np.testing.assert_array_equal(md.cpu().numpy(), cd)
+    w = _C.three_nn_weight_cuda(md)
+    inv = 1.0 / torch.clamp(md, min=1e-10)
+    torch.testing.assert_close(w, inv / inv.sum(2, keepdim=True), rtol=1e-6, atol=0)
+    mo = _C.interpolate_forward_cuda(feat, mi, w)
+    to = ref.interpolate_forward_cuda(feat, mi, w)
+    torch.testing.assert_close(mo, to, rtol=1e-5, atol=1e-6)
+    go = torch.randn_like(mo)
+    torch.testing.assert_close(_C.interpolate_backward_cuda(go, mi, w, 5000), ref.interpolate_backward_cuda(go, mi, w, 5000),
+                               rtol=1e-5, atol=2e-5)
