@@ -167,6 +167,15 @@ int tk3d_interp_bwd(const void *grad_out, const int64_t *index, const void *weig
  */
 int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t k, void *weight, int dtype, void *stream);
 
+/*
+ * Diagnostic with no counterpart in the reference: launches a kernel of dependent FP32 fused
+ * multiply-add chains (`iters` x 64 FMAs per thread, 8 blocks of 256 threads per SM) on `stream`.
+ * *flop (a HOST double, optional) receives the number of floating-point operations the launch
+ * performs; timing the launch with CUDA events gives the device's sustained FP32 FMA rate, the
+ * roofline of the distance kernels.  `sink` is a device float that is never actually written.
+ */
+int tk3d_diag_ffma(int64_t iters, float *sink, double *flop, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

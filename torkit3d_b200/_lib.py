@@ -31,6 +31,7 @@ SIGNATURES = {
     "tk3d_interp_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
     "tk3d_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
     "tk3d_three_nn_weight": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
+    "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
 }
 
 _lib = None

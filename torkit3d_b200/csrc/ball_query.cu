@@ -33,9 +33,9 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
       qy = q[1];
       qz = q[2];
     }
-    const float mx = -2.f * qx, my = -2.f * qy, mz = -2.f * qz;
+    const float mx[1] = {-2.f * qx}, my[1] = {-2.f * qy}, mz[1] = {-2.f * qz};
     const float never = __int_as_float(0xff800000);
-    float thr = valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never;
+    float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
     int cnt = 0;
     int64_t first = -1;
     int64_t *row = index + (b * N1 + (valid ? i : 0)) * (int64_t)k;
@@ -71,19 +71,22 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
           nxt[p] = v;
         }
       }
-      const int lim = (min(BQ_TILE, N2 - t0) + 3) & ~3;
-#pragma unroll 4
-      for (int u = 0; u < lim; ++u) {
-        const float4 r = tl[u];
-        const float a = fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
-        if (__builtin_expect(!(a >= thr), 0)) {
-          const int j = t0 + u;
-          if (j < N2 && cnt < k && thr != never) {
-            const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
-            if (d < r2) {
-              row[cnt] = j;
-              if (cnt == 0) first = j;
-              if (++cnt == k) thr = never;
+      const int lim = (min(BQ_TILE, N2 - t0) + 7) & ~7;
+#pragma unroll 2
+      for (int u0 = 0; u0 < lim; u0 += 8) {
+        float a[8];
+        if (__builtin_expect(sweep_group<1>(tl + u0, mx, my, mz, thr, a), 0)) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int j = t0 + u0 + u;
+            if (!(a[u] >= thr[0]) && j < N2 && cnt < k && thr[0] != never) {
+              const float4 r = tl[u0 + u];
+              const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
+              if (d < r2) {
+                row[cnt] = j;
+                if (cnt == 0) first = j;
+                if (++cnt == k) thr[0] = never;
+              }
             }
           }
         }

@@ -55,7 +55,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         qx[s] = q[0];
         qy[s] = q[1];
         qz[s] = q[2];
-        thr[s] = best[s];  // +inf: everything passes until a first candidate is verified
+        thr[s] = __int_as_float(0x7fc00000);  // NaN: everything passes until a first candidate is verified
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
         thr[s] = __int_as_float(0xff800000);  // -inf: never passes
@@ -105,28 +105,26 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         }
       }
 
-      const int lim = (cnt + 3) & ~3;
-#pragma unroll 4
-      for (int u = 0; u < lim; ++u) {
-        const float4 r = tl[u];
-        bool pass = false;
+      constexpr int U = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
+      const int lim = (cnt + U - 1) / U * U;
+#pragma unroll 2
+      for (int u0 = 0; u0 < lim; u0 += U) {
+        float a[8];
+        if (__builtin_expect(sweep_group<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
-        for (int s = 0; s < Q; ++s) {
-          const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
-          pass |= !(a >= thr[s]);
-        }
-        if (__builtin_expect(pass, 0)) {
-          const int j = t0 + u;
-          if (j < nr) {
+          for (int u = 0; u < U; ++u) {
+            const int j = t0 + u0 + u;
+            if (j < nr) {
+              const float4 r = tl[u0 + u];
 #pragma unroll
-            for (int s = 0; s < Q; ++s) {
-              const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
-              if (!(a >= thr[s])) {
-                const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-                if (d < best[s]) {
-                  best[s] = d;
-                  arg[s] = j;
-                  thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
+              for (int s = 0; s < Q; ++s) {
+                if (!(a[u * Q + s] >= thr[s])) {
+                  const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
+                  if (d < best[s]) {
+                    best[s] = d;
+                    arg[s] = j;
+                    thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
+                  }
                 }
               }
             }

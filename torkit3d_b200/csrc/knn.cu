@@ -92,30 +92,26 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll
         for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2);
       }
-      const int lim = (min(TILE, N2 - t0) + 3) & ~3;
-#pragma unroll 4
-      for (int u = 0; u < lim; ++u) {
-        const float4 r = tl[u];
-        bool pass = false;
+      constexpr int U = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
+      const int lim = (min(TILE, N2 - t0) + U - 1) / U * U;
+#pragma unroll 2
+      for (int u0 = 0; u0 < lim; u0 += U) {
+        float a[8];
+        if (__builtin_expect(sweep_group<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
-        for (int s = 0; s < Q; ++s) {
-          const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
-          pass |= !(a >= thr[s]);
-        }
-        if (__builtin_expect(pass, 0)) {
-          const int j = t0 + u;
-          if (j < N2) {
+          for (int u = 0; u < U; ++u) {
+            const int j = t0 + u0 + u;
+            if (j >= N2) continue;
+            const float4 r = tl[u0 + u];
 #pragma unroll
             for (int s = 0; s < Q; ++s) {
-              const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
-              if (!(a >= thr[s])) {
-                float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-                int jj = j;
+              if (!(a[u * Q + s] >= thr[s])) {
+                const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
                 // (d, j) enters iff it orders before the current last entry; sentinels carry
                 // (+inf, INT_MAX) so real entries always precede them.
-                if (d < kd[s][K - 1] || (d == kd[s][K - 1] && jj < ki[s][K - 1])) {
+                if (d < kd[s][K - 1] || (d == kd[s][K - 1] && j < ki[s][K - 1])) {
                   kd[s][K - 1] = d;
-                  ki[s][K - 1] = jj;
+                  ki[s][K - 1] = j;
 #pragma unroll
                   for (int c = K - 1; c > 0; --c) {
                     const bool lt = kd[s][c] < kd[s][c - 1] || (kd[s][c] == kd[s][c - 1] && ki[s][c] < ki[s][c - 1]);
@@ -251,13 +247,19 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 #pragma unroll
         for (int s = 0; s < Q; ++s) crowded |= cnt[s] > KN_CAP - KN_STEP;
         if (__any_sync(0xffffffffu, crowded)) drain();
+        // All filter values of the step first (independent FMA chains), then the appends.
+        float a[KN_STEP][Q];
 #pragma unroll
         for (int uu = 0; uu < KN_STEP; ++uu) {
           const float4 r = tl[u0 + uu];
 #pragma unroll
+          for (int s = 0; s < Q; ++s) a[uu][s] = sweep_lower(mx[s], my[s], mz[s], r);
+        }
+#pragma unroll
+        for (int uu = 0; uu < KN_STEP; ++uu) {
+#pragma unroll
           for (int s = 0; s < Q; ++s) {
-            const float a = fmaf(mx[s], r.x, fmaf(my[s], r.y, fmaf(mz[s], r.z, r.w)));
-            if (!(a >= thr[s])) {
+            if (!(a[uu][s] >= thr[s])) {
               buf[(s * KN_CAP + cnt[s]) * KN_THREADS + tid] = u0 + uu;
               ++cnt[s];
             }

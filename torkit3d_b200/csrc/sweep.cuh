@@ -39,6 +39,54 @@ __device__ __forceinline__ float sweep_threshold(float lim, float qq) {
 
 __device__ __forceinline__ float sweep_qq(float x, float y, float z) { return fmaf(z, z, fmaf(y, y, x * x)); }
 
+// "Does any of the eight filter values fall below its threshold?"  Written in PTX so that the
+// eight compares chain through ONE predicate (setp.ltu.or) and a single branch follows; left to
+// the compiler, each compare becomes its own branch.  ltu = "less than or unordered", i.e.
+// !(a >= t): a NaN on either side counts as a pass.
+__device__ __forceinline__ bool sweep_any8(float a0, float a1, float a2, float a3, float a4, float a5, float a6,
+                                           float a7, float t0, float t1, float t2, float t3, float t4, float t5,
+                                           float t6, float t7) {
+  unsigned flag;
+  asm("{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ltu.f32 p, %1, %9;\n\t"
+      "setp.ltu.or.f32 p, %2, %10, p;\n\t"
+      "setp.ltu.or.f32 p, %3, %11, p;\n\t"
+      "setp.ltu.or.f32 p, %4, %12, p;\n\t"
+      "setp.ltu.or.f32 p, %5, %13, p;\n\t"
+      "setp.ltu.or.f32 p, %6, %14, p;\n\t"
+      "setp.ltu.or.f32 p, %7, %15, p;\n\t"
+      "setp.ltu.or.f32 p, %8, %16, p;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(flag)
+      : "f"(a0), "f"(a1), "f"(a2), "f"(a3), "f"(a4), "f"(a5), "f"(a6), "f"(a7), "f"(t0), "f"(t1), "f"(t2), "f"(t3),
+        "f"(t4), "f"(t5), "f"(t6), "f"(t7));
+  return flag != 0;
+}
+
+// Filter values of one key against Q queries.
+__device__ __forceinline__ float sweep_lower(float mx, float my, float mz, const float4 &r) {
+  return fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
+}
+
+// Eight filter values for a group of 8/Q consecutive keys x Q queries, and the combined test.
+// a[u*Q + s] belongs to key u of the group and query s.
+template <int Q>
+__device__ __forceinline__ bool sweep_group(const float4 *__restrict__ keys, const float (&mx)[Q],
+                                            const float (&my)[Q], const float (&mz)[Q], const float (&thr)[Q],
+                                            float (&a)[8]) {
+  constexpr int U = 8 / Q;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const float4 r = keys[u];
+#pragma unroll
+    for (int s = 0; s < Q; ++s) a[u * Q + s] = sweep_lower(mx[s], my[s], mz[s], r);
+  }
+  return sweep_any8(a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], thr[0 % Q], thr[1 % Q], thr[2 % Q], thr[3 % Q],
+                    thr[4 % Q], thr[5 % Q], thr[6 % Q], thr[7 % Q]);
+}
+
 // Stage `count` key points starting at `src` (array of xyz triples) into `dst` as (x,y,z,w).
 // Slots beyond `count` up to `padded` get a point that can never pass a filter (w = +inf gives
 // a = +inf or NaN; callers bound their loops by `count`, the padding only keeps LDS in range).

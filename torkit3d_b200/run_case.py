@@ -1,0 +1,84 @@
+"""Run one operator on one benchmark configuration a few times (for profilers and quick timings).
+
+    python -m torkit3d_b200.run_case <case> [--iters 3] [--scale-batch B]
+
+Cases: c1_chamfer, c2_knn, c3_fps, c3_ball, c3_group_fwd, c3_group_bwd, c4_chamfer_fwd,
+c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd.  ``--scale-batch`` overrides the batch
+size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
+"""
+import argparse
+
+import torch
+
+from . import _C, workloads
+from .ops import ball_query, knn_points, sample_farthest_points, three_nn_weight
+
+
+def build_case(name, batch, dev):
+    kw = {} if batch is None else {"B": batch}
+    if name == "c1_chamfer":
+        a, b = [t.to(dev) for t in workloads.c1_chamfer_small(**kw)]
+        return lambda: _C.chamfer_distance_forward_cuda(a, b)
+    if name == "c2_knn":
+        q, r = [t.to(dev) for t in workloads.c2_knn(**kw)]
+        return lambda: knn_points(q, r, 16)
+    if name.startswith("c3"):
+        p, feat = [t.to(dev) for t in workloads.c3_set_abstraction(**kw)]
+        if name == "c3_fps":
+            return lambda: sample_farthest_points(p, 1024)
+        idx = sample_farthest_points(p, 1024)
+        cent = torch.gather(p, 1, idx.unsqueeze(2).expand(-1, -1, 3)).contiguous()
+        if name == "c3_ball":
+            return lambda: ball_query(cent, p, 0.1, 32, transpose=False)
+        nbr = ball_query(cent, p, 0.1, 32, transpose=False)
+        if name == "c3_group_fwd":
+            return lambda: _C.group_points_forward_cuda(feat, nbr)
+        if name == "c3_group_bwd":
+            go = torch.randn(feat.size(0), feat.size(1), 1024, 32, device=dev)
+            return lambda: _C.group_points_backward_cuda(go, nbr, feat.size(2))
+    if name.startswith("c4"):
+        if batch is not None:
+            a, b = [t.to(dev) for t in workloads.c4_chamfer_large(num_clouds=batch)]
+        else:
+            a, b = [t.to(dev) for t in workloads.c4_chamfer_large()]
+        if name == "c4_chamfer_fwd":
+            return lambda: _C.chamfer_distance_forward_cuda(a, b)
+        d1, i1, d2, i2 = _C.chamfer_distance_forward_cuda(a, b)
+        g1, g2 = torch.full_like(d1, 1e-6), torch.full_like(d2, 1e-6)
+        if name == "c4_chamfer_bwd":
+            return lambda: _C.chamfer_distance_backward_cuda(g1, g2, a, b, i1, i2)
+    if name.startswith("c5"):
+        q, r, feat = [t.to(dev) for t in workloads.c5_scene_interp(**kw)]
+        if name == "c5_three_nn":
+            return lambda: knn_points(q, r, 3)
+        d, i = knn_points(q, r, 3)
+        w = three_nn_weight(d)
+        if name == "c5_interp_fwd":
+            return lambda: _C.interpolate_forward_cuda(feat, i, w)
+        if name == "c5_interp_bwd":
+            go = torch.randn(feat.size(0), feat.size(1), q.size(1), device=dev)
+            return lambda: _C.interpolate_backward_cuda(go, i, w, feat.size(2))
+    raise SystemExit("unknown case " + name)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--scale-batch", type=int, default=None)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    fn = build_case(a.case, a.scale_batch, dev)
+    fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(a.iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    print("%s: %.4f ms per call (%d calls)" % (a.case, s.elapsed_time(e) / a.iters, a.iters))
+
+
+if __name__ == "__main__":
+    main()
