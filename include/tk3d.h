@@ -107,6 +107,29 @@ int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t num_samples, int6
              size_t scratch_bytes, int dtype, void *stream);
 
 /*
+ * Farthest point sampling without any caller-provided or freshly allocated scratch memory.
+ * It has no counterpart in the reference (whose sample_farthest_points_cuda allocates its scratch
+ * tensor on every call).  It is meant for callers that cannot allocate device memory where they
+ * sample: inside a region where their framework forbids allocation, with a memory budget fixed at
+ * start-up, or from plain C without an allocator at hand.
+ *   points [B,N,3] in;  index [B,S] out;  same result as tk3d_fps, bit for bit.
+ * The running minimum distances live in a fixed 8 MiB array inside the library image
+ * (tk3d_fps_static_scratch_capacity() bytes; every GPU that loads the library holds one copy until
+ * the process exits), so B*N may not exceed capacity/4 (fp32: 2,097,152) or capacity/8 (fp64:
+ * 1,048,576) elements; larger problems return TK3D_ERR_SCRATCH and must use tk3d_fps.
+ * The call allocates nothing and frees nothing.  The first call on each device looks up the
+ * array's device address (a synchronous CUDA runtime query), so make that first call outside any
+ * stream capture.  All calls on one device share the one array: two calls whose kernels can run
+ * at the same time on that device (different streams, or different host threads) corrupt each
+ * other -- order them on one stream or with events.  Nothing needs clearing between calls.
+ * Every size runs the streaming kernel; for fp32 clouds of at most 8192 points tk3d_fps needs no
+ * scratch at all (pass NULL) and is faster.
+ */
+size_t tk3d_fps_static_scratch_capacity(void);
+int tk3d_fps_static_scratch(const void *points, int64_t B, int64_t N, int64_t num_samples, int64_t *index,
+                            int dtype, void *stream);
+
+/*
  * Ball query: the first k key indices (ascending) with squared distance < radius*radius (radius is
  * squared in `dtype` after conversion from float); short rows are padded with their first hit, rows
  * without a hit are all -1.

@@ -236,3 +236,79 @@ extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int
                                                                  (double *)scratch);
   return check_launch("fps_streaming_kernel");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Farthest point sampling for callers that cannot provide scratch memory.
+//
+// Some hosts of this library may not allocate device memory at the point where they sample: code
+// running under a framework's "no allocation in this region" guard, a plugin whose memory budget
+// was fixed at start-up, or a C caller that has no allocator at hand and does not want one
+// cudaMalloc/cudaFree pair per call.  For them the running-minimum array of
+// the streaming kernel lives in a fixed array inside the library image instead of a caller buffer.
+//
+// The array belongs to the device the library is loaded on (each GPU that loads the library
+// carries its own copy until the process exits).  Host code must not hand the symbol itself to a
+// kernel -- on the host it is only a stand-in -- so the device address is looked up once per
+// device with cudaGetSymbolAddress and cached.
+namespace tk3d {
+namespace {
+
+constexpr size_t FPS_STATIC_SCRATCH_BYTES = 8u << 20;  // 8 MiB: B*N <= 2,097,152 (fp32) / 1,048,576 (fp64)
+
+static __device__ __align__(256) unsigned char g_fps_static_scratch[FPS_STATIC_SCRATCH_BYTES];
+
+constexpr int FPS_MAX_DEVICES = 64;
+void *g_fps_static_ptr[FPS_MAX_DEVICES] = {nullptr};
+
+// Device address of the static scratch on the CURRENT device (looked up on first use).
+int fps_static_scratch_ptr(void **out) {
+  int dev = -1;
+  TK3D_CUDA(cudaGetDevice(&dev));
+  TK3D_REQUIRE(dev >= 0 && dev < FPS_MAX_DEVICES, TK3D_ERR_UNSUPPORTED, "fps_static_scratch: device id %d", dev);
+  void *p = __atomic_load_n(&g_fps_static_ptr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    // Two threads racing here both obtain the same address; the store is idempotent.
+    TK3D_CUDA(cudaGetSymbolAddress(&p, g_fps_static_scratch));
+    TK3D_REQUIRE(p != nullptr, TK3D_ERR_CUDA, "fps_static_scratch: cudaGetSymbolAddress returned NULL");
+    __atomic_store_n(&g_fps_static_ptr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return TK3D_OK;
+}
+
+}  // namespace
+}  // namespace tk3d
+
+extern "C" size_t tk3d_fps_static_scratch_capacity(void) { return tk3d::FPS_STATIC_SCRATCH_BYTES; }
+
+extern "C" int tk3d_fps_static_scratch(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index,
+                                       int dtype, void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "fps_static_scratch: dtype %d", dtype);
+  TK3D_REQUIRE(B >= 0 && N >= 0, TK3D_ERR_SHAPE, "fps_static_scratch: negative size");
+  TK3D_REQUIRE(S > 0, TK3D_ERR_K, "fps_static_scratch: num_samples must be positive (got %lld)", (long long)S);
+  TK3D_REQUIRE(N >= S, TK3D_ERR_K, "fps_static_scratch: num_samples %lld exceeds the %lld points of a cloud",
+               (long long)S, (long long)N);
+  TK3D_REQUIRE(N < (1LL << 31) && B < (1LL << 31), TK3D_ERR_SHAPE, "fps_static_scratch: size too large");
+  const size_t elem = dtype == TK3D_F64 ? 8 : 4;
+  // B and N are below 2^31, so the product cannot overflow 64 bits.
+  const size_t need = (size_t)B * (size_t)N * elem;
+  TK3D_REQUIRE(need <= FPS_STATIC_SCRATCH_BYTES, TK3D_ERR_SCRATCH,
+               "fps_static_scratch: B*N = %lld running minima need %zu bytes, the built-in scratch holds %zu "
+               "(use tk3d_fps with a caller-provided buffer for larger problems)",
+               (long long)(B * N), need, (size_t)FPS_STATIC_SCRATCH_BYTES);
+  if (B == 0) return TK3D_OK;
+  TK3D_REQUIRE(points && index, TK3D_ERR_NULL, "fps_static_scratch: points/index is NULL");
+  void *scratch = nullptr;
+  const int rc = fps_static_scratch_ptr(&scratch);
+  if (rc != TK3D_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = threads_for(N);
+  // The kernel overwrites every running minimum it reads in its first step, so what an earlier
+  // call left in the array does not matter and nothing has to be cleared.
+  if (dtype == TK3D_F32)
+    fps_streaming_kernel<float><<<(unsigned)B, threads, 0, st>>>((const float *)points, N, S, index, (float *)scratch);
+  else
+    fps_streaming_kernel<double><<<(unsigned)B, threads, 0, st>>>((const double *)points, N, S, index,
+                                                                 (double *)scratch);
+  return check_launch("fps_streaming_kernel (static scratch)");
+}
