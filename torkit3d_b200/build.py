@@ -43,7 +43,8 @@ def build(force=False, verbose=False, extra_flags=()):
         obj = os.path.join(odir, s[:-3] + ".o")
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hm):
-            jobs.append([nvcc, "-c", src, "-o", obj] + NVCC_FLAGS + list(extra_flags))
+            jobs.append([nvcc, "-c", src, "-o", obj] + NVCC_FLAGS + list(extra_flags)
+                        + os.environ.get("TK3D_NVCC_FLAGS", "").split())
 
     def run(cmd):
         p = subprocess.run(cmd, capture_output=True, text=True)

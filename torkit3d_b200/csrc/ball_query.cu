@@ -1,6 +1,7 @@
 // Ball query: first k key indices (ascending) whose squared distance is < radius^2.
 //
-// fp32 fast path: the filter-then-verify sweep of sweep.cuh with a constant bound (radius^2).  A
+// fp32 fast path: the filter-then-verify sweep of sweep.cuh (pair layout, packed FMAs) with a
+// constant bound (radius^2).  A
 // verified hit is written straight to the output row; a query stops testing once it has k hits
 // (its threshold becomes -inf) and the block leaves the key loop as soon as all its queries are
 // full -- the reference keeps scanning to the end of the cloud.  Short rows are padded with the
@@ -33,7 +34,8 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
       qy = q[1];
       qz = q[2];
     }
-    const float mx[1] = {-2.f * qx}, my[1] = {-2.f * qy}, mz[1] = {-2.f * qz};
+    const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
+                 mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
     const float never = __int_as_float(0xff800000);
     float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
     int cnt = 0;
@@ -50,7 +52,7 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
         const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
         v = make_float4(x, y, z, sweep_key_w(x, y, z));
       }
-      tile[0][u] = v;
+      sweep_store_key(tile[0], u, v.x, v.y, v.z, v.w);
     }
     __syncthreads();
 
@@ -74,13 +76,14 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
       const int lim = (min(BQ_TILE, N2 - t0) + 7) & ~7;
 #pragma unroll 2
       for (int u0 = 0; u0 < lim; u0 += 8) {
-        float a[8];
-        if (__builtin_expect(sweep_group<1>(tl + u0, mx, my, mz, thr, a), 0)) {
+        float2 a[4];
+        if (__builtin_expect(sweep_group2<1>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int j = t0 + u0 + u;
-            if (!(a[u] >= thr[0]) && j < N2 && cnt < k && thr[0] != never) {
-              const float4 r = tl[u0 + u];
+            const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
+            if (!(av >= thr[0]) && j < N2 && cnt < k && thr[0] != never) {
+              const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {
                 row[cnt] = j;
@@ -94,7 +97,7 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
       if (more) {
         float4 *nx = tile[(t + 1) & 1];
 #pragma unroll
-        for (int p = 0; p < PER; ++p) nx[tid + p * BQ_THREADS] = nxt[p];
+        for (int p = 0; p < PER; ++p) sweep_store_key(nx, tid + p * BQ_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
       }
       // One barrier per tile; it also votes on "every query of this block is complete".
       if (__syncthreads_and(!valid || cnt == k)) break;

@@ -2,14 +2,16 @@
 //
 // A block of 128 threads owns 128*Q query points (Q per thread, 128 apart so loads and stores
 // coalesce) of one cloud and sweeps the whole partner cloud in 512-point tiles.  A tile is staged
-// in shared memory as float4 (x, y, z, w): every lane reads the same 16 bytes (one broadcast
-// LDS.128 per key point serves Q pairs).  The next tile's coordinates are fetched into registers
-// before the current tile is processed and written to the other buffer afterwards, so global
-// latency hides behind the arithmetic with a single barrier per tile.
+// in shared memory in the pair layout of sweep.cuh, (x0,x1,y0,y1)(z0,z1,w0,w1) per two keys; every
+// lane reads the same 32 bytes (two broadcast LDS.128 per key pair) and one packed FMA evaluates
+// the filter of one query against both keys.  The next tile's coordinates are fetched into
+// registers before the current tile is processed and written to the other buffer afterwards, so
+// global latency hides behind the arithmetic with a single barrier per tile.
 //
-// Per pair the hot loop issues 3 FFMA + 1 FSETP; the exactly rounded distance is recomputed only
-// for pairs that pass the filter (about ln(M) + a few per query), and the running minimum is
-// updated with a strict "<" in ascending key order, so the lowest index wins ties.
+// Per (key, query) pair the hot loop issues 1.5 packed FMA + 1 FSETP; the exactly rounded
+// distance is recomputed only for pairs that pass the filter (about ln(M) + a few per query), and
+// the running minimum is updated with a strict "<" in ascending key order, so the lowest index
+// wins ties.
 //
 // Both directions run in one launch; each block adds its partial sum of distances to `sums`.
 #include "sweep.cuh"
@@ -28,9 +30,11 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
                         int64_t *__restrict__ idx2, double *__restrict__ sums, int64_t blocks1,
                         int64_t blocks_total) {
   constexpr int PER = CF_TILE / CF_THREADS;
+  constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
   __shared__ float4 tile[2][CF_TILE];
   __shared__ double ssum[CF_THREADS / 32];
   const int tid = threadIdx.x;
+  const float pinf = __int_as_float(0x7f800000);
 
   for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
     const int dir = blk >= blocks1;
@@ -43,12 +47,13 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
     const int64_t b = id / chunks;
     const int i0 = (int)(id % chunks) * (CF_THREADS * Q) + tid;
 
-    float qx[Q], qy[Q], qz[Q], mx[Q], my[Q], mz[Q], thr[Q], best[Q];
+    float qx[Q], qy[Q], qz[Q], thr[Q], best[Q];
+    float2 mx[Q], my[Q], mz[Q];
     int arg[Q];
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
       const int i = i0 + s * CF_THREADS;
-      best[s] = __int_as_float(0x7f800000);
+      best[s] = pinf;
       arg[s] = -1;
       if (i < nq) {
         const float *q = qpts + (b * nq + i) * 3;
@@ -58,27 +63,27 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         thr[s] = __int_as_float(0x7fc00000);  // NaN: everything passes until a first candidate is verified
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
-        thr[s] = __int_as_float(0xff800000);  // -inf: never passes
+        thr[s] = -pinf;  // never passes
       }
-      mx[s] = -2.f * qx[s];
-      my[s] = -2.f * qy[s];
-      mz[s] = -2.f * qz[s];
+      mx[s] = make_float2(-2.f * qx[s], -2.f * qx[s]);
+      my[s] = make_float2(-2.f * qy[s], -2.f * qy[s]);
+      mz[s] = make_float2(-2.f * qz[s], -2.f * qz[s]);
     }
 
     const float *rb = rpts + b * (int64_t)nr * 3;
     const int ntiles = (nr + CF_TILE - 1) / CF_TILE;
 
-    // Prologue: stage tile 0 (padded to the full tile with points that cannot pass).
+    // Prologue: stage tile 0 (padded to the full tile with points that cannot be accepted).
     if (ntiles > 0) {
 #pragma unroll
       for (int p = 0; p < PER; ++p) {
         const int u = tid + p * CF_THREADS;
-        float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
         if (u < nr) {
           const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
-          v = make_float4(x, y, z, sweep_key_w(x, y, z));
+          sweep_store_key(tile[0], u, x, y, z, sweep_key_w(x, y, z));
+        } else {
+          sweep_store_key(tile[0], u, 0.f, 0.f, 0.f, pinf);
         }
-        tile[0][u] = v;
       }
     }
     __syncthreads();
@@ -100,30 +105,33 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
             py[p] = rb[(int64_t)j * 3 + 1];
             pz[p] = rb[(int64_t)j * 3 + 2];
           } else {
-            px[p] = py[p] = pz[p] = __int_as_float(0x7fc00000);  // marks "no point"
+            px[p] = py[p] = pz[p] = 0.f;
           }
         }
       }
 
-      constexpr int U = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
-      const int lim = (cnt + U - 1) / U * U;
+      const int lim = (cnt + GK - 1) / GK * GK;
 #pragma unroll 2
-      for (int u0 = 0; u0 < lim; u0 += U) {
-        float a[8];
-        if (__builtin_expect(sweep_group<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
+      for (int u0 = 0; u0 < lim; u0 += GK) {
+        float2 a[4];
+        if (__builtin_expect(sweep_group2<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int j = t0 + u0 + u;
-            if (j < nr) {
-              const float4 r = tl[u0 + u];
+          for (int p = 0; p < GK / 2; ++p) {
 #pragma unroll
-              for (int s = 0; s < Q; ++s) {
-                if (!(a[u * Q + s] >= thr[s])) {
-                  const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-                  if (d < best[s]) {
-                    best[s] = d;
-                    arg[s] = j;
-                    thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
+            for (int h = 0; h < 2; ++h) {
+              const int j = t0 + u0 + 2 * p + h;
+              if (j < nr) {
+                const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
+#pragma unroll
+                for (int s = 0; s < Q; ++s) {
+                  const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
+                  if (!(av >= thr[s])) {
+                    const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
+                    if (d < best[s]) {
+                      best[s] = d;
+                      arg[s] = j;
+                      thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
+                    }
                   }
                 }
               }
@@ -137,9 +145,10 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
 #pragma unroll
         for (int p = 0; p < PER; ++p) {
           const int u = tid + p * CF_THREADS;
-          float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
-          if (t0 + CF_TILE + u < nr) v = make_float4(px[p], py[p], pz[p], sweep_key_w(px[p], py[p], pz[p]));
-          nx[u] = v;
+          if (t0 + CF_TILE + u < nr)
+            sweep_store_key(nx, u, px[p], py[p], pz[p], sweep_key_w(px[p], py[p], pz[p]));
+          else
+            sweep_store_key(nx, u, 0.f, 0.f, 0.f, pinf);
         }
       }
       __syncthreads();

@@ -44,14 +44,16 @@ __global__ void __launch_bounds__(KN_THREADS)
 knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
                  float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
   constexpr int TILE = 512, PER = TILE / KN_THREADS;
-  __shared__ float4 tile[2][TILE];
+  constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
+  __shared__ float4 tile[2][TILE];  // pair layout of sweep.cuh
   const int tid = threadIdx.x;
   const int chunks = (N1 + KN_THREADS * Q - 1) / (KN_THREADS * Q);
 
   for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
     const int64_t b = blk / chunks;
     const int i0 = (int)(blk % chunks) * (KN_THREADS * Q) + tid;
-    float qx[Q], qy[Q], qz[Q], mx[Q], my[Q], mz[Q], thr[Q];
+    float qx[Q], qy[Q], qz[Q], thr[Q];
+    float2 mx[Q], my[Q], mz[Q];
     float kd[Q][K];
     int ki[Q][K];
 #pragma unroll
@@ -67,9 +69,9 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
         qx[s] = qy[s] = qz[s] = 0.f;
         thr[s] = -pinf();
       }
-      mx[s] = -2.f * qx[s];
-      my[s] = -2.f * qy[s];
-      mz[s] = -2.f * qz[s];
+      mx[s] = make_float2(-2.f * qx[s], -2.f * qx[s]);
+      my[s] = make_float2(-2.f * qy[s], -2.f * qy[s]);
+      mz[s] = make_float2(-2.f * qz[s], -2.f * qz[s]);
 #pragma unroll
       for (int c = 0; c < K; ++c) {
         kd[s][c] = pinf();
@@ -80,7 +82,11 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
     const float *rb = key + b * (int64_t)N2 * 3;
     const int ntiles = (N2 + TILE - 1) / TILE;
 #pragma unroll
-    for (int p = 0; p < PER; ++p) tile[0][tid + p * KN_THREADS] = make_key(rb, tid + p * KN_THREADS, N2);
+    for (int p = 0; p < PER; ++p) {
+      const int u = tid + p * KN_THREADS;
+      const float4 v = make_key(rb, u, N2);
+      sweep_store_key(tile[0], u, v.x, v.y, v.z, v.w);
+    }
     __syncthreads();
 
     for (int t = 0; t < ntiles; ++t) {
@@ -92,40 +98,44 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll
         for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2);
       }
-      constexpr int U = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
-      const int lim = (min(TILE, N2 - t0) + U - 1) / U * U;
+      const int lim = (min(TILE, N2 - t0) + GK - 1) / GK * GK;
 #pragma unroll 2
-      for (int u0 = 0; u0 < lim; u0 += U) {
-        float a[8];
-        if (__builtin_expect(sweep_group<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
+      for (int u0 = 0; u0 < lim; u0 += GK) {
+        float2 a[4];
+        if (__builtin_expect(sweep_group2<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int j = t0 + u0 + u;
-            if (j >= N2) continue;
-            const float4 r = tl[u0 + u];
+          for (int p = 0; p < GK / 2; ++p) {
 #pragma unroll
-            for (int s = 0; s < Q; ++s) {
-              if (!(a[u * Q + s] >= thr[s])) {
-                const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-                // (d, j) enters iff it orders before the current last entry; sentinels carry
-                // (+inf, INT_MAX) so real entries always precede them.
-                if (d < kd[s][K - 1] || (d == kd[s][K - 1] && j < ki[s][K - 1])) {
-                  kd[s][K - 1] = d;
-                  ki[s][K - 1] = j;
+            for (int h = 0; h < 2; ++h) {
+              const int j = t0 + u0 + 2 * p + h;
+              if (j >= N2) continue;
+              const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
 #pragma unroll
-                  for (int c = K - 1; c > 0; --c) {
-                    const bool lt = kd[s][c] < kd[s][c - 1] || (kd[s][c] == kd[s][c - 1] && ki[s][c] < ki[s][c - 1]);
-                    if (lt) {
-                      const float td = kd[s][c];
-                      kd[s][c] = kd[s][c - 1];
-                      kd[s][c - 1] = td;
-                      const int ti = ki[s][c];
-                      ki[s][c] = ki[s][c - 1];
-                      ki[s][c - 1] = ti;
+              for (int s = 0; s < Q; ++s) {
+                const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
+                if (!(av >= thr[s])) {
+                  const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
+                  // (d, j) enters iff it orders before the current last entry; sentinels carry
+                  // (+inf, INT_MAX) so real entries always precede them.
+                  if (d < kd[s][K - 1] || (d == kd[s][K - 1] && j < ki[s][K - 1])) {
+                    kd[s][K - 1] = d;
+                    ki[s][K - 1] = j;
+#pragma unroll
+                    for (int c = K - 1; c > 0; --c) {
+                      const bool lt =
+                          kd[s][c] < kd[s][c - 1] || (kd[s][c] == kd[s][c - 1] && ki[s][c] < ki[s][c - 1]);
+                      if (lt) {
+                        const float td = kd[s][c];
+                        kd[s][c] = kd[s][c - 1];
+                        kd[s][c - 1] = td;
+                        const int ti = ki[s][c];
+                        ki[s][c] = ki[s][c - 1];
+                        ki[s][c - 1] = ti;
+                      }
                     }
+                    if (ki[s][K - 1] != 0x7fffffff)
+                      thr[s] = sweep_threshold(kd[s][K - 1], sweep_qq(qx[s], qy[s], qz[s]));
                   }
-                  if (ki[s][K - 1] != 0x7fffffff)
-                    thr[s] = sweep_threshold(kd[s][K - 1], sweep_qq(qx[s], qy[s], qz[s]));
                 }
               }
             }
@@ -135,7 +145,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
       if (more) {
         float4 *nx = tile[(t + 1) & 1];
 #pragma unroll
-        for (int p = 0; p < PER; ++p) nx[tid + p * KN_THREADS] = nxt[p];
+        for (int p = 0; p < PER; ++p) sweep_store_key(nx, tid + p * KN_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
       }
       __syncthreads();
     }

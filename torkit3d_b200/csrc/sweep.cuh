@@ -40,8 +40,8 @@ __device__ __forceinline__ float sweep_threshold(float lim, float qq) {
 __device__ __forceinline__ float sweep_qq(float x, float y, float z) { return fmaf(z, z, fmaf(y, y, x * x)); }
 
 // "Does any of the eight filter values fall below its threshold?"  Written in PTX so that the
-// eight compares chain through ONE predicate (setp.ltu.or) and a single branch follows; left to
-// the compiler, each compare becomes its own branch.  ltu = "less than or unordered", i.e.
+// eight compares chain through two predicates (setp.ltu.or) that are OR-ed once, and a single
+// branch follows; left to the compiler, each compare becomes its own branch.  ltu = "less than or unordered", i.e.
 // !(a >= t): a NaN on either side counts as a pass.
 __device__ __forceinline__ bool sweep_any8(float a0, float a1, float a2, float a3, float a4, float a5, float a6,
                                            float a7, float t0, float t1, float t2, float t3, float t4, float t5,
@@ -49,14 +49,16 @@ __device__ __forceinline__ bool sweep_any8(float a0, float a1, float a2, float a
   unsigned flag;
   asm("{\n\t"
       ".reg .pred p;\n\t"
+      ".reg .pred q;\n\t"
       "setp.ltu.f32 p, %1, %9;\n\t"
-      "setp.ltu.or.f32 p, %2, %10, p;\n\t"
+      "setp.ltu.f32 q, %2, %10;\n\t"
       "setp.ltu.or.f32 p, %3, %11, p;\n\t"
-      "setp.ltu.or.f32 p, %4, %12, p;\n\t"
+      "setp.ltu.or.f32 q, %4, %12, q;\n\t"
       "setp.ltu.or.f32 p, %5, %13, p;\n\t"
-      "setp.ltu.or.f32 p, %6, %14, p;\n\t"
+      "setp.ltu.or.f32 q, %6, %14, q;\n\t"
       "setp.ltu.or.f32 p, %7, %15, p;\n\t"
-      "setp.ltu.or.f32 p, %8, %16, p;\n\t"
+      "setp.ltu.or.f32 q, %8, %16, q;\n\t"
+      "or.pred p, p, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(flag)
@@ -70,21 +72,67 @@ __device__ __forceinline__ float sweep_lower(float mx, float my, float mz, const
   return fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
 }
 
-// Eight filter values for a group of 8/Q consecutive keys x Q queries, and the combined test.
-// a[u*Q + s] belongs to key u of the group and query s.
-template <int Q>
+// Filter values for a group of U consecutive keys x Q queries (U*Q a multiple of 8), and the
+// combined test "does any of them pass".  a[u*Q + s] belongs to key u of the group and query s.
+template <int Q, int U>
 __device__ __forceinline__ bool sweep_group(const float4 *__restrict__ keys, const float (&mx)[Q],
                                             const float (&my)[Q], const float (&mz)[Q], const float (&thr)[Q],
-                                            float (&a)[8]) {
-  constexpr int U = 8 / Q;
+                                            float (&a)[U * Q]) {
+  static_assert((U * Q) % 8 == 0, "a filter group holds a multiple of eight pairs");
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const float4 r = keys[u];
 #pragma unroll
     for (int s = 0; s < Q; ++s) a[u * Q + s] = sweep_lower(mx[s], my[s], mz[s], r);
   }
-  return sweep_any8(a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], thr[0 % Q], thr[1 % Q], thr[2 % Q], thr[3 % Q],
-                    thr[4 % Q], thr[5 % Q], thr[6 % Q], thr[7 % Q]);
+  bool any = false;
+#pragma unroll
+  for (int g = 0; g < U * Q; g += 8)
+    any |= sweep_any8(a[g + 0], a[g + 1], a[g + 2], a[g + 3], a[g + 4], a[g + 5], a[g + 6], a[g + 7],
+                      thr[(g + 0) % Q], thr[(g + 1) % Q], thr[(g + 2) % Q], thr[(g + 3) % Q], thr[(g + 4) % Q],
+                      thr[(g + 5) % Q], thr[(g + 6) % Q], thr[(g + 7) % Q]);
+  return any;
+}
+
+// ---- key tiles in "pair" layout, for the packed FP32 instructions of sm_100 ------------------------
+// Two consecutive keys (2p, 2p+1) occupy two float4 slots:
+//     tile[2p]   = (x0, x1, y0, y1)      tile[2p+1] = (z0, z1, w0, w1)
+// so that one fma.rn.f32x2 (FFMA2) evaluates the filter of one query against BOTH keys: the
+// query's multipliers are held duplicated, (m, m), in 64-bit register pairs.  A packed FMA takes
+// one issue slot and three 64-bit register reads for two FMAs, which relieves the issue and
+// register-file limits that cap the scalar loop well below the FMA rate.
+__device__ __forceinline__ void sweep_store_key(float4 *tile, int u, float x, float y, float z, float w) {
+  float *f = reinterpret_cast<float *>(tile) + (u >> 1) * 8 + (u & 1);
+  f[0] = x;
+  f[2] = y;
+  f[4] = z;
+  f[6] = w;
+}
+
+__device__ __forceinline__ float4 sweep_load_key(const float4 *tile, int u) {
+  const float *f = reinterpret_cast<const float *>(tile) + (u >> 1) * 8 + (u & 1);
+  return make_float4(f[0], f[2], f[4], f[6]);
+}
+
+// Filter values of a group of 4/Q key pairs (8/Q keys) x Q queries: a[p*Q + s] = (value for key
+// 2p, value for key 2p+1) of query s; returns "any of the eight passes".  `pairs` points at the
+// first float4 slot of the group (slot index = key index, which must be even).
+template <int Q>
+__device__ __forceinline__ bool sweep_group2(const float4 *__restrict__ pairs, const float2 (&mx)[Q],
+                                             const float2 (&my)[Q], const float2 (&mz)[Q], const float (&thr)[Q],
+                                             float2 (&a)[4]) {
+  static_assert(Q == 1 || Q == 2 || Q == 4, "eight (key, query) pairs per group");
+  constexpr int P = 4 / Q;
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const float4 A = pairs[2 * p], Bv = pairs[2 * p + 1];
+    const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
+    const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
+#pragma unroll
+    for (int s = 0; s < Q; ++s) a[p * Q + s] = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
+  }
+  return sweep_any8(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0 % Q], thr[0 % Q],
+                    thr[1 % Q], thr[1 % Q], thr[2 % Q], thr[2 % Q], thr[3 % Q], thr[3 % Q]);
 }
 
 // Stage `count` key points starting at `src` (array of xyz triples) into `dst` as (x,y,z,w).
