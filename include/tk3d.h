@@ -149,9 +149,15 @@ int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, i
  *   out [B,C,N2,K]                out
  * An index outside [0,N1) yields 0 (the reference faults the device instead); when `status` is not
  * NULL, bit 0 of *status (a device int32 the caller zeroed) is set if any such index was seen.
+ *   scratch   optional device buffer of tk3d_group_fwd_scratch_bytes(...) bytes.  When that function
+ *             returns non-zero and the buffer is given, the features are first transposed into it
+ *             ([B,N1,C]) so that every gather reads whole contiguous rows -- several times faster
+ *             when the output is much larger than the features.  Without it (NULL) the call gathers
+ *             from the native layout.  Results are identical.
  */
+size_t tk3d_group_fwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype);
 int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K,
-                   void *out, int32_t *status, int dtype, void *stream);
+                   void *out, int32_t *status, void *scratch, size_t scratch_bytes, int dtype, void *stream);
 
 /*
  * group_points backward: grad_in[b,c,index[b,m,j]] += grad_out[b,c,m,j] (grad_in is zeroed first).
@@ -168,9 +174,12 @@ int tk3d_group_bwd(const void *grad_out, const int64_t *index, int64_t B, int64_
  * torkit3d/csrc/cuda/interpolate_kernel.cu:49-103).  K must be 3, as in the reference.
  *   in [B,C,N1], index [B,N2,3], weight [B,N2,3]   in
  *   out [B,C,N2]                                   out
+ *   scratch   optional, tk3d_interp_fwd_scratch_bytes(...) bytes: same role as in tk3d_group_fwd.
  */
+size_t tk3d_interp_fwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int dtype);
 int tk3d_interp_fwd(const void *in, const int64_t *index, const void *weight, int64_t B, int64_t C, int64_t N1,
-                    int64_t N2, int64_t K, void *out, int32_t *status, int dtype, void *stream);
+                    int64_t N2, int64_t K, void *out, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
+                    void *stream);
 
 /*
  * Feature interpolation backward (w.r.t. the features only):

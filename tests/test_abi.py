@@ -59,12 +59,18 @@ def test_argument_errors_need_no_gpu(lib):
     assert lib.tk3d_fps_scratch_bytes(4, 8193, F32) == 4 * 8193 * 4
     assert lib.tk3d_fps_scratch_bytes(4, 100, 1) == 4 * 100 * 8
     assert lib.tk3d_ball_query(fake, fake, 1, 8, 8, 0.1, 0, fake, F32, None) == 3
-    assert lib.tk3d_interp_fwd(fake, fake, fake, 1, 1, 8, 8, 4, fake, None, F32, None) == 3  # k != 3
+    assert lib.tk3d_interp_fwd(fake, fake, fake, 1, 1, 8, 8, 4, fake, None, None, 0, F32, None) == 3  # k != 3
     assert lib.tk3d_chamfer_fwd(None, fake, 1, 8, 8, fake, fake, fake, fake, None, F32, None) == 1
     assert lib.tk3d_three_nn_weight(fake, 4, 9, fake, F32, None) == 3
     # empty problems succeed without launching anything
     assert lib.tk3d_knn(None, None, 0, 8, 4, 2, None, None, F32, None) == 0
-    assert lib.tk3d_group_fwd(None, None, 0, 4, 8, 8, 2, None, None, F32, None) == 0
+    assert lib.tk3d_group_fwd(None, None, 0, 4, 8, 8, 2, None, None, None, 0, F32, None) == 0
+    # the row-gather path wants scratch only when the output dwarfs the features
+    assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 1024, 32, F32) == 32 * 64 * 8192 * 4
+    assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 16, 4, F32) == 0
+    assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 1024, 32, 1) == 0
+    assert lib.tk3d_interp_fwd_scratch_bytes(8, 128, 32768, 131072, F32) == 8 * 128 * 32768 * 4
+    assert lib.tk3d_interp_fwd_scratch_bytes(8, 4, 32768, 131072, F32) == 0
 
 
 def test_shim_rejects_cpu_tensors():

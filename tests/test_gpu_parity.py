@@ -324,7 +324,7 @@ def test_group_golden_and_bad_index(golden):
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     lib = _lib.load()
     o2 = torch.empty_like(out)
-    assert lib.tk3d_group_fwd(f.data_ptr(), idx.data_ptr(), 1, 2, 10, 1, 4, o2.data_ptr(), status.data_ptr(), 0,
+    assert lib.tk3d_group_fwd(f.data_ptr(), idx.data_ptr(), 1, 2, 10, 1, 4, o2.data_ptr(), status.data_ptr(), None, 0, 0,
                               torch.cuda.current_stream().cuda_stream) == 0
     assert int(status.item()) == 1 and torch.equal(o2, out)
 
@@ -375,6 +375,49 @@ def test_interpolate_golden_weights_and_errors(oracle, golden):
     np.testing.assert_allclose(N(w), ew, rtol=1e-6)
     out = interpolate_feature(T(feat), i, w)
     np.testing.assert_allclose(N(out), oracle.interp_fwd(feat, ei, ew), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("B,C,n1,n2,k", [(3, 64, 700, 300, 16), (2, 33, 129, 100, 9), (2, 128, 512, 2048, 4), (1, 512, 64, 70, 5),
+                                        (2, 64, 40, 25, 4), (2, 96, 100, 333, 12), (1, 512, 100, 201, 4)])
+def test_group_and_interp_row_gather_path_equals_direct_path(oracle, B, C, n1, n2, k):
+    """With a scratch buffer the forward gathers run on transposed features; same results."""
+    from torkit3d_b200 import _lib
+
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(3)
+    f = torch.randn(B, C, n1, device=DEV)
+    idx = torch.randint(0, n1, (B, n2, k), device=DEV)
+    idx[0, 0, 0] = -1  # bad index: reads as zero on both paths
+    need = lib.tk3d_group_fwd_scratch_bytes(B, C, n1, n2, k, 0)
+    assert need == B * C * n1 * 4
+    scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o_rows = torch.full((B, C, n2, k), float("nan"), device=DEV)
+    o_direct = torch.full((B, C, n2, k), float("nan"), device=DEV)
+    assert lib.tk3d_group_fwd(f.data_ptr(), idx.data_ptr(), B, C, n1, n2, k, o_rows.data_ptr(), status.data_ptr(),
+                              scratch.data_ptr(), need, 0, st) == 0
+    assert lib.tk3d_group_fwd(f.data_ptr(), idx.data_ptr(), B, C, n1, n2, k, o_direct.data_ptr(), None, None, 0, 0, st) == 0
+    assert torch.equal(o_rows, o_direct) and int(status.item()) == 1
+    ref_idx = idx.clone()
+    ref_idx[0, 0, 0] = 0
+    ref = oracle.group_fwd(N(f), N(ref_idx))
+    ref[0, :, 0, 0] = 0
+    np.testing.assert_array_equal(N(o_rows), ref)
+    # interpolation: k=3 neighbours
+    idx3 = torch.randint(0, n1, (B, n2, 3), device=DEV)
+    w = torch.rand(B, n2, 3, device=DEV)
+    need3 = lib.tk3d_interp_fwd_scratch_bytes(B, C, n1, n2, 0)
+    i_rows = torch.full((B, C, n2), float("nan"), device=DEV)
+    i_direct = torch.full((B, C, n2), float("nan"), device=DEV)
+    if need3:
+        scratch3 = torch.empty(need3, dtype=torch.uint8, device=DEV)
+        assert lib.tk3d_interp_fwd(f.data_ptr(), idx3.data_ptr(), w.data_ptr(), B, C, n1, n2, 3, i_rows.data_ptr(), None,
+                                   scratch3.data_ptr(), need3, 0, st) == 0
+        assert lib.tk3d_interp_fwd(f.data_ptr(), idx3.data_ptr(), w.data_ptr(), B, C, n1, n2, 3, i_direct.data_ptr(), None,
+                                   None, 0, 0, st) == 0
+        torch.testing.assert_close(i_rows, i_direct, rtol=1e-6, atol=1e-6)
+        np.testing.assert_allclose(N(i_rows), oracle.interp_fwd(N(f), N(idx3), N(w)), rtol=1e-5, atol=1e-6)
 
 
 def test_non_default_stream_and_determinism():

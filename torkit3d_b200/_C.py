@@ -123,8 +123,10 @@ def group_points_forward_cuda(input, index):
     _, N2, K = index.shape
     with torch.cuda.device(input.device):
         out = torch.empty((B, C, N2, K), dtype=input.dtype, device=input.device)
-        check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None, _dtype(input),
-                                 _stream(input)))
+        need = lib.tk3d_group_fwd_scratch_bytes(B, C, N1, N2, K, _dtype(input))
+        scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
+        check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None,
+                                 _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
     return out
 
 
@@ -171,8 +173,10 @@ def interpolate_forward_cuda(input, index, weight):
     N2 = index.size(1)
     with torch.cuda.device(input.device):
         out = torch.empty((B, C, N2), dtype=input.dtype, device=input.device)
+        need = lib.tk3d_interp_fwd_scratch_bytes(B, C, N1, N2, _dtype(input))
+        scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
         check(lib.tk3d_interp_fwd(_ptr(input), _ptr(index), _ptr(weight), B, C, N1, N2, 3, _ptr(out), None,
-                                  _dtype(input), _stream(input)))
+                                  _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
     return out
 
 

@@ -6,7 +6,7 @@
 // a contiguous run of E elements indexed by the SAME E indices for every channel, so a thread
 // loads its indices once (the reference re-reads the int64 index tensor for every channel) and
 // then walks the channels.
-#include "tk3d_common.cuh"
+#include "rows.cuh"
 
 namespace tk3d {
 
@@ -178,15 +178,26 @@ int check_group_args(const char *what, const void *a, const int64_t *index, cons
 
 using namespace tk3d;
 
+extern "C" size_t tk3d_group_fwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype) {
+  if (dtype != TK3D_F32 || B <= 0 || C <= 0 || N1 <= 0 || N2 <= 0 || K <= 0 || B > 65535) return 0;
+  return rows_profitable(C, N1, N2 * K, 1) ? rows_scratch_bytes(B, C, N1) : 0;
+}
+
 extern "C" int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
-                              int64_t K, void *out, int32_t *status, int dtype, void *stream) {
+                              int64_t K, void *out, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
+                              void *stream) {
   int rc = check_group_args("group_fwd", in, index, out, B, C, N1, N2, K, dtype);
   if (rc) return rc;
   const int64_t E = N2 * K;
   if (B * C * E == 0) return TK3D_OK;
   TK3D_REQUIRE(index && out && (in || N1 == 0), TK3D_ERR_NULL, "group_fwd: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == TK3D_F32) return group_fwd_t<float>((const float *)in, index, B, C, N1, E, (float *)out, status, st);
+  if (dtype == TK3D_F32) {
+    const size_t want = tk3d_group_fwd_scratch_bytes(B, C, N1, N2, K, dtype);
+    if (want != 0 && scratch != nullptr && scratch_bytes >= want)
+      return gather_rows<1>((const float *)in, index, nullptr, B, C, N1, E, (float *)out, status, (float *)scratch, st);
+    return group_fwd_t<float>((const float *)in, index, B, C, N1, E, (float *)out, status, st);
+  }
   return group_fwd_t<double>((const double *)in, index, B, C, N1, E, (double *)out, status, st);
 }
 

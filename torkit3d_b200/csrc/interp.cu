@@ -5,7 +5,7 @@
 // Memory-bound: the [B,C,N2] output dominates.  A thread owns one query m, loads its three indices
 // and weights once (the reference re-reads them for every channel) and walks the channels; lanes
 // of a warp hold consecutive m, so stores coalesce along N2.
-#include "tk3d_common.cuh"
+#include "rows.cuh"
 
 namespace tk3d {
 
@@ -149,16 +149,26 @@ int check_interp_args(const char *what, int64_t B, int64_t C, int64_t N1, int64_
 
 using namespace tk3d;
 
+extern "C" size_t tk3d_interp_fwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int dtype) {
+  if (dtype != TK3D_F32 || B <= 0 || C <= 0 || N1 <= 0 || N2 <= 0 || B > 65535) return 0;
+  return rows_profitable(C, N1, N2, 3) ? rows_scratch_bytes(B, C, N1) : 0;
+}
+
 extern "C" int tk3d_interp_fwd(const void *in, const int64_t *index, const void *weight, int64_t B, int64_t C,
-                               int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, int dtype,
-                               void *stream) {
+                               int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, void *scratch,
+                               size_t scratch_bytes, int dtype, void *stream) {
   int rc = check_interp_args("interp_fwd", B, C, N1, N2, K, dtype);
   if (rc) return rc;
   if (B * C * N2 == 0) return TK3D_OK;
   TK3D_REQUIRE(index && weight && out && (in || N1 == 0), TK3D_ERR_NULL, "interp_fwd: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == TK3D_F32)
+  if (dtype == TK3D_F32) {
+    const size_t want = tk3d_interp_fwd_scratch_bytes(B, C, N1, N2, dtype);
+    if (want != 0 && scratch != nullptr && scratch_bytes >= want)
+      return gather_rows<3>((const float *)in, index, (const float *)weight, B, C, N1, N2, (float *)out, status,
+                            (float *)scratch, st);
     return interp_fwd_t<float>((const float *)in, index, (const float *)weight, B, C, N1, N2, (float *)out, status, st);
+  }
   return interp_fwd_t<double>((const double *)in, index, (const double *)weight, B, C, N1, N2, (double *)out, status,
                               st);
 }
