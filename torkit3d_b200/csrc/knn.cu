@@ -1,10 +1,13 @@
 // Brute-force k nearest neighbours (squared distances, rows sorted ascending by (distance, index)).
 //
-// Three kernels:
+// Four kernels:
 //   knn_small_kernel<K,Q>  fp32, k <= 4: per-thread top-K in registers, filter-then-verify sweep
 //                          (sweep.cuh), insertion straight from the verify branch.  With k << N2
 //                          the branch is rare (about k ln(N2/k) times per query).
-//   knn_buffered_kernel<Q> fp32, 4 < k <= 128: same filter, but passing keys are only appended
+//   knn_twopass_kernel     fp32, 4 < k <= 16 (and N2 >= 32 k): pass 1 bounds the k-th distance from
+//                          class minima of the filter value, pass 2 collects the few candidates
+//                          below the bound, exact selection among them (see the kernel's header).
+//   knn_buffered_kernel<Q> fp32, other k <= 128: same filter, but passing keys are only appended
 //                          (predicated store, no branch) to a small per-query candidate buffer in
 //                          shared memory; buffers are drained into per-query sorted lists (also in
 //                          shared memory) by the whole warp at once, when any lane's buffer is
@@ -305,6 +308,227 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 }
 
 // ---------------------------------------------------------------------------------------------
+// Two-pass kernel for 4 < k <= 16 (fp32).
+//
+// Pass 1 sweeps all keys with the cheap filter value a (3 FMA per pair) and keeps, per query, the
+// minimum of a over NCH interleaved key classes (class = position inside a 256-key tile / 8, so
+// every class is spread over the whole cloud whatever the key order).  The k-th smallest class
+// minimum tau bounds the k-th smallest exact distance from above: the k classes below it each
+// hold a distinct key with a <= tau, and for any key
+//     d <= (a + 22.2u |r|^2 + 3.1u |q|^2 + |q|^2) (1 + 5.1u)
+// (upper counterpart of the bound derived in sweep.cuh; |r|^2 <= the cloud's maximum).
+// Pass 2 sweeps the keys again and records every key whose filter value admits d <= that bound --
+// typically about 1.4 k candidates -- and the exact top-k by (distance, index) is then selected
+// among the candidates only.  No data-dependent work happens inside the sweeps, so the lanes of a
+// warp stay in step however the insert pattern of a one-pass top-k would look.
+//
+// Work split: a block of 4 warps serves 32 queries; warp s sweeps the s-th quarter of every key
+// tile for all 32 queries (lane = query), so a cloud of a few thousand queries still fills the
+// GPU.  Class minima and candidate lists are merged through shared memory; the final selection
+// orders by (distance, index) explicitly, so the order in which candidates arrive does not matter.
+// If a candidate buffer overflows (massive ties, adversarial or non-finite input) the query falls
+// back to an exact insertion scan over all keys.
+constexpr int KT_THREADS = 128;
+constexpr int KT_SPLIT = KT_THREADS / 32;  // key quarters per tile
+constexpr int KT_TILE = 256;
+constexpr int KT_NCH = 32;                 // key classes (8 keys per class per tile)
+constexpr int KT_CAP = 40;                 // candidate slots per (query, quarter); 32 usable + one group of slack
+
+__global__ void __launch_bounds__(KT_THREADS)
+knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k,
+                   float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
+  constexpr int PER = KT_TILE / KT_THREADS;
+  constexpr int CPW = KT_NCH / KT_SPLIT;  // classes per warp = 8
+  __shared__ float4 tile[2][KT_TILE];              // pair layout of sweep.cuh
+  __shared__ float cm[KT_NCH][32];                 // class minima per query
+  __shared__ float ld[32][32];                     // [slot][query] selected distances (k <= 32)
+  __shared__ int li[32][32];                       // [slot][query] selected indices
+  __shared__ int cand[KT_SPLIT][KT_CAP][32];       // candidates per quarter and query
+  __shared__ int ccount[KT_SPLIT][32];
+  __shared__ float s_rmax[KT_SPLIT];
+  __shared__ float s_tau[32];
+  const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
+  const int chunks = (N1 + 31) / 32;
+  const float u = 5.9604645e-8f;
+
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int64_t b = blk / chunks;
+    const int i = (int)(blk % chunks) * 32 + lane;
+    const bool valid = i < N1;
+    float qx = 0.f, qy = 0.f, qz = 0.f;
+    if (valid) {
+      const float *q = query + (b * N1 + i) * 3;
+      qx = q[0];
+      qy = q[1];
+      qz = q[2];
+    }
+    const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
+                 mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
+    const float qq = sweep_qq(qx, qy, qz);
+    const float *rb = key + b * (int64_t)N2 * 3;
+    const int ntiles = (N2 + KT_TILE - 1) / KT_TILE;
+
+    // Key tiles are fetched into registers one tile ahead and committed to the other shared
+    // buffer after the current tile has been processed, so global latency overlaps the sweep.
+    float rmax = 0.f;
+    float4 nxt[PER];
+    auto fetch = [&](int t0) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        nxt[p] = make_key(rb, t0 + tid + p * KT_THREADS, N2);
+        if (t0 + tid + p * KT_THREADS < N2) rmax = fmaxf(rmax, fabsf(nxt[p].w));
+      }
+    };
+    auto commit = [&](float4 *dst) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * KT_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
+    };
+
+    // ---- pass 1: minima of the filter value over this warp's 8 classes
+    float cmin[CPW];
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) cmin[c] = pinf();
+    fetch(0);
+    commit(tile[0]);
+    __syncthreads();
+    for (int t = 0; t < ntiles; ++t) {
+      const float4 *tl = tile[t & 1] + part * (KT_TILE / KT_SPLIT);
+      if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
+#pragma unroll
+      for (int c = 0; c < CPW; ++c) {
+        float m = cmin[c];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float4 A = tl[c * 8 + 2 * p], Bv = tl[c * 8 + 2 * p + 1];
+          const float2 a = __ffma2_rn(mx[0], make_float2(A.x, A.y),
+                                      __ffma2_rn(my[0], make_float2(A.z, A.w),
+                                                 __ffma2_rn(mz[0], make_float2(Bv.x, Bv.y), make_float2(Bv.z, Bv.w))));
+          m = fminf(m, fminf(a.x, a.y));
+        }
+        cmin[c] = m;
+      }
+      if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
+      __syncthreads();
+    }
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) cm[part * CPW + c][lane] = cmin[c];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    if (lane == 0) s_rmax[part] = rmax;
+    __syncthreads();
+    rmax = fmaxf(fmaxf(s_rmax[0], s_rmax[1]), fmaxf(s_rmax[2], s_rmax[3]));
+
+    // k-th smallest class minimum of each query: rank by counting (ties broken by class number);
+    // each warp ranks its own 8 classes and the one with rank k-1 publishes the value.
+    if (part == 0) s_tau[lane] = pinf();
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) {
+      const float v = cmin[c];
+      const int cc = part * CPW + c;
+      int rank = 0;
+#pragma unroll 8
+      for (int o = 0; o < KT_NCH; ++o) {
+        const float w = cm[o][lane];
+        rank += (w < v || (w == v && o < cc)) ? 1 : 0;
+      }
+      if (rank == k - 1) s_tau[lane] = v;
+    }
+    __syncthreads();
+    const float tau = s_tau[lane];
+    // Upper bound of the k-th smallest exact distance (constants rounded up generously to cover
+    // the roundings of this very computation), then the filter threshold that admits every key
+    // at or below it.  Anything non-finite makes the threshold NaN: "accept all".
+    float thr[1];
+    {
+      const float a_up = tau + 32.f * u * rmax + 8.f * u * qq;
+      const float d_up = (a_up + qq * (1.f + 8.f * u)) * (1.f + 10.f * u) + 1e-37f;
+      const float lim = __int_as_float(__float_as_int(fmaxf(d_up, 0.f)) + 1);  // next float up
+      thr[0] = (d_up < 3.0e38f && rmax < 1.0e30f && qq < 1.0e30f) ? sweep_threshold(lim, qq) : qnan();
+      if (!valid) thr[0] = -pinf();
+    }
+
+    // ---- pass 2: collect this warp's candidates
+    int cnt = 0;
+    bool overflow = false;
+    fetch(0);
+    commit(tile[0]);
+    __syncthreads();
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = t * KT_TILE + part * (KT_TILE / KT_SPLIT);
+      const float4 *tl = tile[t & 1] + part * (KT_TILE / KT_SPLIT);
+      if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
+#pragma unroll 2
+      for (int u0 = 0; u0 < KT_TILE / KT_SPLIT; u0 += 8) {
+        // Straight-line append: the slot is always written, the count only advances on a pass.
+        // KT_CAP leaves room for one whole group beyond the checked limit.
+        if (cnt > KT_CAP - 8) {
+          overflow = true;
+          cnt = 0;
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float4 A = tl[u0 + 2 * p], Bv = tl[u0 + 2 * p + 1];
+          const float2 a = __ffma2_rn(mx[0], make_float2(A.x, A.y),
+                                      __ffma2_rn(my[0], make_float2(A.z, A.w),
+                                                 __ffma2_rn(mz[0], make_float2(Bv.x, Bv.y), make_float2(Bv.z, Bv.w))));
+          const int j = t0 + u0 + 2 * p;
+          cand[part][cnt][lane] = j;
+          cnt += (!(a.x >= thr[0]) && j < N2) ? 1 : 0;
+          cand[part][cnt][lane] = j + 1;
+          cnt += (!(a.y >= thr[0]) && j + 1 < N2) ? 1 : 0;
+        }
+      }
+      if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
+      __syncthreads();
+    }
+    ccount[part][lane] = overflow ? -1 : cnt;
+    __syncthreads();
+
+    // ---- exact selection among the candidates, ordered by (distance, index); warp 0, lane = query
+    if (part == 0 && valid) {
+      int nk = 0;
+      auto offer = [&](int j) {
+        const float d = sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], qx, qy, qz);
+        if (nk == k) {
+          const float dl = ld[k - 1][lane];
+          if (!(d < dl || (d == dl && j < li[k - 1][lane]))) return;
+        }
+        int pos = nk < k ? nk : k - 1;
+        while (pos > 0) {
+          const float dp = ld[pos - 1][lane];
+          if (!(d < dp || (d == dp && j < li[pos - 1][lane]))) break;
+          ld[pos][lane] = dp;
+          li[pos][lane] = li[pos - 1][lane];
+          --pos;
+        }
+        ld[pos][lane] = d;
+        li[pos][lane] = j;
+        if (nk < k) ++nk;
+      };
+      bool any_overflow = false;
+#pragma unroll
+      for (int s = 0; s < KT_SPLIT; ++s) any_overflow |= ccount[s][lane] < 0;
+      if (!any_overflow) {
+        for (int s = 0; s < KT_SPLIT; ++s) {
+          const int n = ccount[s][lane];
+          for (int c = 0; c < n; ++c) offer(cand[s][c][lane]);
+        }
+      } else {
+        for (int j = 0; j < N2; ++j) offer(j);
+      }
+      float *od = dist + (b * N1 + i) * (int64_t)k;
+      int64_t *oi = index + (b * N1 + i) * (int64_t)k;
+      for (int c = 0; c < k; ++c) {
+        od[c] = ld[c][lane];
+        oi[c] = (int64_t)li[c][lane];
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
 knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
@@ -407,6 +631,15 @@ int knn_buffered(const float *query, const float *key, int64_t B, int N1, int N2
   return check_launch("knn_buffered_kernel");
 }
 
+int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, int64_t *index,
+                cudaStream_t st) {
+  const int64_t total = B * ((N1 + 31) / 32);
+  const int64_t gcap = (int64_t)sm_count() * 256;
+  knn_twopass_kernel<<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, 0, st>>>(query, key, B, N1, N2, k, dist,
+                                                                                   index, total);
+  return check_launch("knn_twopass_kernel");
+}
+
 }  // namespace
 }  // namespace tk3d
 
@@ -434,6 +667,8 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
     case 4: return knn_small_q<4>(q, r, B, (int)N1, (int)N2, d, index, st);
     default: break;
   }
+  // Two-pass selection needs at least two key classes per wanted neighbour to be tight.
+  if (k <= 16 && N2 >= 32 * k) return knn_twopass(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
   if (k <= 128) {
     const int64_t sms = sm_count();
     if (k <= 32 && B * N1 >= sms * 2 * KN_THREADS * 2)

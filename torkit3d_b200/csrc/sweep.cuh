@@ -10,7 +10,7 @@
 //
 // Per key point the tile holds (x, y, z, w) with  w = fl(|r|^2 * (1 - 12u)),  u = 2^-24.
 // Per query the thread holds m = -2 q (exact) and a threshold t.  For a pair
-//     a = fma(m.x, r.x, fma(m.y, r.y, fma(m.z, r.z, w)))
+//     a = fma(m.x, r.x, fma(m.y, r.y, fma(m.z, r.z, w)))      (scalar or packed FMAs alike)
 // and with A = |r|^2 - 2 q.r (real arithmetic), P = |r|^2 + 2 sum|q_c r_c| <= 2|r|^2 + |q|^2:
 //     w  <= |r|^2 (1+3u)(1-12u)(1+u) <= |r|^2 (1 - 7.9u)      (|r|^2 summed with three roundings)
 //     a  <= (w - 2 q.r) + 3u P (1 + O(u))  <=  A + 3.01u |q|^2 (the |r|^2 terms cancel: -7.9u + 6u < 0)
@@ -72,28 +72,6 @@ __device__ __forceinline__ float sweep_lower(float mx, float my, float mz, const
   return fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
 }
 
-// Filter values for a group of U consecutive keys x Q queries (U*Q a multiple of 8), and the
-// combined test "does any of them pass".  a[u*Q + s] belongs to key u of the group and query s.
-template <int Q, int U>
-__device__ __forceinline__ bool sweep_group(const float4 *__restrict__ keys, const float (&mx)[Q],
-                                            const float (&my)[Q], const float (&mz)[Q], const float (&thr)[Q],
-                                            float (&a)[U * Q]) {
-  static_assert((U * Q) % 8 == 0, "a filter group holds a multiple of eight pairs");
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const float4 r = keys[u];
-#pragma unroll
-    for (int s = 0; s < Q; ++s) a[u * Q + s] = sweep_lower(mx[s], my[s], mz[s], r);
-  }
-  bool any = false;
-#pragma unroll
-  for (int g = 0; g < U * Q; g += 8)
-    any |= sweep_any8(a[g + 0], a[g + 1], a[g + 2], a[g + 3], a[g + 4], a[g + 5], a[g + 6], a[g + 7],
-                      thr[(g + 0) % Q], thr[(g + 1) % Q], thr[(g + 2) % Q], thr[(g + 3) % Q], thr[(g + 4) % Q],
-                      thr[(g + 5) % Q], thr[(g + 6) % Q], thr[(g + 7) % Q]);
-  return any;
-}
-
 // ---- key tiles in "pair" layout, for the packed FP32 instructions of sm_100 ------------------------
 // Two consecutive keys (2p, 2p+1) occupy two float4 slots:
 //     tile[2p]   = (x0, x1, y0, y1)      tile[2p+1] = (z0, z1, w0, w1)
@@ -133,17 +111,6 @@ __device__ __forceinline__ bool sweep_group2(const float4 *__restrict__ pairs, c
   }
   return sweep_any8(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0 % Q], thr[0 % Q],
                     thr[1 % Q], thr[1 % Q], thr[2 % Q], thr[2 % Q], thr[3 % Q], thr[3 % Q]);
-}
-
-// Stage `count` key points starting at `src` (array of xyz triples) into `dst` as (x,y,z,w).
-// Slots beyond `count` up to `padded` get a point that can never pass a filter (w = +inf gives
-// a = +inf or NaN; callers bound their loops by `count`, the padding only keeps LDS in range).
-template <int THREADS>
-__device__ __forceinline__ void sweep_stage_tile(float4 *dst, const float *__restrict__ src, int count, int tid) {
-  for (int u = tid; u < count; u += THREADS) {
-    const float x = src[u * 3 + 0], y = src[u * 3 + 1], z = src[u * 3 + 2];
-    dst[u] = make_float4(x, y, z, sweep_key_w(x, y, z));
-  }
 }
 
 }  // namespace tk3d
