@@ -1,6 +1,6 @@
 // Chamfer forward, fp32 fast path: register-tiled filter-then-verify sweep (see sweep.cuh).
 //
-// A block of 128 threads owns 128*Q query points (Q per thread, 128 apart so loads and stores
+// A block of 128 threads owns 128*Q query points (Q = 2 per thread, 128 apart so loads and stores
 // coalesce) of one cloud and sweeps the whole partner cloud in 512-point tiles.  A tile is staged
 // in shared memory in the pair layout of sweep.cuh, (x0,x1,y0,y1)(z0,z1,w0,w1) per two keys; every
 // lane reads the same 32 bytes (two broadcast LDS.128 per key pair) and one packed FMA evaluates
@@ -23,8 +23,8 @@ namespace {
 constexpr int CF_THREADS = 128;
 constexpr int CF_TILE = 512;
 
-template <int Q>
-__global__ void __launch_bounds__(CF_THREADS)
+template <int Q, int MINB = 1, int UNR = 2>
+__global__ void __launch_bounds__(CF_THREADS, MINB)
 chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int64_t B, int N1, int N2,
                         float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
                         int64_t *__restrict__ idx2, double *__restrict__ sums, int64_t blocks1,
@@ -111,7 +111,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
       }
 
       const int lim = (cnt + GK - 1) / GK * GK;
-#pragma unroll 2
+#pragma unroll UNR
       for (int u0 = 0; u0 < lim; u0 += GK) {
         float2 a[4];
         if (__builtin_expect(sweep_group2<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
@@ -181,7 +181,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
   }
 }
 
-template <int Q>
+template <int Q, int MINB = 1, int UNR = 2>
 int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
            float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
   const int64_t per = CF_THREADS * Q;
@@ -190,7 +190,7 @@ int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, floa
   if (total == 0) return TK3D_OK;
   const int64_t cap = (int64_t)sm_count() * 256;
   const unsigned grid = (unsigned)(total < cap ? total : cap);
-  chamfer_fwd_fast_kernel<Q><<<grid, CF_THREADS, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
+  chamfer_fwd_fast_kernel<Q, MINB, UNR><<<grid, CF_THREADS, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
                                                            blocks1, total);
   return check_launch("chamfer_fwd_fast_kernel");
 }
@@ -202,11 +202,11 @@ int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_
   // Queries per thread: more register tiling when there is enough work to fill the GPU with it.
   const int64_t queries = B * (N1 + N2);
   const int64_t sms = sm_count();
-  if (queries >= sms * 4 * CF_THREADS * 4)
-    return launch<4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+  // Measured on B200 (B=64, N=M=16384): two queries per thread, six resident blocks per SM and a
+  // four-fold unrolled key loop beat four queries per thread by about 10 %.
   if (queries >= sms * 2 * CF_THREADS * 2)
-    return launch<2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
-  return launch<1>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+    return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+  return launch<1, 1, 2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
 }
 
 }  // namespace tk3d

@@ -102,7 +102,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
         for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2);
       }
       const int lim = (min(TILE, N2 - t0) + GK - 1) / GK * GK;
-#pragma unroll 2
+#pragma unroll 4
       for (int u0 = 0; u0 < lim; u0 += GK) {
         float2 a[4];
         if (__builtin_expect(sweep_group2<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
@@ -332,39 +332,53 @@ constexpr int KT_THREADS = 128;
 constexpr int KT_SPLIT = KT_THREADS / 32;  // key quarters per tile
 constexpr int KT_TILE = 256;
 constexpr int KT_NCH = 32;                 // key classes (8 keys per class per tile)
-constexpr int KT_CAP = 40;                 // candidate slots per (query, quarter); 32 usable + one group of slack
+constexpr int KT_CAP = 40;                 // candidate slots per (query, quarter): 32 usable + one group of slack
 
+// Q = queries per lane (1 or 2): a block serves 32*Q queries.  Two queries per lane halve the
+// shared-memory reads per pair, one keeps more blocks in flight when queries are few.
+template <int Q>
 __global__ void __launch_bounds__(KT_THREADS)
 knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k,
                    float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
   constexpr int PER = KT_TILE / KT_THREADS;
   constexpr int CPW = KT_NCH / KT_SPLIT;  // classes per warp = 8
-  __shared__ float4 tile[2][KT_TILE];              // pair layout of sweep.cuh
-  __shared__ float cm[KT_NCH][32];                 // class minima per query
-  __shared__ float ld[32][32];                     // [slot][query] selected distances (k <= 32)
-  __shared__ int li[32][32];                       // [slot][query] selected indices
-  __shared__ int cand[KT_SPLIT][KT_CAP][32];       // candidates per quarter and query
-  __shared__ int ccount[KT_SPLIT][32];
+  constexpr int QS = 32 * Q;              // query slots per block
+  __shared__ float4 tile[2][KT_TILE];            // pair layout of sweep.cuh; reused for the result distances
+  __shared__ float cm[KT_NCH][QS];               // class minima per query; reused for the result indices
+  extern __shared__ __align__(16) int cand_raw[];  // [KT_SPLIT][KT_CAP][QS] candidates per quarter and query
+  int(*cand)[KT_CAP][QS] = reinterpret_cast<int(*)[KT_CAP][QS]>(cand_raw);
+  __shared__ int ccount[KT_SPLIT][QS];
   __shared__ float s_rmax[KT_SPLIT];
-  __shared__ float s_tau[32];
+  __shared__ float s_tau[QS];
+  static_assert(sizeof(tile) >= sizeof(float) * 16 * QS && sizeof(cm) >= sizeof(int) * 16 * QS, "result lists fit");
+  float(*ld)[QS] = reinterpret_cast<float(*)[QS]>(&tile[0][0]);  // [16][QS], valid after pass 2
+  int(*li)[QS] = reinterpret_cast<int(*)[QS]>(&cm[0][0]);        // [16][QS], valid after tau is known
   const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
-  const int chunks = (N1 + 31) / 32;
+  const int chunks = (N1 + QS - 1) / QS;
   const float u = 5.9604645e-8f;
 
   for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
     const int64_t b = blk / chunks;
-    const int i = (int)(blk % chunks) * 32 + lane;
-    const bool valid = i < N1;
-    float qx = 0.f, qy = 0.f, qz = 0.f;
-    if (valid) {
-      const float *q = query + (b * N1 + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
+    const int ibase = (int)(blk % chunks) * QS;
+    float qx[Q], qy[Q], qz[Q], qq[Q];
+    float2 mx[Q], my[Q], mz[Q];
+    bool valid[Q];
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      const int i = ibase + s * 32 + lane;
+      valid[s] = i < N1;
+      qx[s] = qy[s] = qz[s] = 0.f;
+      if (valid[s]) {
+        const float *q = query + (b * N1 + i) * 3;
+        qx[s] = q[0];
+        qy[s] = q[1];
+        qz[s] = q[2];
+      }
+      mx[s] = make_float2(-2.f * qx[s], -2.f * qx[s]);
+      my[s] = make_float2(-2.f * qy[s], -2.f * qy[s]);
+      mz[s] = make_float2(-2.f * qz[s], -2.f * qz[s]);
+      qq[s] = sweep_qq(qx[s], qy[s], qz[s]);
     }
-    const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
-                 mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
-    const float qq = sweep_qq(qx, qy, qz);
     const float *rb = key + b * (int64_t)N2 * 3;
     const int ntiles = (N2 + KT_TILE - 1) / KT_TILE;
 
@@ -385,9 +399,12 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     };
 
     // ---- pass 1: minima of the filter value over this warp's 8 classes
-    float cmin[CPW];
+    float cmin[Q][CPW];
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) cmin[c] = pinf();
+    for (int s = 0; s < Q; ++s)
+#pragma unroll
+      for (int c = 0; c < CPW; ++c) cmin[s][c] = pinf();
+    __syncthreads();  // the previous block iteration's result lists alias the tile
     fetch(0);
     commit(tile[0]);
     __syncthreads();
@@ -396,61 +413,72 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
 #pragma unroll
       for (int c = 0; c < CPW; ++c) {
-        float m = cmin[c];
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
           const float4 A = tl[c * 8 + 2 * p], Bv = tl[c * 8 + 2 * p + 1];
-          const float2 a = __ffma2_rn(mx[0], make_float2(A.x, A.y),
-                                      __ffma2_rn(my[0], make_float2(A.z, A.w),
-                                                 __ffma2_rn(mz[0], make_float2(Bv.x, Bv.y), make_float2(Bv.z, Bv.w))));
-          m = fminf(m, fminf(a.x, a.y));
+          const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
+          const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
+#pragma unroll
+          for (int s = 0; s < Q; ++s) {
+            const float2 a = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
+            cmin[s][c] = fminf(cmin[s][c], fminf(a.x, a.y));
+          }
         }
-        cmin[c] = m;
       }
       if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
       __syncthreads();
     }
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) cm[part * CPW + c][lane] = cmin[c];
+    for (int s = 0; s < Q; ++s)
+#pragma unroll
+      for (int c = 0; c < CPW; ++c) cm[part * CPW + c][s * 32 + lane] = cmin[s][c];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
     if (lane == 0) s_rmax[part] = rmax;
+    if (tid < QS) s_tau[tid] = pinf();
     __syncthreads();
     rmax = fmaxf(fmaxf(s_rmax[0], s_rmax[1]), fmaxf(s_rmax[2], s_rmax[3]));
 
     // k-th smallest class minimum of each query: rank by counting (ties broken by class number);
     // each warp ranks its own 8 classes and the one with rank k-1 publishes the value.
-    if (part == 0) s_tau[lane] = pinf();
-    __syncthreads();
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) {
-      const float v = cmin[c];
-      const int cc = part * CPW + c;
-      int rank = 0;
+    for (int s = 0; s < Q; ++s) {
+#pragma unroll
+      for (int c = 0; c < CPW; ++c) {
+        const float v = cmin[s][c];
+        const int cc = part * CPW + c;
+        int rank = 0;
 #pragma unroll 8
-      for (int o = 0; o < KT_NCH; ++o) {
-        const float w = cm[o][lane];
-        rank += (w < v || (w == v && o < cc)) ? 1 : 0;
+        for (int o = 0; o < KT_NCH; ++o) {
+          const float w = cm[o][s * 32 + lane];
+          rank += (w < v || (w == v && o < cc)) ? 1 : 0;
+        }
+        if (rank == k - 1) s_tau[s * 32 + lane] = v;
       }
-      if (rank == k - 1) s_tau[lane] = v;
     }
     __syncthreads();
-    const float tau = s_tau[lane];
     // Upper bound of the k-th smallest exact distance (constants rounded up generously to cover
     // the roundings of this very computation), then the filter threshold that admits every key
     // at or below it.  Anything non-finite makes the threshold NaN: "accept all".
-    float thr[1];
-    {
-      const float a_up = tau + 32.f * u * rmax + 8.f * u * qq;
-      const float d_up = (a_up + qq * (1.f + 8.f * u)) * (1.f + 10.f * u) + 1e-37f;
+    float thr[Q];
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      const float tau = s_tau[s * 32 + lane];
+      const float a_up = tau + 32.f * u * rmax + 8.f * u * qq[s];
+      const float d_up = (a_up + qq[s] * (1.f + 8.f * u)) * (1.f + 10.f * u) + 1e-37f;
       const float lim = __int_as_float(__float_as_int(fmaxf(d_up, 0.f)) + 1);  // next float up
-      thr[0] = (d_up < 3.0e38f && rmax < 1.0e30f && qq < 1.0e30f) ? sweep_threshold(lim, qq) : qnan();
-      if (!valid) thr[0] = -pinf();
+      thr[s] = (d_up < 3.0e38f && rmax < 1.0e30f && qq[s] < 1.0e30f) ? sweep_threshold(lim, qq[s]) : qnan();
+      if (!valid[s]) thr[s] = -pinf();
     }
 
     // ---- pass 2: collect this warp's candidates
-    int cnt = 0;
-    bool overflow = false;
+    int cnt[Q];
+    bool overflow[Q];
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      cnt[s] = 0;
+      overflow[s] = false;
+    }
     fetch(0);
     commit(tile[0]);
     __syncthreads();
@@ -462,69 +490,82 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       for (int u0 = 0; u0 < KT_TILE / KT_SPLIT; u0 += 8) {
         // Straight-line append: the slot is always written, the count only advances on a pass.
         // KT_CAP leaves room for one whole group beyond the checked limit.
-        if (cnt > KT_CAP - 8) {
-          overflow = true;
-          cnt = 0;
+#pragma unroll
+        for (int s = 0; s < Q; ++s) {
+          if (cnt[s] > KT_CAP - 8) {
+            overflow[s] = true;
+            cnt[s] = 0;
+          }
         }
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
           const float4 A = tl[u0 + 2 * p], Bv = tl[u0 + 2 * p + 1];
-          const float2 a = __ffma2_rn(mx[0], make_float2(A.x, A.y),
-                                      __ffma2_rn(my[0], make_float2(A.z, A.w),
-                                                 __ffma2_rn(mz[0], make_float2(Bv.x, Bv.y), make_float2(Bv.z, Bv.w))));
+          const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
+          const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
           const int j = t0 + u0 + 2 * p;
-          cand[part][cnt][lane] = j;
-          cnt += (!(a.x >= thr[0]) && j < N2) ? 1 : 0;
-          cand[part][cnt][lane] = j + 1;
-          cnt += (!(a.y >= thr[0]) && j + 1 < N2) ? 1 : 0;
+#pragma unroll
+          for (int s = 0; s < Q; ++s) {
+            const float2 a = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
+            cand[part][cnt[s]][s * 32 + lane] = j;
+            cnt[s] += (!(a.x >= thr[s]) && j < N2) ? 1 : 0;
+            cand[part][cnt[s]][s * 32 + lane] = j + 1;
+            cnt[s] += (!(a.y >= thr[s]) && j + 1 < N2) ? 1 : 0;
+          }
         }
       }
       if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
       __syncthreads();
     }
-    ccount[part][lane] = overflow ? -1 : cnt;
+#pragma unroll
+    for (int s = 0; s < Q; ++s) ccount[part][s * 32 + lane] = overflow[s] ? -1 : cnt[s];
     __syncthreads();
 
-    // ---- exact selection among the candidates, ordered by (distance, index); warp 0, lane = query
-    if (part == 0 && valid) {
-      int nk = 0;
-      auto offer = [&](int j) {
-        const float d = sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], qx, qy, qz);
-        if (nk == k) {
-          const float dl = ld[k - 1][lane];
-          if (!(d < dl || (d == dl && j < li[k - 1][lane]))) return;
-        }
-        int pos = nk < k ? nk : k - 1;
-        while (pos > 0) {
-          const float dp = ld[pos - 1][lane];
-          if (!(d < dp || (d == dp && j < li[pos - 1][lane]))) break;
-          ld[pos][lane] = dp;
-          li[pos][lane] = li[pos - 1][lane];
-          --pos;
-        }
-        ld[pos][lane] = d;
-        li[pos][lane] = j;
-        if (nk < k) ++nk;
-      };
-      bool any_overflow = false;
+    // ---- exact selection among the candidates, ordered by (distance, index): warp s serves the
+    // queries of slot s (lane = query); the tile and class-minimum storage is free by now.
 #pragma unroll
-      for (int s = 0; s < KT_SPLIT; ++s) any_overflow |= ccount[s][lane] < 0;
-      if (!any_overflow) {
-        for (int s = 0; s < KT_SPLIT; ++s) {
-          const int n = ccount[s][lane];
-          for (int c = 0; c < n; ++c) offer(cand[s][c][lane]);
+    for (int s = 0; s < Q; ++s) {
+      if (part == s && valid[s]) {
+        const int col = s * 32 + lane;
+        int nk = 0;
+        auto offer = [&](int j) {
+          const float d = sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], qx[s],
+                                        qy[s], qz[s]);
+          if (nk == k) {
+            const float dl = ld[k - 1][col];
+            if (!(d < dl || (d == dl && j < li[k - 1][col]))) return;
+          }
+          int pos = nk < k ? nk : k - 1;
+          while (pos > 0) {
+            const float dp = ld[pos - 1][col];
+            if (!(d < dp || (d == dp && j < li[pos - 1][col]))) break;
+            ld[pos][col] = dp;
+            li[pos][col] = li[pos - 1][col];
+            --pos;
+          }
+          ld[pos][col] = d;
+          li[pos][col] = j;
+          if (nk < k) ++nk;
+        };
+        bool any_overflow = false;
+#pragma unroll
+        for (int w = 0; w < KT_SPLIT; ++w) any_overflow |= ccount[w][col] < 0;
+        if (!any_overflow) {
+          for (int w = 0; w < KT_SPLIT; ++w) {
+            const int n = ccount[w][col];
+            for (int c = 0; c < n; ++c) offer(cand[w][c][col]);
+          }
+        } else {
+          for (int j = 0; j < N2; ++j) offer(j);
         }
-      } else {
-        for (int j = 0; j < N2; ++j) offer(j);
-      }
-      float *od = dist + (b * N1 + i) * (int64_t)k;
-      int64_t *oi = index + (b * N1 + i) * (int64_t)k;
-      for (int c = 0; c < k; ++c) {
-        od[c] = ld[c][lane];
-        oi[c] = (int64_t)li[c][lane];
+        const int i = ibase + col;
+        float *od = dist + (b * N1 + i) * (int64_t)k;
+        int64_t *oi = index + (b * N1 + i) * (int64_t)k;
+        for (int c = 0; c < k; ++c) {
+          od[c] = ld[c][col];
+          oi[c] = (int64_t)li[c][col];
+        }
       }
     }
-    __syncthreads();
   }
 }
 
@@ -609,7 +650,6 @@ template <int K>
 int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2, float *dist, int64_t *index,
                 cudaStream_t st) {
   const int64_t sms = sm_count();
-  if (B * (int64_t)N1 >= sms * 4 * KN_THREADS * 4) return knn_small<K, 4>(query, key, B, N1, N2, dist, index, st);
   if (B * (int64_t)N1 >= sms * 2 * KN_THREADS * 2) return knn_small<K, 2>(query, key, B, N1, N2, dist, index, st);
   return knn_small<K, 1>(query, key, B, N1, N2, dist, index, st);
 }
@@ -631,12 +671,16 @@ int knn_buffered(const float *query, const float *key, int64_t B, int N1, int N2
   return check_launch("knn_buffered_kernel");
 }
 
+template <int Q>
 int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, int64_t *index,
                 cudaStream_t st) {
-  const int64_t total = B * ((N1 + 31) / 32);
+  const int64_t total = B * ((N1 + 32 * Q - 1) / (32 * Q));
   const int64_t gcap = (int64_t)sm_count() * 256;
-  knn_twopass_kernel<<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, 0, st>>>(query, key, B, N1, N2, k, dist,
-                                                                                   index, total);
+  const size_t smem = sizeof(int) * KT_SPLIT * KT_CAP * 32 * Q;
+  if (smem + 20 * 1024 > 48 * 1024)
+    TK3D_CUDA(cudaFuncSetAttribute(knn_twopass_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  knn_twopass_kernel<Q><<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, smem, st>>>(query, key, B, N1, N2, k,
+                                                                                         dist, index, total);
   return check_launch("knn_twopass_kernel");
 }
 
@@ -668,7 +712,10 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
     default: break;
   }
   // Two-pass selection needs at least two key classes per wanted neighbour to be tight.
-  if (k <= 16 && N2 >= 32 * k) return knn_twopass(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+  if (k <= 16 && N2 >= 32 * k) {
+    if (B * N1 >= (int64_t)sm_count() * 4 * 64) return knn_twopass<2>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+    return knn_twopass<1>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+  }
   if (k <= 128) {
     const int64_t sms = sm_count();
     if (k <= 32 && B * N1 >= sms * 2 * KN_THREADS * 2)
