@@ -339,7 +339,10 @@ def run_b200(args, rank, world, local_rank):
     roofline = {"bound": "fp32", "kernel": "chamfer_fwd_fast_kernel", "achieved": achieved,
                 "peak": peak if peak else nominal, "peak_source": "measured live (dependent FFMA chains)" if peak
                 else "nominal 148 SM x 128 lanes x 2 x 1.965 GHz", "unit": "TFLOP/s",
-                "frac": achieved / (peak if peak else nominal), "nominal_peak": nominal, "traffic": None,
+                "frac": achieved / (peak if peak else nominal), "nominal_peak": nominal,
+                # DRAM read+write of this kernel from the committed ncu capture (profiles/chamfer_fwd.md:
+                # 6.32 MB at B=16), scaled to this launch by the clouds it processes
+                "traffic": 6.319e6 * Bl / 16.0, "traffic_unit": "bytes",
                 "flop_per_pair": PAIR_FLOP, "pairs_per_launch": pairs_local, "launch_ms": fwd_ms,
                 "pairs_per_sec": pairs_local / (fwd_ms * 1e-3)}
 
@@ -449,9 +452,38 @@ def run_reference_cuda(args, rank, world, local_rank):
     ms = time_steps(step, args.steps, args.warmup, flush)
     ms_step = sum(ms) / len(ms)
     pairs = 2.0 * C4["B"] * C4["N"] * C4["M"]
+    ext = {}
+    if not args.no_extras:
+        def t(fn, steps=3):
+            v = time_steps(fn, steps, 2, flush)
+            return sum(v) / len(v)
+
+        d1, i1, d2, i2 = ref.chamfer_distance_forward_cuda(x1, x2)
+        ext["c4_chamfer_fwd_ms"] = t(lambda: ref.chamfer_distance_forward_cuda(x1, x2))
+        ext["c4_chamfer_bwd_ms"] = t(lambda: ref.chamfer_distance_backward_cuda(g1, g2, x1, x2, i1, i2))
+        del x1, x2, d1, i1, d2, i2
+        q, r = [v.to(dev) for v in workloads.c2_knn()]
+        ext["c2_knn_k16_ms"] = t(lambda: ref.knn_distance_cuda(q, r, 16, 1))
+        p, feat = [v.to(dev) for v in workloads.c3_set_abstraction()]
+        ext["c3_fps_ms_per_batch"] = t(lambda: ref.sample_farthest_points_cuda(p, 1024))
+        idx = ref.sample_farthest_points_cuda(p, 1024)
+        cent = torch.gather(p, 1, idx.unsqueeze(2).expand(-1, -1, 3)).contiguous()
+        ext["c3_ball_query_ms"] = t(lambda: ref.ball_query_cuda(cent, p, 0.1, 32))
+        nbr = ref.ball_query_cuda(cent, p, 0.1, 32)
+        ext["c3_group_fwd_ms"] = t(lambda: ref.group_points_forward_cuda(feat, nbr))
+        go = torch.ones(32, 64, 1024, 32, device=dev)
+        ext["c3_group_bwd_ms"] = t(lambda: ref.group_points_backward_cuda(go, nbr, 8192))
+        del go
+        qq, rr, ff = [v.to(dev) for v in workloads.c5_scene_interp()]
+        ext["c5_three_nn_ms"] = t(lambda: ref.knn_distance_cuda(qq, rr, 3, 1), steps=2)
+        d, i = ref.knn_distance_cuda(qq, rr, 3, 1)
+        inv = 1.0 / torch.clamp(d, min=1e-10)
+        w = inv / inv.sum(2, keepdim=True)
+        ext["c5_interp_fwd_ms"] = t(lambda: ref.interpolate_forward_cuda(ff, i, w))
     print(json.dumps({"impl": "reference-cuda", "metric": "chamfer_point_pairs_per_sec", "value": pairs / (ms_step * 1e-3),
                       "unit": "pairs/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
                       "higher_is_better": True, "dtype": "f32", "data": "synthetic", "config": workload_config(1, 1),
+                      "extras": ext,
                       "note": "reference torkit3d._C compiled unmodified for sm_100a with default nvcc flags"}), flush=True)
 
 

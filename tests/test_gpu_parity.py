@@ -254,7 +254,7 @@ def test_fps_golden_fp64_and_duplicates(oracle, golden):
 # ---------------------------------------------------------------------------------------- ball query
 @pytest.mark.parametrize("B,n1,n2,r,k", [(2, 64, 128, 0.1, 32), (3, 65, 129, 10.0, 32), (4, 513, 2000, 0.3, 16),
                                         (2, 1000, 5000, 0.2, 64), (1, 1, 1, 1.0, 4), (2, 100, 700, 0.05, 1),
-                                        (30, 300, 600, 0.4, 8)])
+                                        (30, 300, 600, 0.4, 8), (40, 8000, 300, 0.4, 8)])
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_ball_query_bit_exact(oracle, B, n1, n2, r, k, dtype):
     from torkit3d_b200.ops import ball_query

@@ -108,6 +108,131 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
   }
 }
 
+// Few queries (B*N1 below a few hundred thousand): one query per thread cannot fill 148 SMs.  Here a
+// block of 4 warps serves 32 queries (lane = query) and warp s sweeps the s-th quarter of every
+// 256-key tile, so four times as many warps are in flight.  Every (quarter, query) keeps its own
+// ascending hit list in shared memory (at most K entries: a quarter can never contribute more than
+// K of the first K hits); at the end the four ascending lists of a query are merged by key index.
+constexpr int BS_TILE = 256;
+constexpr int BS_SPLIT = 4;
+constexpr int BS_MAX_K = 64;
+
+__global__ void __launch_bounds__(BQ_THREADS)
+ball_query_split_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
+                        float r2, int k, int64_t *__restrict__ index, int64_t blocks_total) {
+  constexpr int PER = BS_TILE / BQ_THREADS;
+  constexpr int QK = BS_TILE / BS_SPLIT;  // keys per warp per tile
+  __shared__ float4 tile[2][BS_TILE];
+  extern __shared__ int hits[];           // [BS_SPLIT][k][32]
+  __shared__ int hcount[BS_SPLIT][32];
+  const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
+  const int chunks = (N1 + 31) / 32;
+  const float never = __int_as_float(0xff800000);
+
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int64_t b = blk / chunks;
+    const int i = (int)(blk % chunks) * 32 + lane;
+    const bool valid = i < N1;
+    float qx = 0.f, qy = 0.f, qz = 0.f;
+    if (valid) {
+      const float *q = query + (b * N1 + i) * 3;
+      qx = q[0];
+      qy = q[1];
+      qz = q[2];
+    }
+    const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
+                 mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
+    float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
+    int cnt = 0;
+    int *mine = hits + (part * k) * 32 + lane;
+    const float *rb = key + b * (int64_t)N2 * 3;
+    const int ntiles = (N2 + BS_TILE - 1) / BS_TILE;
+
+    float4 nxt[PER];
+    auto fetch = [&](int t0) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        const int j = t0 + tid + p * BQ_THREADS;
+        float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
+        if (j < N2) {
+          const float x = rb[(int64_t)j * 3 + 0], y = rb[(int64_t)j * 3 + 1], z = rb[(int64_t)j * 3 + 2];
+          v = make_float4(x, y, z, sweep_key_w(x, y, z));
+        }
+        nxt[p] = v;
+      }
+    };
+    auto commit = [&](float4 *dst) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * BQ_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
+    };
+    fetch(0);
+    commit(tile[0]);
+    __syncthreads();
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = t * BS_TILE + part * QK;
+      const float4 *tl = tile[t & 1] + part * QK;
+      if (t + 1 < ntiles) fetch((t + 1) * BS_TILE);
+#pragma unroll 2
+      for (int u0 = 0; u0 < QK; u0 += 8) {
+        float2 a[4];
+        if (__builtin_expect(sweep_group2<1>(tl + u0, mx, my, mz, thr, a), 0)) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int j = t0 + u0 + u;
+            const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
+            if (!(av >= thr[0]) && j < N2 && cnt < k && thr[0] != never) {
+              const float4 r = sweep_load_key(tl, u0 + u);
+              const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
+              if (d < r2) {
+                mine[cnt * 32] = j;
+                if (++cnt == k) thr[0] = never;
+              }
+            }
+          }
+        }
+      }
+      if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
+      __syncthreads();
+    }
+    hcount[part][lane] = cnt;
+    __syncthreads();
+
+    // Merge: warp 0, lane = query.  Heads of the four ascending lists, smallest key index first.
+    if (part == 0 && valid) {
+      int64_t *row = index + (b * N1 + i) * (int64_t)k;
+      int pos[BS_SPLIT], n[BS_SPLIT];
+#pragma unroll
+      for (int s = 0; s < BS_SPLIT; ++s) {
+        pos[s] = 0;
+        n[s] = hcount[s][lane];
+      }
+      int out = 0;
+      int64_t first = -1;
+      while (out < k) {
+        int best = 0x7fffffff, bs = -1;
+#pragma unroll
+        for (int s = 0; s < BS_SPLIT; ++s) {
+          if (pos[s] < n[s]) {
+            const int h = hits[(s * k + pos[s]) * 32 + lane];
+            if (h < best) {
+              best = h;
+              bs = s;
+            }
+          }
+        }
+        if (bs < 0) break;
+#pragma unroll
+        for (int s = 0; s < BS_SPLIT; ++s)
+          if (s == bs) ++pos[s];
+        if (out == 0) first = best;
+        row[out++] = best;
+      }
+      for (int c = out; c < k; ++c) row[c] = first;
+    }
+    __syncthreads();
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
@@ -174,8 +299,15 @@ extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, in
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == TK3D_F32) {
     const float r2 = radius * radius;  // squared in fp32, as the reference does for float tensors
-    const int64_t total = B * ((N1 + BQ_THREADS - 1) / BQ_THREADS);
     const int64_t cap = (int64_t)sm_count() * 256;
+    if (k <= BS_MAX_K && B * N1 < (int64_t)sm_count() * 16 * BQ_THREADS) {
+      const int64_t total = B * ((N1 + 31) / 32);
+      const size_t smem = sizeof(int) * BS_SPLIT * (size_t)k * 32;
+      ball_query_split_kernel<<<(unsigned)(total < cap ? total : cap), BQ_THREADS, smem, st>>>(
+          (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, index, total);
+      return check_launch("ball_query_split_kernel");
+    }
+    const int64_t total = B * ((N1 + BQ_THREADS - 1) / BQ_THREADS);
     ball_query_fast_kernel<<<(unsigned)(total < cap ? total : cap), BQ_THREADS, 0, st>>>(
         (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, index, total);
     return check_launch("ball_query_fast_kernel");

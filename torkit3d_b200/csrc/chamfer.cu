@@ -119,6 +119,23 @@ chamfer_bwd_own_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const
   }
 }
 
+// Atomic add of a 3-vector to a row of an [.,3] array.  A row starts on an 8-byte boundary every
+// other point, so two of the three floats always go out as one vector reduction (red.v2.f32).
+__device__ __forceinline__ void red_add3(float *p, float a, float b, float c) {
+  if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+    atomicAdd(p + 2, c);
+  } else {
+    atomicAdd(p, a);
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p + 1), "f"(b), "f"(c) : "memory");
+  }
+}
+__device__ __forceinline__ void red_add3(double *p, double a, double b, double c) {
+  atomicAdd(p + 0, a);
+  atomicAdd(p + 1, b);
+  atomicAdd(p + 2, c);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 chamfer_bwd_scatter_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const T *__restrict__ xyz1,
@@ -138,9 +155,7 @@ chamfer_bwd_scatter_kernel(const T *__restrict__ g1, const T *__restrict__ g2, c
     const T *p = a + lin * 3;
     const T *q = bb + (b * nb + j) * 3;
     T *gb = (dir ? grad1 : grad2) + (b * nb + j) * 3;
-    atomicAdd(gb + 0, -(g * (p[0] - q[0])));
-    atomicAdd(gb + 1, -(g * (p[1] - q[1])));
-    atomicAdd(gb + 2, -(g * (p[2] - q[2])));
+    red_add3(gb, -(g * (p[0] - q[0])), -(g * (p[1] - q[1])), -(g * (p[2] - q[2])));
   }
 }
 
