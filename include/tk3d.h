@@ -163,10 +163,14 @@ int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, int64_t C, i
  * group_points backward: grad_in[b,c,index[b,m,j]] += grad_out[b,c,m,j] (grad_in is zeroed first).
  * Replaces group_points_backward_cuda (torkit3d/csrc/include/group_points.h:10-13,
  * torkit3d/csrc/cuda/group_points_kernel.cu:67-114).  Out-of-range indices are skipped and
- * reported through `status` as above.
+ * reported through `status` as above.  `scratch` (optional, tk3d_group_bwd_scratch_bytes(...) bytes): the
+ * gradients are accumulated with 16-byte vector atomics into a transposed [B,N1,C] buffer and transposed
+ * back, instead of scattered single-float atomics.  Its contents on entry are ignored.
  */
+size_t tk3d_group_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype);
 int tk3d_group_bwd(const void *grad_out, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
-                   int64_t K, void *grad_in, int32_t *status, int dtype, void *stream);
+                   int64_t K, void *grad_in, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
+                   void *stream);
 
 /*
  * Feature interpolation forward: out[b,c,m] = sum_{i<K} in[b,c,index[b,m,i]] * weight[b,m,i].
@@ -185,10 +189,13 @@ int tk3d_interp_fwd(const void *in, const int64_t *index, const void *weight, in
  * Feature interpolation backward (w.r.t. the features only):
  * grad_in[b,c,index[b,m,i]] += grad_out[b,c,m] * weight[b,m,i] (grad_in is zeroed first).
  * Replaces interpolate_backward_cuda (torkit3d/csrc/include/interpolate.h:12-16,
- * torkit3d/csrc/cuda/interpolate_kernel.cu:147-201).
+ * torkit3d/csrc/cuda/interpolate_kernel.cu:147-201).  `scratch` (optional,
+ * tk3d_interp_bwd_scratch_bytes(...) bytes) has the same role as in tk3d_group_bwd.
  */
+size_t tk3d_interp_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int dtype);
 int tk3d_interp_bwd(const void *grad_out, const int64_t *index, const void *weight, int64_t B, int64_t C,
-                    int64_t N1, int64_t N2, int64_t K, void *grad_in, int32_t *status, int dtype, void *stream);
+                    int64_t N1, int64_t N2, int64_t K, void *grad_in, int32_t *status, void *scratch,
+                    size_t scratch_bytes, int dtype, void *stream);
 
 /*
  * Inverse squared-distance weights of the k nearest neighbours:

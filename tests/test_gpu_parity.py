@@ -262,7 +262,8 @@ def test_ball_query_bit_exact(oracle, B, n1, n2, r, k, dtype):
     rng = np.random.default_rng(n1 + k)
     key = rng.standard_normal((B, n2, 3)).astype(dtype)
     query = rng.standard_normal((B, n1, 3)).astype(dtype)
-    query[:, : n1 // 2] = key[:, : n1 // 2]  # half of the queries coincide with keys
+    h = min(n1 // 2, n2)
+    query[:, :h] = key[:, :h]  # up to half of the queries coincide with keys
     got = N(ball_query(T(query), T(key), r, k, transpose=False))
     np.testing.assert_array_equal(got, oracle.ball_query(query, key, r, k))
     got_t = N(ball_query(T(query).transpose(1, 2), T(key).transpose(1, 2), r, k))  # default: channel-first
@@ -418,6 +419,52 @@ def test_group_and_interp_row_gather_path_equals_direct_path(oracle, B, C, n1, n
                                    None, 0, 0, st) == 0
         torch.testing.assert_close(i_rows, i_direct, rtol=1e-6, atol=1e-6)
         np.testing.assert_allclose(N(i_rows), oracle.interp_fwd(N(f), N(idx3), N(w)), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("B,C,n1,n2,k", [(3, 64, 700, 300, 16), (2, 128, 512, 2048, 4), (2, 64, 40, 25, 4), (2, 96, 100, 333, 12)])
+def test_group_and_interp_backward_row_path_equals_direct_path(oracle, B, C, n1, n2, k):
+    """With scratch the backward accumulates into a transposed buffer with vector atomics; same sums."""
+    from torkit3d_b200 import _lib
+
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(4)
+    idx = torch.randint(0, n1, (B, n2, k), device=DEV)
+    idx[:, :, k // 2:] = idx[:, :, :1]
+    idx[0, 0, 0] = n1 + 5  # out of range: skipped on both paths
+    go = torch.randn(B, C, n2, k, device=DEV)
+    need = lib.tk3d_group_bwd_scratch_bytes(B, C, n1, n2, k, 0)
+    assert need == B * C * n1 * 4
+    scratch = torch.full((need,), 77, dtype=torch.uint8, device=DEV)  # contents must be ignored
+    g_rows = torch.full((B, C, n1), float("nan"), device=DEV)
+    g_direct = torch.full((B, C, n1), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert lib.tk3d_group_bwd(go.data_ptr(), idx.data_ptr(), B, C, n1, n2, k, g_rows.data_ptr(), status.data_ptr(),
+                              scratch.data_ptr(), need, 0, st) == 0
+    assert lib.tk3d_group_bwd(go.data_ptr(), idx.data_ptr(), B, C, n1, n2, k, g_direct.data_ptr(), None, None, 0, 0, st) == 0
+    assert int(status.item()) == 1
+    torch.testing.assert_close(g_rows, g_direct, rtol=1e-5, atol=2e-5)
+    ref_idx = idx.clone()
+    ref_idx[0, 0, 0] = 0
+    gz = go.clone()
+    gz[0, :, 0, 0] = 0
+    np.testing.assert_allclose(N(g_rows), oracle.group_bwd(N(gz).astype(np.float64), N(ref_idx), n1), rtol=1e-5, atol=2e-5)
+    # interpolation backward (needs n2 % 4 == 0 for the row path)
+    idx3 = torch.randint(0, n1, (B, n2, 3), device=DEV)
+    w = torch.rand(B, n2, 3, device=DEV)
+    go3 = torch.randn(B, C, n2, device=DEV)
+    need3 = lib.tk3d_interp_bwd_scratch_bytes(B, C, n1, n2, 0)
+    i_direct = torch.empty(B, C, n1, device=DEV)
+    assert lib.tk3d_interp_bwd(go3.data_ptr(), idx3.data_ptr(), w.data_ptr(), B, C, n1, n2, 3, i_direct.data_ptr(), None,
+                               None, 0, 0, st) == 0
+    if need3:
+        scratch3 = torch.empty(need3, dtype=torch.uint8, device=DEV)
+        i_rows = torch.empty(B, C, n1, device=DEV)
+        assert lib.tk3d_interp_bwd(go3.data_ptr(), idx3.data_ptr(), w.data_ptr(), B, C, n1, n2, 3, i_rows.data_ptr(), None,
+                                   scratch3.data_ptr(), need3, 0, st) == 0
+        torch.testing.assert_close(i_rows, i_direct, rtol=1e-5, atol=2e-5)
+    np.testing.assert_allclose(N(i_direct), oracle.interp_bwd(N(go3).astype(np.float64), N(idx3), N(w).astype(np.float64), n1),
+                               rtol=1e-5, atol=2e-5)
 
 
 def test_non_default_stream_and_determinism():

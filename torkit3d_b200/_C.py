@@ -145,8 +145,10 @@ def group_points_backward_cuda(grad_output, index, n1):
     n1 = int(n1)
     with torch.cuda.device(grad_output.device):
         gin = torch.empty((B, C, n1), dtype=grad_output.dtype, device=grad_output.device)
+        need = lib.tk3d_group_bwd_scratch_bytes(B, C, n1, N2, K, _dtype(grad_output))
+        scratch = torch.empty((need,), dtype=torch.uint8, device=grad_output.device) if need else None
         check(lib.tk3d_group_bwd(_ptr(grad_output), _ptr(index), B, C, n1, N2, K, _ptr(gin), None,
-                                 _dtype(grad_output), _stream(grad_output)))
+                                 _ptr(scratch) if need else None, need, _dtype(grad_output), _stream(grad_output)))
     return gin
 
 
@@ -189,8 +191,10 @@ def interpolate_backward_cuda(grad_output, index, weight, n1):
     n1 = int(n1)
     with torch.cuda.device(grad_output.device):
         gin = torch.empty((B, C, n1), dtype=grad_output.dtype, device=grad_output.device)
+        need = lib.tk3d_interp_bwd_scratch_bytes(B, C, n1, N2, _dtype(grad_output))
+        scratch = torch.empty((need,), dtype=torch.uint8, device=grad_output.device) if need else None
         check(lib.tk3d_interp_bwd(_ptr(grad_output), _ptr(index), _ptr(weight), B, C, n1, N2, 3, _ptr(gin), None,
-                                  _dtype(grad_output), _stream(grad_output)))
+                                  _ptr(scratch) if need else None, need, _dtype(grad_output), _stream(grad_output)))
     return gin
 
 

@@ -30,11 +30,14 @@ SIGNATURES = {
     "tk3d_ball_query": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _i64, _vp, _int, _vp]),
     "tk3d_group_fwd_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _i64, _int]),
     "tk3d_group_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int, _vp]),
-    "tk3d_group_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_group_bwd_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _i64, _int]),
+    "tk3d_group_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int, _vp]),
     "tk3d_interp_fwd_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _int]),
     "tk3d_interp_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int,
                                _vp]),
-    "tk3d_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_interp_bwd_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _int]),
+    "tk3d_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int,
+                               _vp]),
     "tk3d_three_nn_weight": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
     "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
 }

@@ -201,14 +201,26 @@ extern "C" int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, i
   return group_fwd_t<double>((const double *)in, index, B, C, N1, E, (double *)out, status, st);
 }
 
+extern "C" size_t tk3d_group_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype) {
+  if (dtype != TK3D_F32 || C % 4 != 0 || (N2 * K) % 4 != 0 || (N1 + 31) / 32 > 65535) return 0;
+  return tk3d_group_fwd_scratch_bytes(B, C, N1, N2, K, dtype);
+}
+
 extern "C" int tk3d_group_bwd(const void *gout, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
-                              int64_t K, void *gin, int32_t *status, int dtype, void *stream) {
+                              int64_t K, void *gin, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
+                              void *stream) {
   int rc = check_group_args("group_bwd", gout, index, gin, B, C, N1, N2, K, dtype);
   if (rc) return rc;
   const int64_t E = N2 * K;
   if (B * C * N1 == 0) return TK3D_OK;
   TK3D_REQUIRE(gin && (E == 0 || (index && gout)), TK3D_ERR_NULL, "group_bwd: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == TK3D_F32) return group_bwd_t<float>((const float *)gout, index, B, C, N1, E, (float *)gin, status, st);
+  if (dtype == TK3D_F32) {
+    const size_t want = tk3d_group_bwd_scratch_bytes(B, C, N1, N2, K, dtype);
+    if (want != 0 && scratch != nullptr && scratch_bytes >= want && rows_vec_ok(C, E, gout, scratch))
+      return scatter_rows<1>((const float *)gout, index, nullptr, B, C, N1, E, (float *)gin, status, (float *)scratch,
+                             st);
+    return group_bwd_t<float>((const float *)gout, index, B, C, N1, E, (float *)gin, status, st);
+  }
   return group_bwd_t<double>((const double *)gout, index, B, C, N1, E, (double *)gin, status, st);
 }

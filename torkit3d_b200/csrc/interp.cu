@@ -173,17 +173,27 @@ extern "C" int tk3d_interp_fwd(const void *in, const int64_t *index, const void 
                               st);
 }
 
+extern "C" size_t tk3d_interp_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int dtype) {
+  if (dtype != TK3D_F32 || C % 4 != 0 || N2 % 4 != 0 || (N1 + 31) / 32 > 65535) return 0;
+  return tk3d_interp_fwd_scratch_bytes(B, C, N1, N2, dtype);
+}
+
 extern "C" int tk3d_interp_bwd(const void *gout, const int64_t *index, const void *weight, int64_t B, int64_t C,
-                               int64_t N1, int64_t N2, int64_t K, void *gin, int32_t *status, int dtype,
-                               void *stream) {
+                               int64_t N1, int64_t N2, int64_t K, void *gin, int32_t *status, void *scratch,
+                               size_t scratch_bytes, int dtype, void *stream) {
   int rc = check_interp_args("interp_bwd", B, C, N1, N2, K, dtype);
   if (rc) return rc;
   if (B * C * N1 == 0) return TK3D_OK;
   TK3D_REQUIRE(gin && (N2 == 0 || (index && weight && gout)), TK3D_ERR_NULL, "interp_bwd: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == TK3D_F32)
+  if (dtype == TK3D_F32) {
+    const size_t want = tk3d_interp_bwd_scratch_bytes(B, C, N1, N2, dtype);
+    if (want != 0 && scratch != nullptr && scratch_bytes >= want && rows_vec_ok(C, N2, gout, scratch))
+      return scatter_rows<3>((const float *)gout, index, (const float *)weight, B, C, N1, N2, (float *)gin, status,
+                             (float *)scratch, st);
     return interp_bwd_t<float>((const float *)gout, index, (const float *)weight, B, C, N1, N2, (float *)gin, status,
                                st);
+  }
   return interp_bwd_t<double>((const double *)gout, index, (const double *)weight, B, C, N1, N2, (double *)gin,
                               status, st);
 }

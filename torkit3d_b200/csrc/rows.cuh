@@ -188,6 +188,82 @@ gather_rows_vec4_kernel(const float *__restrict__ featT, const int64_t *__restri
   }
 }
 
+// 16-byte vector reduction: four consecutive floats of one row in a single L2 atomic operation.
+__device__ __forceinline__ void red_add4(float *p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Backward of the row gathers: gradT[b, index[b,e(,i)], :] += gout[b, :, e] (* weight[b,e,i]) into a
+// zeroed transposed accumulator [B,N1,C], which the host transposes back afterwards.  The tile of
+// gout is read with 16-byte loads along the entry axis, turned into rows through the same swizzled
+// shared-memory tile as the forward, and every lane issues 16-byte vector reductions on contiguous
+// row pieces, so the L2 atomics work on full sectors instead of scattered single floats.
+template <int NSRC>
+__global__ void __launch_bounds__(ROWS_THREADS)
+scatter_rows_vec4_kernel(const float *__restrict__ gout, const int64_t *__restrict__ index,
+                         const float *__restrict__ weight, int C, int64_t N1, int64_t E, float *__restrict__ gradT,
+                         int32_t *__restrict__ status) {
+  extern __shared__ __align__(16) float tile[];  // [C][ROWS_TE], chunk-swizzled
+  __shared__ int sidx[ROWS_TE * NSRC];
+  __shared__ float sw[ROWS_TE * NSRC];
+  const int tid = threadIdx.x;
+  const int64_t b = blockIdx.y;
+  const int64_t e0 = (int64_t)blockIdx.x * ROWS_TE;
+  const int n = (int)((E - e0) < ROWS_TE ? (E - e0) : ROWS_TE);  // multiple of 4
+  const int L = C >> 2;
+
+  bool bad = false;
+  for (int t = tid; t < n * NSRC; t += ROWS_THREADS) {
+    int64_t id = index[(b * E + e0) * NSRC + t];
+    if (id < 0 || id >= N1) {
+      id = -1;
+      bad = true;
+    }
+    sidx[t] = (int)id;
+    if (NSRC == 3) sw[t] = weight[(b * E + e0) * NSRC + t];
+  }
+  if (bad && status) atomicOr(status, 1);
+
+  // Phase 1: gout[b, c, e0 + 4*ch ..] -> tile row c, swizzled chunk.
+  const int nchunks = n >> 2;
+  const float *gb = gout + b * C * E + e0;
+  for (int u = tid; u < C * (ROWS_TE / 4); u += ROWS_THREADS) {
+    const int c = u >> 4, ch = u & 15;
+    if (ch < nchunks) {
+      const float4 v = __ldcs(reinterpret_cast<const float4 *>(gb + (int64_t)c * E + 4 * ch));
+      *reinterpret_cast<float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & 15) << 2)) = v;
+    }
+  }
+  __syncthreads();
+
+  // Phase 2: item t = e * L + q -> four channels of entry e, reduced into the row(s) of its index.
+  float *tb = gradT + b * N1 * C;
+  const int items = n * L;
+  int e = tid / L, q = tid - e * L;
+  const int de = ROWS_THREADS / L, dq = ROWS_THREADS - de * L;
+  for (int t = tid; t < items; t += ROWS_THREADS) {
+    const float *src = tile + (4 * q) * ROWS_TE + ((((e >> 2) ^ q) & (ROWS_TE / 4 - 1)) << 2) + (e & 3);
+    const float vx = src[0], vy = src[ROWS_TE], vz = src[2 * ROWS_TE], vw = src[3 * ROWS_TE];
+    if (NSRC == 1) {
+      const int id = sidx[e];
+      if (id >= 0) red_add4(tb + (int64_t)id * C + 4 * q, vx, vy, vz, vw);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int id = sidx[3 * e + i];
+        const float w = sw[3 * e + i];
+        if (id >= 0) red_add4(tb + (int64_t)id * C + 4 * q, vx * w, vy * w, vz * w, vw * w);
+      }
+    }
+    e += de;
+    q += dq;
+    if (q >= L) {
+      q -= L;
+      ++e;
+    }
+  }
+}
+
 inline size_t rows_scratch_bytes(int64_t B, int64_t C, int64_t N1) { return (size_t)B * (size_t)C * (size_t)N1 * 4; }
 
 // Worth it when the gathered output is at least twice the feature tensor and C fits a tile.
@@ -219,6 +295,33 @@ int gather_rows(const float *in, const int64_t *index, const float *weight, int6
     TK3D_CUDA(cudaFuncSetAttribute(gather_rows_kernel<NSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   gather_rows_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out, status);
   return check_launch("gather_rows_kernel");
+}
+
+// Backward through the transposed accumulator; `vec_ok` has been checked by the caller.
+template <int NSRC>
+int scatter_rows(const float *gout, const int64_t *index, const float *weight, int64_t B, int64_t C, int64_t N1,
+                 int64_t E, float *gin, int32_t *status, float *scratch, cudaStream_t st) {
+  TK3D_REQUIRE(B <= 65535 && (N1 + 31) / 32 <= 65535, TK3D_ERR_SHAPE, "scatter: size too large for this path");
+  TK3D_CUDA(cudaMemsetAsync(scratch, 0, rows_scratch_bytes(B, C, N1), st));
+  if (E > 0) {
+    const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
+    if (smem > 48 * 1024)
+      TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<NSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+    dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
+    scatter_rows_vec4_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(gout, index, weight, (int)C, N1, E, scratch,
+                                                                     status);
+    int rc = check_launch("scatter_rows_vec4_kernel");
+    if (rc) return rc;
+  }
+  // scratch [B][N1][C] -> gin [B][C][N1]: the same tile transpose with the roles of the axes swapped
+  dim3 tg((unsigned)((C + 31) / 32), (unsigned)((N1 + 31) / 32), (unsigned)B);
+  transpose_bcn_kernel<<<tg, 256, 0, st>>>(scratch, gin, (int)N1, C);
+  return check_launch("transpose_bcn_kernel");
+}
+
+inline bool rows_vec_ok(int64_t C, int64_t E, const void *a, const void *b) {
+  return C % 4 == 0 && E % 4 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
 }
 
 }  // namespace tk3d
