@@ -277,6 +277,11 @@ def extras(dev, rank, world, flush):
     ms = t(lambda: interpolate_feature(ff, i, w), steps=5)
     out["c5_interp_fwd_ms"] = ms
     out["c5_interp_fwd_GBps"] = 708.9e6 / (ms * 1e-3) / 1e9
+    ffg = ff.clone().requires_grad_(True)
+    o = interpolate_feature(ffg, i, w)
+    go = torch.ones_like(o)
+    ms = t(lambda: torch.autograd.grad(o, ffg, go, retain_graph=True), steps=5)
+    out["c5_interp_bwd_ms"] = ms
     return out
 
 

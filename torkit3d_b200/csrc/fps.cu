@@ -6,9 +6,8 @@
 //  * fp32, N <= 8192 ("resident" kernel): one persistent CTA per cloud keeps every point and its
 //    running minimum distance in REGISTERS for the whole call (up to 8 points per thread), plus a
 //    copy of the coordinates in shared memory from which the newly selected point is broadcast.
-//    A step is: P exact distance updates per thread, a warp arg-max with two REDUX instructions,
-//    one shared-memory exchange between warps (double-buffered slots, a single __syncthreads),
-//    and the same two REDUX again so every warp learns the winner without a second barrier.
+//    A step is: P exact distance updates per thread, a block-wide maximum of the running minima
+//    (REDUX, one shared-memory exchange, REDUX), and the lowest index holding that maximum.
 //    (A variant that spreads one cloud over a thread-block cluster of 2-8 CTAs, exchanging the
 //    per-warp candidates through distributed shared memory with one cluster barrier per step, was
 //    measured slower on B200 -- 1.07 ms against 0.88 ms for 32 clouds of 8192 points -- because
@@ -27,74 +26,89 @@ namespace {
 
 constexpr int FPS_MAX_THREADS = 1024;
 
-// Block-wide arg-max of (bits, inv) pairs, lexicographic.  `slots` points at 2*32 uint32 words
-// that are not reused until the next-but-one call (callers alternate two slot sets).
-__device__ __forceinline__ void block_argmax(unsigned &bits, unsigned &inv, unsigned *slots, int nwarps) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned hb = __reduce_max_sync(0xffffffffu, bits);
-  unsigned hi = __reduce_max_sync(0xffffffffu, bits == hb ? inv : 0u);
-  if (nwarps > 1) {
-    if (lane == 0) {
-      slots[warp] = hb;
-      slots[32 + warp] = hi;
-    }
-    __syncthreads();
-    const unsigned b2 = lane < nwarps ? slots[lane] : 0u;
-    const unsigned i2 = lane < nwarps ? slots[32 + lane] : 0u;
-    hb = __reduce_max_sync(0xffffffffu, b2);
-    hi = __reduce_max_sync(0xffffffffu, b2 == hb ? i2 : 0u);
-  }
-  bits = hb;
-  inv = hi;
-}
-
 // ---- resident kernel (fp32) ------------------------------------------------------------------
-template <int P>
+// A step inside the SM is bound by issue slots and the half-rate ALU pipe rather than by latency,
+// so the per-point work on that pipe is kept to one min and one max: threads track only their
+// largest running minimum, the block reduces the VALUE (REDUX + one shared-memory exchange), and
+// only the threads that hold the winning value look up their lowest index with it and publish it
+// with a shared-memory atomicMin.  That costs a second barrier per step but removes the
+// compare-and-two-selects per point of an index-carrying arg-max (0.835 ms against 0.885 ms for
+// 32 clouds of 8192 points).  Points are held two per float2 register pair.
+// The packed add.f32x2 / mul.f32x2 forms of sm_100 are NOT used for the distance: in this loop
+// their results differed in the last bit from the scalar round-to-nearest sequence for about one
+// distance in five (as a fused multiply-add would), even with explicit .rn and -fmad=false, and an
+// exactly tied pair of points in the benchmark data then picked the wrong winner.
+template <int P2>
 __global__ void __launch_bounds__(FPS_MAX_THREADS)
 fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__restrict__ index) {
-  extern __shared__ float sxyz[];  // [3*N] copy of the cloud, array-of-structures
-  __shared__ unsigned slots[2][64];
-  const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+  extern __shared__ float sxyz[];  // [3*N] copy of the cloud
+  __shared__ unsigned slots[2][32];
+  __shared__ int s_idx[2];
+  const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
   const float *pts = points + (int64_t)blockIdx.x * N * 3;
   int64_t *out = index + (int64_t)blockIdx.x * S;
 
   for (int e = tid; e < 3 * N; e += T) sxyz[e] = pts[e];
+  if (tid < 2) s_idx[tid] = 0x7fffffff;
   __syncthreads();
 
-  float px[P], py[P], pz[P], md[P];
+  // Point (i, h) of this thread is j = (2*i + h) * T + tid: ascending in (i, h).
+  float2 px[P2], py[P2], pz[P2], md[P2];
+  const float qnan = __int_as_float(0x7fc00000), pinf = __int_as_float(0x7f800000);
 #pragma unroll
-  for (int p = 0; p < P; ++p) {
-    const int j = p * T + tid;
-    if (j < N) {
-      px[p] = sxyz[3 * j + 0];
-      py[p] = sxyz[3 * j + 1];
-      pz[p] = sxyz[3 * j + 2];
-      md[p] = __int_as_float(0x7f800000);
-    } else {
-      // Padding never wins: distance 0 and the largest possible index; NaN coordinates keep it 0.
-      px[p] = py[p] = pz[p] = __int_as_float(0x7fc00000);
-      md[p] = 0.f;
-    }
+  for (int i = 0; i < P2; ++i) {
+    const int j0 = (2 * i) * T + tid, j1 = (2 * i + 1) * T + tid;
+    px[i].x = j0 < N ? sxyz[3 * j0 + 0] : qnan;
+    py[i].x = j0 < N ? sxyz[3 * j0 + 1] : qnan;
+    pz[i].x = j0 < N ? sxyz[3 * j0 + 2] : qnan;
+    md[i].x = j0 < N ? pinf : 0.f;  // padding: distance 0, NaN coordinates keep it there
+    px[i].y = j1 < N ? sxyz[3 * j1 + 0] : qnan;
+    py[i].y = j1 < N ? sxyz[3 * j1 + 1] : qnan;
+    pz[i].y = j1 < N ? sxyz[3 * j1 + 2] : qnan;
+    md[i].y = j1 < N ? pinf : 0.f;
   }
 
   int cur = 0;
   if (tid == 0) out[0] = 0;
   for (int it = 1; it < S; ++it) {
+    const int par = it & 1;
     const float cx = sxyz[3 * cur + 0], cy = sxyz[3 * cur + 1], cz = sxyz[3 * cur + 2];
-    float bm = -1.f;
-    int bi = 0;
+    float bm = 0.f;
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const float d = sqdist<float>(px[p], py[p], pz[p], cx, cy, cz);
-      md[p] = fminf(md[p], d);
-      if (md[p] > bm) {  // ascending index within the thread: strict ">" keeps the lowest
-        bm = md[p];
-        bi = p * T + tid;
-      }
+    for (int i = 0; i < P2; ++i) {
+      float2 d;
+      d.x = sqdist<float>(px[i].x, py[i].x, pz[i].x, cx, cy, cz);
+      d.y = sqdist<float>(px[i].y, py[i].y, pz[i].y, cx, cy, cz);
+      md[i].x = fminf(md[i].x, d.x);
+      md[i].y = fminf(md[i].y, d.y);
+      bm = fmaxf(bm, fmaxf(md[i].x, md[i].y));
     }
-    unsigned bits = __float_as_uint(bm), inv = 0xffffffffu - (unsigned)bi;
-    block_argmax(bits, inv, slots[it & 1], nwarps);
-    cur = (int)(0xffffffffu - inv);
+    const unsigned bits = __float_as_uint(bm);
+    unsigned gb = __reduce_max_sync(0xffffffffu, bits);
+    if (nwarps > 1) {
+      if (lane == 0) slots[par][warp] = gb;
+      __syncthreads();
+      gb = __reduce_max_sync(0xffffffffu, lane < nwarps ? slots[par][lane] : 0u);
+    }
+    // Re-arm the other slot for the next step: all its readers are past the barrier above.
+    if (nwarps > 1 && tid == 0) s_idx[par ^ 1] = 0x7fffffff;
+    // Threads that hold the winning value look up their lowest point with it and publish the
+    // smallest such index.
+    if (bits == gb) {
+      int mine = 0x7fffffff;
+#pragma unroll
+      for (int i = P2 - 1; i >= 0; --i) {
+        if (md[i].y == bm) mine = (2 * i + 1) * T + tid;
+        if (md[i].x == bm) mine = (2 * i) * T + tid;
+      }
+      atomicMin(&s_idx[par], mine);
+    }
+    __syncthreads();
+    cur = s_idx[par];
+    if (nwarps == 1) {
+      __syncwarp();
+      if (tid == 0) s_idx[par ^ 1] = 0x7fffffff;
+    }
     if (tid == 0) out[it] = cur;
   }
 }
@@ -218,15 +232,14 @@ extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int
     const int P = (int)((N + threads - 1) / threads);
     const size_t smem = (size_t)N * 12;
     const float *p = (const float *)points;
-#define TK3D_FPS_CASE(PP)                                                                                         \
-  {                                                                                                               \
+#define TK3D_FPS_CASE(PP)                                                                                       \
+  {                                                                                                             \
     TK3D_CUDA(cudaFuncSetAttribute(fps_resident_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)); \
     fps_resident_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index);                        \
   }
-    if (P <= 1) TK3D_FPS_CASE(1)
-    else if (P <= 2) TK3D_FPS_CASE(2)
-    else if (P <= 4) TK3D_FPS_CASE(4)
-    else TK3D_FPS_CASE(8)
+    if (P <= 2) TK3D_FPS_CASE(1)
+    else if (P <= 4) TK3D_FPS_CASE(2)
+    else TK3D_FPS_CASE(4)
 #undef TK3D_FPS_CASE
     return check_launch("fps_resident_kernel");
   }
