@@ -98,7 +98,16 @@ class ClockSampler:
                 if v.lower() == "active":
                     reasons.add(n)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            # the sampler produced nothing in time (many ranks starting nvidia-smi at once): one direct query
+            try:
+                out = subprocess.run(["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-i",
+                                      str(self.idx)], capture_output=True, text=True, timeout=20).stdout.strip()
+                f = [x.strip() for x in out.split(",")]
+                return {"sm_mhz": float(f[1]), "sm_max_mhz": float(f[2]),
+                        "reasons": [n for n, v in zip(names, f[5:9]) if v.lower() == "active"], "samples": 1,
+                        "note": "single query after the timed region"}
+            except Exception:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 

@@ -20,10 +20,9 @@ namespace tk3d {
 
 namespace {
 
-constexpr int CF_THREADS = 128;
 constexpr int CF_TILE = 512;
 
-template <int Q, int MINB = 1, int UNR = 2>
+template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128>
 __global__ void __launch_bounds__(CF_THREADS, MINB)
 chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int64_t B, int N1, int N2,
                         float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
@@ -33,6 +32,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
   constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
   __shared__ float4 tile[2][CF_TILE];
   __shared__ double ssum[CF_THREADS / 32];
+  static_assert(CF_TILE % CF_THREADS == 0, "tile is staged in whole rounds of the block");
   const int tid = threadIdx.x;
   const float pinf = __int_as_float(0x7f800000);
 
@@ -181,7 +181,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
   }
 }
 
-template <int Q, int MINB = 1, int UNR = 2>
+template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128>
 int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
            float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
   const int64_t per = CF_THREADS * Q;
@@ -190,7 +190,7 @@ int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, floa
   if (total == 0) return TK3D_OK;
   const int64_t cap = (int64_t)sm_count() * 256;
   const unsigned grid = (unsigned)(total < cap ? total : cap);
-  chamfer_fwd_fast_kernel<Q, MINB, UNR><<<grid, CF_THREADS, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
+  chamfer_fwd_fast_kernel<Q, MINB, UNR, CF_THREADS><<<grid, CF_THREADS, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
                                                            blocks1, total);
   return check_launch("chamfer_fwd_fast_kernel");
 }
@@ -202,6 +202,7 @@ int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_
   // Queries per thread: more register tiling when there is enough work to fill the GPU with it.
   const int64_t queries = B * (N1 + N2);
   const int64_t sms = sm_count();
+  constexpr int CF_THREADS = 128;
   // Measured on B200 (B=64, N=M=16384): two queries per thread, six resident blocks per SM and a
   // four-fold unrolled key loop beat four queries per thread by about 10 %.
   if (queries >= sms * 2 * CF_THREADS * 2)
