@@ -274,6 +274,20 @@ def extras(dev, rank, world, flush):
     ms = t(lambda: torch.autograd.grad(g, featg, go, retain_graph=True), steps=10)
     out["c3_group_bwd_ms"] = ms
     del g, go, featg
+    # C3 as the layer calls it ([B,3,N] layout): fused front ends against the operator chain
+    from torkit3d_b200 import _fused
+    pcf = p.transpose(1, 2).contiguous()
+    ms = t(lambda: _fused.fps_gather(pcf, 1024), steps=5)
+    out["c3_fps_gather_fused_ms"] = ms
+    _, ccf = _fused.fps_gather(pcf, 1024)
+    ms = t(lambda: _fused.sa_group_forward(pcf, ccf, feat, 0.1, 32, want_index=False), steps=10)
+    out["c3_sa_group_fused_ms"] = ms
+
+    def sa_chain():
+        ii = ball_query(ccf, pcf, 0.1, 32)
+        return torch.cat([group_points(feat, ii), group_points(pcf, ii) - ccf.unsqueeze(-1)], dim=1)
+    out["c3_sa_group_chain_ms"] = t(sa_chain, steps=10)
+    del pcf, ccf
     # C5 three-NN interpolation, query slabs
     qq, rr, ff = workloads.c5_scene_interp()
     qq = query_slab(qq, rank, world).contiguous().to(dev)
@@ -291,6 +305,9 @@ def extras(dev, rank, world, flush):
     go = torch.ones_like(o)
     ms = t(lambda: torch.autograd.grad(o, ffg, go, retain_graph=True), steps=5)
     out["c5_interp_bwd_ms"] = ms
+    del o, go, ffg
+    qcf, rcf = qq.transpose(1, 2).contiguous(), rr.transpose(1, 2).contiguous()
+    out["c5_three_nn_interp_fused_ms"] = t(lambda: _fused.three_nn_interp_forward(qcf, rcf, ff), steps=3)
     return out
 
 

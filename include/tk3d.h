@@ -206,6 +206,85 @@ int tk3d_interp_bwd(const void *grad_out, const int64_t *index, const void *weig
  */
 int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t k, void *weight, int dtype, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Fused front ends of the PointNet++ layers that call the operators above.  They replace Python
+ * glue of the reference, not entry points of its extension; fp32 only.
+ * `xyz_channel_first` selects the coordinate layout of every xyz argument of the call:
+ * 0 = [B,N,3] (the layout of the operators above), 1 = [B,3,N] (the layout the reference's layers
+ * receive and transpose with .transpose(1,2).contiguous() before every operator call).
+ */
+
+/*
+ * Farthest point sampling that also returns the sampled coordinates.
+ * Replaces sample_farthest_points(points, S, transpose=True) followed by
+ * batch_index_select(points, fps_index, dim=2) (torkit3d/models/classification/pointnet2.py:73-74,
+ * torkit3d/nn/functional.py:34-69).
+ *   points  [B,N,3] or [B,3,N] in;  index [B,S] out (as tk3d_fps, bit for bit)
+ *   sampled [B,S,3] or [B,3,S] out, same layout and dtype as points
+ *   scratch as for tk3d_fps.
+ */
+int tk3d_fps_gather(const void *points, int64_t B, int64_t N, int64_t num_samples, int xyz_channel_first,
+                    int64_t *index, void *sampled, void *scratch, size_t scratch_bytes, int dtype, void *stream);
+
+/*
+ * Set-abstraction grouping: ball query + group_points of the features + group_points of the
+ * coordinates + centring + concatenation, i.e. everything SetAbstraction.forward does before its
+ * MLP (torkit3d/layers/pointnet2.py:43-58 with query_neighbor = BallQuery), in two launches (one
+ * transpose of the features into `scratch`, one fused kernel).
+ *   points    [B,N,3]|[B,3,N]  in   coordinates of the N input points ("in_xyz")
+ *   centroids [B,M,3]|[B,3,M]  in   coordinates of the M group centres ("out_xyz")
+ *   feature   [B,C,N]          in   may be NULL when C == 0
+ *   out       [B,C+3,M,K]      out  channels [0,C): feature[b,c,index[b,m,k]];
+ *                                   channels [C,C+3): points[b,index[b,m,k],:] - centroids[b,m,:]
+ *                                   ([B,C,M,K] when use_xyz == 0)
+ *   index32   [B,M,K] int32    out  optional (NULL to skip): the ball-query result, identical to
+ *                                   tk3d_ball_query's; the backward needs it
+ *   status    int32            in/out optional: bit 0 is OR-ed in when a centre has no neighbour
+ *                                   (its K entries are -1; its feature channels are 0 and its
+ *                                   coordinate channels are -centroid)
+ *   scratch   tk3d_sa_group_scratch_bytes(...) bytes, required when C > 0
+ * tk3d_sa_group_supported() tells whether the shape is served (fp32, C <= 512, 1 <= K <= 128);
+ * otherwise compose tk3d_ball_query and tk3d_group_fwd.
+ */
+int tk3d_sa_group_supported(int64_t B, int64_t C, int64_t N, int64_t M, int64_t K, int dtype);
+size_t tk3d_sa_group_scratch_bytes(int64_t B, int64_t C, int64_t N, int64_t M, int64_t K, int dtype);
+int tk3d_sa_group_fwd(const void *points, const void *centroids, const void *feature, int64_t B, int64_t C,
+                      int64_t N, int64_t M, float radius, int64_t K, int xyz_channel_first, int use_xyz, void *out,
+                      int32_t *index32, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
+                      void *stream);
+
+/*
+ * Backward of tk3d_sa_group_fwd.  grad_out is the gradient of `out` ([B,C+3,M,K], dense).
+ *   grad_feature   [B,C,N]            out, optional: scatter-add of the first C channels
+ *   grad_points    like points        out, optional: scatter-add of the coordinate channels
+ *   grad_centroids like centroids     out, optional: minus the sum over K of the coordinate channels
+ * Each output is fully written (zeroed first where it accumulates).  `scratch` as in the forward.
+ */
+int tk3d_sa_group_bwd(const void *grad_out, const int32_t *index32, int64_t B, int64_t C, int64_t N, int64_t M,
+                      int64_t K, int xyz_channel_first, int use_xyz, void *grad_feature, void *grad_points,
+                      void *grad_centroids, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
+                      void *stream);
+
+/*
+ * Feature propagation front end: three nearest keys of every query + inverse-distance weights +
+ * weighted gather, i.e. FeatureInterpolator.forward (torkit3d/layers/pointnet2.py:114-133), in
+ * three launches (3-NN with the weights computed in its epilogue, transpose, gather).
+ *   query_xyz   [B,Nq,3]|[B,3,Nq] in;  key_xyz [B,Nk,3]|[B,3,Nk] in (Nk >= 3)
+ *   key_feature [B,C,Nk] in;  out [B,C,Nq] out
+ *   index32 [B,Nq,3] int32 out, weight [B,Nq,3] out: the neighbours (ascending distance, ties to
+ *                    the lower index, as tk3d_knn) and w_i = (1/max(d_i,eps)) / sum_j (1/max(d_j,eps))
+ *   scratch     tk3d_three_nn_interp_scratch_bytes(...) bytes, required when C > 0
+ * The backward (w.r.t. the features, as in the reference) takes index32 and weight back.
+ */
+size_t tk3d_three_nn_interp_scratch_bytes(int64_t B, int64_t C, int64_t Nq, int64_t Nk, int dtype);
+int tk3d_three_nn_interp_fwd(const void *query_xyz, const void *key_xyz, const void *key_feature, int64_t B,
+                             int64_t C, int64_t Nq, int64_t Nk, int xyz_channel_first, float eps, void *out,
+                             int32_t *index32, void *weight, int32_t *status, void *scratch, size_t scratch_bytes,
+                             int dtype, void *stream);
+int tk3d_three_nn_interp_bwd(const void *grad_out, const int32_t *index32, const void *weight, int64_t B, int64_t C,
+                             int64_t Nq, int64_t Nk, void *grad_feature, int32_t *status, void *scratch,
+                             size_t scratch_bytes, int dtype, void *stream);
+
 /*
  * Diagnostic with no counterpart in the reference: launches a kernel of dependent FP32 fused
  * multiply-add chains (`iters` x 64 FMAs per thread, 8 blocks of 256 threads per SM) on `stream`.

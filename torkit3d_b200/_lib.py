@@ -39,6 +39,18 @@ SIGNATURES = {
     "tk3d_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int,
                                _vp]),
     "tk3d_three_nn_weight": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
+    "tk3d_fps_gather": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, ctypes.c_size_t, _int, _vp]),
+    "tk3d_sa_group_supported": (_int, [_i64, _i64, _i64, _i64, _i64, _int]),
+    "tk3d_sa_group_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _i64, _int]),
+    "tk3d_sa_group_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, ctypes.c_float, _i64, _int, _int, _vp, _vp,
+                                 _vp, _vp, ctypes.c_size_t, _int, _vp]),
+    "tk3d_sa_group_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp,
+                                 ctypes.c_size_t, _int, _vp]),
+    "tk3d_three_nn_interp_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _int]),
+    "tk3d_three_nn_interp_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, ctypes.c_float, _vp, _vp, _vp,
+                                        _vp, _vp, ctypes.c_size_t, _int, _vp]),
+    "tk3d_three_nn_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int,
+                                        _vp]),
     "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
 }
 

@@ -40,7 +40,8 @@ constexpr int FPS_MAX_THREADS = 1024;
 // exactly tied pair of points in the benchmark data then picked the wrong winner.
 template <int P2>
 __global__ void __launch_bounds__(FPS_MAX_THREADS)
-fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__restrict__ index) {
+fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__restrict__ index, int ps, int cs,
+                    float *__restrict__ sampled) {
   extern __shared__ float sxyz[];  // [3*N] copy of the cloud
   __shared__ unsigned slots[2][32];
   __shared__ int s_idx[2];
@@ -48,7 +49,15 @@ fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__r
   const float *pts = points + (int64_t)blockIdx.x * N * 3;
   int64_t *out = index + (int64_t)blockIdx.x * S;
 
-  for (int e = tid; e < 3 * N; e += T) sxyz[e] = pts[e];
+  // Point j, coordinate d sits at pts[j*ps + d*cs]: (3, 1) for [N,3] clouds, (1, N) for [3,N].
+  if (cs == 1) {
+    for (int e = tid; e < 3 * N; e += T) sxyz[e] = pts[e];
+  } else {
+    for (int e = tid; e < 3 * N; e += T) {
+      const int d = e / N, j = e - d * N;
+      sxyz[3 * j + d] = pts[e];
+    }
+  }
   if (tid < 2) s_idx[tid] = 0x7fffffff;
   __syncthreads();
 
@@ -111,6 +120,16 @@ fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__r
     }
     if (tid == 0) out[it] = cur;
   }
+  // Optional epilogue: coordinates of the samples, in the layout of the input ([S,3] or [3,S]).
+  if (sampled != nullptr) {
+    __syncthreads();  // makes thread 0's index stores visible to the block
+    float *sm = sampled + (int64_t)blockIdx.x * S * 3;
+    const int sps = cs == 1 ? 3 : 1, scs = cs == 1 ? 1 : S;
+    for (int e = tid; e < 3 * S; e += T) {
+      const int s = e / 3, d = e - 3 * s;
+      sm[s * sps + d * scs] = sxyz[3 * (int)out[s] + d];
+    }
+  }
 }
 
 // ---- streaming kernel (any type, any N) ------------------------------------------------------
@@ -128,7 +147,7 @@ __device__ __forceinline__ unsigned long long dist_key<double>(double v) {
 template <typename T>
 __global__ void __launch_bounds__(FPS_MAX_THREADS)
 fps_streaming_kernel(const T *__restrict__ points, int64_t N, int64_t S, int64_t *__restrict__ index,
-                     T *__restrict__ min_dist) {
+                     T *__restrict__ min_dist, int64_t ps = 3, int64_t cs = 1, T *__restrict__ sampled = nullptr) {
   // Arg-max over (distance key, ~index) with 64-bit keys for the distance and a separate 64-bit
   // word for the index, reduced through shared memory.
   __shared__ unsigned long long skey[2][32];
@@ -141,12 +160,12 @@ fps_streaming_kernel(const T *__restrict__ points, int64_t N, int64_t S, int64_t
   int64_t cur = 0;
   if (tid == 0) out[0] = 0;
   for (int64_t it = 1; it < S; ++it) {
-    const T cx = pts[3 * cur + 0], cy = pts[3 * cur + 1], cz = pts[3 * cur + 2];
+    const T cx = pts[ps * cur], cy = pts[ps * cur + cs], cz = pts[ps * cur + 2 * cs];
     unsigned long long bk = 0;
     unsigned long long bi = ~0ull;  // holds ~index so that max() prefers the lowest index
     bool any = false;
     for (int64_t j = tid; j < N; j += Tn) {
-      const T d = sqdist<T>(pts[3 * j + 0], pts[3 * j + 1], pts[3 * j + 2], cx, cy, cz);
+      const T d = sqdist<T>(pts[ps * j], pts[ps * j + cs], pts[ps * j + 2 * cs], cx, cy, cz);
       T m = (it == 1) ? Exact<T>::inf() : md[j];
       if (d < m) m = d;
       md[j] = m;
@@ -190,6 +209,15 @@ fps_streaming_kernel(const T *__restrict__ points, int64_t N, int64_t S, int64_t
     cur = (int64_t)(~bi);
     if (tid == 0) out[it] = cur;
   }
+  if (sampled != nullptr) {
+    __syncthreads();  // makes thread 0's index stores visible to the block
+    T *sm = sampled + (int64_t)blockIdx.x * S * 3;
+    const int64_t sps = cs == 1 ? 3 : 1, scs = cs == 1 ? 1 : S;
+    for (int64_t e = tid; e < 3 * S; e += Tn) {
+      const int64_t s = e / 3, d = e - 3 * s;
+      sm[s * sps + d * scs] = pts[ps * out[s] + d * cs];
+    }
+  }
 }
 
 constexpr int64_t FPS_RESIDENT_MAX_N = 8192;
@@ -212,8 +240,8 @@ extern "C" size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype) {
   return (size_t)B * (size_t)N * (dtype == TK3D_F64 ? 8 : 4);
 }
 
-extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index, void *scratch,
-                        size_t scratch_bytes, int dtype, void *stream) {
+static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int channel_first, int64_t *index,
+                    void *sampled, void *scratch, size_t scratch_bytes, int dtype, void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "fps: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N >= 0, TK3D_ERR_SHAPE, "fps: negative size");
   TK3D_REQUIRE(S > 0, TK3D_ERR_K, "fps: num_samples must be positive (got %lld)", (long long)S);
@@ -224,6 +252,7 @@ extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int
   if (B == 0) return TK3D_OK;
   TK3D_REQUIRE(points && index, TK3D_ERR_NULL, "fps: points/index is NULL");
   cudaStream_t st = (cudaStream_t)stream;
+  const int64_t ps = channel_first ? 1 : 3, cs = channel_first ? N : 1;
   const size_t need = tk3d_fps_scratch_bytes(B, N, dtype);
   if (need == 0) {
     // Up to 8 points per thread; at least 4 warps so that every SM sub-partition has work.
@@ -235,7 +264,8 @@ extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int
 #define TK3D_FPS_CASE(PP)                                                                                       \
   {                                                                                                             \
     TK3D_CUDA(cudaFuncSetAttribute(fps_resident_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)); \
-    fps_resident_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index);                        \
+    fps_resident_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,       \
+                                                                (float *)sampled);                                \
   }
     if (P <= 2) TK3D_FPS_CASE(1)
     else if (P <= 4) TK3D_FPS_CASE(2)
@@ -247,11 +277,24 @@ extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int
                "fps: scratch of %zu bytes required, %zu given", need, scratch ? scratch_bytes : (size_t)0);
   const int threads = threads_for(N);
   if (dtype == TK3D_F32)
-    fps_streaming_kernel<float><<<(unsigned)B, threads, 0, st>>>((const float *)points, N, S, index, (float *)scratch);
+    fps_streaming_kernel<float><<<(unsigned)B, threads, 0, st>>>((const float *)points, N, S, index, (float *)scratch,
+                                                                ps, cs, (float *)sampled);
   else
     fps_streaming_kernel<double><<<(unsigned)B, threads, 0, st>>>((const double *)points, N, S, index,
-                                                                 (double *)scratch);
+                                                                 (double *)scratch, ps, cs, (double *)sampled);
   return check_launch("fps_streaming_kernel");
+}
+
+extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index, void *scratch,
+                        size_t scratch_bytes, int dtype, void *stream) {
+  return fps_impl(points, B, N, S, 0, index, nullptr, scratch, scratch_bytes, dtype, stream);
+}
+
+extern "C" int tk3d_fps_gather(const void *points, int64_t B, int64_t N, int64_t S, int channel_first,
+                               int64_t *index, void *sampled, void *scratch, size_t scratch_bytes, int dtype,
+                               void *stream) {
+  TK3D_REQUIRE(sampled != nullptr || B * S == 0, TK3D_ERR_NULL, "fps_gather: sampled is NULL");
+  return fps_impl(points, B, N, S, channel_first, index, sampled, scratch, scratch_bytes, dtype, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -214,3 +214,108 @@ extern "C" int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t 
     three_nn_weight_kernel<double><<<grid, 256, 0, st>>>((const double *)distance, rows, (int)k, (double *)weight);
   return check_launch("three_nn_weight_kernel");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Fused feature interpolation: three nearest keys + inverse-distance weights + weighted gather.
+namespace tk3d {
+
+int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t N1, int64_t N2, int channel_first,
+                       float eps, float *weight, int32_t *index32, cudaStream_t st);
+
+namespace {
+
+// Backward without the row path: one thread per gradient element, 32-bit indices.
+__global__ void __launch_bounds__(256)
+interp32_bwd_kernel(const float *__restrict__ gout, const int32_t *__restrict__ index32,
+                    const float *__restrict__ weight, int64_t B, int C, int64_t Nk, int64_t Nq,
+                    float *__restrict__ gfeat, int32_t *__restrict__ status) {
+  const int64_t total = B * C * Nq;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t q = t % Nq;
+    const int64_t bc = t / Nq;
+    const int64_t b = bc / C;
+    const float g = gout[t];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int id = index32[(b * Nq + q) * 3 + i];
+      if (id < 0 || id >= Nk) {
+        if (status) atomicOr(status, 1);
+        continue;
+      }
+      atomicAdd(gfeat + bc * Nk + id, g * weight[(b * Nq + q) * 3 + i]);
+    }
+  }
+}
+
+bool fused_interp_shape_ok(int64_t B, int64_t C, int64_t Nq, int64_t Nk) {
+  return B >= 0 && B <= 65535 && C >= 0 && C <= ROWS_MAX_C && Nq >= 0 && Nq < (1LL << 30) && Nk >= 3 &&
+         Nk < (1LL << 30);
+}
+
+}  // namespace
+}  // namespace tk3d
+
+extern "C" size_t tk3d_three_nn_interp_scratch_bytes(int64_t B, int64_t C, int64_t Nq, int64_t Nk, int dtype) {
+  if (dtype != TK3D_F32 || !fused_interp_shape_ok(B, C, Nq, Nk) || B * C == 0) return 0;
+  return rows_scratch_bytes(B, C, Nk);
+}
+
+extern "C" int tk3d_three_nn_interp_fwd(const void *query_xyz, const void *key_xyz, const void *key_feature,
+                                        int64_t B, int64_t C, int64_t Nq, int64_t Nk, int xyz_channel_first,
+                                        float eps, void *out, int32_t *index32, void *weight, int32_t *status,
+                                        void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "three_nn_interp_fwd: only fp32 has a fused path (dtype %d)", dtype);
+  TK3D_REQUIRE(B >= 0 && C >= 0 && Nq >= 0 && Nk >= 0, TK3D_ERR_SHAPE, "three_nn_interp_fwd: negative size");
+  TK3D_REQUIRE(Nk >= 3, TK3D_ERR_K, "three_nn_interp_fwd: needs at least 3 key points (got %lld)", (long long)Nk);
+  TK3D_REQUIRE(fused_interp_shape_ok(B, C, Nq, Nk), TK3D_ERR_SHAPE,
+               "three_nn_interp_fwd: unsupported shape B=%lld C=%lld Nq=%lld Nk=%lld (C <= %d)", (long long)B,
+               (long long)C, (long long)Nq, (long long)Nk, ROWS_MAX_C);
+  if (B * Nq == 0) return TK3D_OK;
+  TK3D_REQUIRE(query_xyz && key_xyz && index32 && weight && (C == 0 || (key_feature && out)), TK3D_ERR_NULL,
+               "three_nn_interp_fwd: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = three_nn_fused_f32((const float *)query_xyz, (const float *)key_xyz, B, Nq, Nk, xyz_channel_first, eps,
+                              (float *)weight, index32, st);
+  if (rc || C == 0) return rc;
+  const size_t want = rows_scratch_bytes(B, C, Nk);
+  TK3D_REQUIRE(scratch != nullptr && scratch_bytes >= want, TK3D_ERR_SCRATCH,
+               "three_nn_interp_fwd: scratch of %zu bytes required (got %zu)", want, scratch ? scratch_bytes : (size_t)0);
+  return gather_rows<3, int32_t>((const float *)key_feature, index32, (const float *)weight, B, C, Nk, Nq,
+                                 (float *)out, status, (float *)scratch, st);
+}
+
+extern "C" int tk3d_three_nn_interp_bwd(const void *gout, const int32_t *index32, const void *weight, int64_t B,
+                                        int64_t C, int64_t Nq, int64_t Nk, void *gfeature, int32_t *status,
+                                        void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "three_nn_interp_bwd: only fp32 has a fused path (dtype %d)", dtype);
+  TK3D_REQUIRE(fused_interp_shape_ok(B, C, Nq, Nk), TK3D_ERR_SHAPE, "three_nn_interp_bwd: unsupported shape");
+  if (B * C * Nk == 0) return TK3D_OK;
+  TK3D_REQUIRE(gfeature && (Nq == 0 || (gout && index32 && weight)), TK3D_ERR_NULL,
+               "three_nn_interp_bwd: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = C % 4 == 0 && Nq % 4 == 0 && (Nk + 31) / 32 <= 65535 && scratch != nullptr &&
+                   scratch_bytes >= rows_scratch_bytes(B, C, Nk) && rows_vec_ok(C, Nq, gout, scratch);
+  if (vec) {
+    TK3D_CUDA(cudaMemsetAsync(scratch, 0, rows_scratch_bytes(B, C, Nk), st));
+    if (Nq > 0) {
+      const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
+      if (smem > 48 * 1024)
+        TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<3, int32_t>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      dim3 grid((unsigned)((Nq + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
+      scatter_rows_vec4_kernel<3, int32_t><<<grid, ROWS_THREADS, smem, st>>>(
+          (const float *)gout, index32, (const float *)weight, (int)C, Nk, Nq, C * Nq, (float *)scratch, status);
+      int rc = check_launch("scatter_rows_vec4_kernel");
+      if (rc) return rc;
+    }
+    dim3 tg((unsigned)((C + 31) / 32), (unsigned)((Nk + 31) / 32), (unsigned)B);
+    transpose_bcn_kernel<<<tg, 256, 0, st>>>((const float *)scratch, (float *)gfeature, (int)Nk, C);
+    return check_launch("transpose_bcn_kernel");
+  }
+  TK3D_CUDA(cudaMemsetAsync(gfeature, 0, sizeof(float) * (size_t)(B * C * Nk), st));
+  if (Nq == 0) return TK3D_OK;
+  const int64_t blocks = (B * C * Nq + 255) / 256, cap = (int64_t)sm_count() * 32;
+  interp32_bwd_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(
+      (const float *)gout, index32, (const float *)weight, B, (int)C, Nk, Nq, (float *)gfeature, status);
+  return check_launch("interp32_bwd_kernel");
+}

@@ -41,11 +41,32 @@ __device__ __forceinline__ float4 make_key(const float *__restrict__ rb, int j, 
   return make_float4(0.f, 0.f, 0.f, pinf());
 }
 
+__device__ __forceinline__ float4 make_key_strided(const float *__restrict__ rb, int j, int nr, int ps, int cs) {
+  if (j < nr) {
+    const float *r = rb + (int64_t)j * ps;
+    const float x = r[0], y = r[cs], z = r[2 * (int64_t)cs];
+    return make_float4(x, y, z, sweep_key_w(x, y, z));
+  }
+  return make_float4(0.f, 0.f, 0.f, pinf());
+}
+
 // ---------------------------------------------------------------------------------------------
-template <int K, int Q>
+// FUSED (three-nearest-neighbour front end of feature interpolation): coordinates are read
+// through strides (point j, coordinate d at base[j*ps + d*cs], so [N,3] and [3,N] clouds both
+// work), and instead of distances and 64-bit indices the epilogue writes the normalised
+// inverse-distance weights  w_i = (1/max(d_i, eps)) / sum_j (1/max(d_j, eps))  and 32-bit indices.
+struct KnnFused {
+  int qps, qcs, kps, kcs;
+  float eps;
+  float *weight;
+  int32_t *index32;
+};
+
+template <int K, int Q, bool FUSED = false>
 __global__ void __launch_bounds__(KN_THREADS)
 knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
-                 float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
+                 float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total,
+                 KnnFused fu = KnnFused()) {
   constexpr int TILE = 512, PER = TILE / KN_THREADS;
   constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
   __shared__ float4 tile[2][TILE];  // pair layout of sweep.cuh
@@ -63,10 +84,17 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
     for (int s = 0; s < Q; ++s) {
       const int i = i0 + s * KN_THREADS;
       if (i < N1) {
-        const float *q = query + (b * N1 + i) * 3;
-        qx[s] = q[0];
-        qy[s] = q[1];
-        qz[s] = q[2];
+        if constexpr (FUSED) {
+          const float *q = query + b * 3 * (int64_t)N1 + (int64_t)i * fu.qps;
+          qx[s] = q[0];
+          qy[s] = q[fu.qcs];
+          qz[s] = q[2 * (int64_t)fu.qcs];
+        } else {
+          const float *q = query + (b * N1 + i) * 3;
+          qx[s] = q[0];
+          qy[s] = q[1];
+          qz[s] = q[2];
+        }
         thr[s] = qnan();  // accept everything until the list is full
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
@@ -87,7 +115,9 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll
     for (int p = 0; p < PER; ++p) {
       const int u = tid + p * KN_THREADS;
-      const float4 v = make_key(rb, u, N2);
+      float4 v;
+      if constexpr (FUSED) v = make_key_strided(rb, u, N2, fu.kps, fu.kcs);
+      else v = make_key(rb, u, N2);
       sweep_store_key(tile[0], u, v.x, v.y, v.z, v.w);
     }
     __syncthreads();
@@ -99,7 +129,10 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
       float4 nxt[PER];
       if (more) {
 #pragma unroll
-        for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2);
+        for (int p = 0; p < PER; ++p) {
+          if constexpr (FUSED) nxt[p] = make_key_strided(rb, t0 + TILE + tid + p * KN_THREADS, N2, fu.kps, fu.kcs);
+          else nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2);
+        }
       }
       const int lim = (min(TILE, N2 - t0) + GK - 1) / GK * GK;
 #pragma unroll 4
@@ -157,12 +190,28 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
     for (int s = 0; s < Q; ++s) {
       const int i = i0 + s * KN_THREADS;
       if (i < N1) {
-        float *od = dist + (b * N1 + i) * K;
-        int64_t *oi = index + (b * N1 + i) * K;
+        if constexpr (FUSED) {
+          float inv[K], sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < K; ++c) {
-          od[c] = kd[s][c];
-          oi[c] = (int64_t)ki[s][c];
+          for (int c = 0; c < K; ++c) {
+            inv[c] = __fdiv_rn(1.0f, fmaxf(kd[s][c], fu.eps));
+            sum = c == 0 ? inv[0] : __fadd_rn(sum, inv[c]);
+          }
+          float *ow = fu.weight + (b * N1 + i) * K;
+          int32_t *oi = fu.index32 + (b * N1 + i) * K;
+#pragma unroll
+          for (int c = 0; c < K; ++c) {
+            ow[c] = __fdiv_rn(inv[c], sum);
+            oi[c] = ki[s][c];
+          }
+        } else {
+          float *od = dist + (b * N1 + i) * K;
+          int64_t *oi = index + (b * N1 + i) * K;
+#pragma unroll
+          for (int c = 0; c < K; ++c) {
+            od[c] = kd[s][c];
+            oi[c] = (int64_t)ki[s][c];
+          }
         }
       }
     }
@@ -654,6 +703,17 @@ int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2,
   return knn_small<K, 1>(query, key, B, N1, N2, dist, index, st);
 }
 
+template <int Q>
+int three_nn_fused_q(const float *query, const float *key, int64_t B, int N1, int N2, const KnnFused &fu,
+                     cudaStream_t st) {
+  const int64_t per = KN_THREADS * Q;
+  const int64_t total = B * ((N1 + per - 1) / per);
+  const int64_t cap = (int64_t)sm_count() * 256;
+  knn_small_kernel<3, Q, true><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
+      query, key, B, N1, N2, nullptr, nullptr, total, fu);
+  return check_launch("knn_small_kernel (fused weights)");
+}
+
 size_t buffered_smem(int Q, int k) {
   return (size_t)2 * KN_TILE * 16 + (size_t)Q * k * KN_THREADS * 8 + (size_t)Q * KN_CAP * KN_THREADS * 4;
 }
@@ -685,6 +745,24 @@ int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2,
 }
 
 }  // namespace
+
+// Three nearest keys of every query with inverse-distance weights (see KnnFused); N2 >= 3.
+int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t N1, int64_t N2, int channel_first,
+                       float eps, float *weight, int32_t *index32, cudaStream_t st) {
+  if (B * N1 == 0) return TK3D_OK;
+  KnnFused fu;
+  fu.qps = channel_first ? 1 : 3;
+  fu.qcs = channel_first ? (int)N1 : 1;
+  fu.kps = channel_first ? 1 : 3;
+  fu.kcs = channel_first ? (int)N2 : 1;
+  fu.eps = eps;
+  fu.weight = weight;
+  fu.index32 = index32;
+  if (B * N1 >= (int64_t)sm_count() * 2 * KN_THREADS * 2)
+    return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, st);
+  return three_nn_fused_q<1>(query, key, B, (int)N1, (int)N2, fu, st);
+}
+
 }  // namespace tk3d
 
 using namespace tk3d;

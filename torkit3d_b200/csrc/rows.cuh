@@ -44,9 +44,9 @@ static __global__ void __launch_bounds__(256) transpose_bcn_kernel(const float *
 // NSRC = 1: out[b,c,e] = featT[b, index[b,e], c]                       (group_points, e = m*K + j)
 // NSRC = 3: out[b,c,e] = sum_i featT[b, index[b,e,i], c] * weight[b,e,i]  (interpolation, e = m)
 // An index outside [0,N1) contributes 0 and raises bit 0 of *status.
-template <int NSRC>
+template <int NSRC, typename IndexT = int64_t>
 __global__ void __launch_bounds__(ROWS_THREADS)
-gather_rows_kernel(const float *__restrict__ featT, const int64_t *__restrict__ index,
+gather_rows_kernel(const float *__restrict__ featT, const IndexT *__restrict__ index,
                    const float *__restrict__ weight, int C, int64_t N1, int64_t E, float *__restrict__ out,
                    int32_t *__restrict__ status) {
   extern __shared__ float tile[];  // [C][ROWS_TE + 1]
@@ -104,9 +104,9 @@ gather_rows_kernel(const float *__restrict__ featT, const int64_t *__restrict__ 
 // XOR-swizzled by the channel group so that the transposing scalar stores are at most 4-way
 // conflicted and the float4 reads of the second phase are conflict-free, and 16-byte streaming
 // stores of four consecutive entries per lane.
-template <int NSRC>
+template <int NSRC, typename IndexT = int64_t>
 __global__ void __launch_bounds__(ROWS_THREADS)
-gather_rows_vec4_kernel(const float *__restrict__ featT, const int64_t *__restrict__ index,
+gather_rows_vec4_kernel(const float *__restrict__ featT, const IndexT *__restrict__ index,
                         const float *__restrict__ weight, int C, int64_t N1, int64_t E, float *__restrict__ out,
                         int32_t *__restrict__ status) {
   extern __shared__ __align__(16) float tile[];  // [C][ROWS_TE], chunk-swizzled
@@ -198,11 +198,13 @@ __device__ __forceinline__ void red_add4(float *p, float a, float b, float c, fl
 // gout is read with 16-byte loads along the entry axis, turned into rows through the same swizzled
 // shared-memory tile as the forward, and every lane issues 16-byte vector reductions on contiguous
 // row pieces, so the L2 atomics work on full sectors instead of scattered single floats.
-template <int NSRC>
+// `gstride` is the distance in elements between the gout slabs of consecutive clouds (C*E when gout
+// is a dense [B,C,E] tensor; larger when the C channels are the leading part of a wider tensor).
+template <int NSRC, typename IndexT = int64_t>
 __global__ void __launch_bounds__(ROWS_THREADS)
-scatter_rows_vec4_kernel(const float *__restrict__ gout, const int64_t *__restrict__ index,
-                         const float *__restrict__ weight, int C, int64_t N1, int64_t E, float *__restrict__ gradT,
-                         int32_t *__restrict__ status) {
+scatter_rows_vec4_kernel(const float *__restrict__ gout, const IndexT *__restrict__ index,
+                         const float *__restrict__ weight, int C, int64_t N1, int64_t E, int64_t gstride,
+                         float *__restrict__ gradT, int32_t *__restrict__ status) {
   extern __shared__ __align__(16) float tile[];  // [C][ROWS_TE], chunk-swizzled
   __shared__ int sidx[ROWS_TE * NSRC];
   __shared__ float sw[ROWS_TE * NSRC];
@@ -226,7 +228,7 @@ scatter_rows_vec4_kernel(const float *__restrict__ gout, const int64_t *__restri
 
   // Phase 1: gout[b, c, e0 + 4*ch ..] -> tile row c, swizzled chunk.
   const int nchunks = n >> 2;
-  const float *gb = gout + b * C * E + e0;
+  const float *gb = gout + b * gstride + e0;
   for (int u = tid; u < C * (ROWS_TE / 4); u += ROWS_THREADS) {
     const int c = u >> 4, ch = u & 15;
     if (ch < nchunks) {
@@ -271,8 +273,8 @@ inline bool rows_profitable(int64_t C, int64_t N1, int64_t E, int nsrc) {
   return C >= 16 && C <= ROWS_MAX_C && N1 > 0 && E * nsrc >= 2 * N1;
 }
 
-template <int NSRC>
-int gather_rows(const float *in, const int64_t *index, const float *weight, int64_t B, int64_t C, int64_t N1,
+template <int NSRC, typename IndexT = int64_t>
+int gather_rows(const float *in, const IndexT *index, const float *weight, int64_t B, int64_t C, int64_t N1,
                 int64_t E, float *out, int32_t *status, float *scratch, cudaStream_t st) {
   TK3D_REQUIRE(B <= 65535, TK3D_ERR_SHAPE, "gather: batch too large for this path (B=%lld)", (long long)B);
   dim3 tg((unsigned)((N1 + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)B);
@@ -284,16 +286,16 @@ int gather_rows(const float *in, const int64_t *index, const float *weight, int6
   if (vec) {
     const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
     if (smem > 48 * 1024)
-      TK3D_CUDA(cudaFuncSetAttribute(gather_rows_vec4_kernel<NSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      TK3D_CUDA(cudaFuncSetAttribute(gather_rows_vec4_kernel<NSRC, IndexT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
-    gather_rows_vec4_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out,
+    gather_rows_vec4_kernel<NSRC, IndexT><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out,
                                                                     status);
     return check_launch("gather_rows_vec4_kernel");
   }
   const size_t smem = (size_t)C * (ROWS_TE + 1) * sizeof(float);
   if (smem > 48 * 1024)
-    TK3D_CUDA(cudaFuncSetAttribute(gather_rows_kernel<NSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  gather_rows_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out, status);
+    TK3D_CUDA(cudaFuncSetAttribute(gather_rows_kernel<NSRC, IndexT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  gather_rows_kernel<NSRC, IndexT><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out, status);
   return check_launch("gather_rows_kernel");
 }
 
@@ -309,8 +311,8 @@ int scatter_rows(const float *gout, const int64_t *index, const float *weight, i
       TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<NSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
     dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
-    scatter_rows_vec4_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(gout, index, weight, (int)C, N1, E, scratch,
-                                                                     status);
+    scatter_rows_vec4_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(gout, index, weight, (int)C, N1, E, C * E,
+                                                                     scratch, status);
     int rc = check_launch("scatter_rows_vec4_kernel");
     if (rc) return rc;
   }

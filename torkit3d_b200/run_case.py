@@ -3,7 +3,9 @@
     python -m torkit3d_b200.run_case <case> [--iters 3] [--scale-batch B]
 
 Cases: c1_chamfer, c2_knn, c3_fps, c3_ball, c3_group_fwd, c3_group_bwd, c4_chamfer_fwd,
-c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd.  ``--scale-batch`` overrides the batch
+c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd, and the layer front ends on the same
+inputs in channel-first layout, fused and spelled operator by operator: c3_fps_gather,
+c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain.  ``--scale-batch`` overrides the batch
 size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
 """
 import argparse
@@ -26,6 +28,31 @@ def build_case(name, batch, dev):
         p, feat = [t.to(dev) for t in workloads.c3_set_abstraction(**kw)]
         if name == "c3_fps":
             return lambda: sample_farthest_points(p, 1024)
+        if name in ("c3_fps_gather", "c3_fps_chain", "c3_sa_fused", "c3_sa_chain", "c3_sa_fused_bwd"):
+            from . import _fused
+            from .layers import set_abstraction_group
+            from .ops import group_points
+
+            pcf = p.transpose(1, 2).contiguous()  # [B,3,N], the layout the reference's layers pass around
+            if name == "c3_fps_gather":
+                return lambda: _fused.fps_gather(pcf, 1024)
+            if name == "c3_fps_chain":
+                def fps_chain():
+                    i = sample_farthest_points(pcf, 1024, True)
+                    return torch.gather(pcf, 2, i.unsqueeze(1).expand(-1, 3, -1))
+                return fps_chain
+            _, ccf = _fused.fps_gather(pcf, 1024)
+            if name == "c3_sa_fused":
+                return lambda: _fused.sa_group_forward(pcf, ccf, feat, 0.1, 32, want_index=False)
+            if name == "c3_sa_fused_bwd":
+                out, i32 = _fused.sa_group_forward(pcf, ccf, feat, 0.1, 32)
+                go = torch.randn_like(out)
+                return lambda: _fused.sa_group_backward(go, i32, feat.size(1), feat.size(2))
+
+            def sa_chain():
+                i = ball_query(ccf, pcf, 0.1, 32)
+                return torch.cat([group_points(feat, i), group_points(pcf, i) - ccf.unsqueeze(-1)], dim=1)
+            return sa_chain
         idx = sample_farthest_points(p, 1024)
         cent = torch.gather(p, 1, idx.unsqueeze(2).expand(-1, -1, 3)).contiguous()
         if name == "c3_ball":
@@ -49,6 +76,20 @@ def build_case(name, batch, dev):
             return lambda: _C.chamfer_distance_backward_cuda(g1, g2, a, b, i1, i2)
     if name.startswith("c5"):
         q, r, feat = [t.to(dev) for t in workloads.c5_scene_interp(**kw)]
+        if name in ("c5_fp_fused", "c5_fp_chain"):
+            from . import _fused
+            from .ops import interpolate_feature
+
+            qcf, rcf = q.transpose(1, 2).contiguous(), r.transpose(1, 2).contiguous()
+            if name == "c5_fp_fused":
+                return lambda: _fused.three_nn_interp_forward(qcf, rcf, feat)
+
+            def fp_chain():
+                d, i = knn_points(qcf, rcf, 3, transpose=True)
+                inv = 1.0 / torch.clamp(d, min=1e-10)
+                w = inv / torch.sum(inv, dim=2, keepdim=True)
+                return interpolate_feature(feat, i, w)
+            return fp_chain
         if name == "c5_three_nn":
             return lambda: knn_points(q, r, 3)
         d, i = knn_points(q, r, 3)
