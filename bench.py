@@ -308,6 +308,22 @@ def extras(dev, rank, world, flush):
     del o, go, ffg
     qcf, rcf = qq.transpose(1, 2).contiguous(), rr.transpose(1, 2).contiguous()
     out["c5_three_nn_interp_fused_ms"] = t(lambda: _fused.three_nn_interp_forward(qcf, rcf, ff), steps=3)
+    del qcf, rcf, qq, rr, ff
+    # EdgeConv edge features of one DGCNN layer (B=32, 1024 points, C=64, K=20), batch-sharded
+    from torkit3d_b200.ops import get_edge_feature
+    gen = torch.Generator().manual_seed(7)
+    pts = batch_shard(torch.randn(32, 1024, 3, generator=gen), rank, world).to(dev)
+    x = batch_shard(torch.randn(32, 64, 1024, generator=gen), rank, world).to(dev)
+    _, ind = knn_points(pts, pts, 20)
+    ms = t(lambda: get_edge_feature(x, x, ind), steps=10)
+    out["edge_feature_fused_ms"] = ms
+    out["edge_feature_fused_GBps"] = (32 * 128 * 1024 * 20 * 4 + 32 * 1024 * 20 * 8 + 2 * 32 * 64 * 1024 * 4) / (ms * 1e-3) / 1e9
+
+    def edge_chain():
+        grouped = group_points(x, ind)
+        xe = x.unsqueeze(3).expand_as(grouped)
+        return torch.cat([grouped - xe, xe], dim=1)
+    out["edge_feature_chain_ms"] = t(edge_chain, steps=10)
     return out
 
 

@@ -286,6 +286,29 @@ int tk3d_three_nn_interp_bwd(const void *grad_out, const int32_t *index32, const
                              size_t scratch_bytes, int dtype, void *stream);
 
 /*
+ * EdgeConv edge features: group_points of the key features + subtraction of the query feature +
+ * concatenation with the broadcast query feature, i.e. get_edge_feature_custom
+ * (torkit3d/ops/edge_conv.py:73-93), in one pass over the output.  fp32 and fp64.
+ *   query_feature [B,C,N1] in;  key_feature [B,C,N2] in;  index [B,N1,K] int64 in
+ *   out [B,2C,N1,K] out ([B,C,N1,K] when include_query == 0):
+ *       out[b,c,n,k]   = key_feature[b,c,index[b,n,k]] - query_feature[b,c,n]
+ *       out[b,C+c,n,k] = query_feature[b,c,n]
+ *   An index outside [0,N2) gathers 0 and ORs bit 0 into *status (optional).
+ *   scratch (optional, tk3d_edge_feature_scratch_bytes(...) bytes; 0 = no fast path for the shape):
+ *   same role as in tk3d_group_fwd / tk3d_group_bwd.
+ * Backward: grad_key[b,c,index[b,n,k]] += grad_out[b,c,n,k];
+ *           grad_query[b,c,n] = sum_k (grad_out[b,C+c,n,k] - grad_out[b,c,n,k]).
+ * Either gradient pointer may be NULL; each one given is fully written.
+ */
+size_t tk3d_edge_feature_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype);
+int tk3d_edge_feature_fwd(const void *query_feature, const void *key_feature, const int64_t *index, int64_t B,
+                          int64_t C, int64_t N1, int64_t N2, int64_t K, int include_query, void *out,
+                          int32_t *status, void *scratch, size_t scratch_bytes, int dtype, void *stream);
+int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
+                          int64_t K, int include_query, void *grad_query, void *grad_key, int32_t *status,
+                          void *scratch, size_t scratch_bytes, int dtype, void *stream);
+
+/*
  * Diagnostic with no counterpart in the reference: launches a kernel of dependent FP32 fused
  * multiply-add chains (`iters` x 64 FMAs per thread, 8 blocks of 256 threads per SM) on `stream`.
  * *flop (a HOST double, optional) receives the number of floating-point operations the launch

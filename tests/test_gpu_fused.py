@@ -239,3 +239,63 @@ def test_fused_rejects_unsupported():
     with pytest.raises(RuntimeError):
         _fused.three_nn_interp_forward(pts, pts[:, :2].contiguous(), torch.zeros(1, 4, 2, device=DEV),
                                        channel_first=False)  # fewer than 3 keys
+
+
+# ---- EdgeConv edge features -----------------------------------------------------------------------
+def edge_expected(q, k, index, include_query):
+    grouped = group_np(k, index)
+    qe = np.broadcast_to(q[..., None], grouped.shape)
+    edge = (grouped - qe).astype(q.dtype)
+    return np.concatenate([edge, qe], axis=1) if include_query else edge
+
+
+@pytest.mark.parametrize("B,C,n1,n2,K,dtype", [
+    (2, 64, 1024, 1024, 20, torch.float32),   # row path (DGCNN shape)
+    (2, 6, 500, 700, 20, torch.float32),      # direct path: C not a multiple of 4
+    (1, 128, 333, 400, 7, torch.float32),     # direct path: N1*K not a multiple of 4
+    (2, 8, 300, 300, 3, torch.float32),       # K smaller than a 16-byte chunk
+    (2, 16, 200, 260, 10, torch.float64),
+])
+@pytest.mark.parametrize("include_query", [True, False])
+def test_edge_feature_forward(B, C, n1, n2, K, dtype, include_query):
+    from torkit3d_b200.ops import get_edge_feature
+
+    g = torch.Generator().manual_seed(81)
+    q = torch.randn(B, C, n1, generator=g, dtype=dtype)
+    k = torch.randn(B, C, n2, generator=g, dtype=dtype)
+    index = torch.randint(0, n2, (B, n1, K), generator=g)
+    out = get_edge_feature(q.to(DEV), k.to(DEV), index.to(DEV), include_query)
+    np.testing.assert_array_equal(N(out), edge_expected(q.numpy(), k.numpy(), index.numpy(), include_query))
+
+
+@pytest.mark.parametrize("C,n1,K", [(64, 512, 20), (6, 300, 7)])
+def test_edge_feature_backward(oracle, C, n1, K):
+    from torkit3d_b200.ops import get_edge_feature
+
+    B, n2 = 2, 400
+    g = torch.Generator().manual_seed(82)
+    q = torch.randn(B, C, n1, generator=g)
+    k = torch.randn(B, C, n2, generator=g)
+    index = torch.randint(0, n2, (B, n1, K), generator=g)
+    qd, kd = q.to(DEV).requires_grad_(True), k.to(DEV).requires_grad_(True)
+    out = get_edge_feature(qd, kd, index.to(DEV))
+    go = torch.randn(out.shape, generator=g)
+    out.backward(go.to(DEV))
+    g64 = go.numpy().astype(np.float64)
+    gk = oracle.group_bwd(np.ascontiguousarray(g64[:, :C]), index.numpy(), n2)
+    gq = (g64[:, C:] - g64[:, :C]).sum(axis=3)
+    np.testing.assert_allclose(N(kd.grad), gk, rtol=1e-5, atol=2e-5)
+    np.testing.assert_allclose(N(qd.grad), gq, rtol=1e-5, atol=2e-5)
+
+
+def test_edge_feature_matches_operator_chain():
+    from torkit3d_b200.ops import get_edge_feature, group_points, knn_points
+
+    B, C, n, K = 4, 64, 2048, 20
+    pts = sphere(B, n, 83).to(DEV)
+    _, ind = knn_points(pts, pts, K)
+    x = torch.randn(B, C, n, device=DEV)
+    out = get_edge_feature(x, x, ind)
+    grouped = group_points(x, ind)
+    ref = torch.cat([grouped - x.unsqueeze(3), x.unsqueeze(3).expand_as(grouped)], dim=1)
+    assert torch.equal(out, ref)

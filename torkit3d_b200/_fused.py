@@ -158,3 +158,55 @@ def three_nn_interp_backward(grad_out, index32, weight, Nk):
                                            None, _ptr(scratch) if need else None, need, _lib.F32,
                                            _stream(grad_out)))
     return gfeat
+
+
+def edge_feature_forward(query_feature, key_feature, index, include_query=True):
+    """query_feature [B,C,N1], key_feature [B,C,N2], index [B,N1,K] int64 -> [B,2C,N1,K] (or [B,C,N1,K])."""
+    from ._C import _dtype, _index
+
+    _check_cuda(query_feature=query_feature, key_feature=key_feature, index=index)
+    _index(index, "index")
+    if query_feature.dtype != key_feature.dtype:
+        raise RuntimeError("query_feature and key_feature must share one dtype.")
+    query_feature, key_feature, index = query_feature.contiguous(), key_feature.contiguous(), index.contiguous()
+    _check_eq(query_feature.dim(), 3, "query_feature.dim() == 3")
+    _check_eq(key_feature.dim(), 3, "key_feature.dim() == 3")
+    _check_eq(index.dim(), 3, "index.dim() == 3")
+    B, C, N1 = query_feature.shape
+    _check_eq(key_feature.size(0), B, "key_feature.size(0) == query_feature.size(0)")
+    _check_eq(index.size(0), B, "index.size(0) == query_feature.size(0)")
+    _check_eq(key_feature.size(1), C, "key_feature.size(1) == query_feature.size(1)")
+    _check_eq(index.size(1), N1, "index.size(1) == query_feature.size(2)")
+    N2, K = key_feature.size(2), index.size(2)
+    dt = _dtype(query_feature)
+    lib = load()
+    dev = query_feature.device
+    with torch.cuda.device(dev):
+        out = torch.empty((B, 2 * C if include_query else C, N1, K), dtype=query_feature.dtype, device=dev)
+        need = lib.tk3d_edge_feature_scratch_bytes(B, C, N1, N2, K, dt)
+        scratch = _scratch(need, dev)
+        check(lib.tk3d_edge_feature_fwd(_ptr(query_feature), _ptr(key_feature), _ptr(index), B, C, N1, N2, K,
+                                        1 if include_query else 0, _ptr(out), None,
+                                        _ptr(scratch) if need else None, need, dt, _stream(query_feature)))
+    return out
+
+
+def edge_feature_backward(grad_out, index, C, N2, include_query=True, need_query=True, need_key=True):
+    """-> (grad_query [B,C,N1] | None, grad_key [B,C,N2] | None)."""
+    from ._C import _dtype
+
+    _check_cuda(grad_out=grad_out, index=index)
+    grad_out, index = grad_out.contiguous(), index.contiguous()
+    B, N1, K = index.shape
+    dt = _dtype(grad_out)
+    lib = load()
+    dev = grad_out.device
+    with torch.cuda.device(dev):
+        gq = torch.empty((B, C, N1), dtype=grad_out.dtype, device=dev) if need_query else None
+        gk = torch.empty((B, C, N2), dtype=grad_out.dtype, device=dev) if need_key else None
+        need = lib.tk3d_edge_feature_scratch_bytes(B, C, N1, N2, K, dt) if need_key else 0
+        scratch = _scratch(need, dev)
+        check(lib.tk3d_edge_feature_bwd(_ptr(grad_out), _ptr(index), B, C, N1, N2, K, 1 if include_query else 0,
+                                        _ptr(gq) if need_query else None, _ptr(gk) if need_key else None, None,
+                                        _ptr(scratch) if need else None, need, dt, _stream(grad_out)))
+    return gq, gk

@@ -51,6 +51,11 @@ SIGNATURES = {
                                         _vp, _vp, ctypes.c_size_t, _int, _vp]),
     "tk3d_three_nn_interp_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int,
                                         _vp]),
+    "tk3d_edge_feature_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64, _i64, _int]),
+    "tk3d_edge_feature_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp,
+                                     ctypes.c_size_t, _int, _vp]),
+    "tk3d_edge_feature_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp,
+                                     ctypes.c_size_t, _int, _vp]),
     "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
 }
 

@@ -1,6 +1,7 @@
 """Operator layer: same public names as ``torkit3d.ops``."""
 from .ball_query import ball_query
 from .chamfer_distance import chamfer_distance, nn_distance
+from .edge_conv import get_edge_feature
 from .group_points import group_points
 from .interpolate_feature import interpolate_feature, three_nn_weight
 from .knn_points import knn_points
@@ -8,4 +9,4 @@ from .native import knn
 from .sample_farthest_points import sample_farthest_points
 
 __all__ = ["ball_query", "chamfer_distance", "nn_distance", "group_points", "interpolate_feature",
-           "three_nn_weight", "knn_points", "knn", "sample_farthest_points"]
+           "three_nn_weight", "knn_points", "knn", "sample_farthest_points", "get_edge_feature"]

@@ -5,7 +5,8 @@
 Cases: c1_chamfer, c2_knn, c3_fps, c3_ball, c3_group_fwd, c3_group_bwd, c4_chamfer_fwd,
 c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd, and the layer front ends on the same
 inputs in channel-first layout, fused and spelled operator by operator: c3_fps_gather,
-c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain.  ``--scale-batch`` overrides the batch
+c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain; and the EdgeConv edge
+features of a DGCNN layer (B=32, 1024 points, C=64, K=20): edge_fused, edge_chain.  ``--scale-batch`` overrides the batch
 size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
 """
 import argparse
@@ -24,6 +25,22 @@ def build_case(name, batch, dev):
     if name == "c2_knn":
         q, r = [t.to(dev) for t in workloads.c2_knn(**kw)]
         return lambda: knn_points(q, r, 16)
+    if name.startswith("edge"):
+        from .ops import get_edge_feature, group_points
+
+        B = batch or 32
+        g = torch.Generator().manual_seed(7)
+        pts = torch.randn(B, 1024, 3, generator=g).to(dev)
+        x = torch.randn(B, 64, 1024, generator=g).to(dev)
+        _, ind = knn_points(pts, pts, 20)
+        if name == "edge_fused":
+            return lambda: get_edge_feature(x, x, ind)
+
+        def edge_chain():
+            grouped = group_points(x, ind)
+            xe = x.unsqueeze(3).expand_as(grouped)
+            return torch.cat([grouped - xe, xe], dim=1)
+        return edge_chain
     if name.startswith("c3"):
         p, feat = [t.to(dev) for t in workloads.c3_set_abstraction(**kw)]
         if name == "c3_fps":
