@@ -247,6 +247,25 @@ def extras(dev, rank, world, flush):
     x1, x2 = [v.to(dev) for v in workloads.c1_chamfer_small()]
     ms = t(lambda: nn_distance(x1, x2), steps=10)
     out["c1_chamfer_fwd_ms"] = ms
+    # the same configuration, forward + backward, eager launches against a replayed CUDA graph
+    from torkit3d_b200 import _C
+    g1 = torch.full((x1.size(0), x1.size(1)), 1e-3, device=dev)
+    g2 = torch.full((x2.size(0), x2.size(1)), 1e-3, device=dev)
+
+    def c1_chain():
+        d1, i1, d2, i2 = _C.chamfer_distance_forward_cuda(x1, x2)
+        return _C.chamfer_distance_backward_cuda(g1, g2, x1, x2, i1, i2)
+    out["c1_chamfer_fwd_bwd_eager_ms"] = t(c1_chain, steps=10)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        c1_chain()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        keep = c1_chain()
+    out["c1_chamfer_fwd_bwd_graph_ms"] = t(graph.replay, steps=10)
+    del graph, keep
     # C2 KNN, batch-sharded
     q, r = workloads.c2_knn()
     q, r = batch_shard(q, rank, world).to(dev), batch_shard(r, rank, world).to(dev)

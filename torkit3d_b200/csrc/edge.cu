@@ -70,15 +70,19 @@ edge_rows_vec4_kernel(const float *__restrict__ keyT, const float *__restrict__ 
     const int c = u >> 4, ch = u & 15;
     if (ch < nchunks) {
       float4 v = *reinterpret_cast<const float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & 15) << 2));
-      const int64_t eg = e0 + 4 * ch;
-      const int64_t n0 = eg / K;
-      const int r = (int)(eg - n0 * K);
-      const float *qp = qb + (int64_t)c * N1 + n0;
+      // query point of each of the four entries: one 32-bit division, then a carry chain
+      const unsigned eg = (unsigned)(e0 + 4 * ch);
+      unsigned nq = eg / (unsigned)K;
+      int r = (int)(eg - nq * (unsigned)K);
+      const float *qp = qb + (int64_t)c * N1;
       float4 qv;
-      qv.x = __ldg(qp + (r + 0) / K);
-      qv.y = __ldg(qp + (r + 1) / K);
-      qv.z = __ldg(qp + (r + 2) / K);
-      qv.w = __ldg(qp + (r + 3) / K);
+      qv.x = __ldg(qp + nq);
+      if (++r == K) { r = 0; ++nq; }
+      qv.y = __ldg(qp + nq);
+      if (++r == K) { r = 0; ++nq; }
+      qv.z = __ldg(qp + nq);
+      if (++r == K) { r = 0; ++nq; }
+      qv.w = __ldg(qp + nq);
       v.x = __fsub_rn(v.x, qv.x);
       v.y = __fsub_rn(v.y, qv.y);
       v.z = __fsub_rn(v.z, qv.z);
@@ -176,7 +180,7 @@ using namespace tk3d;
 extern "C" size_t tk3d_edge_feature_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K,
                                                   int dtype) {
   if (dtype != TK3D_F32 || B <= 0 || B > 65535 || C < 4 || C > ROWS_MAX_C || C % 4 != 0 || N1 <= 0 || N2 <= 0 ||
-      K <= 0 || (N1 * K) % 4 != 0 || (N2 + 31) / 32 > 65535)
+      K <= 0 || (N1 * K) % 4 != 0 || N1 * K >= (1LL << 32) || (N2 + 31) / 32 > 65535)
     return 0;
   return rows_scratch_bytes(B, C, N2);
 }
