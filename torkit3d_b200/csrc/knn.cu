@@ -371,40 +371,72 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 // among the candidates only.  No data-dependent work happens inside the sweeps, so the lanes of a
 // warp stay in step however the insert pattern of a one-pass top-k would look.
 //
-// Work split: a block of 4 warps serves 32 queries; warp s sweeps the s-th quarter of every key
-// tile for all 32 queries (lane = query), so a cloud of a few thousand queries still fills the
-// GPU.  Class minima and candidate lists are merged through shared memory; the final selection
-// orders by (distance, index) explicitly, so the order in which candidates arrive does not matter.
-// If a candidate buffer overflows (massive ties, adversarial or non-finite input) the query falls
-// back to an exact insertion scan over all keys.
+// Work split: a block of 4 warps serves 32*Q queries; warp s sweeps the s-th quarter of every key
+// tile for all of them (lane = query), so a cloud of a few thousand queries still fills the GPU.
+// Class minima are merged through shared memory.  Candidates of a query go to ONE list per query
+// (slot claimed with a shared-memory atomic, so the four warps share the space and its order is
+// arbitrary); the final selection ranks every candidate by (distance, index) against all others of
+// its query, which is order independent, and writes it straight to its output position.
+// Shared memory is laid out so that the exact candidate distances reuse the key tiles and class
+// minima (dead by then): 30 KB per block for Q = 2, which keeps seven blocks (28 warps) per SM.
+// If a list overflows (massive ties, adversarial or non-finite input) the query falls back to an
+// exact insertion scan over all keys.
 constexpr int KT_THREADS = 128;
 constexpr int KT_SPLIT = KT_THREADS / 32;  // key quarters per tile
 constexpr int KT_TILE = 256;
 constexpr int KT_NCH = 32;                 // key classes (8 keys per class per tile)
-constexpr int KT_CAP = 40;                 // candidate slots per (query, quarter): 32 usable + one group of slack
+constexpr int KT_QCAP = 56;                // candidate slots per query (about 1.4 k are expected)
+
+template <int Q>
+constexpr size_t kt_smem_bytes() {
+  return (size_t)2 * KT_TILE * 16 + (size_t)KT_NCH * 32 * Q * 4 + (size_t)KT_QCAP * 32 * Q * 4;
+}
+
+// Predicated append: if !(a >= thr), claim a slot of the query's list and store j there (when the
+// slot exists).  Written in PTX so that it stays five straight-line instructions per pair.
+template <int STRIDE_BYTES>
+__device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr, unsigned cand_addr, int j) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .pred q;\n\t"
+      ".reg .s32 sl;\n\t"
+      ".reg .u32 ad;\n\t"
+      "setp.ltu.f32 p, %0, %1;\n\t"
+      "@p atom.shared.add.s32 sl, [%2], 1;\n\t"
+      "setp.lt.and.s32 q, sl, %5, p;\n\t"
+      "mad.lo.u32 ad, sl, %6, %3;\n\t"
+      "@q st.shared.s32 [ad], %4;\n\t"
+      "}" ::"f"(a),
+      "f"(thr), "r"(cnt_addr), "r"(cand_addr), "r"(j), "n"(KT_QCAP), "n"(STRIDE_BYTES));
+}
 
 // Q = queries per lane (1 or 2): a block serves 32*Q queries.  Two queries per lane halve the
 // shared-memory reads per pair, one keeps more blocks in flight when queries are few.
 template <int Q>
-__global__ void __launch_bounds__(KT_THREADS)
+__global__ void __launch_bounds__(KT_THREADS, 7)
 knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k,
                    float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
   constexpr int PER = KT_TILE / KT_THREADS;
   constexpr int CPW = KT_NCH / KT_SPLIT;  // classes per warp = 8
   constexpr int QS = 32 * Q;              // query slots per block
-  __shared__ float4 tile[2][KT_TILE];            // pair layout of sweep.cuh; reused for the result distances
-  __shared__ float cm[KT_NCH][QS];               // class minima per query; reused for the result indices
-  extern __shared__ __align__(16) int cand_raw[];  // [KT_SPLIT][KT_CAP][QS] candidates per quarter and query
-  int(*cand)[KT_CAP][QS] = reinterpret_cast<int(*)[KT_CAP][QS]>(cand_raw);
-  __shared__ int ccount[KT_SPLIT][QS];
+  constexpr int NSUB = KT_THREADS / QS;   // threads per query in the selection
+  extern __shared__ __align__(16) unsigned char kt_smem[];
+  float4 *tile = reinterpret_cast<float4 *>(kt_smem);                                  // [2][KT_TILE], pair layout
+  float *cm = reinterpret_cast<float *>(kt_smem + 2 * KT_TILE * 16);                   // [KT_NCH][QS] class minima
+  int *cand = reinterpret_cast<int *>(kt_smem + 2 * KT_TILE * 16 + KT_NCH * QS * 4);   // [KT_QCAP][QS]
+  float *cd = reinterpret_cast<float *>(kt_smem);  // [KT_QCAP][QS] exact distances; reuses tile + cm after pass 2
+  static_assert(2 * KT_TILE * 16 + KT_NCH * QS * 4 >= KT_QCAP * QS * 4, "candidate distances fit into tile + cm");
+  static_assert(KT_QCAP >= 16, "the fallback keeps its k <= 16 list in the query's own column");
+  __shared__ int ccnt[QS];
   __shared__ float s_rmax[KT_SPLIT];
   __shared__ float s_tau[QS];
-  static_assert(sizeof(tile) >= sizeof(float) * 16 * QS && sizeof(cm) >= sizeof(int) * 16 * QS, "result lists fit");
-  float(*ld)[QS] = reinterpret_cast<float(*)[QS]>(&tile[0][0]);  // [16][QS], valid after pass 2
-  int(*li)[QS] = reinterpret_cast<int(*)[QS]>(&cm[0][0]);        // [16][QS], valid after tau is known
+  __shared__ float sq[3][QS];
   const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
   const int chunks = (N1 + QS - 1) / QS;
   const float u = 5.9604645e-8f;
+  const unsigned cnt_base = (unsigned)__cvta_generic_to_shared(ccnt);
+  const unsigned cand_base = (unsigned)__cvta_generic_to_shared(cand);
 
   for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
     const int64_t b = blk / chunks;
@@ -412,6 +444,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     float qx[Q], qy[Q], qz[Q], qq[Q];
     float2 mx[Q], my[Q], mz[Q];
     bool valid[Q];
+    __syncthreads();  // the previous iteration's candidate distances alias the tile; sq is rewritten
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
       const int i = ibase + s * 32 + lane;
@@ -422,6 +455,11 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
         qx[s] = q[0];
         qy[s] = q[1];
         qz[s] = q[2];
+      }
+      if (part == 0) {
+        sq[0][s * 32 + lane] = qx[s];
+        sq[1][s * 32 + lane] = qy[s];
+        sq[2][s * 32 + lane] = qz[s];
       }
       mx[s] = make_float2(-2.f * qx[s], -2.f * qx[s]);
       my[s] = make_float2(-2.f * qy[s], -2.f * qy[s]);
@@ -453,12 +491,11 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     for (int s = 0; s < Q; ++s)
 #pragma unroll
       for (int c = 0; c < CPW; ++c) cmin[s][c] = pinf();
-    __syncthreads();  // the previous block iteration's result lists alias the tile
     fetch(0);
-    commit(tile[0]);
+    commit(tile);
     __syncthreads();
     for (int t = 0; t < ntiles; ++t) {
-      const float4 *tl = tile[t & 1] + part * (KT_TILE / KT_SPLIT);
+      const float4 *tl = tile + (t & 1) * KT_TILE + part * (KT_TILE / KT_SPLIT);
       if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
 #pragma unroll
       for (int c = 0; c < CPW; ++c) {
@@ -474,13 +511,13 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
           }
         }
       }
-      if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
+      if (t + 1 < ntiles) commit(tile + ((t + 1) & 1) * KT_TILE);
       __syncthreads();
     }
 #pragma unroll
     for (int s = 0; s < Q; ++s)
 #pragma unroll
-      for (int c = 0; c < CPW; ++c) cm[part * CPW + c][s * 32 + lane] = cmin[s][c];
+      for (int c = 0; c < CPW; ++c) cm[(part * CPW + c) * QS + s * 32 + lane] = cmin[s][c];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
     if (lane == 0) s_rmax[part] = rmax;
@@ -499,7 +536,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
         int rank = 0;
 #pragma unroll 8
         for (int o = 0; o < KT_NCH; ++o) {
-          const float w = cm[o][s * 32 + lane];
+          const float w = cm[o * QS + s * 32 + lane];
           rank += (w < v || (w == v && o < cc)) ? 1 : 0;
         }
         if (rank == k - 1) s_tau[s * 32 + lane] = v;
@@ -508,7 +545,8 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     __syncthreads();
     // Upper bound of the k-th smallest exact distance (constants rounded up generously to cover
     // the roundings of this very computation), then the filter threshold that admits every key
-    // at or below it.  Anything non-finite makes the threshold NaN: "accept all".
+    // at or below it.  Anything non-finite sends the query to the exact fallback: its counter
+    // starts beyond the capacity and its threshold admits nothing.
     float thr[Q];
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
@@ -516,36 +554,21 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       const float a_up = tau + 32.f * u * rmax + 8.f * u * qq[s];
       const float d_up = (a_up + qq[s] * (1.f + 8.f * u)) * (1.f + 10.f * u) + 1e-37f;
       const float lim = __int_as_float(__float_as_int(fmaxf(d_up, 0.f)) + 1);  // next float up
-      thr[s] = (d_up < 3.0e38f && rmax < 1.0e30f && qq[s] < 1.0e30f) ? sweep_threshold(lim, qq[s]) : qnan();
-      if (!valid[s]) thr[s] = -pinf();
+      const bool finite = d_up < 3.0e38f && rmax < 1.0e30f && qq[s] < 1.0e30f;
+      thr[s] = (finite && valid[s]) ? sweep_threshold(lim, qq[s]) : -pinf();
+      if (part == 0) ccnt[s * 32 + lane] = (finite || !valid[s]) ? 0 : KT_QCAP + 1;
     }
 
-    // ---- pass 2: collect this warp's candidates
-    int cnt[Q];
-    bool overflow[Q];
-#pragma unroll
-    for (int s = 0; s < Q; ++s) {
-      cnt[s] = 0;
-      overflow[s] = false;
-    }
+    // ---- pass 2: collect the candidates (padding keys carry w = +inf and never pass)
     fetch(0);
-    commit(tile[0]);
+    commit(tile);
     __syncthreads();
     for (int t = 0; t < ntiles; ++t) {
       const int t0 = t * KT_TILE + part * (KT_TILE / KT_SPLIT);
-      const float4 *tl = tile[t & 1] + part * (KT_TILE / KT_SPLIT);
+      const float4 *tl = tile + (t & 1) * KT_TILE + part * (KT_TILE / KT_SPLIT);
       if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
 #pragma unroll 2
       for (int u0 = 0; u0 < KT_TILE / KT_SPLIT; u0 += 8) {
-        // Straight-line append: the slot is always written, the count only advances on a pass.
-        // KT_CAP leaves room for one whole group beyond the checked limit.
-#pragma unroll
-        for (int s = 0; s < Q; ++s) {
-          if (cnt[s] > KT_CAP - 8) {
-            overflow[s] = true;
-            cnt[s] = 0;
-          }
-        }
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
           const float4 A = tl[u0 + 2 * p], Bv = tl[u0 + 2 * p + 1];
@@ -555,63 +578,76 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
 #pragma unroll
           for (int s = 0; s < Q; ++s) {
             const float2 a = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
-            cand[part][cnt[s]][s * 32 + lane] = j;
-            cnt[s] += (!(a.x >= thr[s]) && j < N2) ? 1 : 0;
-            cand[part][cnt[s]][s * 32 + lane] = j + 1;
-            cnt[s] += (!(a.y >= thr[s]) && j + 1 < N2) ? 1 : 0;
+            const unsigned ca = cnt_base + 4u * (s * 32 + lane), da = cand_base + 4u * (s * 32 + lane);
+            kt_append<QS * 4>(a.x, thr[s], ca, da, j);
+            kt_append<QS * 4>(a.y, thr[s], ca, da, j + 1);
           }
         }
       }
-      if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
+      if (t + 1 < ntiles) commit(tile + ((t + 1) & 1) * KT_TILE);
       __syncthreads();
     }
-#pragma unroll
-    for (int s = 0; s < Q; ++s) ccount[part][s * 32 + lane] = overflow[s] ? -1 : cnt[s];
-    __syncthreads();
 
-    // ---- exact selection among the candidates, ordered by (distance, index): warp s serves the
-    // queries of slot s (lane = query); the tile and class-minimum storage is free by now.
-#pragma unroll
-    for (int s = 0; s < Q; ++s) {
-      if (part == s && valid[s]) {
-        const int col = s * 32 + lane;
+    // ---- exact selection: NSUB threads per query.  First the exact distance of every candidate,
+    // then each candidate's rank by (distance, index) among its query's candidates; ranks below k
+    // go straight to the output row.
+    const int col = tid % QS, sub = tid / QS;
+    const int iq = ibase + col;
+    const bool qvalid = iq < N1;
+    const int n = ccnt[col];
+    const float cqx = sq[0][col], cqy = sq[1][col], cqz = sq[2][col];
+    if (qvalid && n <= KT_QCAP) {
+      for (int c = sub; c < n; c += NSUB) {
+        const int j = cand[c * QS + col];
+        cd[c * QS + col] =
+            sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], cqx, cqy, cqz);
+      }
+    }
+    __syncthreads();
+    if (qvalid) {
+      float *od = dist + (b * N1 + iq) * (int64_t)k;
+      int64_t *oi = index + (b * N1 + iq) * (int64_t)k;
+      if (n <= KT_QCAP) {
+        for (int c = sub; c < n; c += NSUB) {
+          const float d = cd[c * QS + col];
+          const int j = cand[c * QS + col];
+          int rank = 0;
+          for (int o = 0; o < n; ++o) {
+            const float w = cd[o * QS + col];
+            const int jo = cand[o * QS + col];
+            rank += (w < d || (w == d && jo < j)) ? 1 : 0;
+          }
+          if (rank < k) {
+            od[rank] = d;
+            oi[rank] = (int64_t)j;
+          }
+        }
+      } else if (sub == 0) {
+        // Exact insertion scan; the sorted list lives in the first k slots of this query's own
+        // column of cd / cand (nobody else touches the column of an overflowed query).
         int nk = 0;
-        auto offer = [&](int j) {
-          const float d = sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], qx[s],
-                                        qy[s], qz[s]);
+        for (int j = 0; j < N2; ++j) {
+          const float d =
+              sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], cqx, cqy, cqz);
           if (nk == k) {
-            const float dl = ld[k - 1][col];
-            if (!(d < dl || (d == dl && j < li[k - 1][col]))) return;
+            const float dl = cd[(k - 1) * QS + col];
+            if (!(d < dl || (d == dl && j < cand[(k - 1) * QS + col]))) continue;
           }
           int pos = nk < k ? nk : k - 1;
           while (pos > 0) {
-            const float dp = ld[pos - 1][col];
-            if (!(d < dp || (d == dp && j < li[pos - 1][col]))) break;
-            ld[pos][col] = dp;
-            li[pos][col] = li[pos - 1][col];
+            const float dp = cd[(pos - 1) * QS + col];
+            if (!(d < dp || (d == dp && j < cand[(pos - 1) * QS + col]))) break;
+            cd[pos * QS + col] = dp;
+            cand[pos * QS + col] = cand[(pos - 1) * QS + col];
             --pos;
           }
-          ld[pos][col] = d;
-          li[pos][col] = j;
+          cd[pos * QS + col] = d;
+          cand[pos * QS + col] = j;
           if (nk < k) ++nk;
-        };
-        bool any_overflow = false;
-#pragma unroll
-        for (int w = 0; w < KT_SPLIT; ++w) any_overflow |= ccount[w][col] < 0;
-        if (!any_overflow) {
-          for (int w = 0; w < KT_SPLIT; ++w) {
-            const int n = ccount[w][col];
-            for (int c = 0; c < n; ++c) offer(cand[w][c][col]);
-          }
-        } else {
-          for (int j = 0; j < N2; ++j) offer(j);
         }
-        const int i = ibase + col;
-        float *od = dist + (b * N1 + i) * (int64_t)k;
-        int64_t *oi = index + (b * N1 + i) * (int64_t)k;
         for (int c = 0; c < k; ++c) {
-          od[c] = ld[c][col];
-          oi[c] = (int64_t)li[c][col];
+          od[c] = cd[c * QS + col];
+          oi[c] = (int64_t)cand[c * QS + col];
         }
       }
     }
@@ -736,8 +772,8 @@ int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2,
                 cudaStream_t st) {
   const int64_t total = B * ((N1 + 32 * Q - 1) / (32 * Q));
   const int64_t gcap = (int64_t)sm_count() * 256;
-  const size_t smem = sizeof(int) * KT_SPLIT * KT_CAP * 32 * Q;
-  if (smem + 20 * 1024 > 48 * 1024)
+  const size_t smem = kt_smem_bytes<Q>();
+  if (smem > 48 * 1024)
     TK3D_CUDA(cudaFuncSetAttribute(knn_twopass_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   knn_twopass_kernel<Q><<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, smem, st>>>(query, key, B, N1, N2, k,
                                                                                          dist, index, total);
