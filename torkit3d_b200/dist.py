@@ -117,10 +117,9 @@ def chamfer_step_from_host(xyz1_host, xyz2_host, device, global_batch=None, grou
     stream while the forward and backward kernels of slice i run on the current stream.  This is
     possible because the mean loss is linear in the per-point distances: d loss / d dist is the
     constant 1/count, known before any distance is, so each slice's gradient kernels can run right
-    after its forward kernel.  Slicing pays only when every slice still fills the GPU for many waves
-    of thread blocks (one block sweeps 256 points against a whole cloud): on B200, 64 pairs of
-    16384-point clouds in 8 slices ran slower (7.3 ms) than unsliced (6.85 ms), because a slice of 8
-    clouds is 1.15 waves.  To hide the copy of such batches use ``HostCloudPrefetcher`` across steps.
+    after its forward kernel.  Slicing adds launches and host work per slice: on B200, 64 pairs of
+    16384-point clouds in 8 slices ran slower (7.3 ms) than unsliced (6.85 ms).  To hide the copy of
+    such batches use ``HostCloudPrefetcher`` across steps.
 
     Args:
         xyz1_host: [B_local, N1, 3] float32 CPU tensor (pin it for asynchronous copies).
