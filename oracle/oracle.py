@@ -224,3 +224,56 @@ def three_nn_weight(dist):
     out = np.empty_like(dist)
     getattr(lib(), "orc_three_nn_weight" + _sfx(dist))(_p(dist), I64(dist.size // k), I64(k), _p(out))
     return out
+
+
+# ---- callers of the operators (compositions, numpy) ------------------------------------------------
+def _group_safe(x, index):
+    """group_points with -1 entries (empty ball-query rows) reading as 0: [B,C,N],[B,M,K] -> [B,C,M,K]."""
+    safe = np.where(index < 0, 0, index)
+    out = np.stack([x[b][:, safe[b]] for b in range(x.shape[0])])
+    return np.where((index >= 0)[:, None], out, 0).astype(x.dtype)
+
+
+def fps_gather(points_cf, num_samples):
+    """sample_farthest_points(points, S, transpose=True) + batch_index_select(points, idx, dim=2)
+    (torkit3d/models/classification/pointnet2.py:73-74).  points_cf [B,3,N] -> (idx [B,S], xyz [B,3,S])."""
+    pts = np.ascontiguousarray(points_cf.transpose(0, 2, 1))
+    idx = fps(pts, num_samples)
+    xyz = np.take_along_axis(points_cf, np.broadcast_to(idx[:, None, :], (idx.shape[0], 3, idx.shape[1])), axis=2)
+    return idx, xyz
+
+
+def sa_group(in_xyz_cf, out_xyz_cf, feature, radius, k, use_xyz=True):
+    """The tensor entering the MLP of SetAbstraction.forward (torkit3d/layers/pointnet2.py:43-58) with a
+    BallQuery neighbour search: [B, C(+3), N2, K]."""
+    pts = np.ascontiguousarray(in_xyz_cf.transpose(0, 2, 1))
+    cen = np.ascontiguousarray(out_xyz_cf.transpose(0, 2, 1))
+    index = ball_query(cen, pts, radius, k)
+    parts = []
+    if feature is not None:
+        parts.append(_group_safe(feature, index))
+    if use_xyz:
+        parts.append((_group_safe(in_xyz_cf, index) - out_xyz_cf[..., None]).astype(in_xyz_cf.dtype))
+    return np.concatenate(parts, axis=1), index
+
+
+def edge_feature(query_feature, key_feature, index, include_query=True):
+    """get_edge_feature_custom (torkit3d/ops/edge_conv.py:73-93): [B,2C,N1,K] (or [B,C,N1,K])."""
+    grouped = _group_safe(key_feature, index)
+    qe = np.broadcast_to(query_feature[..., None], grouped.shape)
+    edge = (grouped - qe).astype(query_feature.dtype)
+    return np.concatenate([edge, qe], axis=1) if include_query else edge
+
+
+def three_nn_interp(query_cf, key_cf, key_feature, eps=1e-10):
+    """FeatureInterpolator.forward (torkit3d/layers/pointnet2.py:114-133) on channel-first coordinates:
+    -> (out [B,C,Nq] in float64 accumulation, index [B,Nq,3], weight [B,Nq,3])."""
+    q = np.ascontiguousarray(query_cf.transpose(0, 2, 1))
+    r = np.ascontiguousarray(key_cf.transpose(0, 2, 1))
+    d, idx = knn(q, r, 3)
+    one = d.dtype.type(1.0)
+    inv = (one / np.maximum(d, d.dtype.type(eps))).astype(d.dtype)
+    norm = ((inv[..., 0] + inv[..., 1]).astype(d.dtype) + inv[..., 2]).astype(d.dtype)
+    w = (inv / norm[..., None]).astype(d.dtype)
+    out = interp_fwd(key_feature.astype(np.float64), idx, w.astype(np.float64))
+    return out, idx, w

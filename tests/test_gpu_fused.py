@@ -299,3 +299,41 @@ def test_edge_feature_matches_operator_chain():
     grouped = group_points(x, ind)
     ref = torch.cat([grouped - x.unsqueeze(3), x.unsqueeze(3).expand_as(grouped)], dim=1)
     assert torch.equal(out, ref)
+
+
+# ---- golden fixtures produced by the reference's own layer code (tests/golden/make_golden.py) ---------
+def test_golden_fps_gather(golden):
+    g = golden("fps_gather")
+    for tag in "ab":
+        idx, xyz = sample_and_gather(torch.from_numpy(g[tag + "_points"]).to(DEV), int(g[tag + "_s"]))
+        np.testing.assert_array_equal(N(idx), g[tag + "_index"])
+        np.testing.assert_array_equal(N(xyz), g[tag + "_xyz"])
+
+
+def test_golden_sa_group(golden):
+    g = golden("sa_group")
+    for tag in "abcd":
+        feat = torch.from_numpy(g[tag + "_feature"]).to(DEV) if (tag + "_feature") in g.files else None
+        out = set_abstraction_group(torch.from_numpy(g[tag + "_in_xyz"]).to(DEV),
+                                    torch.from_numpy(g[tag + "_out_xyz"]).to(DEV), feat, float(g[tag + "_radius"]),
+                                    int(g[tag + "_k"]), bool(g[tag + "_use_xyz"]))
+        np.testing.assert_array_equal(N(out), g[tag + "_nbr"])
+
+
+def test_golden_edge_feature(golden):
+    from torkit3d_b200.ops import get_edge_feature
+
+    g = golden("edge_feature")
+    for tag in "ab":
+        q, k, i = [torch.from_numpy(g[tag + n]).to(DEV) for n in ("_query", "_key", "_index")]
+        np.testing.assert_array_equal(N(get_edge_feature(q, k, i)), g[tag + "_edge"])
+        np.testing.assert_array_equal(N(get_edge_feature(q, k, i, include_query=False)), g[tag + "_edge_noquery"])
+
+
+def test_golden_three_nn_interp(golden):
+    g = golden("three_nn_interp")
+    for tag in "ab":
+        q, k, f = [torch.from_numpy(g[tag + n]).to(DEV) for n in ("_query", "_key", "_feature")]
+        out = FeatureInterpolator()(q, k, f)
+        # the reference formulation gets its distances from cdist (a square root, squared again)
+        np.testing.assert_allclose(N(out), g[tag + "_out"], rtol=1e-4, atol=1e-5)

@@ -147,3 +147,39 @@ def test_empty_and_edge(oracle):
     q = np.random.default_rng(1).standard_normal((1, 4, 3)).astype(np.float32)
     d, i = oracle.knn(q, q, 4)
     assert (np.sort(i, 2) == np.arange(4)).all() and (i[:, :, 0] == np.arange(4)).all()
+
+
+# ---- callers of the operators: the oracle's compositions against the reference's own layer code ----
+def test_fps_gather_golden(oracle, golden):
+    g = golden("fps_gather")
+    for tag in "ab":
+        idx, xyz = oracle.fps_gather(g[tag + "_points"], int(g[tag + "_s"]))
+        np.testing.assert_array_equal(idx, g[tag + "_index"])
+        np.testing.assert_array_equal(xyz, g[tag + "_xyz"])
+
+
+def test_sa_group_golden(oracle, golden):
+    g = golden("sa_group")
+    for tag in "abcd":
+        feat = g[tag + "_feature"] if (tag + "_feature") in g.files else None
+        out, _ = oracle.sa_group(g[tag + "_in_xyz"], g[tag + "_out_xyz"], feat, float(g[tag + "_radius"]),
+                                 int(g[tag + "_k"]), bool(g[tag + "_use_xyz"]))
+        np.testing.assert_array_equal(out, g[tag + "_nbr"])
+
+
+def test_edge_feature_golden(oracle, golden):
+    g = golden("edge_feature")
+    for tag in "ab":
+        np.testing.assert_array_equal(oracle.edge_feature(g[tag + "_query"], g[tag + "_key"], g[tag + "_index"]),
+                                      g[tag + "_edge"])
+        np.testing.assert_array_equal(
+            oracle.edge_feature(g[tag + "_query"], g[tag + "_key"], g[tag + "_index"], include_query=False),
+            g[tag + "_edge_noquery"])
+
+
+def test_three_nn_interp_golden(oracle, golden):
+    g = golden("three_nn_interp")
+    for tag in "ab":
+        out, _, _ = oracle.three_nn_interp(g[tag + "_query"], g[tag + "_key"], g[tag + "_feature"])
+        # the reference formulation gets its distances from cdist (a square root, squared again)
+        np.testing.assert_allclose(out, g[tag + "_out"], rtol=1e-4, atol=1e-5)
