@@ -60,7 +60,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         qx[s] = q[0];
         qy[s] = q[1];
         qz[s] = q[2];
-        thr[s] = __int_as_float(0x7fc00000);  // NaN: everything passes until a first candidate is verified
+        thr[s] = Q == 2 ? pinf : __int_as_float(0x7fc00000);  // accept everything until a first candidate is verified
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
         thr[s] = -pinf;  // never passes
@@ -114,7 +114,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
 #pragma unroll UNR
       for (int u0 = 0; u0 < lim; u0 += GK) {
         float2 a[4];
-        if (__builtin_expect(sweep_group2<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
+        if (__builtin_expect(sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
           for (int p = 0; p < GK / 2; ++p) {
 #pragma unroll

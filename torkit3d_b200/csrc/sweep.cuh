@@ -67,6 +67,30 @@ __device__ __forceinline__ bool sweep_any8(float a0, float a1, float a2, float a
   return flag != 0;
 }
 
+// Variant on minima: "is the smallest of a0..a3 below t01, or the smallest of a4..a7 below t23?".
+// Three-input minima (one instruction each on sm_100) replace six of the eight compares.  A NaN
+// filter value is ignored here (its exact distance could never be accepted anyway), so the
+// "accept everything" state of a threshold is +inf, not NaN.
+__device__ __forceinline__ bool sweep_any8_min(float a0, float a1, float a2, float a3, float a4, float a5, float a6,
+                                               float a7, float t0123, float t4567) {
+  unsigned flag;
+  asm("{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .f32 m0;\n\t"
+      ".reg .f32 m1;\n\t"
+      "min.f32 m0, %1, %2, %3;\n\t"
+      "min.f32 m1, %5, %6, %7;\n\t"
+      "min.f32 m0, m0, %4;\n\t"
+      "min.f32 m1, m1, %8;\n\t"
+      "setp.lt.f32 p, m0, %9;\n\t"
+      "setp.lt.or.f32 p, m1, %10, p;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(flag)
+      : "f"(a0), "f"(a1), "f"(a2), "f"(a3), "f"(a4), "f"(a5), "f"(a6), "f"(a7), "f"(t0123), "f"(t4567));
+  return flag != 0;
+}
+
 // Filter values of one key against Q queries.
 __device__ __forceinline__ float sweep_lower(float mx, float my, float mz, const float4 &r) {
   return fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
@@ -95,7 +119,7 @@ __device__ __forceinline__ float4 sweep_load_key(const float4 *tile, int u) {
 // Filter values of a group of 4/Q key pairs (8/Q keys) x Q queries: a[p*Q + s] = (value for key
 // 2p, value for key 2p+1) of query s; returns "any of the eight passes".  `pairs` points at the
 // first float4 slot of the group (slot index = key index, which must be even).
-template <int Q>
+template <int Q, bool MINV = false>
 __device__ __forceinline__ bool sweep_group2(const float4 *__restrict__ pairs, const float2 (&mx)[Q],
                                              const float2 (&my)[Q], const float2 (&mz)[Q], const float (&thr)[Q],
                                              float2 (&a)[4]) {
@@ -109,6 +133,8 @@ __device__ __forceinline__ bool sweep_group2(const float4 *__restrict__ pairs, c
 #pragma unroll
     for (int s = 0; s < Q; ++s) a[p * Q + s] = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
   }
+  if constexpr (MINV && Q == 2)  // a[0], a[2] belong to query 0; a[1], a[3] to query 1
+    return sweep_any8_min(a[0].x, a[0].y, a[2].x, a[2].y, a[1].x, a[1].y, a[3].x, a[3].y, thr[0], thr[1]);
   return sweep_any8(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0 % Q], thr[0 % Q],
                     thr[1 % Q], thr[1 % Q], thr[2 % Q], thr[2 % Q], thr[3 % Q], thr[3 % Q]);
 }
