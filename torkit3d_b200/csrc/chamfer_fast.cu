@@ -60,7 +60,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         qx[s] = q[0];
         qy[s] = q[1];
         qz[s] = q[2];
-        thr[s] = Q == 2 ? pinf : __int_as_float(0x7fc00000);  // accept everything until a first candidate is verified
+        thr[s] = pinf;  // accept everything until a first candidate is verified (minima-based test)
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
         thr[s] = -pinf;  // never passes

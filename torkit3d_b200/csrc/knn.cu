@@ -95,7 +95,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
           qy[s] = q[1];
           qz[s] = q[2];
         }
-        thr[s] = qnan();  // accept everything until the list is full
+        thr[s] = Q <= 2 ? pinf() : qnan();  // accept everything until the list is full
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
         thr[s] = -pinf();
@@ -138,7 +138,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll 4
       for (int u0 = 0; u0 < lim; u0 += GK) {
         float2 a[4];
-        if (__builtin_expect(sweep_group2<Q>(tl + u0, mx, my, mz, thr, a), 0)) {
+        if (__builtin_expect(sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
           for (int p = 0; p < GK / 2; ++p) {
 #pragma unroll

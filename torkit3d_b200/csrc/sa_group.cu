@@ -134,7 +134,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
 #pragma unroll 2
       for (int u0 = 0; u0 < QK; u0 += 8) {
         float2 a[4];
-        if (__builtin_expect(sweep_group2<1>(tl + u0, mx, my, mz, thr, a), 0)) {
+        if (__builtin_expect(sweep_group2<1, true>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int j = t0 + u0 + u;

@@ -67,12 +67,19 @@ __device__ __forceinline__ bool sweep_any8(float a0, float a1, float a2, float a
   return flag != 0;
 }
 
-// Variant on minima: "is the smallest of a0..a3 below t01, or the smallest of a4..a7 below t23?".
-// Three-input minima (one instruction each on sm_100) replace six of the eight compares.  A NaN
-// filter value is ignored here (its exact distance could never be accepted anyway), so the
-// "accept everything" state of a threshold is +inf, not NaN.
-__device__ __forceinline__ bool sweep_any8_min(float a0, float a1, float a2, float a3, float a4, float a5, float a6,
-                                               float a7, float t0123, float t4567) {
+// The same question asked through minima: three-input minima (one instruction each on sm_100)
+// feed one compare per query, which takes most of the compares off the half-rate pipe.  A NaN filter
+// value is ignored by the minimum (its exact distance could never be accepted anyway), so with this
+// test the "accept everything" state of a threshold is +inf, not NaN.
+__device__ __forceinline__ float sweep_min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// v0..v3 against t0, v4..v7 against t1.
+__device__ __forceinline__ bool sweep_any8_min(float v0, float v1, float v2, float v3, float v4, float v5, float v6,
+                                               float v7, float t0, float t1) {
   unsigned flag;
   asm("{\n\t"
       ".reg .pred p;\n\t"
@@ -87,7 +94,7 @@ __device__ __forceinline__ bool sweep_any8_min(float a0, float a1, float a2, flo
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(flag)
-      : "f"(a0), "f"(a1), "f"(a2), "f"(a3), "f"(a4), "f"(a5), "f"(a6), "f"(a7), "f"(t0123), "f"(t4567));
+      : "f"(v0), "f"(v1), "f"(v2), "f"(v3), "f"(v4), "f"(v5), "f"(v6), "f"(v7), "f"(t0), "f"(t1));
   return flag != 0;
 }
 
@@ -135,6 +142,8 @@ __device__ __forceinline__ bool sweep_group2(const float4 *__restrict__ pairs, c
   }
   if constexpr (MINV && Q == 2)  // a[0], a[2] belong to query 0; a[1], a[3] to query 1
     return sweep_any8_min(a[0].x, a[0].y, a[2].x, a[2].y, a[1].x, a[1].y, a[3].x, a[3].y, thr[0], thr[1]);
+  if constexpr (MINV && Q == 1)
+    return sweep_any8_min(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0], thr[0]);
   return sweep_any8(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0 % Q], thr[0 % Q],
                     thr[1 % Q], thr[1 % Q], thr[2 % Q], thr[2 % Q], thr[3 % Q], thr[3 % Q]);
 }
