@@ -507,7 +507,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
 #pragma unroll
           for (int s = 0; s < Q; ++s) {
             const float2 a = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
-            cmin[s][c] = fminf(cmin[s][c], fminf(a.x, a.y));
+            cmin[s][c] = sweep_min3(cmin[s][c], a.x, a.y);
           }
         }
       }
@@ -568,19 +568,30 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       const float4 *tl = tile + (t & 1) * KT_TILE + part * (KT_TILE / KT_SPLIT);
       if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
 #pragma unroll 2
-      for (int u0 = 0; u0 < KT_TILE / KT_SPLIT; u0 += 8) {
+      for (int u0 = 0; u0 < KT_TILE / KT_SPLIT; u0 += 4) {
+        // Two key pairs (four keys) at a time: one minimum and one compare per query decide
+        // whether any of its four filter values passes; only then are the four appends executed
+        // (about 2 % of the lanes, half of the warps).
+        float2 a[2][Q];
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
+        for (int p = 0; p < 2; ++p) {
           const float4 A = tl[u0 + 2 * p], Bv = tl[u0 + 2 * p + 1];
           const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
           const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
-          const int j = t0 + u0 + 2 * p;
 #pragma unroll
-          for (int s = 0; s < Q; ++s) {
-            const float2 a = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
+          for (int s = 0; s < Q; ++s)
+            a[p][s] = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
+        }
+        const int j = t0 + u0;
+#pragma unroll
+        for (int s = 0; s < Q; ++s) {
+          const float m = fminf(sweep_min3(a[0][s].x, a[0][s].y, a[1][s].x), a[1][s].y);
+          if (m < thr[s]) {
             const unsigned ca = cnt_base + 4u * (s * 32 + lane), da = cand_base + 4u * (s * 32 + lane);
-            kt_append<QS * 4>(a.x, thr[s], ca, da, j);
-            kt_append<QS * 4>(a.y, thr[s], ca, da, j + 1);
+            kt_append<QS * 4>(a[0][s].x, thr[s], ca, da, j);
+            kt_append<QS * 4>(a[0][s].y, thr[s], ca, da, j + 1);
+            kt_append<QS * 4>(a[1][s].x, thr[s], ca, da, j + 2);
+            kt_append<QS * 4>(a[1][s].y, thr[s], ca, da, j + 3);
           }
         }
       }
