@@ -119,19 +119,18 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
           for (int p = 0; p < GK / 2; ++p) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
+              // no bounds test: padding keys carry a filter value of +inf, which no threshold admits
               const int j = t0 + u0 + 2 * p + h;
-              if (j < nr) {
-                const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
+              const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
 #pragma unroll
-                for (int s = 0; s < Q; ++s) {
-                  const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
-                  if (!(av >= thr[s])) {
-                    const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-                    if (d < best[s]) {
-                      best[s] = d;
-                      arg[s] = j;
-                      thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
-                    }
+              for (int s = 0; s < Q; ++s) {
+                const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
+                if (av < thr[s]) {
+                  const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
+                  if (d < best[s]) {
+                    best[s] = d;
+                    arg[s] = j;
+                    thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
                   }
                 }
               }

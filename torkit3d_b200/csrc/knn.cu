@@ -95,7 +95,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
           qy[s] = q[1];
           qz[s] = q[2];
         }
-        thr[s] = Q <= 2 ? pinf() : qnan();  // accept everything until the list is full
+        thr[s] = pinf();  // accept everything until the list is full
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
         thr[s] = -pinf();
@@ -143,13 +143,13 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
           for (int p = 0; p < GK / 2; ++p) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
+              // no bounds test: padding keys carry a filter value of +inf, which no threshold admits
               const int j = t0 + u0 + 2 * p + h;
-              if (j >= N2) continue;
               const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
 #pragma unroll
               for (int s = 0; s < Q; ++s) {
                 const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
-                if (!(av >= thr[s])) {
+                if (av < thr[s]) {
                   const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
                   // (d, j) enters iff it orders before the current last entry; sentinels carry
                   // (+inf, INT_MAX) so real entries always precede them.
