@@ -81,6 +81,21 @@ int tk3d_chamfer_bwd(const void *grad_dist1, const void *grad_dist2, const void 
                      void *grad_xyz1, void *grad_xyz2, int dtype, void *stream);
 
 /*
+ * Mean chamfer loss helpers (no counterpart in the reference, whose callers spell these steps as
+ * element-wise PyTorch expressions): with sums = [sum(dist1), sum(dist2)] from tk3d_chamfer_fwd
+ * (all-reduced over the ranks of a sharded batch), count1 = global number of cloud-1 points and
+ * count2 likewise,
+ *   tk3d_chamfer_mean_loss   loss[0] = sums[0]/count1 + sums[1]/count2          (one element of `dtype`)
+ *   tk3d_chamfer_bwd_mean    gradients of that loss: tk3d_chamfer_bwd with the per-point upstream
+ *                            gradients grad_loss[0]/count1 and grad_loss[0]/count2 (grad_loss is a
+ *                            device scalar of `dtype`), without materialising them.
+ */
+int tk3d_chamfer_mean_loss(const double *sums, double count1, double count2, void *loss, int dtype, void *stream);
+int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, double count2, const void *xyz1, const void *xyz2,
+                          const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
+                          void *grad_xyz1, void *grad_xyz2, int dtype, void *stream);
+
+/*
  * Brute-force k nearest neighbours.
  * Replaces knn_distance_cuda (torkit3d/csrc/include/knn_distance.h:7-11,
  * torkit3d/csrc/cuda/knn_distance_kernel.cu:187-298), both of its `version`s.

@@ -22,6 +22,9 @@ SIGNATURES = {
     "tk3d_last_error": (ctypes.c_char_p, []),
     "tk3d_chamfer_fwd": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "tk3d_chamfer_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_chamfer_mean_loss": (_int, [_vp, ctypes.c_double, ctypes.c_double, _vp, _int, _vp]),
+    "tk3d_chamfer_bwd_mean": (_int, [_vp, ctypes.c_double, ctypes.c_double, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                     _vp, _vp, _int, _vp]),
     "tk3d_knn": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
     "tk3d_fps_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _int]),
     "tk3d_fps": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, ctypes.c_size_t, _int, _vp]),

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256)
 chamfer_bwd_own_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const T *__restrict__ xyz1,
                        const T *__restrict__ xyz2, const int64_t *__restrict__ idx1,
                        const int64_t *__restrict__ idx2, int64_t B, int64_t N1, int64_t N2, T *__restrict__ grad1,
-                       T *__restrict__ grad2) {
+                       T *__restrict__ grad2, int gstride, T scale1, T scale2) {
   const int64_t tot1 = B * N1, total = B * (N1 + N2);
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int dir = t >= tot1;
@@ -110,7 +110,8 @@ chamfer_bwd_own_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const
       ga[2] = 0;
       continue;
     }
-    const T g = (dir ? g2 : g1)[lin] * (T)2;
+    // gstride 0: one upstream value for the whole cloud set; scale is 1 for per-point gradients
+    const T g = (dir ? g2 : g1)[lin * gstride] * (dir ? scale2 : scale1) * (T)2;
     const T *p = a + lin * 3;
     const T *q = bb + (b * nb + j) * 3;
     ga[0] = g * (p[0] - q[0]);
@@ -140,7 +141,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 chamfer_bwd_scatter_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const T *__restrict__ xyz1,
                            const T *__restrict__ xyz2, const int64_t *__restrict__ idx1,
-                           const int64_t *__restrict__ idx2, int64_t B, int64_t N1, int64_t N2, T *grad1, T *grad2) {
+                           const int64_t *__restrict__ idx2, int64_t B, int64_t N1, int64_t N2, T *grad1, T *grad2,
+                           int gstride, T scale1, T scale2) {
   const int64_t tot1 = B * N1, total = B * (N1 + N2);
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int dir = t >= tot1;
@@ -151,7 +153,8 @@ chamfer_bwd_scatter_kernel(const T *__restrict__ g1, const T *__restrict__ g2, c
     const int64_t b = lin / na;
     const int64_t j = (dir ? idx2 : idx1)[lin];
     if (j < 0 || j >= nb) continue;
-    const T g = (dir ? g2 : g1)[lin] * (T)2;
+    // gstride 0: one upstream value for the whole cloud set; scale is 1 for per-point gradients
+    const T g = (dir ? g2 : g1)[lin * gstride] * (dir ? scale2 : scale1) * (T)2;
     const T *p = a + lin * 3;
     const T *q = bb + (b * nb + j) * 3;
     T *gb = (dir ? grad1 : grad2) + (b * nb + j) * 3;
@@ -178,21 +181,62 @@ static int chamfer_fwd_generic(const T *xyz1, const T *xyz2, int64_t B, int64_t 
 template <typename T>
 static int chamfer_bwd_t(const T *g1, const T *g2, const T *xyz1, const T *xyz2, const int64_t *idx1,
                          const int64_t *idx2, int64_t B, int64_t N1, int64_t N2, T *grad1, T *grad2,
-                         cudaStream_t st) {
+                         cudaStream_t st, int gstride = 1, T scale1 = (T)1, T scale2 = (T)1) {
   const int64_t total = B * (N1 + N2);
   if (total == 0) return TK3D_OK;
   const int64_t want = (total + 255) / 256, cap = (int64_t)sm_count() * 32;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
-  chamfer_bwd_own_kernel<T><<<grid, 256, 0, st>>>(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, grad1, grad2);
+  chamfer_bwd_own_kernel<T><<<grid, 256, 0, st>>>(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, grad1, grad2, gstride,
+                                                  scale1, scale2);
   int rc = check_launch("chamfer_bwd_own_kernel");
   if (rc) return rc;
-  chamfer_bwd_scatter_kernel<T><<<grid, 256, 0, st>>>(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, grad1, grad2);
+  chamfer_bwd_scatter_kernel<T><<<grid, 256, 0, st>>>(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, grad1, grad2,
+                                                      gstride, scale1, scale2);
   return check_launch("chamfer_bwd_scatter_kernel");
+}
+
+// loss = sums[0] / count1 + sums[1] / count2, written as one element of type T
+template <typename T>
+__global__ void chamfer_mean_loss_kernel(const double *__restrict__ sums, double count1, double count2,
+                                         T *__restrict__ loss) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) loss[0] = (T)(sums[0] / count1 + sums[1] / count2);
 }
 
 }  // namespace tk3d
 
 using namespace tk3d;
+
+extern "C" int tk3d_chamfer_mean_loss(const double *sums, double count1, double count2, void *loss, int dtype,
+                                      void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_mean_loss: dtype %d", dtype);
+  TK3D_REQUIRE(sums && loss, TK3D_ERR_NULL, "chamfer_mean_loss: a pointer is NULL");
+  TK3D_REQUIRE(count1 > 0 && count2 > 0, TK3D_ERR_SHAPE, "chamfer_mean_loss: counts must be positive");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == TK3D_F32)
+    chamfer_mean_loss_kernel<float><<<1, 32, 0, st>>>(sums, count1, count2, (float *)loss);
+  else
+    chamfer_mean_loss_kernel<double><<<1, 32, 0, st>>>(sums, count1, count2, (double *)loss);
+  return check_launch("chamfer_mean_loss_kernel");
+}
+
+extern "C" int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, double count2, const void *xyz1,
+                                     const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B,
+                                     int64_t N1, int64_t N2, void *grad1, void *grad2, int dtype, void *stream) {
+  TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_bwd_mean: dtype %d", dtype);
+  TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "chamfer_bwd_mean: negative size");
+  TK3D_REQUIRE(count1 > 0 && count2 > 0, TK3D_ERR_SHAPE, "chamfer_bwd_mean: counts must be positive");
+  TK3D_REQUIRE(grad_loss, TK3D_ERR_NULL, "chamfer_bwd_mean: grad_loss is NULL");
+  TK3D_REQUIRE(B * N1 == 0 || (xyz1 && idx1 && grad1), TK3D_ERR_NULL, "chamfer_bwd_mean: a cloud-1 pointer is NULL");
+  TK3D_REQUIRE(B * N2 == 0 || (xyz2 && idx2 && grad2), TK3D_ERR_NULL, "chamfer_bwd_mean: a cloud-2 pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == TK3D_F32)
+    return chamfer_bwd_t<float>((const float *)grad_loss, (const float *)grad_loss, (const float *)xyz1,
+                                (const float *)xyz2, idx1, idx2, B, N1, N2, (float *)grad1, (float *)grad2, st, 0,
+                                (float)(1.0 / count1), (float)(1.0 / count2));
+  return chamfer_bwd_t<double>((const double *)grad_loss, (const double *)grad_loss, (const double *)xyz1,
+                               (const double *)xyz2, idx1, idx2, B, N1, N2, (double *)grad1, (double *)grad2, st, 0,
+                               1.0 / count1, 1.0 / count2);
+}
 
 extern "C" int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, void *dist1,
                                 int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype, void *stream) {
