@@ -491,8 +491,8 @@ def run_b200(args, rank, world, local_rank):
         line = {"metric": "chamfer_point_pairs_per_sec", "value": value, "unit": "pairs/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": workload_config(world, world), "clocks": clocks, "e2e": e2e, "gpu_launches": 3,
-                "gpu_launches_detail": "per step: chamfer_fwd_fast_kernel, chamfer_bwd_own_kernel, chamfer_bwd_scatter_kernel",
+                "config": workload_config(world, world), "clocks": clocks, "e2e": e2e, "gpu_launches": 4,
+                "gpu_launches_detail": "per step: chamfer_fwd_fast_kernel, chamfer_mean_loss_kernel, chamfer_bwd_own_kernel, chamfer_bwd_scatter_kernel",
                 "roofline": roofline, "roofline_backward": bwd, "cpu_baseline": cpu, "extras": ext}
         print(json.dumps(line), flush=True)
     if world > 1:
