@@ -8,7 +8,8 @@
 // registers before the current tile is processed and written to the other buffer afterwards, so
 // global latency hides behind the arithmetic with a single barrier per tile.
 //
-// Per (key, query) pair the hot loop issues 1.5 packed FMA + 1 FSETP; the exactly rounded
+// Per (key, query) pair the hot loop issues 1.5 packed FMA, half a three-input minimum and a
+// quarter of a compare (eight pairs share two compares and one branch); the exactly rounded
 // distance is recomputed only for pairs that pass the filter (about ln(M) + a few per query), and
 // the running minimum is updated with a strict "<" in ascending key order, so the lowest index
 // wins ties.

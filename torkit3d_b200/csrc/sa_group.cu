@@ -16,10 +16,10 @@
 //     through a chunk-swizzled shared tile (which reuses the memory of phase A) and stored with
 //     16-byte streaming stores; the three coordinate channels are gathered, centred and stored by
 //     the same block.
-// Measured on B200 (B=32, 8192 points, 1024 centres, K=32, C=64): 0.27 ms against 0.40 ms for the
+// Measured on B200 (B=32, 8192 points, 1024 centres, K=32, C=64): 0.25 ms against 0.37 ms for the
 // same result spelled as ball query + two gathers + subtraction + concatenation.  With this shape
 // all 1024 blocks are resident at once and pass through the two phases together, so the time is
-// close to the sum of a ball query (0.16 ms) and a gather (0.11 ms); larger batches, whose blocks
+// close to the sum of a ball query (0.13 ms) and a gather (0.11 ms); larger batches, whose blocks
 // come in several waves, let the sweep of one block overlap the traffic of another.
 #include "rows.cuh"
 #include "sweep.cuh"

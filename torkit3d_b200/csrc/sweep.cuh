@@ -18,8 +18,13 @@
 //     d < lim   ==>   a < lim (1 + 5.1u) - |q|^2 (1 - 3.01u)
 // threshold(lim, qq) below returns a float that is >= that right-hand side including the rounding
 // of its own three operations and of qq = fl(|q|^2) (16u on both terms, plus an absolute slack for
-// gradual underflow), so  "a < t" can never reject a pair with d < lim.  The test is written
-// !(a >= t) so that a NaN or inf produced by enormous coordinates falls into the verify path.
+// gradual underflow), so  "a < t" can never reject a pair with d < lim.
+// Non-finite values: a pair whose filter value is NaN or +inf has a NaN or infinite exact distance,
+// which the strict "d < bound" of every operator rejects anyway, so it does not matter whether the
+// filter lets it through (sweep_any8, written !(a >= t)) or not (sweep_any8_min, which tests
+// minima).  Key tiles are padded with (0, 0, 0, w = +inf): a padding key's filter value is +inf and
+// no threshold admits it, which is why the verify paths need no bounds test.  A threshold of +inf
+// means "accept every real key", -inf "accept nothing".
 #pragma once
 
 #include "tk3d_common.cuh"
