@@ -68,7 +68,8 @@ def test_chamfer_far_from_origin_and_huge_values(oracle):
     from torkit3d_b200.ops import nn_distance
 
     rng = np.random.default_rng(4)
-    for offset, scale in ((1000.0, 1.0), (-3.0e4, 10.0), (0.0, 1e-20), (0.0, 1e18), (5e18, 1e18)):
+    # last case: |p|^2 overflows fp32 for every point while all distances are finite
+    for offset, scale in ((1000.0, 1.0), (-3.0e4, 10.0), (0.0, 1e-20), (0.0, 1e18), (5e18, 1e18), (1.85e19, 1e17)):
         a = (rng.standard_normal((2, 300, 3)) * scale + offset).astype(np.float32)
         b = (rng.standard_normal((2, 700, 3)) * scale + offset).astype(np.float32)
         d1, i1, d2, i2 = [N(t) for t in nn_distance(T(a), T(b))]
@@ -77,6 +78,22 @@ def test_chamfer_far_from_origin_and_huge_values(oracle):
         np.testing.assert_array_equal(i2, j2)
         np.testing.assert_array_equal(d1, e1)
         np.testing.assert_array_equal(d2, e2)
+
+
+def test_knn_and_ball_query_where_squared_norms_overflow(oracle):
+    """Coordinates near 1.85e19: |p|^2 = inf in fp32, pairwise distances about 1e34."""
+    from torkit3d_b200.ops import ball_query, knn_points
+
+    rng = np.random.default_rng(5)
+    q = (rng.standard_normal((2, 200, 3)) * 1e17 + 1.85e19).astype(np.float32)
+    r = (rng.standard_normal((2, 600, 3)) * 1e17 + 1.85e19).astype(np.float32)
+    for k in (3, 16):
+        d, i = knn_points(T(q), T(r), k)
+        ed, ei = oracle.knn(q, r, k)
+        np.testing.assert_array_equal(N(i), ei)
+        np.testing.assert_array_equal(N(d), ed)
+    idx = ball_query(T(q), T(r), 1.5e17, 8, transpose=False)
+    np.testing.assert_array_equal(N(idx), oracle.ball_query(q, r, 1.5e17, 8))
 
 
 def test_chamfer_empty_partner_and_empty_batch():

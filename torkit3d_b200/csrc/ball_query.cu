@@ -82,7 +82,7 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
           for (int u = 0; u < 8; ++u) {
             const int j = t0 + u0 + u;
             const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
-            if (av < thr[0]) {  // padding keys carry +inf; a full row has thr = -inf
+            if (!(av >= thr[0])) {  // padding keys carry +inf; a full row has thr = -inf
               const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {
@@ -180,7 +180,7 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
           for (int u = 0; u < 8; ++u) {
             const int j = t0 + u0 + u;
             const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
-            if (av < thr[0]) {  // padding keys carry +inf; a full row has thr = -inf
+            if (!(av >= thr[0])) {  // padding keys carry +inf; a full row has thr = -inf
               const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {

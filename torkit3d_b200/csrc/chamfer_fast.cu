@@ -126,7 +126,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
 #pragma unroll
               for (int s = 0; s < Q; ++s) {
                 const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
-                if (av < thr[s]) {
+                if (!(av >= thr[s])) {
                   const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
                   if (d < best[s]) {
                     best[s] = d;

@@ -149,7 +149,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll
               for (int s = 0; s < Q; ++s) {
                 const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
-                if (av < thr[s]) {
+                if (!(av >= thr[s])) {
                   const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
                   // (d, j) enters iff it orders before the current last entry; sentinels carry
                   // (+inf, INT_MAX) so real entries always precede them.

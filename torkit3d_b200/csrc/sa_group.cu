@@ -139,7 +139,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
           for (int u = 0; u < 8; ++u) {
             const int j = t0 + u0 + u;
             const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
-            if (av < thr[0]) {  // padding keys carry +inf; a full row has thr = -inf
+            if (!(av >= thr[0])) {  // padding keys carry +inf; a full row has thr = -inf
               const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {

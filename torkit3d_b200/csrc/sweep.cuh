@@ -19,12 +19,15 @@
 // threshold(lim, qq) below returns a float that is >= that right-hand side including the rounding
 // of its own three operations and of qq = fl(|q|^2) (16u on both terms, plus an absolute slack for
 // gradual underflow), so  "a < t" can never reject a pair with d < lim.
-// Non-finite values: a pair whose filter value is NaN or +inf has a NaN or infinite exact distance,
-// which the strict "d < bound" of every operator rejects anyway, so it does not matter whether the
-// filter lets it through (sweep_any8, written !(a >= t)) or not (sweep_any8_min, which tests
-// minima).  Key tiles are padded with (0, 0, 0, w = +inf): a padding key's filter value is +inf and
-// no threshold admits it, which is why the verify paths need no bounds test.  A threshold of +inf
-// means "accept every real key", -inf "accept nothing".
+// Non-finite values.  Coordinates beyond about 1e19 overflow |r|^2, |q|^2 or q.r although the
+// distance of two such points can be finite.  The tests are therefore written "a < t or unordered"
+// (!(a >= t)): a NaN filter value (inf - inf) reaches the verify path, -inf passes, and +inf only
+// arises where the exact distance is infinite too.  |q|^2 and the key term w are clamped to the
+// largest finite float (sweep_qq, sweep_key_w), so that a threshold is never NaN or -inf for a real
+// query and a real key never carries the +inf that marks padding.  Key tiles are padded with
+// (0, 0, 0, w = +inf): a padding key's filter value is +inf, which no threshold admits, so the
+// verify paths need no bounds test.  A threshold of +inf means "accept every real key", -inf
+// "accept nothing".
 #pragma once
 
 #include "tk3d_common.cuh"
@@ -33,7 +36,9 @@ namespace tk3d {
 
 __device__ __forceinline__ float sweep_key_w(float x, float y, float z) {
   const float rr = fmaf(z, z, fmaf(y, y, x * x));
-  return rr * (1.0f - 12.0f * 5.9604645e-8f);
+  // Clamped to the largest finite float: an overflowed |r|^2 must not turn the filter value into
+  // +inf ("never passes") for a key whose distance is finite; too small a w only passes more keys.
+  return fminf(rr * (1.0f - 12.0f * 5.9604645e-8f), 3.402823466e38f);
 }
 
 __device__ __forceinline__ float sweep_threshold(float lim, float qq) {
@@ -42,7 +47,9 @@ __device__ __forceinline__ float sweep_threshold(float lim, float qq) {
   return __fadd_rn(__fsub_rn(__fmul_rn(lim, up), __fmul_rn(qq, dn)), 1e-37f);
 }
 
-__device__ __forceinline__ float sweep_qq(float x, float y, float z) { return fmaf(z, z, fmaf(y, y, x * x)); }
+__device__ __forceinline__ float sweep_qq(float x, float y, float z) {
+  return fminf(fmaf(z, z, fmaf(y, y, x * x)), 3.402823466e38f);  // NaN and +inf become FLT_MAX
+}
 
 // "Does any of the eight filter values fall below its threshold?"  Written in PTX so that the
 // eight compares chain through two predicates (setp.ltu.or) that are OR-ed once, and a single
@@ -73,9 +80,9 @@ __device__ __forceinline__ bool sweep_any8(float a0, float a1, float a2, float a
 }
 
 // The same question asked through minima: three-input minima (one instruction each on sm_100)
-// feed one compare per query, which takes most of the compares off the half-rate pipe.  A NaN filter
-// value is ignored by the minimum (its exact distance could never be accepted anyway), so with this
-// test the "accept everything" state of a threshold is +inf, not NaN.
+// feed one compare per query, which takes most of the compares off the half-rate pipe.  The minima
+// propagate NaN and the compare is "less than or unordered", so a NaN filter value (inf - inf, when
+// |r|^2 or q.r overflow although the distance itself is finite) still reaches the verify path.
 __device__ __forceinline__ float sweep_min3(float a, float b, float c) {
   float d;
   asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -90,12 +97,12 @@ __device__ __forceinline__ bool sweep_any8_min(float v0, float v1, float v2, flo
       ".reg .pred p;\n\t"
       ".reg .f32 m0;\n\t"
       ".reg .f32 m1;\n\t"
-      "min.f32 m0, %1, %2, %3;\n\t"
-      "min.f32 m1, %5, %6, %7;\n\t"
-      "min.f32 m0, m0, %4;\n\t"
-      "min.f32 m1, m1, %8;\n\t"
-      "setp.lt.f32 p, m0, %9;\n\t"
-      "setp.lt.or.f32 p, m1, %10, p;\n\t"
+      "min.NaN.f32 m0, %1, %2, %3;\n\t"
+      "min.NaN.f32 m1, %5, %6, %7;\n\t"
+      "min.NaN.f32 m0, m0, %4;\n\t"
+      "min.NaN.f32 m1, m1, %8;\n\t"
+      "setp.ltu.f32 p, m0, %9;\n\t"
+      "setp.ltu.or.f32 p, m1, %10, p;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(flag)
