@@ -170,7 +170,10 @@ def test_chamfer_partial_sums():
 # ----------------------------------------------------------------------------------------------- knn
 KNN_CASES = [(1, 1, 1, 1), (2, 33, 64, 1), (2, 100, 300, 3), (3, 511, 1025, 31), (2, 512, 1024, 32), (1, 700, 2000, 4),
              (2, 257, 900, 5), (4, 1000, 1111, 16), (2, 300, 1300, 64), (1, 200, 700, 100), (1, 130, 400, 128),
-             (1, 64, 300, 200), (2, 50, 16, 16), (40, 600, 700, 16), (40, 600, 700, 3)]
+             (1, 64, 300, 200), (2, 50, 16, 16), (40, 600, 700, 16), (40, 600, 700, 3),
+             # two-pass variants with 64 / 128 / 256 key classes (need N2 >= 32 k)
+             (2, 300, 2100, 20), (2, 300, 2100, 32), (2, 257, 2200, 64), (1, 100, 3300, 65), (1, 200, 4200, 100),
+             (1, 130, 4100, 128)]
 
 
 @pytest.mark.parametrize("B,n1,n2,k", KNN_CASES)
@@ -180,6 +183,22 @@ def test_knn_bit_exact(oracle, B, n1, n2, k):
     rng = np.random.default_rng(n1 * 7 + k)
     q = rng.standard_normal((B, n1, 3)).astype(np.float32)
     r = rng.standard_normal((B, n2, 3)).astype(np.float32)
+    d, i = knn_points(T(q), T(r), k)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
+@pytest.mark.parametrize("k", [20, 32, 64, 128])
+def test_knn_large_k_with_massive_ties(oracle, k):
+    """Every key appears 8 times and many queries coincide with keys: candidate lists overflow and
+    the exact fallback has to reproduce the (distance, index) order."""
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(k)
+    base = rng.standard_normal((2, 520, 3)).astype(np.float32)
+    r = np.tile(base, (1, 8, 1))  # 4160 keys
+    q = np.concatenate([base[:, :100], rng.standard_normal((2, 100, 3)).astype(np.float32)], axis=1)
     d, i = knn_points(T(q), T(r), k)
     e, j = oracle.knn(q, r, k)
     np.testing.assert_array_equal(N(i), j)

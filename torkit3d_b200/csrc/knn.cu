@@ -4,10 +4,10 @@
 //   knn_small_kernel<K,Q>  fp32, k <= 4: per-thread top-K in registers, filter-then-verify sweep
 //                          (sweep.cuh), insertion straight from the verify branch.  With k << N2
 //                          the branch is rare (about k ln(N2/k) times per query).
-//   knn_twopass_kernel     fp32, 4 < k <= 16 (and N2 >= 32 k): pass 1 bounds the k-th distance from
+//   knn_twopass_kernel     fp32, 4 < k <= 128 (and N2 >= 32 k): pass 1 bounds the k-th distance from
 //                          class minima of the filter value, pass 2 collects the few candidates
 //                          below the bound, exact selection among them (see the kernel's header).
-//   knn_buffered_kernel<Q> fp32, other k <= 128: same filter, but passing keys are only appended
+//   knn_buffered_kernel<Q> fp32, other k <= 128 (small key clouds): same filter, but passing keys are only appended
 //                          (predicated store, no branch) to a small per-query candidate buffer in
 //                          shared memory; buffers are drained into per-query sorted lists (also in
 //                          shared memory) by the whole warp at once, when any lane's buffer is
@@ -357,11 +357,11 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 }
 
 // ---------------------------------------------------------------------------------------------
-// Two-pass kernel for 4 < k <= 16 (fp32).
+// Two-pass kernel for 4 < k <= 128 (fp32).
 //
 // Pass 1 sweeps all keys with the cheap filter value a (3 FMA per pair) and keeps, per query, the
-// minimum of a over NCH interleaved key classes (class = position inside a 256-key tile / 8, so
-// every class is spread over the whole cloud whatever the key order).  The k-th smallest class
+// minimum of a over NCH >= 2k interleaved key classes (class = position inside a key tile divided by
+// the keys per class, so every class is spread over the whole cloud whatever the key order).  The k-th smallest class
 // minimum tau bounds the k-th smallest exact distance from above: the k classes below it each
 // hold a distinct key with a <= tau, and for any key
 //     d <= (a + 22.2u |r|^2 + 3.1u |q|^2 + |q|^2) (1 + 5.1u)
@@ -383,18 +383,21 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 // exact insertion scan over all keys.
 constexpr int KT_THREADS = 128;
 constexpr int KT_SPLIT = KT_THREADS / 32;  // key quarters per tile
-constexpr int KT_TILE = 256;
-constexpr int KT_NCH = 32;                 // key classes (8 keys per class per tile)
-constexpr int KT_QCAP = 56;                // candidate slots per query (about 1.4 k are expected)
-
-template <int Q>
+// KT_NCH key classes (32 to 256: at least two per wanted neighbour, i.e. k <= KT_NCH / 2; a warp
+// holds the minima of its KT_NCH / 4 classes in registers) and KT_QCAP candidate slots per query
+// (about 1.4 k candidates are expected) are template parameters of the kernel:
+//     k <= 16: 32 classes, 56 slots, one or two queries per lane
+//     k <= 32: 64 classes, 104 slots, one query per lane
+//     k <= 64: 128 classes, 192 slots, one query per lane
+//     k <= 128: 256 classes, 384 slots, one query per lane, 512-key tiles (KT_TILE; 256 otherwise)
+template <int Q, int KT_NCH, int KT_QCAP, int KT_TILE>
 constexpr size_t kt_smem_bytes() {
   return (size_t)2 * KT_TILE * 16 + (size_t)KT_NCH * 32 * Q * 4 + (size_t)KT_QCAP * 32 * Q * 4;
 }
 
 // Predicated append: if !(a >= thr), claim a slot of the query's list and store j there (when the
 // slot exists).  Written in PTX so that it stays five straight-line instructions per pair.
-template <int STRIDE_BYTES>
+template <int STRIDE_BYTES, int KT_QCAP>
 __device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr, unsigned cand_addr, int j) {
   asm volatile(
       "{\n\t"
@@ -413,12 +416,13 @@ __device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr,
 
 // Q = queries per lane (1 or 2): a block serves 32*Q queries.  Two queries per lane halve the
 // shared-memory reads per pair, one keeps more blocks in flight when queries are few.
-template <int Q>
-__global__ void __launch_bounds__(KT_THREADS, 7)
+template <int Q, int KT_NCH, int KT_QCAP, int MINB, int KT_TILE>
+__global__ void __launch_bounds__(KT_THREADS, MINB)
 knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k,
                    float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
   constexpr int PER = KT_TILE / KT_THREADS;
-  constexpr int CPW = KT_NCH / KT_SPLIT;  // classes per warp = 8
+  constexpr int CPW = KT_NCH / KT_SPLIT;          // classes per warp: 8, 16 or 32
+  constexpr int PPC = KT_TILE / KT_SPLIT / CPW / 2;  // key pairs per class, tile and warp: 4, 2 or 1
   constexpr int QS = 32 * Q;              // query slots per block
   constexpr int NSUB = KT_THREADS / QS;   // threads per query in the selection
   extern __shared__ __align__(16) unsigned char kt_smem[];
@@ -427,7 +431,8 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
   int *cand = reinterpret_cast<int *>(kt_smem + 2 * KT_TILE * 16 + KT_NCH * QS * 4);   // [KT_QCAP][QS]
   float *cd = reinterpret_cast<float *>(kt_smem);  // [KT_QCAP][QS] exact distances; reuses tile + cm after pass 2
   static_assert(2 * KT_TILE * 16 + KT_NCH * QS * 4 >= KT_QCAP * QS * 4, "candidate distances fit into tile + cm");
-  static_assert(KT_QCAP >= 16, "the fallback keeps its k <= 16 list in the query's own column");
+  static_assert(KT_QCAP >= KT_NCH / 2, "the fallback keeps its k <= KT_NCH / 2 list in the query's own column");
+  static_assert(PPC >= 1, "at least one key pair per class, tile and warp");
   __shared__ int ccnt[QS];
   __shared__ float s_rmax[KT_SPLIT];
   __shared__ float s_tau[QS];
@@ -500,8 +505,8 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
 #pragma unroll
       for (int c = 0; c < CPW; ++c) {
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          const float4 A = tl[c * 8 + 2 * p], Bv = tl[c * 8 + 2 * p + 1];
+        for (int p = 0; p < PPC; ++p) {
+          const float4 A = tl[c * 2 * PPC + 2 * p], Bv = tl[c * 2 * PPC + 2 * p + 1];
           const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
           const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
 #pragma unroll
@@ -588,10 +593,10 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
           const float m = fminf(sweep_min3(a[0][s].x, a[0][s].y, a[1][s].x), a[1][s].y);
           if (m < thr[s]) {
             const unsigned ca = cnt_base + 4u * (s * 32 + lane), da = cand_base + 4u * (s * 32 + lane);
-            kt_append<QS * 4>(a[0][s].x, thr[s], ca, da, j);
-            kt_append<QS * 4>(a[0][s].y, thr[s], ca, da, j + 1);
-            kt_append<QS * 4>(a[1][s].x, thr[s], ca, da, j + 2);
-            kt_append<QS * 4>(a[1][s].y, thr[s], ca, da, j + 3);
+            kt_append<QS * 4, KT_QCAP>(a[0][s].x, thr[s], ca, da, j);
+            kt_append<QS * 4, KT_QCAP>(a[0][s].y, thr[s], ca, da, j + 1);
+            kt_append<QS * 4, KT_QCAP>(a[1][s].x, thr[s], ca, da, j + 2);
+            kt_append<QS * 4, KT_QCAP>(a[1][s].y, thr[s], ca, da, j + 3);
           }
         }
       }
@@ -778,16 +783,17 @@ int knn_buffered(const float *query, const float *key, int64_t B, int N1, int N2
   return check_launch("knn_buffered_kernel");
 }
 
-template <int Q>
+template <int Q, int NCH, int QCAP, int MINB, int TILE = 256>
 int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, int64_t *index,
                 cudaStream_t st) {
   const int64_t total = B * ((N1 + 32 * Q - 1) / (32 * Q));
   const int64_t gcap = (int64_t)sm_count() * 256;
-  const size_t smem = kt_smem_bytes<Q>();
-  if (smem > 48 * 1024)
-    TK3D_CUDA(cudaFuncSetAttribute(knn_twopass_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  knn_twopass_kernel<Q><<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, smem, st>>>(query, key, B, N1, N2, k,
-                                                                                         dist, index, total);
+  const size_t smem = kt_smem_bytes<Q, NCH, QCAP, TILE>();
+  if (smem + 4096 > 48 * 1024)  // static shared memory of the kernel counts towards the 48 KB default limit
+    TK3D_CUDA(cudaFuncSetAttribute(knn_twopass_kernel<Q, NCH, QCAP, MINB, TILE>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  knn_twopass_kernel<Q, NCH, QCAP, MINB, TILE><<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, smem, st>>>(
+      query, key, B, N1, N2, k, dist, index, total);
   return check_launch("knn_twopass_kernel");
 }
 
@@ -837,9 +843,15 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
     default: break;
   }
   // Two-pass selection needs at least two key classes per wanted neighbour to be tight.
-  if (k <= 16 && N2 >= 32 * k) {
-    if (B * N1 >= (int64_t)sm_count() * 4 * 64) return knn_twopass<2>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
-    return knn_twopass<1>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+  if (k <= 128 && N2 >= 32 * k) {
+    if (k <= 16) {
+      if (B * N1 >= (int64_t)sm_count() * 4 * 64)
+        return knn_twopass<2, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+      return knn_twopass<1, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+    }
+    if (k <= 32) return knn_twopass<1, 64, 104, 5>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+    if (k <= 64) return knn_twopass<1, 128, 192, 4>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+    return knn_twopass<1, 256, 384, 2, 512>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
   }
   if (k <= 128) {
     const int64_t sms = sm_count();
