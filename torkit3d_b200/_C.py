@@ -64,6 +64,25 @@ def _stream(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device):
+    """Context that makes ``device`` current; free when it already is (the usual case: the small
+    operators are dominated by host time, and torch.cuda.device() costs several microseconds)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _ptr(t):
     return t.data_ptr() if t.numel() > 0 else (t.data_ptr() or 0)
 
@@ -81,9 +100,9 @@ def sample_farthest_points_cuda(points, num_samples):
     lib = load()
     B, N = points.size(0), points.size(1)
     dt = _dtype(points)
-    with torch.cuda.device(points.device):
+    with _on(points.device):
         index = torch.empty((B, num_samples), dtype=torch.int64, device=points.device)
-        need = lib.tk3d_fps_scratch_bytes(B, N, dt)
+        need = _lib.scratch_bytes("tk3d_fps", B, N, dt)
         scratch = torch.empty((need,), dtype=torch.uint8, device=points.device) if need else None
         check(lib.tk3d_fps(_ptr(points), B, N, num_samples, _ptr(index), _ptr(scratch) if need else None, need, dt,
                            _stream(points)))
@@ -102,7 +121,7 @@ def ball_query_cuda(query, key, radius, max_neighbors):
     lib = load()
     B, N1, N2 = query.size(0), query.size(1), key.size(1)
     k = int(max_neighbors)
-    with torch.cuda.device(query.device):
+    with _on(query.device):
         index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
         check(lib.tk3d_ball_query(_ptr(query), _ptr(key), B, N1, N2, float(radius), k, _ptr(index), _dtype(query),
                                   _stream(query)))
@@ -121,9 +140,9 @@ def group_points_forward_cuda(input, index):
     lib = load()
     B, C, N1 = input.shape
     _, N2, K = index.shape
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         out = torch.empty((B, C, N2, K), dtype=input.dtype, device=input.device)
-        need = lib.tk3d_group_fwd_scratch_bytes(B, C, N1, N2, K, _dtype(input))
+        need = _lib.scratch_bytes("tk3d_group_fwd", B, C, N1, N2, K, _dtype(input))
         scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
         check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None,
                                  _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
@@ -143,9 +162,9 @@ def group_points_backward_cuda(grad_output, index, n1):
     lib = load()
     B, C, N2, K = grad_output.shape
     n1 = int(n1)
-    with torch.cuda.device(grad_output.device):
+    with _on(grad_output.device):
         gin = torch.empty((B, C, n1), dtype=grad_output.dtype, device=grad_output.device)
-        need = lib.tk3d_group_bwd_scratch_bytes(B, C, n1, N2, K, _dtype(grad_output))
+        need = _lib.scratch_bytes("tk3d_group_bwd", B, C, n1, N2, K, _dtype(grad_output))
         scratch = torch.empty((need,), dtype=torch.uint8, device=grad_output.device) if need else None
         check(lib.tk3d_group_bwd(_ptr(grad_output), _ptr(index), B, C, n1, N2, K, _ptr(gin), None,
                                  _ptr(scratch) if need else None, need, _dtype(grad_output), _stream(grad_output)))
@@ -173,9 +192,9 @@ def interpolate_forward_cuda(input, index, weight):
     lib = load()
     B, C, N1 = input.shape
     N2 = index.size(1)
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         out = torch.empty((B, C, N2), dtype=input.dtype, device=input.device)
-        need = lib.tk3d_interp_fwd_scratch_bytes(B, C, N1, N2, _dtype(input))
+        need = _lib.scratch_bytes("tk3d_interp_fwd", B, C, N1, N2, _dtype(input))
         scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
         check(lib.tk3d_interp_fwd(_ptr(input), _ptr(index), _ptr(weight), B, C, N1, N2, 3, _ptr(out), None,
                                   _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
@@ -189,9 +208,9 @@ def interpolate_backward_cuda(grad_output, index, weight, n1):
     lib = load()
     B, C, N2 = grad_output.shape
     n1 = int(n1)
-    with torch.cuda.device(grad_output.device):
+    with _on(grad_output.device):
         gin = torch.empty((B, C, n1), dtype=grad_output.dtype, device=grad_output.device)
-        need = lib.tk3d_interp_bwd_scratch_bytes(B, C, n1, N2, _dtype(grad_output))
+        need = _lib.scratch_bytes("tk3d_interp_bwd", B, C, n1, N2, _dtype(grad_output))
         scratch = torch.empty((need,), dtype=torch.uint8, device=grad_output.device) if need else None
         check(lib.tk3d_interp_bwd(_ptr(grad_output), _ptr(index), _ptr(weight), B, C, n1, N2, 3, _ptr(gin), None,
                                   _ptr(scratch) if need else None, need, _dtype(grad_output), _stream(grad_output)))
@@ -214,7 +233,7 @@ def knn_distance_cuda(query, key, k, version=0):
     _same_device_dtype(query, key, floats=(key,))
     lib = load()
     B, N1, N2 = query.size(0), query.size(1), key.size(1)
-    with torch.cuda.device(query.device):
+    with _on(query.device):
         distance = torch.empty((B, N1, k), dtype=query.dtype, device=query.device)
         index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
         check(lib.tk3d_knn(_ptr(query), _ptr(key), B, N1, N2, k, _ptr(distance), _ptr(index), _dtype(query),
@@ -238,7 +257,7 @@ def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None):
     lib = load()
     B, N1, N2 = xyz1.size(0), xyz1.size(1), xyz2.size(1)
     dev = xyz1.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         dist1 = torch.empty((B, N1), dtype=xyz1.dtype, device=dev)
         idx1 = torch.empty((B, N1), dtype=torch.int64, device=dev)
         dist2 = torch.empty((B, N2), dtype=xyz1.dtype, device=dev)
@@ -272,7 +291,7 @@ def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx
     _same_device_dtype(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, floats=(grad_dist2, xyz1, xyz2))
     lib = load()
     dev = grad_dist1.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         g1 = torch.empty((bs, n1, 3), dtype=grad_dist1.dtype, device=dev)
         g2 = torch.empty((bs, n2, 3), dtype=grad_dist1.dtype, device=dev)
         check(lib.tk3d_chamfer_bwd(_ptr(grad_dist1), _ptr(grad_dist2), _ptr(xyz1), _ptr(xyz2), _ptr(idx1),
@@ -286,7 +305,7 @@ def three_nn_weight_cuda(distance):
     _check_cuda_contig(distance=distance)
     lib = load()
     k = distance.size(-1)
-    with torch.cuda.device(distance.device):
+    with _on(distance.device):
         w = torch.empty_like(distance)
         check(lib.tk3d_three_nn_weight(_ptr(distance), distance.numel() // max(k, 1), k, _ptr(w), _dtype(distance),
                                        _stream(distance)))

@@ -7,7 +7,7 @@ and element-wise PyTorch expressions in ``torkit3d/layers/pointnet2.py`` and
 import torch
 
 from . import _lib
-from ._C import _check_cuda, _check_eq, _ptr, _stream
+from ._C import _check_cuda, _check_eq, _on, _ptr, _stream
 from ._lib import check, load
 
 
@@ -42,10 +42,10 @@ def fps_gather(points, num_samples, channel_first=True):
     else:
         raise RuntimeError("points must be float32 or float64.")
     lib = load()
-    with torch.cuda.device(points.device):
+    with _on(points.device):
         index = torch.empty((B, S), dtype=torch.int64, device=points.device)
         sampled = torch.empty((B, 3, S) if channel_first else (B, S, 3), dtype=points.dtype, device=points.device)
-        need = lib.tk3d_fps_scratch_bytes(B, N, dt)
+        need = _lib.scratch_bytes("tk3d_fps", B, N, dt)
         scratch = _scratch(need, points.device)
         check(lib.tk3d_fps_gather(_ptr(points), B, N, S, 1 if channel_first else 0, _ptr(index), _ptr(sampled),
                                   _ptr(scratch) if need else None, need, dt, _stream(points)))
@@ -76,10 +76,10 @@ def sa_group_forward(points, centroids, feature, radius, max_neighbors, use_xyz=
     K = int(max_neighbors)
     lib = load()
     dev = points.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         out = torch.empty((B, C + (3 if use_xyz else 0), M, K), dtype=torch.float32, device=dev)
         index32 = torch.empty((B, M, K), dtype=torch.int32, device=dev) if want_index else None
-        need = lib.tk3d_sa_group_scratch_bytes(B, C, N, M, K, _lib.F32)
+        need = _lib.scratch_bytes("tk3d_sa_group", B, C, N, M, K, _lib.F32)
         scratch = _scratch(need, dev)
         check(lib.tk3d_sa_group_fwd(_ptr(points), _ptr(centroids), _ptr(feature) if C else None, B, C, N, M,
                                     float(radius), K, 1 if channel_first else 0, 1 if use_xyz else 0, _ptr(out),
@@ -98,14 +98,14 @@ def sa_group_backward(grad_out, index32, C, N, use_xyz=True, channel_first=True,
     _check_eq(grad_out.size(1), C + (3 if use_xyz else 0), "grad_out channels")
     lib = load()
     dev = grad_out.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         gfeat = torch.empty((B, C, N), dtype=torch.float32, device=dev) if (need_feature and C) else None
         xyz = use_xyz and (need_points or need_centroids)
         gpts = torch.empty((B, 3, N) if channel_first else (B, N, 3), dtype=torch.float32, device=dev) \
             if (xyz and need_points) else None
         gcen = torch.empty((B, 3, M) if channel_first else (B, M, 3), dtype=torch.float32, device=dev) \
             if (xyz and need_centroids) else None
-        need = lib.tk3d_sa_group_scratch_bytes(B, C, N, M, K, _lib.F32) if gfeat is not None else 0
+        need = _lib.scratch_bytes("tk3d_sa_group", B, C, N, M, K, _lib.F32) if gfeat is not None else 0
         scratch = _scratch(need, dev)
         check(lib.tk3d_sa_group_bwd(_ptr(grad_out), _ptr(index32), B, C, N, M, K, 1 if channel_first else 0,
                                     1 if use_xyz else 0, _ptr(gfeat) if gfeat is not None else None,
@@ -129,11 +129,11 @@ def three_nn_interp_forward(query_xyz, key_xyz, key_feature, eps=1e-10, channel_
     C = key_feature.size(1)
     lib = load()
     dev = query_xyz.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         out = torch.empty((B, C, Nq), dtype=torch.float32, device=dev)
         index32 = torch.empty((B, Nq, 3), dtype=torch.int32, device=dev)
         weight = torch.empty((B, Nq, 3), dtype=torch.float32, device=dev)
-        need = lib.tk3d_three_nn_interp_scratch_bytes(B, C, Nq, Nk, _lib.F32)
+        need = _lib.scratch_bytes("tk3d_three_nn_interp", B, C, Nq, Nk, _lib.F32)
         scratch = _scratch(need, dev)
         check(lib.tk3d_three_nn_interp_fwd(_ptr(query_xyz), _ptr(key_xyz), _ptr(key_feature), B, C, Nq, Nk,
                                            1 if channel_first else 0, float(eps), _ptr(out), _ptr(index32),
@@ -150,9 +150,9 @@ def three_nn_interp_backward(grad_out, index32, weight, Nk):
     B, C, Nq = grad_out.shape
     lib = load()
     dev = grad_out.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         gfeat = torch.empty((B, C, Nk), dtype=torch.float32, device=dev)
-        need = lib.tk3d_three_nn_interp_scratch_bytes(B, C, Nq, Nk, _lib.F32)
+        need = _lib.scratch_bytes("tk3d_three_nn_interp", B, C, Nq, Nk, _lib.F32)
         scratch = _scratch(need, dev)
         check(lib.tk3d_three_nn_interp_bwd(_ptr(grad_out), _ptr(index32), _ptr(weight), B, C, Nq, Nk, _ptr(gfeat),
                                            None, _ptr(scratch) if need else None, need, _lib.F32,
@@ -181,9 +181,9 @@ def edge_feature_forward(query_feature, key_feature, index, include_query=True):
     dt = _dtype(query_feature)
     lib = load()
     dev = query_feature.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         out = torch.empty((B, 2 * C if include_query else C, N1, K), dtype=query_feature.dtype, device=dev)
-        need = lib.tk3d_edge_feature_scratch_bytes(B, C, N1, N2, K, dt)
+        need = _lib.scratch_bytes("tk3d_edge_feature", B, C, N1, N2, K, dt)
         scratch = _scratch(need, dev)
         check(lib.tk3d_edge_feature_fwd(_ptr(query_feature), _ptr(key_feature), _ptr(index), B, C, N1, N2, K,
                                         1 if include_query else 0, _ptr(out), None,
@@ -201,10 +201,10 @@ def edge_feature_backward(grad_out, index, C, N2, include_query=True, need_query
     dt = _dtype(grad_out)
     lib = load()
     dev = grad_out.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         gq = torch.empty((B, C, N1), dtype=grad_out.dtype, device=dev) if need_query else None
         gk = torch.empty((B, C, N2), dtype=grad_out.dtype, device=dev) if need_key else None
-        need = lib.tk3d_edge_feature_scratch_bytes(B, C, N1, N2, K, dt) if need_key else 0
+        need = _lib.scratch_bytes("tk3d_edge_feature", B, C, N1, N2, K, dt) if need_key else 0
         scratch = _scratch(need, dev)
         check(lib.tk3d_edge_feature_bwd(_ptr(grad_out), _ptr(index), B, C, N1, N2, K, 1 if include_query else 0,
                                         _ptr(gq) if need_query else None, _ptr(gk) if need_key else None, None,

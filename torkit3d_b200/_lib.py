@@ -89,3 +89,19 @@ def check(rc):
         lib = load()
         detail = lib.tk3d_last_error().decode()
         raise RuntimeError("tk3d: %s%s" % (lib.tk3d_strerror(rc).decode(), (": " + detail) if detail else ""))
+
+
+_scratch_cache = {}
+
+
+def scratch_bytes(name, *args):
+    """Result of the library's ``<name>_scratch_bytes(*args)`` query, memoised per argument tuple
+    (the answer depends on the shape only; repeated calls of one shape skip a foreign-function call)."""
+    key = (name,) + args
+    v = _scratch_cache.get(key)
+    if v is None:
+        if len(_scratch_cache) > 4096:
+            _scratch_cache.clear()
+        v = int(getattr(load(), name + "_scratch_bytes")(*args))
+        _scratch_cache[key] = v
+    return v

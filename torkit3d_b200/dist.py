@@ -65,10 +65,10 @@ class _ChamferLoss(torch.autograd.Function):
         ctx.backward_fn = backward_fn
         if fused:
             from . import _lib
-            from ._C import _dtype, _ptr, _stream
+            from ._C import _dtype, _on, _ptr, _stream
 
             loss = torch.empty((), dtype=a.dtype, device=a.device)
-            with torch.cuda.device(a.device):
+            with _on(a.device):
                 _lib.check(_lib.load().tk3d_chamfer_mean_loss(_ptr(sums), count1, count2, _ptr(loss), _dtype(a),
                                                               _stream(a)))
             return loss
@@ -82,11 +82,11 @@ class _ChamferLoss(torch.autograd.Function):
         if ctx.backward_fn is None:
             # one launch pair: the constant upstream gradients grad_loss/count are formed inside the kernels
             from . import _lib
-            from ._C import _dtype, _ptr, _stream
+            from ._C import _dtype, _on, _ptr, _stream
 
             gl = grad_loss.to(a.dtype).contiguous()
             ga, gb = torch.empty_like(a), torch.empty_like(b)
-            with torch.cuda.device(a.device):
+            with _on(a.device):
                 _lib.check(_lib.load().tk3d_chamfer_bwd_mean(_ptr(gl), c1, c2, _ptr(a), _ptr(b), _ptr(idx1), _ptr(idx2),
                                                              a.size(0), a.size(1), b.size(1), _ptr(ga), _ptr(gb),
                                                              _dtype(a), _stream(a)))
