@@ -50,7 +50,8 @@ def sa_expected(oracle, pts, cen, feat, radius, K, use_xyz):
 
 # ---- FPS + gather ------------------------------------------------------------------------------
 @pytest.mark.parametrize("n,s,dtype", [(1000, 100, torch.float32), (8192, 512, torch.float32),
-                                       (9000, 64, torch.float32), (700, 50, torch.float64)])
+                                       (9000, 64, torch.float32), (16384, 300, torch.float32), (16500, 40, torch.float32),
+                                       (700, 50, torch.float64)])
 @pytest.mark.parametrize("channel_first", [True, False])
 def test_fps_gather(oracle, n, s, dtype, channel_first):
     p = sphere(3, n, 11).to(dtype)

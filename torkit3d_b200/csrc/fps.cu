@@ -3,9 +3,11 @@
 // The algorithm is a chain of S-1 dependent steps per cloud (update every point's distance to the
 // selected set, pick the arg-max), so the design goal is latency per step, not bandwidth:
 //
-//  * fp32, N <= 8192 ("resident" kernel): one persistent CTA per cloud keeps every point and its
+//  * fp32, N <= 16384 ("resident" kernel): one persistent CTA per cloud keeps every point and its
 //    running minimum distance in REGISTERS for the whole call (up to 8 points per thread), plus a
 //    copy of the coordinates in shared memory from which the newly selected point is broadcast.
+//    Clouds of 8193 to 16384 points keep 16 running minima per thread in registers and read the
+//    coordinates from the shared-memory copy (192 KB at most) in every step.
 //    A step is: P exact distance updates per thread, a block-wide maximum of the running minima
 //    (REDUX, one shared-memory exchange, REDUX), and the lowest index holding that maximum.
 //    (A variant that spreads one cloud over a thread-block cluster of 2-8 CTAs, exchanging the
@@ -38,7 +40,9 @@ constexpr int FPS_MAX_THREADS = 1024;
 // their results differed in the last bit from the scalar round-to-nearest sequence for about one
 // distance in five (as a fused multiply-add would), even with explicit .rn and -fmad=false, and an
 // exactly tied pair of points in the benchmark data then picked the wrong winner.
-template <int P2>
+// REG = false (clouds of 8193 to 16384 points, 16 per thread): only the running minima stay in
+// registers, the coordinates are read from the shared-memory copy in every step.
+template <int P2, bool REG = true>
 __global__ void __launch_bounds__(FPS_MAX_THREADS)
 fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__restrict__ index, int ps, int cs,
                     float *__restrict__ sampled) {
@@ -62,18 +66,20 @@ fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__r
   __syncthreads();
 
   // Point (i, h) of this thread is j = (2*i + h) * T + tid: ascending in (i, h).
-  float2 px[P2], py[P2], pz[P2], md[P2];
+  float2 px[REG ? P2 : 1], py[REG ? P2 : 1], pz[REG ? P2 : 1], md[P2];
   const float qnan = __int_as_float(0x7fc00000), pinf = __int_as_float(0x7f800000);
 #pragma unroll
   for (int i = 0; i < P2; ++i) {
     const int j0 = (2 * i) * T + tid, j1 = (2 * i + 1) * T + tid;
-    px[i].x = j0 < N ? sxyz[3 * j0 + 0] : qnan;
-    py[i].x = j0 < N ? sxyz[3 * j0 + 1] : qnan;
-    pz[i].x = j0 < N ? sxyz[3 * j0 + 2] : qnan;
+    if (REG) {
+      px[i].x = j0 < N ? sxyz[3 * j0 + 0] : qnan;
+      py[i].x = j0 < N ? sxyz[3 * j0 + 1] : qnan;
+      pz[i].x = j0 < N ? sxyz[3 * j0 + 2] : qnan;
+      px[i].y = j1 < N ? sxyz[3 * j1 + 0] : qnan;
+      py[i].y = j1 < N ? sxyz[3 * j1 + 1] : qnan;
+      pz[i].y = j1 < N ? sxyz[3 * j1 + 2] : qnan;
+    }
     md[i].x = j0 < N ? pinf : 0.f;  // padding: distance 0, NaN coordinates keep it there
-    px[i].y = j1 < N ? sxyz[3 * j1 + 0] : qnan;
-    py[i].y = j1 < N ? sxyz[3 * j1 + 1] : qnan;
-    pz[i].y = j1 < N ? sxyz[3 * j1 + 2] : qnan;
     md[i].y = j1 < N ? pinf : 0.f;
   }
 
@@ -86,8 +92,15 @@ fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__r
 #pragma unroll
     for (int i = 0; i < P2; ++i) {
       float2 d;
-      d.x = sqdist<float>(px[i].x, py[i].x, pz[i].x, cx, cy, cz);
-      d.y = sqdist<float>(px[i].y, py[i].y, pz[i].y, cx, cy, cz);
+      if (REG) {
+        d.x = sqdist<float>(px[i].x, py[i].x, pz[i].x, cx, cy, cz);
+        d.y = sqdist<float>(px[i].y, py[i].y, pz[i].y, cx, cy, cz);
+      } else {
+        // beyond N the running minimum is 0 and stays 0 whatever is read (the index is clamped)
+        const int j0 = min((2 * i) * T + tid, N - 1), j1 = min((2 * i + 1) * T + tid, N - 1);
+        d.x = sqdist<float>(sxyz[3 * j0], sxyz[3 * j0 + 1], sxyz[3 * j0 + 2], cx, cy, cz);
+        d.y = sqdist<float>(sxyz[3 * j1], sxyz[3 * j1 + 1], sxyz[3 * j1 + 2], cx, cy, cz);
+      }
       md[i].x = fminf(md[i].x, d.x);
       md[i].y = fminf(md[i].y, d.y);
       bm = fmaxf(bm, fmaxf(md[i].x, md[i].y));
@@ -220,7 +233,7 @@ fps_streaming_kernel(const T *__restrict__ points, int64_t N, int64_t S, int64_t
   }
 }
 
-constexpr int64_t FPS_RESIDENT_MAX_N = 8192;
+constexpr int64_t FPS_RESIDENT_MAX_N = 16384;  // 3*N floats of shared memory: 192 KB
 
 int threads_for(int64_t N) {
   int t = 32;
@@ -255,7 +268,8 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
   const int64_t ps = channel_first ? 1 : 3, cs = channel_first ? N : 1;
   const size_t need = tk3d_fps_scratch_bytes(B, N, dtype);
   if (need == 0) {
-    // Up to 8 points per thread; at least 4 warps so that every SM sub-partition has work.
+    // Up to 8 points per thread in registers (16 with the coordinates left in shared memory); at
+    // least 4 warps so that every SM sub-partition has work.
     int threads = threads_for((N + 7) / 8);
     if (threads < 128) threads = 128;
     const int P = (int)((N + threads - 1) / threads);
@@ -269,7 +283,13 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
   }
     if (P <= 2) TK3D_FPS_CASE(1)
     else if (P <= 4) TK3D_FPS_CASE(2)
-    else TK3D_FPS_CASE(4)
+    else if (P <= 8) TK3D_FPS_CASE(4)
+    else {  // 8193..16384 points: 16 per thread, coordinates stay in shared memory (up to 192 KB)
+      TK3D_CUDA(cudaFuncSetAttribute(fps_resident_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(FPS_RESIDENT_MAX_N * 12)));
+      fps_resident_kernel<8, false><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,
+                                                                        (float *)sampled);
+    }
 #undef TK3D_FPS_CASE
     return check_launch("fps_resident_kernel");
   }
