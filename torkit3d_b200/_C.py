@@ -60,7 +60,14 @@ def _index(t, name):
         raise RuntimeError("%s must be an int64 tensor." % name)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t):
+    """Handle of the current CUDA stream of the tensor's device (the raw getter avoids building a
+    torch.cuda.Stream object per call)."""
+    if _raw_stream is not None and t.device.index is not None:
+        return _raw_stream(t.device.index)
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
@@ -81,6 +88,11 @@ def _on(device):
     if device.index is None or device.index == torch.cuda.current_device():
         return _NO_SWITCH
     return torch.cuda.device(device)
+
+
+# Below this output size the forward gathers run without the transposed scratch copy: one launch
+# instead of two (measured on B200: 16 MB of grouped output 0.039 ms with it, 0.020 ms without).
+_ROWS_MIN_OUTPUT_BYTES = 48 << 20
 
 
 def _ptr(t):
@@ -142,7 +154,9 @@ def group_points_forward_cuda(input, index):
     _, N2, K = index.shape
     with _on(input.device):
         out = torch.empty((B, C, N2, K), dtype=input.dtype, device=input.device)
-        need = _lib.scratch_bytes("tk3d_group_fwd", B, C, N1, N2, K, _dtype(input))
+        # the row-gather path (transpose into scratch, then gather) pays from about 48 MB of output on
+        big = out.numel() * out.element_size() >= _ROWS_MIN_OUTPUT_BYTES
+        need = _lib.scratch_bytes("tk3d_group_fwd", B, C, N1, N2, K, _dtype(input)) if big else 0
         scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
         check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None,
                                  _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
@@ -194,7 +208,8 @@ def interpolate_forward_cuda(input, index, weight):
     N2 = index.size(1)
     with _on(input.device):
         out = torch.empty((B, C, N2), dtype=input.dtype, device=input.device)
-        need = _lib.scratch_bytes("tk3d_interp_fwd", B, C, N1, N2, _dtype(input))
+        big = out.numel() * out.element_size() >= _ROWS_MIN_OUTPUT_BYTES
+        need = _lib.scratch_bytes("tk3d_interp_fwd", B, C, N1, N2, _dtype(input)) if big else 0
         scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
         check(lib.tk3d_interp_fwd(_ptr(input), _ptr(index), _ptr(weight), B, C, N1, N2, 3, _ptr(out), None,
                                   _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
