@@ -671,11 +671,30 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
 }
 
 // ---------------------------------------------------------------------------------------------
+// Generic kernel (any floating type, any k): one query per thread, exact distances, key tiles in
+// shared memory.  The k best so far are kept UNSORTED in the query's output row together with the
+// position of their largest element (by distance, then index) in registers: a key enters only if it
+// beats that element, overwrites it, and the row is rescanned for the new largest (k reads, no
+// shifting).  Keys arrive in ascending index order, so among equal distances the earlier index is
+// already in the row and "d < largest" is the whole acceptance test.  Each row is sorted by
+// (distance, index) at the end.
+// (v, jv) orders after (m, jm): by distance, then index; a NaN distance orders after every number.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ bool knn_larger(T v, int64_t jv, T m, int64_t jm) {
+  const bool vn = !(v == v), mn = !(m == m);
+  if (vn != mn) return vn;
+  if (vn) return jv > jm;
+  return v > m || (v == m && jv > jm);
+}
+
+// Blocks of 64 threads: the per-query work is long and serial, so many small blocks keep every SM
+// busy even for a few thousand queries.
+constexpr int KG_THREADS = 64;
+template <typename T>
+__global__ void __launch_bounds__(KG_THREADS)
 knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
                    int64_t k, T *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
-  constexpr int TILE = 256;
+  constexpr int TILE = KG_THREADS;
   __shared__ T sx[TILE], sy[TILE], sz[TILE];
   const int tid = threadIdx.x;
   const int64_t chunks = (N1 + TILE - 1) / TILE;
@@ -692,8 +711,8 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
     }
     T *od = dist + (b * N1 + (valid ? i : 0)) * k;
     int64_t *oi = index + (b * N1 + (valid ? i : 0)) * k;
-    int64_t cnt = 0;
-    T last = Exact<T>::inf();
+    int64_t cnt = 0, maxpos = 0, maxj = -1;
+    T maxd = -Exact<T>::inf();
     const T *rb = key + b * N2 * 3;
     for (int64_t t0 = 0; t0 < N2; t0 += TILE) {
       const int64_t jl = t0 + tid;
@@ -707,20 +726,68 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
       if (valid) {
         for (int u = 0; u < lim; ++u) {
           const T d = sqdist<T>(sx[u], sy[u], sz[u], qx, qy, qz);
-          if (cnt == k && !(d < last)) continue;
-          int64_t pos = cnt < k ? cnt : k - 1;
-          while (pos > 0 && d < od[pos - 1]) {
-            od[pos] = od[pos - 1];
-            oi[pos] = oi[pos - 1];
-            --pos;
+          const int64_t j = t0 + u;
+          if (cnt < k) {  // filling: append, remember the largest
+            od[cnt] = d;
+            oi[cnt] = j;
+            if (cnt == 0 || knn_larger<T>(d, j, maxd, maxj)) {
+              maxd = d;
+              maxj = j;
+              maxpos = cnt;
+            }
+            ++cnt;
+          } else if (d < maxd) {  // false when either is NaN: a NaN among the first k keys stays
+            od[maxpos] = d;
+            oi[maxpos] = j;
+            // Rescan for the new largest element.  The distances are loaded eight at a time before
+            // any compare, so that the loads of a batch are in flight together (with one or two
+            // warps per SM sub-partition this loop is bound by load latency); the index of an
+            // element is read only when its distance ties or beats the running maximum.
+            const int kk = (int)k;
+            maxd = od[0];
+            maxj = oi[0];
+            maxpos = 0;
+            auto consider = [&](T v, int c) {
+              if (v >= maxd) {
+                const int64_t jv = oi[c];
+                if (v > maxd || jv > maxj) {
+                  maxd = v;
+                  maxj = jv;
+                  maxpos = c;
+                }
+              }
+            };
+            int c = 1;
+            for (; c + 8 <= kk; c += 8) {
+              T v[8];
+#pragma unroll
+              for (int w = 0; w < 8; ++w) v[w] = od[c + w];
+#pragma unroll
+              for (int w = 0; w < 8; ++w) consider(v[w], c + w);
+            }
+            for (; c < kk; ++c) consider(od[c], c);
           }
-          od[pos] = d;
-          oi[pos] = t0 + u;
-          if (cnt < k) ++cnt;
-          if (cnt == k) last = od[k - 1];
         }
       }
       __syncthreads();
+    }
+    if (valid) {
+      // insertion sort of the row by (distance, index)
+      for (int64_t c = 1; c < cnt; ++c) {
+        const T d = od[c];
+        const int64_t j = oi[c];
+        int64_t pos = c;
+        while (pos > 0) {
+          const T dp = od[pos - 1];
+          const int64_t jp = oi[pos - 1];
+          if (!knn_larger<T>(dp, jp, d, j)) break;
+          od[pos] = dp;
+          oi[pos] = jp;
+          --pos;
+        }
+        od[pos] = d;
+        oi[pos] = j;
+      }
     }
   }
 }
@@ -728,11 +795,11 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
 template <typename T>
 int knn_generic(const T *query, const T *key, int64_t B, int64_t N1, int64_t N2, int64_t k, T *dist,
                 int64_t *index, cudaStream_t st) {
-  const int64_t total = B * ((N1 + 255) / 256);
+  const int64_t total = B * ((N1 + KG_THREADS - 1) / KG_THREADS);
   if (total == 0) return TK3D_OK;
-  const int64_t cap = (int64_t)sm_count() * 64;
-  knn_generic_kernel<T><<<(unsigned)(total < cap ? total : cap), 256, 0, st>>>(query, key, B, N1, N2, k, dist, index,
-                                                                              total);
+  const int64_t cap = (int64_t)sm_count() * 256;
+  knn_generic_kernel<T><<<(unsigned)(total < cap ? total : cap), KG_THREADS, 0, st>>>(query, key, B, N1, N2, k, dist,
+                                                                                     index, total);
   return check_launch("knn_generic_kernel");
 }
 
