@@ -672,12 +672,11 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
 
 // ---------------------------------------------------------------------------------------------
 // Generic kernel (any floating type, any k): one query per thread, exact distances, key tiles in
-// shared memory.  The k best so far are kept UNSORTED in the query's output row together with the
-// position of their largest element (by distance, then index) in registers: a key enters only if it
-// beats that element, overwrites it, and the row is rescanned for the new largest (k reads, no
-// shifting).  Keys arrive in ascending index order, so among equal distances the earlier index is
-// already in the row and "d < largest" is the whole acceptance test.  Each row is sorted by
-// (distance, index) at the end.
+// shared memory.  The k best so far live in the query's output row as a binary MAX-HEAP ordered by
+// (distance, index): the root is the current k-th neighbour, a key enters only if it beats the root
+// (keys arrive in ascending index order, so "d < root distance" is the whole test), replaces it and
+// sifts down in O(log k) steps -- the reference rescans all k entries for every accepted key.  At
+// the end the heap is turned into an ascending row by heap sort.
 // (v, jv) orders after (m, jm): by distance, then index; a NaN distance orders after every number.
 template <typename T>
 __device__ __forceinline__ bool knn_larger(T v, int64_t jv, T m, int64_t jm) {
@@ -685,6 +684,33 @@ __device__ __forceinline__ bool knn_larger(T v, int64_t jv, T m, int64_t jm) {
   if (vn != mn) return vn;
   if (vn) return jv > jm;
   return v > m || (v == m && jv > jm);
+}
+
+// Sift (d, j) down from the root of the max-heap od/oi[0, n).
+template <typename T>
+__device__ __forceinline__ void knn_sift_down(T *__restrict__ od, int64_t *__restrict__ oi, int64_t n, T d, int64_t j) {
+  int64_t pos = 0;
+  while (true) {
+    int64_t child = 2 * pos + 1;
+    if (child >= n) break;
+    T dc = od[child];
+    int64_t jc = oi[child];
+    if (child + 1 < n) {
+      const T dr = od[child + 1];
+      const int64_t jr = oi[child + 1];
+      if (knn_larger<T>(dr, jr, dc, jc)) {
+        ++child;
+        dc = dr;
+        jc = jr;
+      }
+    }
+    if (!knn_larger<T>(dc, jc, d, j)) break;
+    od[pos] = dc;
+    oi[pos] = jc;
+    pos = child;
+  }
+  od[pos] = d;
+  oi[pos] = j;
 }
 
 // Blocks of 64 threads: the per-query work is long and serial, so many small blocks keep every SM
@@ -695,8 +721,15 @@ __global__ void __launch_bounds__(KG_THREADS)
 knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
                    int64_t k, T *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
   constexpr int TILE = KG_THREADS;
+  static_assert((TILE & (TILE - 1)) == 0 && TILE % 8 == 0, "tile indices are masked; batches of eight");
   __shared__ T sx[TILE], sy[TILE], sz[TILE];
   const int tid = threadIdx.x;
+  if (blockIdx.x < blocks_total) {  // defined contents for the slots a short first tile leaves unwritten
+    sx[tid] = 0;
+    sy[tid] = 0;
+    sz[tid] = 0;
+  }
+  __syncthreads();
   const int64_t chunks = (N1 + TILE - 1) / TILE;
   for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
     const int64_t b = blk / chunks;
@@ -711,8 +744,8 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
     }
     T *od = dist + (b * N1 + (valid ? i : 0)) * k;
     int64_t *oi = index + (b * N1 + (valid ? i : 0)) * k;
-    int64_t cnt = 0, maxpos = 0, maxj = -1;
-    T maxd = -Exact<T>::inf();
+    int64_t cnt = 0;
+    T root = Exact<T>::inf();  // distance at the heap's root once the heap is full
     const T *rb = key + b * N2 * 3;
     for (int64_t t0 = 0; t0 < N2; t0 += TILE) {
       const int64_t jl = t0 + tid;
@@ -724,69 +757,51 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
       __syncthreads();
       const int lim = (int)((N2 - t0) < TILE ? (N2 - t0) : TILE);
       if (valid) {
-        for (int u = 0; u < lim; ++u) {
-          const T d = sqdist<T>(sx[u], sy[u], sz[u], qx, qy, qz);
-          const int64_t j = t0 + u;
-          if (cnt < k) {  // filling: append, remember the largest
-            od[cnt] = d;
-            oi[cnt] = j;
-            if (cnt == 0 || knn_larger<T>(d, j, maxd, maxj)) {
-              maxd = d;
-              maxj = j;
-              maxpos = cnt;
-            }
-            ++cnt;
-          } else if (d < maxd) {  // false when either is NaN: a NaN among the first k keys stays
-            od[maxpos] = d;
-            oi[maxpos] = j;
-            // Rescan for the new largest element.  The distances are loaded eight at a time before
-            // any compare, so that the loads of a batch are in flight together (with one or two
-            // warps per SM sub-partition this loop is bound by load latency); the index of an
-            // element is read only when its distance ties or beats the running maximum.
-            const int kk = (int)k;
-            maxd = od[0];
-            maxj = oi[0];
-            maxpos = 0;
-            auto consider = [&](T v, int c) {
-              if (v >= maxd) {
-                const int64_t jv = oi[c];
-                if (v > maxd || jv > maxj) {
-                  maxd = v;
-                  maxj = jv;
-                  maxpos = c;
-                }
+        // Eight distances at a time: with one or two warps per SM sub-partition the loop is bound
+        // by the latency of the dependent arithmetic, which independent chains hide.  (Slots beyond
+        // lim hold stale coordinates; their distances are computed and ignored.)
+        for (int u0 = 0; u0 < lim; u0 += 8) {
+          T dd[8];
+#pragma unroll
+          for (int w = 0; w < 8; ++w) dd[w] = sqdist<T>(sx[(u0 + w) & (TILE - 1)], sy[(u0 + w) & (TILE - 1)],
+                                                        sz[(u0 + w) & (TILE - 1)], qx, qy, qz);
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            const T d = dd[w];
+            const int64_t j = t0 + u0 + w;
+            if (u0 + w >= lim) break;
+            if (cnt < k) {
+              // filling: sift the new element UP from the end of the heap
+              int64_t pos = cnt++;
+              while (pos > 0) {
+                const int64_t par = (pos - 1) >> 1;
+                const T dp = od[par];
+                const int64_t jp = oi[par];
+                if (!knn_larger<T>(d, j, dp, jp)) break;
+                od[pos] = dp;
+                oi[pos] = jp;
+                pos = par;
               }
-            };
-            int c = 1;
-            for (; c + 8 <= kk; c += 8) {
-              T v[8];
-#pragma unroll
-              for (int w = 0; w < 8; ++w) v[w] = od[c + w];
-#pragma unroll
-              for (int w = 0; w < 8; ++w) consider(v[w], c + w);
+              od[pos] = d;
+              oi[pos] = j;
+              if (cnt == k) root = od[0];
+            } else if (d < root) {  // false when either is NaN
+              knn_sift_down<T>(od, oi, k, d, j);
+              root = od[0];
             }
-            for (; c < kk; ++c) consider(od[c], c);
           }
         }
       }
       __syncthreads();
     }
     if (valid) {
-      // insertion sort of the row by (distance, index)
-      for (int64_t c = 1; c < cnt; ++c) {
-        const T d = od[c];
-        const int64_t j = oi[c];
-        int64_t pos = c;
-        while (pos > 0) {
-          const T dp = od[pos - 1];
-          const int64_t jp = oi[pos - 1];
-          if (!knn_larger<T>(dp, jp, d, j)) break;
-          od[pos] = dp;
-          oi[pos] = jp;
-          --pos;
-        }
-        od[pos] = d;
-        oi[pos] = j;
+      // heap sort: move the largest to the end, restore the heap on the shorter prefix
+      for (int64_t end = cnt - 1; end > 0; --end) {
+        const T dl = od[end];
+        const int64_t jl2 = oi[end];
+        od[end] = od[0];
+        oi[end] = oi[0];
+        knn_sift_down<T>(od, oi, end, dl, jl2);
       }
     }
   }
