@@ -4,7 +4,7 @@
 //   knn_small_kernel<K,Q>  fp32, k <= 4: per-thread top-K in registers, filter-then-verify sweep
 //                          (sweep.cuh), insertion straight from the verify branch.  With k << N2
 //                          the branch is rare (about k ln(N2/k) times per query).
-//   knn_twopass_kernel     fp32, 4 < k <= 128 (and N2 >= 32 k): pass 1 bounds the k-th distance from
+//   knn_twopass_kernel     fp32, 4 < k <= 128 (and N2 >= 4 k, at least 256): pass 1 bounds the k-th distance from
 //                          class minima of the filter value, pass 2 collects the few candidates
 //                          below the bound, exact selection among them (see the kernel's header).
 //   knn_buffered_kernel<Q> fp32, other k <= 128 (small key clouds): same filter, but passing keys are only appended
@@ -17,6 +17,8 @@
 //                          directly in the output rows.
 // All of them take decisions on the exactly rounded distance and scan keys in ascending order with
 // strict comparisons, so the retained set and its order are reproducible bit for bit.
+#include <stdlib.h>
+
 #include "sweep.cuh"
 
 namespace tk3d {
@@ -924,8 +926,9 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
     case 4: return knn_small_q<4>(q, r, B, (int)N1, (int)N2, d, index, st);
     default: break;
   }
-  // Two-pass selection needs at least two key classes per wanted neighbour to be tight.
-  if (k <= 128 && N2 >= 32 * k) {
+  // Two-pass selection needs at least two key classes per wanted neighbour to be tight (the class
+  // counts below) and a few keys in every class: N2 >= 4 k, at least 256 (512 for k > 64).
+  if (k <= 128 && N2 >= 4 * k && N2 >= (k > 64 ? 512 : 256)) {
     if (k <= 16) {
       if (B * N1 >= (int64_t)sm_count() * 4 * 64)
         return knn_twopass<2, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
