@@ -137,8 +137,8 @@ int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t num_samples, int6
  * stream capture.  All calls on one device share the one array: two calls whose kernels can run
  * at the same time on that device (different streams, or different host threads) corrupt each
  * other -- order them on one stream or with events.  Nothing needs clearing between calls.
- * Every size runs the streaming kernel; for fp32 clouds of at most 16384 points tk3d_fps needs no
- * scratch at all (pass NULL) and is faster.
+ * Every size runs the streaming kernel; for fp32 clouds of at most 16384 points (fp64: 8192) tk3d_fps
+ * needs no scratch at all (pass NULL) and is faster.
  */
 size_t tk3d_fps_static_scratch_capacity(void);
 int tk3d_fps_static_scratch(const void *points, int64_t B, int64_t N, int64_t num_samples, int64_t *index,

@@ -57,7 +57,8 @@ def test_argument_errors_need_no_gpu(lib):
     assert lib.tk3d_fps(fake, 1, 100000, 9, fake, None, 0, F32, None) == 6       # scratch required
     assert lib.tk3d_fps_scratch_bytes(4, 16384, F32) == 0
     assert lib.tk3d_fps_scratch_bytes(4, 16385, F32) == 4 * 16385 * 4
-    assert lib.tk3d_fps_scratch_bytes(4, 100, 1) == 4 * 100 * 8
+    assert lib.tk3d_fps_scratch_bytes(4, 8192, 1) == 0            # fp64 clouds up to 8192 points are resident too
+    assert lib.tk3d_fps_scratch_bytes(4, 8193, 1) == 4 * 8193 * 8
     assert lib.tk3d_ball_query(fake, fake, 1, 8, 8, 0.1, 0, fake, F32, None) == 3
     assert lib.tk3d_interp_fwd(fake, fake, fake, 1, 1, 8, 8, 4, fake, None, None, 0, F32, None) == 3  # k != 3
     assert lib.tk3d_chamfer_fwd(None, fake, 1, 8, 8, fake, fake, fake, fake, None, F32, None) == 1

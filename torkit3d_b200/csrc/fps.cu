@@ -14,8 +14,10 @@
 //    per-warp candidates through distributed shared memory with one cluster barrier per step, was
 //    measured slower on B200 -- 1.07 ms against 0.88 ms for 32 clouds of 8192 points -- because
 //    the cluster barrier costs more per step than the divided arithmetic saves.)
-//  * any other case ("streaming" kernel, also fp64): points are re-read from global memory (L1/L2
-//    resident) and the running minimum lives in a caller-provided global scratch array.
+//  * fp64, N <= 8192: the same persistent structure with the coordinates in shared memory and up to
+//    8 running minima per thread; the block maximum is taken on the 64-bit pattern in two REDUX steps.
+//  * any other case ("streaming" kernel): points are re-read from global memory (L1/L2 resident)
+//    and the running minimum lives in a caller-provided global scratch array.
 //
 // Arg-max rule: highest running minimum distance, lowest index among exact ties.  Distances are
 // non-negative, so their IEEE bit patterns order like unsigned integers and the pair
@@ -145,6 +147,93 @@ fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__r
   }
 }
 
+// ---- resident kernel, fp64 ------------------------------------------------------------------------
+// Same structure for double precision clouds of up to 8192 points: coordinates in shared memory
+// (24 bytes per point), up to 8 running minima per thread in registers.  Distances are
+// non-negative, so their bit patterns order like unsigned 64-bit integers; a warp takes the maximum
+// of the high words, then of the low words among the lanes that hold that high word.
+constexpr int64_t FPS_RESIDENT64_MAX_N = 8192;
+
+__device__ __forceinline__ unsigned long long fps_warp_max64(unsigned long long v) {
+  const unsigned hi = (unsigned)(v >> 32), lo = (unsigned)v;
+  const unsigned whi = __reduce_max_sync(0xffffffffu, hi);
+  const unsigned wlo = __reduce_max_sync(0xffffffffu, hi == whi ? lo : 0u);
+  return ((unsigned long long)whi << 32) | wlo;
+}
+
+template <int P>
+__global__ void __launch_bounds__(FPS_MAX_THREADS)
+fps_resident64_kernel(const double *__restrict__ points, int N, int S, int64_t *__restrict__ index, int ps, int cs,
+                      double *__restrict__ sampled) {
+  extern __shared__ double dxyz[];  // [3*N] copy of the cloud
+  __shared__ unsigned long long slots64[2][32];
+  __shared__ int s_idx[2];
+  const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
+  const double *pts = points + (int64_t)blockIdx.x * N * 3;
+  int64_t *out = index + (int64_t)blockIdx.x * S;
+  if (cs == 1) {
+    for (int e = tid; e < 3 * N; e += T) dxyz[e] = pts[e];
+  } else {
+    for (int e = tid; e < 3 * N; e += T) {
+      const int d = e / N, j = e - d * N;
+      dxyz[3 * j + d] = pts[e];
+    }
+  }
+  if (tid < 2) s_idx[tid] = 0x7fffffff;
+  __syncthreads();
+
+  // Point i of this thread is j = i * T + tid; beyond N the running minimum is 0 and stays 0.
+  double md[P];
+#pragma unroll
+  for (int i = 0; i < P; ++i) md[i] = (i * T + tid) < N ? Exact<double>::inf() : 0.0;
+
+  int cur = 0;
+  if (tid == 0) out[0] = 0;
+  for (int it = 1; it < S; ++it) {
+    const int par = it & 1;
+    const double cx = dxyz[3 * cur + 0], cy = dxyz[3 * cur + 1], cz = dxyz[3 * cur + 2];
+    double bm = 0.0;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const int j = min(i * T + tid, N - 1);
+      const double d = sqdist<double>(dxyz[3 * j], dxyz[3 * j + 1], dxyz[3 * j + 2], cx, cy, cz);
+      md[i] = fmin(md[i], d);
+      bm = fmax(bm, md[i]);
+    }
+    const unsigned long long bits = (unsigned long long)__double_as_longlong(bm);
+    unsigned long long gb = fps_warp_max64(bits);
+    if (nwarps > 1) {
+      if (lane == 0) slots64[par][warp] = gb;
+      __syncthreads();
+      gb = fps_warp_max64(lane < nwarps ? slots64[par][lane] : 0ull);
+    }
+    if (nwarps > 1 && tid == 0) s_idx[par ^ 1] = 0x7fffffff;
+    if (bits == gb) {
+      int mine = 0x7fffffff;
+#pragma unroll
+      for (int i = P - 1; i >= 0; --i)
+        if (md[i] == bm) mine = i * T + tid;
+      atomicMin(&s_idx[par], mine);
+    }
+    __syncthreads();
+    cur = s_idx[par];
+    if (nwarps == 1) {
+      __syncwarp();
+      if (tid == 0) s_idx[par ^ 1] = 0x7fffffff;
+    }
+    if (tid == 0) out[it] = cur;
+  }
+  if (sampled != nullptr) {
+    __syncthreads();
+    double *sm = sampled + (int64_t)blockIdx.x * S * 3;
+    const int sps = cs == 1 ? 3 : 1, scs = cs == 1 ? 1 : S;
+    for (int e = tid; e < 3 * S; e += T) {
+      const int s = e / 3, d = e - 3 * s;
+      sm[s * sps + d * scs] = dxyz[3 * (int)out[s] + d];
+    }
+  }
+}
+
 // ---- streaming kernel (any type, any N) ------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ unsigned long long dist_key(T v);
@@ -250,6 +339,7 @@ using namespace tk3d;
 extern "C" size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype) {
   if (B <= 0 || N <= 0) return 0;
   if (dtype == TK3D_F32 && N <= FPS_RESIDENT_MAX_N) return 0;
+  if (dtype == TK3D_F64 && N <= FPS_RESIDENT64_MAX_N) return 0;
   return (size_t)B * (size_t)N * (dtype == TK3D_F64 ? 8 : 4);
 }
 
@@ -267,6 +357,26 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t ps = channel_first ? 1 : 3, cs = channel_first ? N : 1;
   const size_t need = tk3d_fps_scratch_bytes(B, N, dtype);
+  if (need == 0 && dtype == TK3D_F64) {
+    int threads = threads_for((N + 7) / 8);
+    if (threads < 128) threads = 128;
+    const int P = (int)((N + threads - 1) / threads);
+    const size_t smem = (size_t)N * 24;
+    const double *p = (const double *)points;
+#define TK3D_FPS64_CASE(PP)                                                                                          \
+  {                                                                                                                  \
+    TK3D_CUDA(cudaFuncSetAttribute(fps_resident64_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                   (int)(FPS_RESIDENT64_MAX_N * 24)));                                               \
+    fps_resident64_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,        \
+                                                                  (double *)sampled);                                \
+  }
+    if (P <= 1) TK3D_FPS64_CASE(1)
+    else if (P <= 2) TK3D_FPS64_CASE(2)
+    else if (P <= 4) TK3D_FPS64_CASE(4)
+    else TK3D_FPS64_CASE(8)
+#undef TK3D_FPS64_CASE
+    return check_launch("fps_resident64_kernel");
+  }
   if (need == 0) {
     // Up to 8 points per thread in registers (16 with the coordinates left in shared memory); at
     // least 4 warps so that every SM sub-partition has work.
