@@ -402,7 +402,8 @@ def run_b200(args, rank, world, local_rank):
     peak = measure_fp32_peak(lib, dev)
     nominal = 148 * 128 * 2 * 1.965e9 / 1e12
     achieved = pairs_local * PAIR_FLOP / (fwd_ms * 1e-3) / 1e12
-    roofline = {"bound": "fp32", "kernel": "chamfer_fwd_fast_kernel", "achieved": achieved,
+    fwd_kernel = lib.tk3d_chamfer_fwd_kernel_name(Bl, C4["N"], C4["M"], 0).decode()
+    roofline = {"bound": "fp32", "kernel": fwd_kernel, "achieved": achieved,
                 "peak": peak if peak else nominal, "peak_source": "measured live (dependent FFMA chains)" if peak
                 else "nominal 148 SM x 128 lanes x 2 x 1.965 GHz", "unit": "TFLOP/s",
                 "frac": achieved / (peak if peak else nominal), "nominal_peak": nominal,
@@ -492,7 +493,7 @@ def run_b200(args, rank, world, local_rank):
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": workload_config(world, world), "clocks": clocks, "e2e": e2e, "gpu_launches": 4,
-                "gpu_launches_detail": "per step: chamfer_fwd_fast_kernel, chamfer_mean_loss_kernel, chamfer_bwd_own_kernel, chamfer_bwd_scatter_kernel",
+                "gpu_launches_detail": "per step: %s, chamfer_mean_loss_kernel, chamfer_bwd_own_kernel, chamfer_bwd_scatter_kernel" % roofline["kernel"],
                 "roofline": roofline, "roofline_backward": bwd, "cpu_baseline": cpu, "extras": ext}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -332,6 +332,16 @@ int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index, int64_t B,
  */
 int tk3d_diag_ffma(int64_t iters, float *sink, double *flop, void *stream);
 
+/*
+ * Diagnostic with no counterpart in the reference: the name of the kernel that tk3d_chamfer_fwd
+ * launches for these sizes on the current device (a static string; launches nothing).  The fp32
+ * forward has three: "chamfer_fwd_fast_kernel<1>" (small inputs, one query per thread),
+ * "chamfer_fwd_smwide_kernel" (one 896-thread block per SM, for one or two nearly full rounds of
+ * 256-query tasks) and "chamfer_fwd_fast_kernel<2>" (everything larger); fp64 has
+ * "chamfer_fwd_generic_kernel".  Profilers and benchmarks use it to label their figures.
+ */
+const char *tk3d_chamfer_fwd_kernel_name(int64_t B, int64_t N1, int64_t N2, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

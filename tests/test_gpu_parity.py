@@ -50,6 +50,36 @@ def test_chamfer_forward_bit_exact(oracle, B, n1, n2, dtype):
     np.testing.assert_array_equal(d2, e2)
 
 
+# At least 148 * 512 queries but no more than two rounds of 256-query tasks per SM: the launcher
+# runs these as one 896-thread block per SM (seven independent 128-thread groups).
+SM_WIDE_SHAPES = [(3, 20001, 9999), (1, 100000, 3), (2, 70000, 0), (8, 16384, 16384), (16, 4097, 5003),
+                  (5, 16000, 30000)]
+
+
+@pytest.mark.parametrize("B,n1,n2", SM_WIDE_SHAPES)
+def test_chamfer_forward_sm_wide_path_bit_exact(oracle, B, n1, n2):
+    from torkit3d_b200 import _C
+
+    rng = np.random.default_rng(B * 7 + n2)
+    if B == 8:   # one rank's share of the 8-GPU benchmark batch, checked on two of its clouds
+        from torkit3d_b200 import workloads
+        a, b = [t.numpy() for t in workloads.c4_chamfer_large(B=8)]
+        check = [2, 7]
+    else:        # coarse lattice: plenty of exactly tied distances
+        a = (rng.integers(-40, 41, size=(B, n1, 3)) / 16).astype(np.float32)
+        b = (rng.integers(-40, 41, size=(B, n2, 3)) / 16).astype(np.float32)
+        check = list(range(B))
+    sums = torch.zeros(2, dtype=torch.float64, device="cuda")
+    d1, i1, d2, i2 = [N(t) for t in _C.chamfer_distance_forward_cuda(T(a), T(b), sums=sums)]
+    e1, j1, e2, j2 = oracle.chamfer_fwd(a[check], b[check])
+    np.testing.assert_array_equal(i1[check], j1)
+    np.testing.assert_array_equal(i2[check], j2)
+    np.testing.assert_array_equal(d1[check], e1)
+    np.testing.assert_array_equal(d2[check], e2)
+    if n2 > 0:
+        np.testing.assert_allclose(N(sums), [d1.sum(dtype=np.float64), d2.sum(dtype=np.float64)], rtol=1e-12)
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_chamfer_ties_go_to_lowest_index(oracle, dtype):
     from torkit3d_b200.ops import nn_distance

@@ -238,6 +238,15 @@ extern "C" int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, doubl
                                1.0 / count1, 1.0 / count2);
 }
 
+namespace tk3d {
+const char *chamfer_fwd_f32_kernel_name(int64_t B, int64_t N1, int64_t N2);
+}
+
+extern "C" const char *tk3d_chamfer_fwd_kernel_name(int64_t B, int64_t N1, int64_t N2, int dtype) {
+  if (dtype != TK3D_F32) return "chamfer_fwd_generic_kernel";
+  return chamfer_fwd_f32_kernel_name(B < 0 ? 0 : B, N1 < 0 ? 0 : N1, N2 < 0 ? 0 : N2);
+}
+
 extern "C" int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, void *dist1,
                                 int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype, void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_fwd: dtype %d", dtype);

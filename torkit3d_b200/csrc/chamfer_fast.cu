@@ -23,6 +23,43 @@ namespace {
 
 constexpr int CF_TILE = 512;
 
+// Barrier of one 128-thread group of a larger block (named barrier 1 + group).
+__device__ __forceinline__ void group_barrier(int grp) {
+  asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");
+}
+
+// Verify path of one filter group (8 / Q keys starting at tile slot u0, global index t0 + u0):
+// recompute the exact distance of every (key, query) pair whose filter value passed and update the
+// running minimum in ascending key order with a strict "<".  With two queries per thread, m[s] is
+// the smallest filter value of query s over the group, and a query none of whose values passes is
+// skipped as a whole.  No bounds test: padding keys carry a filter value of +inf, which no
+// threshold admits.
+template <int Q>
+__device__ __forceinline__ void chamfer_verify(const float4 *tl, int u0, int t0, const float2 (&a)[4],
+                                               const float (&m)[2], const float (&qx)[Q], const float (&qy)[Q],
+                                               const float (&qz)[Q], float (&thr)[Q], float (&best)[Q],
+                                               int (&arg)[Q]) {
+  constexpr int GK = 8 / Q;
+#pragma unroll
+  for (int s = 0; s < Q; ++s) {
+    if (Q != 2 || !(m[s] >= thr[s])) {
+#pragma unroll
+      for (int k = 0; k < GK; ++k) {
+        const float av = (k & 1) ? a[(k >> 1) * Q + s].y : a[(k >> 1) * Q + s].x;
+        if (!(av >= thr[s])) {
+          const float4 r = sweep_load_key(tl, u0 + k);
+          const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
+          if (d < best[s]) {
+            best[s] = d;
+            arg[s] = t0 + u0 + k;
+            thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128>
 __global__ void __launch_bounds__(CF_THREADS, MINB)
 chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int64_t B, int N1, int N2,
@@ -115,29 +152,11 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
 #pragma unroll UNR
       for (int u0 = 0; u0 < lim; u0 += GK) {
         float2 a[4];
-        if (__builtin_expect(sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a), 0)) {
-#pragma unroll
-          for (int p = 0; p < GK / 2; ++p) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              // no bounds test: padding keys carry a filter value of +inf, which no threshold admits
-              const int j = t0 + u0 + 2 * p + h;
-              const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
-#pragma unroll
-              for (int s = 0; s < Q; ++s) {
-                const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
-                if (!(av >= thr[s])) {
-                  const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-                  if (d < best[s]) {
-                    best[s] = d;
-                    arg[s] = j;
-                    thr[s] = sweep_threshold(d, sweep_qq(qx[s], qy[s], qz[s]));
-                  }
-                }
-              }
-            }
-          }
-        }
+        float m[2];
+        bool any;
+        if constexpr (Q == 2) any = sweep_group2_gated(tl + u0, mx, my, mz, thr, a, m);
+        else any = sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a);
+        if (__builtin_expect(any, 0)) chamfer_verify<Q>(tl, u0, t0, a, m, qx, qy, qz, thr, best, arg);
       }
 
       if (more) {
@@ -195,19 +214,194 @@ int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, floa
   return check_launch("chamfer_fwd_fast_kernel");
 }
 
+// ---- one block per SM, for launches of one or two rounds of tasks --------------------------------
+// A launch of the kernel above pays a fixed cost of about 15 % of the time one round of tasks
+// takes (measured for task lengths from 4096 to 32768 keys), which is nothing for many rounds
+// but all of it for one rank's share of a batch split over several GPUs (8 clouds of 16384
+// points are 1024 tasks for 148 SMs: 0.80 ms where 0.70 ms would be an eighth of the 64-cloud
+// launch).  Measured on B200, the same sweep run as ONE block of 896 threads per SM -- seven
+// groups of 128 threads, each group working through its own task with its own pair of tile
+// buffers and its own named barrier, exactly like a block of the kernel above -- does not pay it
+// (0.74 ms), while over many rounds it is about 5 % slower than independently scheduled blocks
+// (its groups are bound to their block, so an SM's last tasks of a round run with the SM partly
+// empty).  The launcher therefore picks this kernel only for one or two nearly full rounds of
+// tasks.  896 threads leave 72 registers per thread.
+template <int UNR>
+__global__ void __launch_bounds__(896, 1)
+chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int N1, int N2,
+                          float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
+                          int64_t *__restrict__ idx2, double *__restrict__ sums, int blocks1,
+                          int blocks_total) {
+  constexpr int Q = 2, TH = 128;
+  constexpr int PER = CF_TILE / TH;
+  extern __shared__ float4 group_tiles[];  // [groups][2][CF_TILE]
+  const int tid = threadIdx.x & (TH - 1);
+  const int grp = threadIdx.x >> 7;
+  const int groups = blockDim.x >> 7;
+  float4(*tile)[CF_TILE] = reinterpret_cast<float4(*)[CF_TILE]>(group_tiles + (size_t)grp * 2 * CF_TILE);
+  const float pinf = __int_as_float(0x7f800000);
+
+  // Every group walks its own tasks; groups never wait for one another.
+  for (int blk = blockIdx.x * groups + grp; blk < blocks_total; blk += gridDim.x * groups) {
+    const int dir = blk >= blocks1;
+    const int id = dir ? blk - blocks1 : blk;
+    const float *qpts = dir ? xyz2 : xyz1;
+    const float *rpts = dir ? xyz1 : xyz2;
+    const int nq = dir ? N2 : N1;
+    const int nr = dir ? N1 : N2;
+    const int chunks = (nq + TH * Q - 1) / (TH * Q);
+    const int64_t b = id / chunks;
+    const int i0 = (id % chunks) * (TH * Q) + tid;
+
+    float qx[Q], qy[Q], qz[Q], thr[Q], best[Q];
+    float2 mx[Q], my[Q], mz[Q];
+    int arg[Q];
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      const int i = i0 + s * TH;
+      best[s] = pinf;
+      arg[s] = -1;
+      if (i < nq) {
+        const float *q = qpts + (b * nq + i) * 3;
+        qx[s] = q[0];
+        qy[s] = q[1];
+        qz[s] = q[2];
+        thr[s] = pinf;  // accept everything until a first candidate is verified
+      } else {
+        qx[s] = qy[s] = qz[s] = 0.f;
+        thr[s] = -pinf;  // never passes
+      }
+      mx[s] = make_float2(-2.f * qx[s], -2.f * qx[s]);
+      my[s] = make_float2(-2.f * qy[s], -2.f * qy[s]);
+      mz[s] = make_float2(-2.f * qz[s], -2.f * qz[s]);
+    }
+
+    const float *rb = rpts + b * (int64_t)nr * 3;
+    const int ntiles = (nr + CF_TILE - 1) / CF_TILE;
+    if (ntiles > 0) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        const int u = tid + p * TH;
+        if (u < nr) {
+          const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
+          sweep_store_key(tile[0], u, x, y, z, sweep_key_w(x, y, z));
+        } else {
+          sweep_store_key(tile[0], u, 0.f, 0.f, 0.f, pinf);
+        }
+      }
+    }
+    group_barrier(grp);
+
+    for (int t = 0; t < ntiles; ++t) {
+      const int t0 = t * CF_TILE;
+      const int cnt = min(CF_TILE, nr - t0);
+      const float4 *tl = tile[t & 1];
+
+      float px[PER], py[PER], pz[PER];
+      const bool more = t + 1 < ntiles;
+      if (more) {
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+          const int j = t0 + CF_TILE + tid + p * TH;
+          if (j < nr) {
+            px[p] = rb[(int64_t)j * 3 + 0];
+            py[p] = rb[(int64_t)j * 3 + 1];
+            pz[p] = rb[(int64_t)j * 3 + 2];
+          } else {
+            px[p] = py[p] = pz[p] = 0.f;
+          }
+        }
+      }
+
+      const int lim = (cnt + 3) / 4 * 4;
+#pragma unroll UNR
+      for (int u0 = 0; u0 < lim; u0 += 4) {
+        float2 a[4];
+        float m[2];
+        if (__builtin_expect(sweep_group2_gated(tl + u0, mx, my, mz, thr, a, m), 0))
+          chamfer_verify<Q>(tl, u0, t0, a, m, qx, qy, qz, thr, best, arg);
+      }
+
+      if (more) {
+        float4 *nx = tile[(t + 1) & 1];
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+          const int u = tid + p * TH;
+          if (t0 + CF_TILE + u < nr)
+            sweep_store_key(nx, u, px[p], py[p], pz[p], sweep_key_w(px[p], py[p], pz[p]));
+          else
+            sweep_store_key(nx, u, 0.f, 0.f, 0.f, pinf);
+        }
+      }
+      group_barrier(grp);
+    }
+
+    float *dist = dir ? dist2 : dist1;
+    int64_t *idx = dir ? idx2 : idx1;
+    double part = 0.0;
+#pragma unroll
+    for (int s = 0; s < Q; ++s) {
+      const int i = i0 + s * TH;
+      if (i < nq) {
+        dist[b * nq + i] = best[s];
+        idx[b * nq + i] = (int64_t)arg[s];
+        part += (double)best[s];
+      }
+    }
+    if (sums != nullptr) {
+      part = warp_sum(part);
+      if ((tid & 31) == 0) atomicAdd(sums + dir, part);
+    }
+  }
+}
+
+constexpr int SMWIDE_GROUPS = 7;
+
+int launch_smwide(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
+                  float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+  const int64_t blocks1 = B * ((N1 + 255) / 256), blocks2 = B * ((N2 + 255) / 256);
+  const int64_t total = blocks1 + blocks2;
+  const size_t smem = (size_t)SMWIDE_GROUPS * 2 * CF_TILE * sizeof(float4);  // 112 KB
+  TK3D_CUDA(cudaFuncSetAttribute(chamfer_fwd_smwide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+  const int64_t blocks = (total + SMWIDE_GROUPS - 1) / SMWIDE_GROUPS;
+  const int64_t cap = sm_count();
+  chamfer_fwd_smwide_kernel<4><<<(unsigned)(blocks < cap ? blocks : cap), 128 * SMWIDE_GROUPS, smem, st>>>(
+      xyz1, xyz2, N1, N2, dist1, idx1, dist2, idx2, sums, (int)blocks1, (int)total);
+  return check_launch("chamfer_fwd_smwide_kernel");
+}
+
 }  // namespace
+
+// 0: one query per thread, 1: one block per SM, 2: two queries per thread in independent blocks.
+static int chamfer_fwd_f32_plan(int64_t B, int64_t N1, int64_t N2) {
+  const int64_t queries = B * (N1 + N2);
+  const int64_t sms = sm_count();
+  // Queries per thread: more register tiling when there is enough work to fill the GPU with it.
+  if (queries < sms * 2 * 128 * 2) return 0;
+  const int64_t tasks = B * ((N1 + 255) / 256) + B * ((N2 + 255) / 256);
+  // In units of one round (seven tasks per SM): independent blocks take about rounds + 0.15, the
+  // one-block-per-SM kernel 1.055 x the rounds rounded up.
+  const int64_t round = SMWIDE_GROUPS * sms, rounds_up = (tasks + round - 1) / round;
+  if (tasks < (1LL << 30) && 1055 * rounds_up * round < 1000 * tasks + 150 * round) return 1;
+  return 2;
+}
+
+const char *chamfer_fwd_f32_kernel_name(int64_t B, int64_t N1, int64_t N2) {
+  static const char *const names[3] = {"chamfer_fwd_fast_kernel<1>", "chamfer_fwd_smwide_kernel",
+                                       "chamfer_fwd_fast_kernel<2>"};
+  return names[chamfer_fwd_f32_plan(B, N1, N2)];
+}
 
 int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_t N1, int64_t N2, float *dist1,
                          int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
-  // Queries per thread: more register tiling when there is enough work to fill the GPU with it.
-  const int64_t queries = B * (N1 + N2);
-  const int64_t sms = sm_count();
-  constexpr int CF_THREADS = 128;
   // Measured on B200 (B=64, N=M=16384): two queries per thread, six resident blocks per SM and a
   // four-fold unrolled key loop beat four queries per thread by about 10 %.
-  if (queries >= sms * 2 * CF_THREADS * 2)
-    return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
-  return launch<1, 1, 2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+  switch (chamfer_fwd_f32_plan(B, N1, N2)) {
+    case 0: return launch<1, 1, 2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+    case 1: return launch_smwide(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+    default: return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+  }
 }
 
 }  // namespace tk3d

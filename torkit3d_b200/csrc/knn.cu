@@ -140,18 +140,22 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll 4
       for (int u0 = 0; u0 < lim; u0 += GK) {
         float2 a[4];
-        if (__builtin_expect(sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a), 0)) {
+        float m[2];
+        bool any;
+        if constexpr (Q == 2) any = sweep_group2_gated(tl + u0, mx, my, mz, thr, a, m);
+        else any = sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a);
+        if (__builtin_expect(any, 0)) {
 #pragma unroll
-          for (int p = 0; p < GK / 2; ++p) {
+          for (int s = 0; s < Q; ++s) {
+            // with two queries per thread, skip the one whose four filter values all fail
+            if (Q != 2 || !(m[s] >= thr[s])) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              // no bounds test: padding keys carry a filter value of +inf, which no threshold admits
-              const int j = t0 + u0 + 2 * p + h;
-              const float4 r = sweep_load_key(tl, u0 + 2 * p + h);
-#pragma unroll
-              for (int s = 0; s < Q; ++s) {
-                const float av = h ? a[p * Q + s].y : a[p * Q + s].x;
+              for (int k = 0; k < GK; ++k) {
+                // no bounds test: padding keys carry a filter value of +inf, which no threshold admits
+                const float av = (k & 1) ? a[(k >> 1) * Q + s].y : a[(k >> 1) * Q + s].x;
                 if (!(av >= thr[s])) {
+                  const int j = t0 + u0 + k;
+                  const float4 r = sweep_load_key(tl, u0 + k);
                   const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
                   // (d, j) enters iff it orders before the current last entry; sentinels carry
                   // (+inf, INT_MAX) so real entries always precede them.

@@ -110,6 +110,26 @@ __device__ __forceinline__ bool sweep_any8_min(float v0, float v1, float v2, flo
   return flag != 0;
 }
 
+// As sweep_any8_min, and the two minima themselves (m0 over v0..v3, m1 over v4..v7) for callers
+// that gate their verify path per query.
+__device__ __forceinline__ bool sweep_any8_min2(float v0, float v1, float v2, float v3, float v4, float v5, float v6,
+                                                float v7, float t0, float t1, float &m0, float &m1) {
+  unsigned flag;
+  asm("{\n\t"
+      ".reg .pred p;\n\t"
+      "min.NaN.f32 %1, %3, %4, %5;\n\t"
+      "min.NaN.f32 %2, %7, %8, %9;\n\t"
+      "min.NaN.f32 %1, %1, %6;\n\t"
+      "min.NaN.f32 %2, %2, %10;\n\t"
+      "setp.ltu.f32 p, %1, %11;\n\t"
+      "setp.ltu.or.f32 p, %2, %12, p;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(flag), "=&f"(m0), "=&f"(m1)
+      : "f"(v0), "f"(v1), "f"(v2), "f"(v3), "f"(v4), "f"(v5), "f"(v6), "f"(v7), "f"(t0), "f"(t1));
+  return flag != 0;
+}
+
 // Filter values of one key against Q queries.
 __device__ __forceinline__ float sweep_lower(float mx, float my, float mz, const float4 &r) {
   return fmaf(mx, r.x, fmaf(my, r.y, fmaf(mz, r.z, r.w)));
@@ -158,6 +178,22 @@ __device__ __forceinline__ bool sweep_group2(const float4 *__restrict__ pairs, c
     return sweep_any8_min(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0], thr[0]);
   return sweep_any8(a[0].x, a[0].y, a[1].x, a[1].y, a[2].x, a[2].y, a[3].x, a[3].y, thr[0 % Q], thr[0 % Q],
                     thr[1 % Q], thr[1 % Q], thr[2 % Q], thr[2 % Q], thr[3 % Q], thr[3 % Q]);
+}
+
+// Two queries against four keys (two key pairs) as sweep_group2<2, true>, also returning the
+// minimum filter value of each query, m[s], so that the verify path can skip a whole query.
+__device__ __forceinline__ bool sweep_group2_gated(const float4 *__restrict__ pairs, const float2 (&mx)[2],
+                                                   const float2 (&my)[2], const float2 (&mz)[2],
+                                                   const float (&thr)[2], float2 (&a)[4], float (&m)[2]) {
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const float4 A = pairs[2 * p], Bv = pairs[2 * p + 1];
+    const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
+    const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) a[p * 2 + s] = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
+  }
+  return sweep_any8_min2(a[0].x, a[0].y, a[2].x, a[2].y, a[1].x, a[1].y, a[3].x, a[3].y, thr[0], thr[1], m[0], m[1]);
 }
 
 }  // namespace tk3d
