@@ -408,8 +408,9 @@ def run_b200(args, rank, world, local_rank):
                 else "nominal 148 SM x 128 lanes x 2 x 1.965 GHz", "unit": "TFLOP/s",
                 "frac": achieved / (peak if peak else nominal), "nominal_peak": nominal,
                 # DRAM read+write of this kernel from the committed ncu capture (profiles/chamfer_fwd.md:
-                # 6.32 MB at B=16), scaled to this launch by the clouds it processes
-                "traffic": 6.319e6 * Bl / 16.0, "traffic_unit": "bytes",
+                # 9.47 MB at B=24; profiles/chamfer_fwd_smwide.md: 3.17 MB at B=8), scaled to this
+                # launch by the clouds it processes
+                "traffic": 9.465e6 * Bl / 24.0, "traffic_unit": "bytes",
                 "flop_per_pair": PAIR_FLOP, "pairs_per_launch": pairs_local, "launch_ms": fwd_ms,
                 "pairs_per_sec": pairs_local / (fwd_ms * 1e-3)}
 

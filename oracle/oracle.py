@@ -124,6 +124,28 @@ def knn(query, key, k, threads=None):
     return d, i
 
 
+def feature_knn(query, key, k, channel_first=True, threads=None):
+    """KNN on C-dimensional features: squared distances (fma over the channels in order) and
+    indices, rows sorted ascending by (distance, index).  [B, C, N] tensors, or [B, N, C] with
+    ``channel_first=False``."""
+    query, key = _c(query), _c(key)
+    B = query.shape[0]
+    C, N1 = (query.shape[1], query.shape[2]) if channel_first else (query.shape[2], query.shape[1])
+    N2 = key.shape[2] if channel_first else key.shape[1]
+    assert N2 >= k
+    d = np.empty((B, N1, k), query.dtype)
+    i = np.empty((B, N1, k), np.int64)
+    f = getattr(lib(), "orc_feature_knn" + _sfx(query))
+
+    def run(b0, b1):
+        if b1 > b0:
+            f(_p(query[b0:b1]), _p(key[b0:b1]), I64(b1 - b0), I64(C), I64(N1), I64(N2), I64(k),
+              ctypes.c_int(1 if channel_first else 0), _p(d[b0:b1]), _p(i[b0:b1]))
+
+    _pool(B, threads, run)
+    return d, i
+
+
 def fps(points, num_samples, threads=None):
     points = _c(points)
     B, N, _ = points.shape

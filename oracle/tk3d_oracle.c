@@ -17,7 +17,9 @@
 
 #define T float
 #define SUFFIX _f32
+#define ORC_T_IS_FLOAT 1
 #include "tk3d_oracle_impl.h"
+#undef ORC_T_IS_FLOAT
 #undef T
 #undef SUFFIX
 

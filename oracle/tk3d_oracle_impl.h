@@ -120,6 +120,47 @@ void FN(orc_knn)(const T *query, const T *key, int64_t bs, int64_t n1, int64_t n
   }
 }
 
+/* KNN in a C-dimensional feature space: the operator torkit3d/ops/native.py:4-30 defines as
+ * torch.cdist + torch.topk (called on [B, C, N] features by models/classification/dgcnn.py:58-61).
+ * cdist goes through a matrix product whose rounding is not specified, so this restatement fixes
+ * the arithmetic instead: acc = fma(d_c, d_c, acc) over the channels in order, d_c = key_c - query_c
+ * (fmaf is correctly rounded whatever -ffp-contract says).  Rows are the k smallest under
+ * (squared distance, index), sorted ascending.  `cf` != 0: tensors are [B, C, N], else [B, N, C]. */
+void FN(orc_feature_knn)(const T *query, const T *key, int64_t bs, int64_t c, int64_t n1, int64_t n2, int64_t k,
+                         int cf, T *dist, int64_t *idx) {
+  for (int64_t s = 0; s < bs; ++s) {
+    const T *qb = query + s * c * n1, *kb = key + s * c * n2;
+    for (int64_t i = 0; i < n1; ++i) {
+      T *od = dist + (s * n1 + i) * k;
+      int64_t *oi = idx + (s * n1 + i) * k;
+      int64_t cnt = 0;
+      for (int64_t j = 0; j < n2; ++j) {
+        T d = 0;
+        for (int64_t ch = 0; ch < c; ++ch) {
+          const T qv = cf ? qb[ch * n1 + i] : qb[i * c + ch];
+          const T kv = cf ? kb[ch * n2 + j] : kb[j * c + ch];
+          const T df = kv - qv;
+#if defined(ORC_T_IS_FLOAT)
+          d = fmaf(df, df, d);
+#else
+          d = fma(df, df, d);
+#endif
+        }
+        if (cnt == k && !(d < od[k - 1])) continue;
+        int64_t pos = (cnt < k) ? cnt : k - 1;
+        while (pos > 0 && d < od[pos - 1]) { /* stable: an equal distance with a higher index stays behind */
+          od[pos] = od[pos - 1];
+          oi[pos] = oi[pos - 1];
+          --pos;
+        }
+        od[pos] = d;
+        oi[pos] = j;
+        if (cnt < k) ++cnt;
+      }
+    }
+  }
+}
+
 /* Farthest point sampling from index 0; min-distance update then arg-max, lowest index among exact
  * maxima (numpy argmax rule of tests/ops/test_sample_farthest_points.py:24-36; the kernel is
  * torkit3d/csrc/cuda/sample_farthest_points_kernel.cu:28-103, which differs only when two distinct
