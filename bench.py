@@ -343,6 +343,13 @@ def extras(dev, rank, world, flush):
         xe = x.unsqueeze(3).expand_as(grouped)
         return torch.cat([grouped - xe, xe], dim=1)
     out["edge_feature_chain_ms"] = t(edge_chain, steps=10)
+    # DGCNN's feature-space KNN on the same layer (k=20 among 1024 points, 64 channels)
+    from torkit3d_b200.ops import knn as feature_knn
+    ms = t(lambda: feature_knn(x, x, 20, transpose=True), steps=10)
+    out["feature_knn_ms"] = ms
+    out["feature_knn_pair_channels_per_sec"] = x.size(0) * 1024 * 1024 * 64 / (ms * 1e-3)
+    xt = x.transpose(1, 2)
+    out["feature_knn_cdist_topk_ms"] = t(lambda: torch.topk(torch.cdist(xt, xt), 20, dim=2, largest=False), steps=10)
     return out
 
 

@@ -324,6 +324,19 @@ int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index, int64_t B,
                           void *scratch, size_t scratch_bytes, int dtype, void *stream);
 
 /*
+ * Brute-force k nearest neighbours in a C-dimensional feature space (float32 only, k <= 128).
+ * Replaces the cdist + topk formulation of torkit3d/ops/native.py:4-30 where DGCNN builds its
+ * dynamic graph on features (torkit3d/models/classification/dgcnn.py:58-61).
+ *   query [B,C,N1], key [B,C,N2] in  (channel_first != 0), or [B,N1,C], [B,N2,C] (channel_first == 0);
+ *                                    requires 1 <= k <= N2
+ *   distance [B,N1,k] out: SQUARED distances, acc = fma(d_c, d_c, acc) over c = 0..C-1 in order with
+ *                          d_c = key_c - query_c (cdist's matrix-product rounding is unspecified)
+ *   index [B,N1,k] out;    each row sorted ascending by (distance, index)
+ */
+int tk3d_feature_knn(const void *query, const void *key, int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t k,
+                     int channel_first, void *distance, int64_t *index, int dtype, void *stream);
+
+/*
  * Diagnostic with no counterpart in the reference: launches a kernel of dependent FP32 fused
  * multiply-add chains (`iters` x 64 FMAs per thread, 8 blocks of 256 threads per SM) on `stream`.
  * *flop (a HOST double, optional) receives the number of floating-point operations the launch

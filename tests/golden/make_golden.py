@@ -195,6 +195,19 @@ def main():
                     tag + "_idx": idx.numpy(), tag + "_k": np.int64(k)})
     np.savez_compressed(os.path.join(HERE, "knn.npz"), **out)
 
+    # ---- knn on C-dimensional features, [B, C, N] tensors as DGCNN holds them (transpose=True), and
+    # [B, N, C]; float64 so that cdist's own rounding cannot reorder neighbours ----
+    out = {}
+    for tag, (b, c, n1, n2, k, cf) in {"a": (2, 16, 300, 300, 20, True), "b": (1, 67, 129, 257, 33, True),
+                                       "c": (3, 5, 64, 200, 7, False), "d": (1, 130, 40, 150, 70, True)}.items():
+        torch.manual_seed(11)
+        q = torch.randn(b, c, n1).double() if cf else torch.randn(b, n1, c).double()
+        r = torch.randn(b, c, n2).double() if cf else torch.randn(b, n2, c).double()
+        dist, idx = native_knn(q, r, k, sorted=True, transpose=cf)
+        out.update({tag + "_query": q.numpy(), tag + "_key": r.numpy(), tag + "_dist": dist.numpy(),
+                    tag + "_idx": idx.numpy(), tag + "_k": np.int64(k), tag + "_cf": np.int64(cf)})
+    np.savez_compressed(os.path.join(HERE, "feature_knn.npz"), **out)
+
     # ---- fps ----
     out = {}
     for tag, (b, n, s, dt) in {"a": (1, 31, 2, np.float64), "b": (3, 1025, 129, np.float64),

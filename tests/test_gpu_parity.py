@@ -280,6 +280,62 @@ def test_knn_far_from_origin(oracle):
         np.testing.assert_array_equal(N(d), e)
 
 
+# ----------------------------------------------------------------------------- knn on features
+FEATURE_KNN_SHAPES = [(2, 16, 300, 300, 20, True), (1, 67, 129, 257, 33, True), (3, 5, 64, 200, 7, False),
+                      (1, 130, 40, 150, 70, True), (2, 64, 1024, 1024, 20, True), (1, 3, 100, 500, 128, False),
+                      (4, 8, 33, 128, 1, True), (2, 40, 257, 129, 64, False)]
+
+
+@pytest.mark.parametrize("B,C,n1,n2,k,cf", FEATURE_KNN_SHAPES)
+@pytest.mark.parametrize("ties", [False, True])
+def test_feature_knn_bit_exact(oracle, B, C, n1, n2, k, cf, ties):
+    from torkit3d_b200 import _C
+
+    rng = np.random.default_rng(C * 100 + n2 + k)
+    shape_q, shape_r = ((B, C, n1), (B, C, n2)) if cf else ((B, n1, C), (B, n2, C))
+    if ties:   # small integer lattice: many exactly equal distances, ties must go to the lower index
+        q = rng.integers(-2, 3, size=shape_q).astype(np.float32)
+        r = rng.integers(-2, 3, size=shape_r).astype(np.float32)
+    else:
+        q = rng.standard_normal(shape_q).astype(np.float32)
+        r = rng.standard_normal(shape_r).astype(np.float32)
+    d, i = [N(t) for t in _C.feature_knn_cuda(T(q), T(r), k, channel_first=cf)]
+    e, j = oracle.feature_knn(q, r, k, channel_first=cf)
+    np.testing.assert_array_equal(i, j)
+    np.testing.assert_array_equal(d, e)
+
+
+def test_feature_knn_golden_wrapper_and_errors(golden):
+    from torkit3d_b200 import _C
+    from torkit3d_b200.ops import knn
+
+    g = golden("feature_knn")
+    for tag in "abcd":
+        k, cf = int(g[tag + "_k"]), bool(g[tag + "_cf"])
+        q, r = T(g[tag + "_query"], torch.float32), T(g[tag + "_key"], torch.float32)
+        d, i = knn(q, r, k, sorted=True, transpose=cf)
+        assert (N(i) == g[tag + "_idx"]).mean() > 0.995
+        np.testing.assert_allclose(N(d), g[tag + "_dist"], rtol=1e-5, atol=1e-6)
+    # differentiable distances when an input requires grad; same neighbours
+    q = T(g["a_query"], torch.float32).requires_grad_(True)
+    r = T(g["a_key"], torch.float32)
+    d, i = knn(q, r, 20, transpose=True)
+    d0, i0 = knn(q.detach(), r, 20, transpose=True)
+    assert torch.equal(i, i0)
+    np.testing.assert_allclose(N(d), N(d0), rtol=1e-5, atol=1e-6)
+    d.sum().backward()
+    assert q.grad is not None and torch.isfinite(q.grad).all()
+    with pytest.raises(RuntimeError):
+        _C.feature_knn_cuda(r, r, 301)          # k > N2
+    with pytest.raises(RuntimeError):
+        _C.feature_knn_cuda(r, r.double(), 3)    # dtype mismatch
+    with pytest.raises(RuntimeError):
+        _C.feature_knn_cuda(r, r, 129)          # k beyond the kernel's list capacity
+    # beyond that capacity the wrapper runs the reference formulation on the same device
+    d, i = knn(r, r, 130, sorted=True, transpose=True)
+    assert d.shape == (2, 300, 130) and i.is_cuda
+
+
 # ----------------------------------------------------------------------------------------------- fps
 FPS_CASES = [(1, 31, 2), (2, 1024, 128), (3, 1025, 129), (16, 1024, 512), (4, 4096, 300), (2, 8192, 1024),
              (2, 100, 100), (1, 1, 1), (3, 33, 33), (2, 8193, 200), (1, 20000, 64)]

@@ -36,6 +36,21 @@ def test_knn_golden(oracle, golden):
         np.testing.assert_allclose(np.sqrt(d), g[tag + "_dist"], rtol=1e-4, atol=5e-5)
 
 
+def test_feature_knn_golden(oracle, golden):
+    """The reference's native.knn (cdist + topk) on float64 features: same neighbours, same distances.
+    The float32 oracle (the arithmetic the CUDA kernel follows) agrees with it up to rounding."""
+    g = golden("feature_knn")
+    for tag in "abcd":
+        k, cf = int(g[tag + "_k"]), bool(g[tag + "_cf"])
+        q, r = g[tag + "_query"], g[tag + "_key"]
+        d, i = oracle.feature_knn(q, r, k, channel_first=cf)
+        np.testing.assert_array_equal(i, g[tag + "_idx"])
+        np.testing.assert_allclose(np.sqrt(d), g[tag + "_dist"], rtol=1e-9, atol=1e-9)
+        d32, i32 = oracle.feature_knn(q.astype(np.float32), r.astype(np.float32), k, channel_first=cf)
+        assert (i32 == g[tag + "_idx"]).mean() > 0.995
+        np.testing.assert_allclose(np.sqrt(d32), g[tag + "_dist"], rtol=1e-5, atol=1e-6)
+
+
 def test_fps_golden(oracle, golden):
     g = golden("fps")
     for tag in "abcd":

@@ -256,6 +256,35 @@ def knn_distance_cuda(query, key, k, version=0):
     return [distance, index]
 
 
+def feature_knn_cuda(query, key, k, channel_first=True):
+    """query [B,C,N1], key [B,C,N2] (or [B,N1,C], [B,N2,C] with ``channel_first=False``), float32 ->
+    [distance [B,N1,k] (squared), index [B,N1,k] int64], rows sorted by (distance, index).
+
+    No counterpart in the reference's extension: its models get these neighbours from
+    ``torkit3d.ops.native.knn`` (cdist + topk, torkit3d/ops/native.py:4-30).
+    """
+    _check_cuda_contig(query=query, key=key)
+    _check_eq(query.dim(), 3, "query.dim() == 3")
+    _check_eq(key.dim(), 3, "key.dim() == 3")
+    _check_eq(key.size(0), query.size(0), "key.size(0) == query.size(0)")
+    cdim, ndim = (1, 2) if channel_first else (2, 1)
+    _check_eq(key.size(cdim), query.size(cdim), "key channels == query channels")
+    k = int(k)
+    if not key.size(ndim) >= k:
+        raise RuntimeError("Check failed: key.size(%d) >= k (%d vs. %d)" % (ndim, key.size(ndim), k))
+    _same_device_dtype(query, key, floats=(key,))
+    if query.dtype != torch.float32:
+        raise RuntimeError("feature_knn_cuda: float32 tensors only")
+    lib = load()
+    B, C, N1, N2 = query.size(0), query.size(cdim), query.size(ndim), key.size(ndim)
+    with _on(query.device):
+        distance = torch.empty((B, N1, k), dtype=query.dtype, device=query.device)
+        index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
+        check(lib.tk3d_feature_knn(_ptr(query), _ptr(key), B, C, N1, N2, k, 1 if channel_first else 0,
+                                   _ptr(distance), _ptr(index), _dtype(query), _stream(query)))
+    return [distance, index]
+
+
 def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None):
     """xyz1 [B,N1,3], xyz2 [B,N2,3] -> [dist1, idx1, dist2, idx2].
 

@@ -6,7 +6,8 @@ Cases: c1_chamfer, c2_knn, c3_fps, c3_ball, c3_group_fwd, c3_group_bwd, c4_chamf
 c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd, and the layer front ends on the same
 inputs in channel-first layout, fused and spelled operator by operator: c3_fps_gather,
 c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain; and the EdgeConv edge
-features of a DGCNN layer (B=32, 1024 points, C=64, K=20): edge_fused, edge_chain.  ``--scale-batch`` overrides the batch
+features of a DGCNN layer (B=32, 1024 points, C=64, K=20): edge_fused, edge_chain; and its feature-space
+KNN: feature_knn, feature_knn_chain (cdist + topk in PyTorch).  ``--scale-batch`` overrides the batch
 size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
 """
 import argparse
@@ -25,6 +26,20 @@ def build_case(name, batch, dev):
     if name == "c2_knn":
         q, r = [t.to(dev) for t in workloads.c2_knn(**kw)]
         return lambda: knn_points(q, r, 16)
+    if name.startswith("feature_knn"):
+        # DGCNN's dynamic graph on 64-channel features: B=32 clouds of 1024 points, k=20
+        from .ops import knn
+
+        B = batch or 32
+        g = torch.Generator().manual_seed(9)
+        x = torch.randn(B, 64, 1024, generator=g).to(dev)
+        if name == "feature_knn":
+            return lambda: knn(x, x, 20, transpose=True)
+
+        def knn_chain():  # the reference's formulation on the same GPU
+            xt = x.transpose(1, 2)
+            return torch.topk(torch.cdist(xt, xt), 20, dim=2, largest=False, sorted=False)
+        return knn_chain
     if name.startswith("edge"):
         from .ops import get_edge_feature, group_points
 
