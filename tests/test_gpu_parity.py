@@ -248,6 +248,24 @@ def test_knn_ties(oracle, k, dtype):
     np.testing.assert_array_equal(N(d), e)
 
 
+# float64 with few queries: several warps per query group, per-segment lists merged at the end
+@pytest.mark.parametrize("B,n1,n2,k", [(8, 2048, 2048, 16), (2, 100, 300, 16), (1, 33, 1000, 64), (3, 500, 257, 3),
+                                       (2, 700, 5000, 1), (1, 40, 9000, 33)])
+@pytest.mark.parametrize("ties", [False, True])
+def test_knn_fp64_split_path_bit_exact(oracle, B, n1, n2, k, ties):
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(n2 + k)
+    if ties:
+        q, r = grid_cloud(rng, B, n1, np.float64), grid_cloud(rng, B, n2, np.float64)
+    else:
+        q, r = rng.standard_normal((B, n1, 3)), rng.standard_normal((B, n2, 3))
+    d, i = knn_points(T(q), T(r), k, sorted=True)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
 def test_knn_golden_fp64_and_options(golden):
     from torkit3d_b200.ops import knn_points
 

@@ -906,6 +906,11 @@ int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t 
 
 }  // namespace tk3d
 
+namespace tk3d {
+bool knn_split_f64(const double *query, const double *key, int64_t B, int64_t N1, int64_t N2, int64_t k, double *dist,
+                   int64_t *index, cudaStream_t st, int *rc);
+}
+
 using namespace tk3d;
 
 extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
@@ -918,9 +923,13 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
   if (B * N1 == 0) return TK3D_OK;
   TK3D_REQUIRE(query && key && distance && index, TK3D_ERR_NULL, "knn: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == TK3D_F64)
+  if (dtype == TK3D_F64) {
+    int rc = TK3D_OK;  // few queries and k <= 64: several warps per query group (knn_split.cu)
+    if (knn_split_f64((const double *)query, (const double *)key, B, N1, N2, k, (double *)distance, index, st, &rc))
+      return rc;
     return knn_generic<double>((const double *)query, (const double *)key, B, N1, N2, k, (double *)distance, index,
                                st);
+  }
   const float *q = (const float *)query, *r = (const float *)key;
   float *d = (float *)distance;
   switch (k) {
