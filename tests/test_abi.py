@@ -63,6 +63,17 @@ def test_argument_errors_need_no_gpu(lib):
     assert lib.tk3d_interp_fwd(fake, fake, fake, 1, 1, 8, 8, 4, fake, None, None, 0, F32, None) == 3  # k != 3
     assert lib.tk3d_chamfer_fwd(None, fake, 1, 8, 8, fake, fake, fake, fake, None, F32, None) == 1
     assert lib.tk3d_three_nn_weight(fake, 4, 9, fake, F32, None) == 3
+    assert lib.tk3d_feature_knn(fake, fake, 1, 16, 8, 4, 5, 1, fake, fake, F32, None) == 3     # k > N2
+    assert lib.tk3d_feature_knn(fake, fake, 1, 16, 8, 400, 129, 1, fake, fake, F32, None) == 7  # k > 128
+    assert lib.tk3d_feature_knn(fake, fake, 1, 16, 8, 4, 2, 1, fake, fake, 1, None) == 7        # float64
+    assert lib.tk3d_feature_knn(fake, fake, 1, 0, 8, 4, 2, 1, fake, fake, F32, None) == 2       # no channels
+    assert lib.tk3d_feature_knn(fake, None, 1, 16, 8, 4, 2, 1, fake, fake, F32, None) == 1      # NULL
+    assert lib.tk3d_feature_knn(None, None, 0, 16, 8, 4, 2, 1, None, None, F32, None) == 0      # empty batch
+    # which forward kernel a chamfer call would launch (one string per regime; fp64 has one kernel)
+    names = {lib.tk3d_chamfer_fwd_kernel_name(b, 16384, 16384, F32) for b in (1, 2, 8, 16, 24, 64)}
+    assert names <= {b"chamfer_fwd_fast_kernel<1>", b"chamfer_fwd_smwide_kernel", b"chamfer_fwd_fast_kernel<2>"}
+    assert lib.tk3d_chamfer_fwd_kernel_name(2, 1024, 1024, F32) == b"chamfer_fwd_fast_kernel<1>"
+    assert lib.tk3d_chamfer_fwd_kernel_name(2, 1024, 1024, 1) == b"chamfer_fwd_generic_kernel"
     # empty problems succeed without launching anything
     assert lib.tk3d_knn(None, None, 0, 8, 4, 2, None, None, F32, None) == 0
     assert lib.tk3d_group_fwd(None, None, 0, 4, 8, 8, 2, None, None, None, 0, F32, None) == 0
