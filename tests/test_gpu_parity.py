@@ -248,6 +248,20 @@ def test_knn_ties(oracle, k, dtype):
     np.testing.assert_array_equal(N(d), e)
 
 
+@pytest.mark.parametrize("k", [1, 2, 3, 4])
+def test_knn_small_full_round_of_blocks_bit_exact(oracle, k):
+    """Two queries per thread, about one full round of 256-query blocks per SM (1016 blocks), with ties."""
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(40 + k)
+    q = (rng.integers(-30, 31, size=(2, 130000, 3)) / 8).astype(np.float32)   # lattice: many ties
+    r = (rng.integers(-30, 31, size=(2, 3000, 3)) / 8).astype(np.float32)
+    d, i = knn_points(T(q), T(r), k, sorted=True)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
 # float64 with few queries: several warps per query group, per-segment lists merged at the end
 @pytest.mark.parametrize("B,n1,n2,k", [(8, 2048, 2048, 16), (2, 100, 300, 16), (1, 33, 1000, 64), (3, 500, 257, 3),
                                        (2, 700, 5000, 1), (1, 40, 9000, 33)])
