@@ -7,7 +7,7 @@ c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd, and the layer front e
 inputs in channel-first layout, fused and spelled operator by operator: c3_fps_gather,
 c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain; and the EdgeConv edge
 features of a DGCNN layer (B=32, 1024 points, C=64, K=20): edge_fused, edge_chain; and its feature-space
-KNN: feature_knn, feature_knn_chain (cdist + topk in PyTorch).  ``--scale-batch`` overrides the batch
+KNN: feature_knn, feature_knn_chain (cdist + topk in PyTorch); knn_f64 (float64 KNN, 8 x 2048 x 2048, k=16).  ``--scale-batch`` overrides the batch
 size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
 """
 import argparse
@@ -25,6 +25,13 @@ def build_case(name, batch, dev):
         return lambda: _C.chamfer_distance_forward_cuda(a, b)
     if name == "c2_knn":
         q, r = [t.to(dev) for t in workloads.c2_knn(**kw)]
+        return lambda: knn_points(q, r, 16)
+    if name == "knn_f64":
+        # float64 clouds with few queries: 8 clouds of 2048 points against 2048 keys, k=16
+        B = batch or 8
+        g = torch.Generator().manual_seed(8)
+        q = torch.randn(B, 2048, 3, generator=g, dtype=torch.float64).to(dev)
+        r = torch.randn(B, 2048, 3, generator=g, dtype=torch.float64).to(dev)
         return lambda: knn_points(q, r, 16)
     if name.startswith("feature_knn"):
         # DGCNN's dynamic graph on 64-channel features: B=32 clouds of 1024 points, k=20
