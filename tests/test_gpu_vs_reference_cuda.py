@@ -110,3 +110,49 @@ def test_interpolate(ref):
     go = torch.randn_like(mo)
     torch.testing.assert_close(_C.interpolate_backward_cuda(go, mi, w, 5000), ref.interpolate_backward_cuda(go, mi, w, 5000),
                                rtol=1e-5, atol=2e-5)
+
+
+def test_full_size_chamfer_batch(ref):
+    """All 64 cloud pairs of the 16384-point batch: distances and indices of both directions equal the
+    reference extension's, element for element."""
+    from torkit3d_b200 import _C, workloads
+
+    x1, x2 = workloads.c4_chamfer_large()
+    a, b = x1.to(DEV), x2.to(DEV)
+    mine = _C.chamfer_distance_forward_cuda(a, b)
+    theirs = ref.chamfer_distance_forward_cuda(a, b)
+    for m, t in zip(mine, theirs):
+        assert torch.equal(m, t)
+
+
+def test_full_size_scene_three_nn(ref):
+    """All 8 x 131072 queries of the scene-scale three-NN search against the reference extension (k=3,
+    version 1), rows canonicalised by (distance, index) on the GPU."""
+    from torkit3d_b200 import _C, workloads
+
+    q, r, _ = workloads.c5_scene_interp(C=1)
+    q, r = q.to(DEV), r.to(DEV)
+    md, mi = _C.knn_distance_cuda(q, r, 3, 1)
+    td, ti = ref.knn_distance_cuda(q, r, 3, 1)
+    # canonical order on the device: sort by index, then stably by distance
+    o = torch.argsort(ti, dim=2, stable=True)
+    td, ti = torch.gather(td, 2, o), torch.gather(ti, 2, o)
+    o = torch.argsort(td, dim=2, stable=True)
+    td, ti = torch.gather(td, 2, o), torch.gather(ti, 2, o)
+    assert torch.equal(mi, ti)
+    assert torch.equal(md, td)
+
+
+def test_knn_largest_shape_of_the_reference_tests(ref):
+    """(32, 2048, 8192, k=64): the largest case of the reference's tests/ops/test_knn_distance.py, here in
+    float32 against the reference extension (its own test runs it in float64 against cdist + topk)."""
+    from torkit3d_b200 import _C
+
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(32, 2048, 3, generator=g).to(DEV)
+    r = torch.randn(32, 8192, 3, generator=g).to(DEV)
+    md, mi = _C.knn_distance_cuda(q, r, 64, 1)
+    td, ti = ref.knn_distance_cuda(q, r, 64, 1)
+    cd, ci = canon(td, ti)
+    np.testing.assert_array_equal(mi.cpu().numpy(), ci)
+    np.testing.assert_array_equal(md.cpu().numpy(), cd)
