@@ -10,9 +10,13 @@
  *   - every pointer is a DEVICE pointer into the current CUDA device's memory unless stated;
  *     tensors are dense, row-major ("contiguous") in the shapes written beside them;
  *   - `dtype` is TK3D_F32 or TK3D_F64 and applies to every `void*` floating-point tensor;
- *     indices are always int64;
+ *     indices are int64 unless an entry point says otherwise;
  *   - the caller allocates and owns every output and scratch buffer; the library allocates no
- *     device memory, keeps no state between calls and never synchronises the host;
+ *     device memory and never synchronises the host.  Between calls it keeps only per-device
+ *     caches of facts that cannot change (the SM count, which kernels already had their
+ *     shared-memory limit raised, the address of the array behind tk3d_fps_static_scratch);
+ *     these are valid for the lifetime of the device's primary context, i.e. until the process
+ *     ends or the device is reset;
  *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default
  *     stream) of the device that is current on the calling thread;
  *   - every output element is written by the call (no pre-zeroing needed);
@@ -36,6 +40,10 @@ extern "C" {
 
 #define TK3D_F32 0
 #define TK3D_F64 1
+
+/* type of an index tensor, for the *_layout entry points */
+#define TK3D_I64 0
+#define TK3D_I32 1
 
 #define TK3D_OK 0
 #define TK3D_ERR_NULL 1        /* a required pointer is NULL */
@@ -220,6 +228,35 @@ int tk3d_interp_bwd(const void *grad_out, const int64_t *index, const void *weig
  *   distance [rows,k] (squared) in;  weight [rows,k] out;  1 <= k <= 8
  */
 int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t k, void *weight, int dtype, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Layout variants of the operators above.  The reference's Python operators copy channel-first
+ * clouds with .transpose(1, 2).contiguous() before every call (torkit3d/ops/ball_query.py:32-36,
+ * torkit3d/ops/sample_farthest_points.py:28-30, torkit3d/ops/knn_points.py:40-44,
+ * torkit3d/ops/chamfer_distance.py:49-52); these entry points read the [B,3,N] tensor in place.
+ *   xyz_channel_first  0 = every xyz argument is [B,N,3] (exactly the plain entry point),
+ *                      1 = every xyz argument -- and every xyz gradient -- is [B,3,N]
+ *   index_dtype        TK3D_I64 (the reference's type) or TK3D_I32 (half the index bytes; every
+ *                      index fits because clouds are limited to 2^30 points); `index` then points
+ *                      at int32 elements of the same shape
+ * Results are identical to the plain entry points, element for element.
+ */
+int tk3d_chamfer_fwd_layout(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2,
+                            int xyz_channel_first, void *dist1, int64_t *idx1, void *dist2, int64_t *idx2,
+                            double *sums, int dtype, void *stream);
+int tk3d_chamfer_bwd_layout(const void *grad_dist1, const void *grad_dist2, const void *xyz1, const void *xyz2,
+                            const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
+                            int xyz_channel_first, void *grad_xyz1, void *grad_xyz2, int dtype, void *stream);
+int tk3d_chamfer_bwd_mean_layout(const void *grad_loss, double count1, double count2, const void *xyz1,
+                                 const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1,
+                                 int64_t N2, int xyz_channel_first, void *grad_xyz1, void *grad_xyz2, int dtype,
+                                 void *stream);
+int tk3d_knn_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
+                    int xyz_channel_first, void *distance, void *index, int index_dtype, int dtype, void *stream);
+int tk3d_fps_layout(const void *points, int64_t B, int64_t N, int64_t num_samples, int xyz_channel_first,
+                    int64_t *index, void *scratch, size_t scratch_bytes, int dtype, void *stream);
+int tk3d_ball_query_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
+                           int64_t k, int xyz_channel_first, void *index, int index_dtype, int dtype, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Fused front ends of the PointNet++ layers that call the operators above.  They replace Python

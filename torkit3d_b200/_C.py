@@ -5,6 +5,12 @@ allocates the outputs on the inputs' device) as ``torkit3d/csrc/torkit3d.cpp:13-
 each call goes through the C ABI of libtk3d_b200.so on the current CUDA stream of the tensors'
 device.  float32 and float64 tensors are accepted, indices are int64.
 
+Keyword-only extras (no counterpart in the reference, whose callers copy instead): the coordinate
+operators take ``channel_first=True`` for [B,3,N] clouds, which are then read in place -- the
+``.transpose(1, 2).contiguous()`` copy of torkit3d/ops/ball_query.py:32-36,
+ops/sample_farthest_points.py:28-30, ops/knn_points.py:40-44 disappears -- and the index-producing
+ones take ``index_dtype=torch.int32`` for half the index bytes.
+
 Differences a caller can observe, all deliberate:
   * ``knn_distance_cuda`` returns every row sorted ascending by (distance, index); the reference
     leaves the row order unspecified.  ``version`` is validated (0 or 1) and otherwise ignored.
@@ -60,6 +66,19 @@ def _index(t, name):
         raise RuntimeError("%s must be an int64 tensor." % name)
 
 
+def _index_code(index_dtype):
+    if index_dtype == torch.int64:
+        return _lib.I64
+    if index_dtype == torch.int32:
+        return _lib.I32
+    raise RuntimeError("index_dtype must be torch.int64 or torch.int32, got %s" % (index_dtype,))
+
+
+def _xyz_dims(channel_first):
+    """(point axis, coordinate axis) of a cloud tensor."""
+    return (2, 1) if channel_first else (1, 2)
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
@@ -99,44 +118,56 @@ def _ptr(t):
     return t.data_ptr() if t.numel() > 0 else (t.data_ptr() or 0)
 
 
-def sample_farthest_points_cuda(points, num_samples):
-    """points [B,N,3] -> index [B,num_samples] int64 (first sample is point 0)."""
+def sample_farthest_points_cuda(points, num_samples, *, channel_first=False):
+    """points [B,N,3] ([B,3,N] with ``channel_first``) -> index [B,num_samples] int64 (first sample is point 0)."""
     _check_cuda_contig(points=points)
     _check_eq(points.dim(), 3, "points.dim() == 3")
-    _check_eq(points.size(2), 3, "points.size(2) == 3")
+    pdim, cdim = _xyz_dims(channel_first)
+    _check_eq(points.size(cdim), 3, "points.size(%d) == 3" % cdim)
     num_samples = int(num_samples)
     if not num_samples > 0:
         raise RuntimeError("Check failed: num_samples > 0 (%d vs. 0)" % num_samples)
-    if not points.size(1) >= num_samples:
-        raise RuntimeError("Check failed: points.size(1) >= num_samples (%d vs. %d)" % (points.size(1), num_samples))
+    if not points.size(pdim) >= num_samples:
+        raise RuntimeError("Check failed: points.size(%d) >= num_samples (%d vs. %d)"
+                           % (pdim, points.size(pdim), num_samples))
     lib = load()
-    B, N = points.size(0), points.size(1)
+    B, N = points.size(0), points.size(pdim)
     dt = _dtype(points)
     with _on(points.device):
         index = torch.empty((B, num_samples), dtype=torch.int64, device=points.device)
         need = _lib.scratch_bytes("tk3d_fps", B, N, dt)
         scratch = torch.empty((need,), dtype=torch.uint8, device=points.device) if need else None
-        check(lib.tk3d_fps(_ptr(points), B, N, num_samples, _ptr(index), _ptr(scratch) if need else None, need, dt,
-                           _stream(points)))
+        if channel_first:
+            check(lib.tk3d_fps_layout(_ptr(points), B, N, num_samples, 1, _ptr(index),
+                                      _ptr(scratch) if need else None, need, dt, _stream(points)))
+        else:
+            check(lib.tk3d_fps(_ptr(points), B, N, num_samples, _ptr(index), _ptr(scratch) if need else None, need,
+                               dt, _stream(points)))
     return index
 
 
-def ball_query_cuda(query, key, radius, max_neighbors):
-    """query [B,N1,3], key [B,N2,3] -> index [B,N1,max_neighbors] int64."""
+def ball_query_cuda(query, key, radius, max_neighbors, *, channel_first=False, index_dtype=torch.int64):
+    """query [B,N1,3], key [B,N2,3] ([B,3,N1], [B,3,N2] with ``channel_first``) -> index [B,N1,max_neighbors]."""
     _check_cuda_contig(query=query, key=key)
     _check_eq(query.dim(), 3, "query.dim() == 3")
     _check_eq(key.dim(), 3, "key.dim() == 3")
     _check_eq(query.size(0), key.size(0), "query.size(0) == key.size(0)")
-    _check_eq(query.size(2), 3, "query.size(2) == 3")
-    _check_eq(key.size(2), 3, "key.size(2) == 3")
+    pdim, cdim = _xyz_dims(channel_first)
+    _check_eq(query.size(cdim), 3, "query.size(%d) == 3" % cdim)
+    _check_eq(key.size(cdim), 3, "key.size(%d) == 3" % cdim)
     _same_device_dtype(query, key, floats=(key,))
     lib = load()
-    B, N1, N2 = query.size(0), query.size(1), key.size(1)
+    B, N1, N2 = query.size(0), query.size(pdim), key.size(pdim)
     k = int(max_neighbors)
     with _on(query.device):
-        index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
-        check(lib.tk3d_ball_query(_ptr(query), _ptr(key), B, N1, N2, float(radius), k, _ptr(index), _dtype(query),
-                                  _stream(query)))
+        index = torch.empty((B, N1, k), dtype=index_dtype, device=query.device)
+        if channel_first or index_dtype != torch.int64:
+            check(lib.tk3d_ball_query_layout(_ptr(query), _ptr(key), B, N1, N2, float(radius), k,
+                                             1 if channel_first else 0, _ptr(index), _index_code(index_dtype),
+                                             _dtype(query), _stream(query)))
+        else:
+            check(lib.tk3d_ball_query(_ptr(query), _ptr(key), B, N1, N2, float(radius), k, _ptr(index),
+                                      _dtype(query), _stream(query)))
     return index
 
 
@@ -232,27 +263,34 @@ def interpolate_backward_cuda(grad_output, index, weight, n1):
     return gin
 
 
-def knn_distance_cuda(query, key, k, version=0):
-    """query [B,N1,3], key [B,N2,3] -> [distance [B,N1,k] (squared), index [B,N1,k] int64]."""
+def knn_distance_cuda(query, key, k, version=0, *, channel_first=False, index_dtype=torch.int64):
+    """query [B,N1,3], key [B,N2,3] ([B,3,N1], [B,3,N2] with ``channel_first``) ->
+    [distance [B,N1,k] (squared), index [B,N1,k]]."""
     _check_cuda_contig(query=query, key=key)
+    pdim, cdim = _xyz_dims(channel_first)
     _check_eq(query.dim(), 3, "query.dim() == 3")
-    _check_eq(query.size(2), 3, "query.size(2) == 3")
+    _check_eq(query.size(cdim), 3, "query.size(%d) == 3" % cdim)
     _check_eq(key.dim(), 3, "key.dim() == 3")
     _check_eq(key.size(0), query.size(0), "key.size(0) == query.size(0)")
     k = int(k)
-    if not key.size(1) >= k:
-        raise RuntimeError("Check failed: key.size(1) >= k (%d vs. %d)" % (key.size(1), k))
-    _check_eq(key.size(2), 3, "key.size(2) == 3")
+    if not key.size(pdim) >= k:
+        raise RuntimeError("Check failed: key.size(%d) >= k (%d vs. %d)" % (pdim, key.size(pdim), k))
+    _check_eq(key.size(cdim), 3, "key.size(%d) == 3" % cdim)
     if version not in (0, 1):
         raise RuntimeError("Invalid version")
     _same_device_dtype(query, key, floats=(key,))
     lib = load()
-    B, N1, N2 = query.size(0), query.size(1), key.size(1)
+    B, N1, N2 = query.size(0), query.size(pdim), key.size(pdim)
     with _on(query.device):
         distance = torch.empty((B, N1, k), dtype=query.dtype, device=query.device)
-        index = torch.empty((B, N1, k), dtype=torch.int64, device=query.device)
-        check(lib.tk3d_knn(_ptr(query), _ptr(key), B, N1, N2, k, _ptr(distance), _ptr(index), _dtype(query),
-                           _stream(query)))
+        index = torch.empty((B, N1, k), dtype=index_dtype, device=query.device)
+        if channel_first or index_dtype != torch.int64:
+            check(lib.tk3d_knn_layout(_ptr(query), _ptr(key), B, N1, N2, k, 1 if channel_first else 0,
+                                      _ptr(distance), _ptr(index), _index_code(index_dtype), _dtype(query),
+                                      _stream(query)))
+        else:
+            check(lib.tk3d_knn(_ptr(query), _ptr(key), B, N1, N2, k, _ptr(distance), _ptr(index), _dtype(query),
+                               _stream(query)))
     return [distance, index]
 
 
@@ -285,8 +323,8 @@ def feature_knn_cuda(query, key, k, channel_first=True):
     return [distance, index]
 
 
-def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None):
-    """xyz1 [B,N1,3], xyz2 [B,N2,3] -> [dist1, idx1, dist2, idx2].
+def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None, *, channel_first=False):
+    """xyz1 [B,N1,3], xyz2 [B,N2,3] ([B,3,N1], [B,3,N2] with ``channel_first``) -> [dist1, idx1, dist2, idx2].
 
     ``sums`` (optional, a float64 CUDA tensor of 2 elements) receives sum(dist1), sum(dist2); it has
     no counterpart in the reference and is what the multi-GPU loss helper reduces.
@@ -295,11 +333,12 @@ def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None):
     _check_eq(xyz1.dim(), 3, "xyz1.dim() == 3")
     _check_eq(xyz2.dim(), 3, "xyz2.dim() == 3")
     _check_eq(xyz1.size(0), xyz2.size(0), "xyz1.size(0) == xyz2.size(0)")
-    _check_eq(xyz1.size(2), 3, "xyz1.size(2) == 3")
-    _check_eq(xyz2.size(2), 3, "xyz2.size(2) == 3")
+    pdim, cdim = _xyz_dims(channel_first)
+    _check_eq(xyz1.size(cdim), 3, "xyz1.size(%d) == 3" % cdim)
+    _check_eq(xyz2.size(cdim), 3, "xyz2.size(%d) == 3" % cdim)
     _same_device_dtype(xyz1, xyz2, floats=(xyz2,))
     lib = load()
-    B, N1, N2 = xyz1.size(0), xyz1.size(1), xyz2.size(1)
+    B, N1, N2 = xyz1.size(0), xyz1.size(pdim), xyz2.size(pdim)
     dev = xyz1.device
     with _on(dev):
         dist1 = torch.empty((B, N1), dtype=xyz1.dtype, device=dev)
@@ -309,23 +348,29 @@ def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None):
         if sums is not None:
             if not (sums.is_cuda and sums.dtype == torch.float64 and sums.numel() == 2 and sums.is_contiguous()):
                 raise RuntimeError("sums must be a contiguous float64 CUDA tensor with 2 elements")
-        check(lib.tk3d_chamfer_fwd(_ptr(xyz1), _ptr(xyz2), B, N1, N2, _ptr(dist1), _ptr(idx1), _ptr(dist2),
-                                   _ptr(idx2), _ptr(sums) if sums is not None else None, _dtype(xyz1),
-                                   _stream(xyz1)))
+        if channel_first:
+            check(lib.tk3d_chamfer_fwd_layout(_ptr(xyz1), _ptr(xyz2), B, N1, N2, 1, _ptr(dist1), _ptr(idx1),
+                                              _ptr(dist2), _ptr(idx2), _ptr(sums) if sums is not None else None,
+                                              _dtype(xyz1), _stream(xyz1)))
+        else:
+            check(lib.tk3d_chamfer_fwd(_ptr(xyz1), _ptr(xyz2), B, N1, N2, _ptr(dist1), _ptr(idx1), _ptr(dist2),
+                                       _ptr(idx2), _ptr(sums) if sums is not None else None, _dtype(xyz1),
+                                       _stream(xyz1)))
     return [dist1, idx1, dist2, idx2]
 
 
-def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2):
-    """-> [grad_xyz1 [B,N1,3], grad_xyz2 [B,N2,3]]."""
+def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, *, channel_first=False):
+    """-> [grad_xyz1 [B,N1,3], grad_xyz2 [B,N2,3]] (the clouds' own layout: [B,3,N] with ``channel_first``)."""
     _check_cuda_contig(grad_dist1=grad_dist1, grad_dist2=grad_dist2, xyz1=xyz1, xyz2=xyz2, idx1=idx1, idx2=idx2)
     bs, n1, n2 = grad_dist1.size(0), grad_dist1.size(1), grad_dist2.size(1)
     _check_eq(grad_dist2.size(0), bs, "grad_dist2.size(0) == bs")
     _check_eq(xyz1.size(0), bs, "xyz1.size(0) == bs")
     _check_eq(xyz2.size(0), bs, "xyz2.size(0) == bs")
-    _check_eq(xyz1.size(1), n1, "xyz1.size(1) == n1")
-    _check_eq(xyz2.size(1), n2, "xyz2.size(1) == n2")
-    _check_eq(xyz1.size(2), 3, "xyz1.size(2) == 3")
-    _check_eq(xyz2.size(2), 3, "xyz2.size(2) == 3")
+    pdim, cdim = _xyz_dims(channel_first)
+    _check_eq(xyz1.size(pdim), n1, "xyz1.size(%d) == n1" % pdim)
+    _check_eq(xyz2.size(pdim), n2, "xyz2.size(%d) == n2" % pdim)
+    _check_eq(xyz1.size(cdim), 3, "xyz1.size(%d) == 3" % cdim)
+    _check_eq(xyz2.size(cdim), 3, "xyz2.size(%d) == 3" % cdim)
     _check_eq(idx1.size(0), bs, "idx1.size(0) == bs")
     _check_eq(idx2.size(0), bs, "idx2.size(0) == bs")
     _check_eq(idx1.size(1), n1, "idx1.size(1) == n1")
@@ -336,11 +381,16 @@ def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx
     lib = load()
     dev = grad_dist1.device
     with _on(dev):
-        g1 = torch.empty((bs, n1, 3), dtype=grad_dist1.dtype, device=dev)
-        g2 = torch.empty((bs, n2, 3), dtype=grad_dist1.dtype, device=dev)
-        check(lib.tk3d_chamfer_bwd(_ptr(grad_dist1), _ptr(grad_dist2), _ptr(xyz1), _ptr(xyz2), _ptr(idx1),
-                                   _ptr(idx2), bs, n1, n2, _ptr(g1), _ptr(g2), _dtype(grad_dist1),
-                                   _stream(grad_dist1)))
+        g1 = torch.empty_like(xyz1)
+        g2 = torch.empty_like(xyz2)
+        if channel_first:
+            check(lib.tk3d_chamfer_bwd_layout(_ptr(grad_dist1), _ptr(grad_dist2), _ptr(xyz1), _ptr(xyz2), _ptr(idx1),
+                                              _ptr(idx2), bs, n1, n2, 1, _ptr(g1), _ptr(g2), _dtype(grad_dist1),
+                                              _stream(grad_dist1)))
+        else:
+            check(lib.tk3d_chamfer_bwd(_ptr(grad_dist1), _ptr(grad_dist2), _ptr(xyz1), _ptr(xyz2), _ptr(idx1),
+                                       _ptr(idx2), bs, n1, n2, _ptr(g1), _ptr(g2), _dtype(grad_dist1),
+                                       _stream(grad_dist1)))
     return [g1, g2]
 
 

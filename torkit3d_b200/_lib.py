@@ -10,6 +10,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtk3d_b200.so")
 
 F32, F64 = 0, 1
+I64, I32 = 0, 1
 
 _i64 = ctypes.c_int64
 _vp = ctypes.c_void_p
@@ -62,6 +63,14 @@ SIGNATURES = {
     "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
     "tk3d_feature_knn": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _int, _vp]),
     "tk3d_chamfer_fwd_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _int]),
+    # layout variants: [B,3,N] coordinates read in place, optional int32 index tensors
+    "tk3d_chamfer_fwd_layout": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
+    "tk3d_chamfer_bwd_layout": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _int, _vp]),
+    "tk3d_chamfer_bwd_mean_layout": (_int, [_vp, ctypes.c_double, ctypes.c_double, _vp, _vp, _vp, _vp, _i64, _i64,
+                                            _i64, _int, _vp, _vp, _int, _vp]),
+    "tk3d_knn_layout": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _int, _int, _vp]),
+    "tk3d_fps_layout": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, ctypes.c_size_t, _int, _vp]),
+    "tk3d_ball_query_layout": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _i64, _int, _vp, _int, _int, _vp]),
 }
 
 _lib = None

@@ -2,6 +2,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "tk3d_common.cuh"
 
 namespace tk3d {
@@ -29,6 +31,43 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+// cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), issued only when
+// this (kernel, device) pair has not been given at least `bytes` yet.  The attribute sticks to the
+// function for the life of the context, and re-issuing it on every call costs host time that the
+// small, launch-bound operators notice.  A fixed table with a mutex: a few dozen kernels exist.
+cudaError_t raise_smem_limit(const void *func, int bytes) {
+  struct Entry {
+    const void *func;
+    int dev;
+    int bytes;
+  };
+  constexpr int CAP = 256;
+  static Entry table[CAP];
+  static int used = 0;
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  Entry *slot = nullptr;
+  for (int i = 0; i < used; ++i)
+    if (table[i].func == func && table[i].dev == dev) {
+      slot = &table[i];
+      break;
+    }
+  if (slot && slot->bytes >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return e;
+  if (!slot && used < CAP) {
+    slot = &table[used++];
+    slot->func = func;
+    slot->dev = dev;
+    slot->bytes = 0;
+  }
+  if (slot) slot->bytes = bytes;
+  return cudaSuccess;
 }
 
 }  // namespace tk3d

@@ -17,7 +17,7 @@ constexpr int BQ_TILE = 512;
 
 __global__ void __launch_bounds__(BQ_THREADS)
 ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
-                       float r2, int k, int64_t *__restrict__ index, int64_t blocks_total) {
+                       float r2, int k, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int PER = BQ_TILE / BQ_THREADS;
   __shared__ float4 tile[2][BQ_TILE];
   const int tid = threadIdx.x;
@@ -28,19 +28,14 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
     const int i = (int)(blk % chunks) * BQ_THREADS + tid;
     const bool valid = i < N1;
     float qx = 0.f, qy = 0.f, qz = 0.f;
-    if (valid) {
-      const float *q = query + (b * N1 + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
-    }
+    if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
     const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
                  mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
     const float never = __int_as_float(0xff800000);
     float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
     int cnt = 0;
     int64_t first = -1;
-    int64_t *row = index + (b * N1 + (valid ? i : 0)) * (int64_t)k;
+    const int64_t row = (b * N1 + (valid ? i : 0)) * (int64_t)k;  // offset of this query's output row
 
     const float *rb = key + b * (int64_t)N2 * 3;
     const int ntiles = (N2 + BQ_TILE - 1) / BQ_TILE;
@@ -49,7 +44,8 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
       const int u = tid + p * BQ_THREADS;
       float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
       if (u < N2) {
-        const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
+        float x, y, z;
+        load_xyz(rb, u, kl, x, y, z);
         v = make_float4(x, y, z, sweep_key_w(x, y, z));
       }
       sweep_store_key(tile[0], u, v.x, v.y, v.z, v.w);
@@ -67,7 +63,8 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
           const int j = t0 + BQ_TILE + tid + p * BQ_THREADS;
           float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
           if (j < N2) {
-            const float x = rb[(int64_t)j * 3 + 0], y = rb[(int64_t)j * 3 + 1], z = rb[(int64_t)j * 3 + 2];
+            float x, y, z;
+            load_xyz(rb, j, kl, x, y, z);
             v = make_float4(x, y, z, sweep_key_w(x, y, z));
           }
           nxt[p] = v;
@@ -86,7 +83,7 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
               const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {
-                row[cnt] = j;
+                index.put(row + cnt, j);
                 if (cnt == 0) first = j;
                 if (++cnt == k) thr[0] = never;
               }
@@ -103,7 +100,7 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
       if (__syncthreads_and(!valid || cnt == k)) break;
     }
     if (valid)
-      for (int c = cnt; c < k; ++c) row[c] = first;
+      for (int c = cnt; c < k; ++c) index.put(row + c, first);
     __syncthreads();
   }
 }
@@ -119,7 +116,7 @@ constexpr int BS_MAX_K = 64;
 
 __global__ void __launch_bounds__(BQ_THREADS)
 ball_query_split_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
-                        float r2, int k, int64_t *__restrict__ index, int64_t blocks_total) {
+                        float r2, int k, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int PER = BS_TILE / BQ_THREADS;
   constexpr int QK = BS_TILE / BS_SPLIT;  // keys per warp per tile
   __shared__ float4 tile[2][BS_TILE];
@@ -134,12 +131,7 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
     const int i = (int)(blk % chunks) * 32 + lane;
     const bool valid = i < N1;
     float qx = 0.f, qy = 0.f, qz = 0.f;
-    if (valid) {
-      const float *q = query + (b * N1 + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
-    }
+    if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
     const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
                  mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
     float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
@@ -155,7 +147,8 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
         const int j = t0 + tid + p * BQ_THREADS;
         float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
         if (j < N2) {
-          const float x = rb[(int64_t)j * 3 + 0], y = rb[(int64_t)j * 3 + 1], z = rb[(int64_t)j * 3 + 2];
+          float x, y, z;
+          load_xyz(rb, j, kl, x, y, z);
           v = make_float4(x, y, z, sweep_key_w(x, y, z));
         }
         nxt[p] = v;
@@ -199,7 +192,7 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
 
     // Merge: warp 0, lane = query.  Heads of the four ascending lists, smallest key index first.
     if (part == 0 && valid) {
-      int64_t *row = index + (b * N1 + i) * (int64_t)k;
+      const int64_t row = (b * N1 + i) * (int64_t)k;
       int pos[BS_SPLIT], n[BS_SPLIT];
 #pragma unroll
       for (int s = 0; s < BS_SPLIT; ++s) {
@@ -225,9 +218,9 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
         for (int s = 0; s < BS_SPLIT; ++s)
           if (s == bs) ++pos[s];
         if (out == 0) first = best;
-        row[out++] = best;
+        index.put(row + out++, best);
       }
-      for (int c = out; c < k; ++c) row[c] = first;
+      for (int c = out; c < k; ++c) index.put(row + c, first);
     }
     __syncthreads();
   }
@@ -236,7 +229,7 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
 template <typename T>
 __global__ void __launch_bounds__(256)
 ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
-                          T r2, int64_t k, int64_t *__restrict__ index, int64_t blocks_total) {
+                          T r2, int64_t k, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int TILE = 256;
   __shared__ T sx[TILE], sy[TILE], sz[TILE];
   const int tid = threadIdx.x;
@@ -246,29 +239,20 @@ ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key
     const int64_t i = (blk % chunks) * TILE + tid;
     const bool valid = i < N1;
     T qx = 0, qy = 0, qz = 0;
-    if (valid) {
-      const T *q = query + (b * N1 + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
-    }
-    int64_t *row = index + (b * N1 + (valid ? i : 0)) * k;
+    if (valid) load_xyz(query + b * 3 * N1, i, ql, qx, qy, qz);
+    const int64_t row = (b * N1 + (valid ? i : 0)) * k;
     int64_t cnt = 0, first = -1;
     const T *rb = key + b * N2 * 3;
     for (int64_t t0 = 0; t0 < N2; t0 += TILE) {
       const int64_t jl = t0 + tid;
-      if (jl < N2) {
-        sx[tid] = rb[jl * 3 + 0];
-        sy[tid] = rb[jl * 3 + 1];
-        sz[tid] = rb[jl * 3 + 2];
-      }
+      if (jl < N2) load_xyz(rb, jl, kl, sx[tid], sy[tid], sz[tid]);
       __syncthreads();
       const int lim = (int)((N2 - t0) < TILE ? (N2 - t0) : TILE);
       if (valid && cnt < k) {
         for (int u = 0; u < lim && cnt < k; ++u) {
           const T d = sqdist<T>(sx[u], sy[u], sz[u], qx, qy, qz);
           if (d < r2) {
-            row[cnt] = t0 + u;
+            index.put(row + cnt, t0 + u);
             if (cnt == 0) first = t0 + u;
             ++cnt;
           }
@@ -277,7 +261,7 @@ ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key
       if (__syncthreads_and(!valid || cnt == k)) break;
     }
     if (valid)
-      for (int64_t c = cnt; c < k; ++c) row[c] = first;
+      for (int64_t c = cnt; c < k; ++c) index.put(row + c, first);
     __syncthreads();
   }
 }
@@ -287,8 +271,8 @@ ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key
 
 using namespace tk3d;
 
-extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
-                               int64_t k, int64_t *index, int dtype, void *stream) {
+static int ball_query_impl(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
+                           int64_t k, int channel_first, void *index, int index32, int dtype, void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "ball_query: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "ball_query: negative size");
   TK3D_REQUIRE(k >= 1 && k < (1LL << 31), TK3D_ERR_K, "ball_query: max_neighbors must be >= 1 (got %lld)",
@@ -297,6 +281,8 @@ extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, in
   if (B * N1 == 0) return TK3D_OK;
   TK3D_REQUIRE(query && index && (key || N2 == 0), TK3D_ERR_NULL, "ball_query: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
+  const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
+  const IndexOut io = index_out(index, index32);
   if (dtype == TK3D_F32) {
     const float r2 = radius * radius;  // squared in fp32, as the reference does for float tensors
     const int64_t cap = (int64_t)sm_count() * 256;
@@ -304,18 +290,32 @@ extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, in
       const int64_t total = B * ((N1 + 31) / 32);
       const size_t smem = sizeof(int) * BS_SPLIT * (size_t)k * 32;
       ball_query_split_kernel<<<(unsigned)(total < cap ? total : cap), BQ_THREADS, smem, st>>>(
-          (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, index, total);
+          (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, io, total, ql, kl);
       return check_launch("ball_query_split_kernel");
     }
     const int64_t total = B * ((N1 + BQ_THREADS - 1) / BQ_THREADS);
     ball_query_fast_kernel<<<(unsigned)(total < cap ? total : cap), BQ_THREADS, 0, st>>>(
-        (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, index, total);
+        (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, io, total, ql, kl);
     return check_launch("ball_query_fast_kernel");
   }
   const double r = (double)radius;
   const int64_t total = B * ((N1 + 255) / 256);
   const int64_t cap = (int64_t)sm_count() * 64;
   ball_query_generic_kernel<double><<<(unsigned)(total < cap ? total : cap), 256, 0, st>>>(
-      (const double *)query, (const double *)key, B, N1, N2, r * r, k, index, total);
+      (const double *)query, (const double *)key, B, N1, N2, r * r, k, io, total, ql, kl);
   return check_launch("ball_query_generic_kernel");
+}
+
+extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
+                               int64_t k, int64_t *index, int dtype, void *stream) {
+  return ball_query_impl(query, key, B, N1, N2, radius, k, 0, index, 0, dtype, stream);
+}
+
+extern "C" int tk3d_ball_query_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2,
+                                      float radius, int64_t k, int xyz_channel_first, void *index, int index_dtype,
+                                      int dtype, void *stream) {
+  TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "ball_query: index_dtype %d",
+               index_dtype);
+  return ball_query_impl(query, key, B, N1, N2, radius, k, xyz_channel_first != 0, index, index_dtype == TK3D_I32,
+                         dtype, stream);
 }

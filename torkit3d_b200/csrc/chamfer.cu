@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(256)
 chamfer_fwd_generic_kernel(const T *__restrict__ xyz1, const T *__restrict__ xyz2, int64_t B, int64_t N1,
                            int64_t N2, T *__restrict__ dist1, int64_t *__restrict__ idx1, T *__restrict__ dist2,
                            int64_t *__restrict__ idx2, double *__restrict__ sums, int64_t blocks1,
-                           int64_t blocks_total) {
+                           int64_t blocks_total, XyzLayout l1, XyzLayout l2) {
   constexpr int TILE = 256;
   __shared__ T sx[TILE], sy[TILE], sz[TILE];
   __shared__ double ssum[8];
@@ -28,6 +28,7 @@ chamfer_fwd_generic_kernel(const T *__restrict__ xyz1, const T *__restrict__ xyz
     const T *rpts = dir ? xyz1 : xyz2;
     const int64_t nq = dir ? N2 : N1;
     const int64_t nr = dir ? N1 : N2;
+    const XyzLayout lq = dir ? l2 : l1, lr = dir ? l1 : l2;
     T *dist = dir ? dist2 : dist1;
     int64_t *idx = dir ? idx2 : idx1;
     const int64_t chunks = (nq + TILE - 1) / TILE;
@@ -36,22 +37,13 @@ chamfer_fwd_generic_kernel(const T *__restrict__ xyz1, const T *__restrict__ xyz
     const bool valid = i < nq;
 
     T qx = 0, qy = 0, qz = 0;
-    if (valid) {
-      const T *q = qpts + (b * nq + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
-    }
+    if (valid) load_xyz(qpts + b * nq * 3, i, lq, qx, qy, qz);
     T best = Exact<T>::inf();
     int64_t arg = -1;
     const T *rb = rpts + b * nr * 3;
     for (int64_t t0 = 0; t0 < nr; t0 += TILE) {
       const int64_t j = t0 + tid;
-      if (j < nr) {
-        sx[tid] = rb[j * 3 + 0];
-        sy[tid] = rb[j * 3 + 1];
-        sz[tid] = rb[j * 3 + 2];
-      }
+      if (j < nr) load_xyz(rb, j, lr, sx[tid], sy[tid], sz[tid]);
       __syncthreads();
       const int lim = (int)((nr - t0) < TILE ? (nr - t0) : TILE);
       for (int u = 0; u < lim; ++u) {
@@ -93,30 +85,32 @@ __global__ void __launch_bounds__(256)
 chamfer_bwd_own_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const T *__restrict__ xyz1,
                        const T *__restrict__ xyz2, const int64_t *__restrict__ idx1,
                        const int64_t *__restrict__ idx2, int64_t B, int64_t N1, int64_t N2, T *__restrict__ grad1,
-                       T *__restrict__ grad2, int gstride, T scale1, T scale2) {
+                       T *__restrict__ grad2, int gstride, T scale1, T scale2, XyzLayout l1, XyzLayout l2) {
   const int64_t tot1 = B * N1, total = B * (N1 + N2);
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int dir = t >= tot1;
     const int64_t lin = dir ? t - tot1 : t;
     const int64_t na = dir ? N2 : N1, nb = dir ? N1 : N2;
+    const XyzLayout la = dir ? l2 : l1, lb = dir ? l1 : l2;
     const T *a = dir ? xyz2 : xyz1;
     const T *bb = dir ? xyz1 : xyz2;
-    const int64_t b = lin / na;
+    const int64_t b = lin / na, i = lin - b * na;
     const int64_t j = (dir ? idx2 : idx1)[lin];
-    T *ga = (dir ? grad2 : grad1) + lin * 3;
+    T *ga = (dir ? grad2 : grad1) + b * na * 3 + i * la.ps;  // gradients share their cloud's layout
     if (j < 0 || j >= nb) {
       ga[0] = 0;
-      ga[1] = 0;
-      ga[2] = 0;
+      ga[la.cs] = 0;
+      ga[2 * (int64_t)la.cs] = 0;
       continue;
     }
     // gstride 0: one upstream value for the whole cloud set; scale is 1 for per-point gradients
     const T g = (dir ? g2 : g1)[lin * gstride] * (dir ? scale2 : scale1) * (T)2;
-    const T *p = a + lin * 3;
-    const T *q = bb + (b * nb + j) * 3;
-    ga[0] = g * (p[0] - q[0]);
-    ga[1] = g * (p[1] - q[1]);
-    ga[2] = g * (p[2] - q[2]);
+    T px, py, pz, qx, qy, qz;
+    load_xyz(a + b * na * 3, i, la, px, py, pz);
+    load_xyz(bb + b * nb * 3, j, lb, qx, qy, qz);
+    ga[0] = g * (px - qx);
+    ga[la.cs] = g * (py - qy);
+    ga[2 * (int64_t)la.cs] = g * (pz - qz);
   }
 }
 
@@ -142,56 +136,67 @@ __global__ void __launch_bounds__(256)
 chamfer_bwd_scatter_kernel(const T *__restrict__ g1, const T *__restrict__ g2, const T *__restrict__ xyz1,
                            const T *__restrict__ xyz2, const int64_t *__restrict__ idx1,
                            const int64_t *__restrict__ idx2, int64_t B, int64_t N1, int64_t N2, T *grad1, T *grad2,
-                           int gstride, T scale1, T scale2) {
+                           int gstride, T scale1, T scale2, XyzLayout l1, XyzLayout l2) {
   const int64_t tot1 = B * N1, total = B * (N1 + N2);
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
     const int dir = t >= tot1;
     const int64_t lin = dir ? t - tot1 : t;
     const int64_t na = dir ? N2 : N1, nb = dir ? N1 : N2;
+    const XyzLayout la = dir ? l2 : l1, lb = dir ? l1 : l2;
     const T *a = dir ? xyz2 : xyz1;
     const T *bb = dir ? xyz1 : xyz2;
-    const int64_t b = lin / na;
+    const int64_t b = lin / na, i = lin - b * na;
     const int64_t j = (dir ? idx2 : idx1)[lin];
     if (j < 0 || j >= nb) continue;
     // gstride 0: one upstream value for the whole cloud set; scale is 1 for per-point gradients
     const T g = (dir ? g2 : g1)[lin * gstride] * (dir ? scale2 : scale1) * (T)2;
-    const T *p = a + lin * 3;
-    const T *q = bb + (b * nb + j) * 3;
-    T *gb = (dir ? grad1 : grad2) + (b * nb + j) * 3;
-    red_add3(gb, -(g * (p[0] - q[0])), -(g * (p[1] - q[1])), -(g * (p[2] - q[2])));
+    T px, py, pz, qx, qy, qz;
+    load_xyz(a + b * na * 3, i, la, px, py, pz);
+    load_xyz(bb + b * nb * 3, j, lb, qx, qy, qz);
+    T *gb = (dir ? grad1 : grad2) + b * nb * 3 + j * lb.ps;
+    if (lb.cs == 1) {
+      red_add3(gb, -(g * (px - qx)), -(g * (py - qy)), -(g * (pz - qz)));
+    } else {
+      atomicAdd(gb, -(g * (px - qx)));
+      atomicAdd(gb + lb.cs, -(g * (py - qy)));
+      atomicAdd(gb + 2 * (int64_t)lb.cs, -(g * (pz - qz)));
+    }
   }
 }
 
 int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_t N1, int64_t N2, float *dist1,
-                         int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st);
+                         int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1,
+                         XyzLayout l2);
 
 template <typename T>
 static int chamfer_fwd_generic(const T *xyz1, const T *xyz2, int64_t B, int64_t N1, int64_t N2, T *dist1,
-                               int64_t *idx1, T *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+                               int64_t *idx1, T *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1,
+                               XyzLayout l2) {
   const int64_t blocks1 = B * ((N1 + 255) / 256), blocks2 = B * ((N2 + 255) / 256);
   const int64_t total = blocks1 + blocks2;
   if (total == 0) return TK3D_OK;
   const int64_t cap = (int64_t)sm_count() * 64;
   const unsigned grid = (unsigned)(total < cap ? total : cap);
   chamfer_fwd_generic_kernel<T><<<grid, 256, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
-                                                       blocks1, total);
+                                                       blocks1, total, l1, l2);
   return check_launch("chamfer_fwd_generic_kernel");
 }
 
 template <typename T>
 static int chamfer_bwd_t(const T *g1, const T *g2, const T *xyz1, const T *xyz2, const int64_t *idx1,
                          const int64_t *idx2, int64_t B, int64_t N1, int64_t N2, T *grad1, T *grad2,
-                         cudaStream_t st, int gstride = 1, T scale1 = (T)1, T scale2 = (T)1) {
+                         cudaStream_t st, int channel_first, int gstride = 1, T scale1 = (T)1, T scale2 = (T)1) {
   const int64_t total = B * (N1 + N2);
+  const XyzLayout l1 = xyz_layout(channel_first, N1), l2 = xyz_layout(channel_first, N2);
   if (total == 0) return TK3D_OK;
   const int64_t want = (total + 255) / 256, cap = (int64_t)sm_count() * 32;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   chamfer_bwd_own_kernel<T><<<grid, 256, 0, st>>>(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, grad1, grad2, gstride,
-                                                  scale1, scale2);
+                                                  scale1, scale2, l1, l2);
   int rc = check_launch("chamfer_bwd_own_kernel");
   if (rc) return rc;
   chamfer_bwd_scatter_kernel<T><<<grid, 256, 0, st>>>(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, grad1, grad2,
-                                                      gstride, scale1, scale2);
+                                                      gstride, scale1, scale2, l1, l2);
   return check_launch("chamfer_bwd_scatter_kernel");
 }
 
@@ -219,9 +224,9 @@ extern "C" int tk3d_chamfer_mean_loss(const double *sums, double count1, double 
   return check_launch("chamfer_mean_loss_kernel");
 }
 
-extern "C" int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, double count2, const void *xyz1,
-                                     const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B,
-                                     int64_t N1, int64_t N2, void *grad1, void *grad2, int dtype, void *stream) {
+static int chamfer_bwd_mean_impl(const void *grad_loss, double count1, double count2, const void *xyz1,
+                                 const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1,
+                                 int64_t N2, int channel_first, void *grad1, void *grad2, int dtype, void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_bwd_mean: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "chamfer_bwd_mean: negative size");
   TK3D_REQUIRE(count1 > 0 && count2 > 0, TK3D_ERR_SHAPE, "chamfer_bwd_mean: counts must be positive");
@@ -231,11 +236,26 @@ extern "C" int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, doubl
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == TK3D_F32)
     return chamfer_bwd_t<float>((const float *)grad_loss, (const float *)grad_loss, (const float *)xyz1,
-                                (const float *)xyz2, idx1, idx2, B, N1, N2, (float *)grad1, (float *)grad2, st, 0,
-                                (float)(1.0 / count1), (float)(1.0 / count2));
+                                (const float *)xyz2, idx1, idx2, B, N1, N2, (float *)grad1, (float *)grad2, st,
+                                channel_first, 0, (float)(1.0 / count1), (float)(1.0 / count2));
   return chamfer_bwd_t<double>((const double *)grad_loss, (const double *)grad_loss, (const double *)xyz1,
-                               (const double *)xyz2, idx1, idx2, B, N1, N2, (double *)grad1, (double *)grad2, st, 0,
-                               1.0 / count1, 1.0 / count2);
+                               (const double *)xyz2, idx1, idx2, B, N1, N2, (double *)grad1, (double *)grad2, st,
+                               channel_first, 0, 1.0 / count1, 1.0 / count2);
+}
+
+extern "C" int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, double count2, const void *xyz1,
+                                     const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B,
+                                     int64_t N1, int64_t N2, void *grad1, void *grad2, int dtype, void *stream) {
+  return chamfer_bwd_mean_impl(grad_loss, count1, count2, xyz1, xyz2, idx1, idx2, B, N1, N2, 0, grad1, grad2, dtype,
+                               stream);
+}
+
+extern "C" int tk3d_chamfer_bwd_mean_layout(const void *grad_loss, double count1, double count2, const void *xyz1,
+                                            const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B,
+                                            int64_t N1, int64_t N2, int xyz_channel_first, void *grad1, void *grad2,
+                                            int dtype, void *stream) {
+  return chamfer_bwd_mean_impl(grad_loss, count1, count2, xyz1, xyz2, idx1, idx2, B, N1, N2, xyz_channel_first != 0,
+                               grad1, grad2, dtype, stream);
 }
 
 namespace tk3d {
@@ -247,8 +267,9 @@ extern "C" const char *tk3d_chamfer_fwd_kernel_name(int64_t B, int64_t N1, int64
   return chamfer_fwd_f32_kernel_name(B < 0 ? 0 : B, N1 < 0 ? 0 : N1, N2 < 0 ? 0 : N2);
 }
 
-extern "C" int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, void *dist1,
-                                int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype, void *stream) {
+static int chamfer_fwd_impl(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, int channel_first,
+                            void *dist1, int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype,
+                            void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_fwd: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "chamfer_fwd: negative size (B=%lld N1=%lld N2=%lld)",
                (long long)B, (long long)N1, (long long)N2);
@@ -257,16 +278,29 @@ extern "C" int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, i
   TK3D_REQUIRE(B * N2 == 0 || (xyz2 && dist2 && idx2), TK3D_ERR_NULL, "chamfer_fwd: xyz2/dist2/idx2 is NULL");
   cudaStream_t st = (cudaStream_t)stream;
   if (sums) TK3D_CUDA(cudaMemsetAsync(sums, 0, 2 * sizeof(double), st));
+  const XyzLayout l1 = xyz_layout(channel_first, N1), l2 = xyz_layout(channel_first, N2);
   if (dtype == TK3D_F32)
     return chamfer_fwd_f32_fast((const float *)xyz1, (const float *)xyz2, B, N1, N2, (float *)dist1, idx1,
-                                (float *)dist2, idx2, sums, st);
+                                (float *)dist2, idx2, sums, st, l1, l2);
   return chamfer_fwd_generic<double>((const double *)xyz1, (const double *)xyz2, B, N1, N2, (double *)dist1, idx1,
-                                     (double *)dist2, idx2, sums, st);
+                                     (double *)dist2, idx2, sums, st, l1, l2);
 }
 
-extern "C" int tk3d_chamfer_bwd(const void *g1, const void *g2, const void *xyz1, const void *xyz2,
-                                const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
-                                void *grad1, void *grad2, int dtype, void *stream) {
+extern "C" int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, void *dist1,
+                                int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype, void *stream) {
+  return chamfer_fwd_impl(xyz1, xyz2, B, N1, N2, 0, dist1, idx1, dist2, idx2, sums, dtype, stream);
+}
+
+extern "C" int tk3d_chamfer_fwd_layout(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2,
+                                       int xyz_channel_first, void *dist1, int64_t *idx1, void *dist2, int64_t *idx2,
+                                       double *sums, int dtype, void *stream) {
+  return chamfer_fwd_impl(xyz1, xyz2, B, N1, N2, xyz_channel_first != 0, dist1, idx1, dist2, idx2, sums, dtype,
+                          stream);
+}
+
+static int chamfer_bwd_impl(const void *g1, const void *g2, const void *xyz1, const void *xyz2, const int64_t *idx1,
+                            const int64_t *idx2, int64_t B, int64_t N1, int64_t N2, int channel_first, void *grad1,
+                            void *grad2, int dtype, void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_bwd: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "chamfer_bwd: negative size");
   TK3D_REQUIRE(B * N1 == 0 || (g1 && xyz1 && idx1 && grad1), TK3D_ERR_NULL, "chamfer_bwd: a cloud-1 pointer is NULL");
@@ -274,7 +308,20 @@ extern "C" int tk3d_chamfer_bwd(const void *g1, const void *g2, const void *xyz1
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == TK3D_F32)
     return chamfer_bwd_t<float>((const float *)g1, (const float *)g2, (const float *)xyz1, (const float *)xyz2, idx1,
-                                idx2, B, N1, N2, (float *)grad1, (float *)grad2, st);
+                                idx2, B, N1, N2, (float *)grad1, (float *)grad2, st, channel_first);
   return chamfer_bwd_t<double>((const double *)g1, (const double *)g2, (const double *)xyz1, (const double *)xyz2,
-                               idx1, idx2, B, N1, N2, (double *)grad1, (double *)grad2, st);
+                               idx1, idx2, B, N1, N2, (double *)grad1, (double *)grad2, st, channel_first);
+}
+
+extern "C" int tk3d_chamfer_bwd(const void *g1, const void *g2, const void *xyz1, const void *xyz2,
+                                const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
+                                void *grad1, void *grad2, int dtype, void *stream) {
+  return chamfer_bwd_impl(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, 0, grad1, grad2, dtype, stream);
+}
+
+extern "C" int tk3d_chamfer_bwd_layout(const void *g1, const void *g2, const void *xyz1, const void *xyz2,
+                                       const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
+                                       int xyz_channel_first, void *grad1, void *grad2, int dtype, void *stream) {
+  return chamfer_bwd_impl(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, xyz_channel_first != 0, grad1, grad2, dtype,
+                          stream);
 }

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(CF_THREADS, MINB)
 chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int64_t B, int N1, int N2,
                         float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
                         int64_t *__restrict__ idx2, double *__restrict__ sums, int64_t blocks1,
-                        int64_t blocks_total) {
+                        int64_t blocks_total, XyzLayout l1, XyzLayout l2) {
   constexpr int PER = CF_TILE / CF_THREADS;
   constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
   __shared__ float4 tile[2][CF_TILE];
@@ -81,6 +81,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
     const float *rpts = dir ? xyz1 : xyz2;
     const int nq = dir ? N2 : N1;
     const int nr = dir ? N1 : N2;
+    const XyzLayout lq = dir ? l2 : l1, lr = dir ? l1 : l2;
     const int chunks = (nq + CF_THREADS * Q - 1) / (CF_THREADS * Q);
     const int64_t b = id / chunks;
     const int i0 = (int)(id % chunks) * (CF_THREADS * Q) + tid;
@@ -94,10 +95,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
       best[s] = pinf;
       arg[s] = -1;
       if (i < nq) {
-        const float *q = qpts + (b * nq + i) * 3;
-        qx[s] = q[0];
-        qy[s] = q[1];
-        qz[s] = q[2];
+        load_xyz(qpts + b * 3 * (int64_t)nq, i, lq, qx[s], qy[s], qz[s]);
         thr[s] = pinf;  // accept everything until a first candidate is verified (minima-based test)
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
@@ -117,7 +115,8 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
       for (int p = 0; p < PER; ++p) {
         const int u = tid + p * CF_THREADS;
         if (u < nr) {
-          const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
+          float x, y, z;
+          load_xyz(rb, u, lr, x, y, z);
           sweep_store_key(tile[0], u, x, y, z, sweep_key_w(x, y, z));
         } else {
           sweep_store_key(tile[0], u, 0.f, 0.f, 0.f, pinf);
@@ -139,9 +138,7 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         for (int p = 0; p < PER; ++p) {
           const int j = t0 + CF_TILE + tid + p * CF_THREADS;
           if (j < nr) {
-            px[p] = rb[(int64_t)j * 3 + 0];
-            py[p] = rb[(int64_t)j * 3 + 1];
-            pz[p] = rb[(int64_t)j * 3 + 2];
+            load_xyz(rb, j, lr, px[p], py[p], pz[p]);
           } else {
             px[p] = py[p] = pz[p] = 0.f;
           }
@@ -202,15 +199,15 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
 
 template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128>
 int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
-           float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+           float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1, XyzLayout l2) {
   const int64_t per = CF_THREADS * Q;
   const int64_t blocks1 = B * ((N1 + per - 1) / per), blocks2 = B * ((N2 + per - 1) / per);
   const int64_t total = blocks1 + blocks2;
   if (total == 0) return TK3D_OK;
   const int64_t cap = (int64_t)sm_count() * 256;
   const unsigned grid = (unsigned)(total < cap ? total : cap);
-  chamfer_fwd_fast_kernel<Q, MINB, UNR, CF_THREADS><<<grid, CF_THREADS, 0, st>>>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums,
-                                                           blocks1, total);
+  chamfer_fwd_fast_kernel<Q, MINB, UNR, CF_THREADS><<<grid, CF_THREADS, 0, st>>>(
+      xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums, blocks1, total, l1, l2);
   return check_launch("chamfer_fwd_fast_kernel");
 }
 
@@ -231,7 +228,7 @@ __global__ void __launch_bounds__(896, 1)
 chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int N1, int N2,
                           float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
                           int64_t *__restrict__ idx2, double *__restrict__ sums, int blocks1,
-                          int blocks_total) {
+                          int blocks_total, XyzLayout l1, XyzLayout l2) {
   constexpr int Q = 2, TH = 128;
   constexpr int PER = CF_TILE / TH;
   extern __shared__ float4 group_tiles[];  // [groups][2][CF_TILE]
@@ -249,6 +246,7 @@ chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restric
     const float *rpts = dir ? xyz1 : xyz2;
     const int nq = dir ? N2 : N1;
     const int nr = dir ? N1 : N2;
+    const XyzLayout lq = dir ? l2 : l1, lr = dir ? l1 : l2;
     const int chunks = (nq + TH * Q - 1) / (TH * Q);
     const int64_t b = id / chunks;
     const int i0 = (id % chunks) * (TH * Q) + tid;
@@ -262,10 +260,7 @@ chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restric
       best[s] = pinf;
       arg[s] = -1;
       if (i < nq) {
-        const float *q = qpts + (b * nq + i) * 3;
-        qx[s] = q[0];
-        qy[s] = q[1];
-        qz[s] = q[2];
+        load_xyz(qpts + b * 3 * (int64_t)nq, i, lq, qx[s], qy[s], qz[s]);
         thr[s] = pinf;  // accept everything until a first candidate is verified
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
@@ -283,7 +278,8 @@ chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restric
       for (int p = 0; p < PER; ++p) {
         const int u = tid + p * TH;
         if (u < nr) {
-          const float x = rb[u * 3 + 0], y = rb[u * 3 + 1], z = rb[u * 3 + 2];
+          float x, y, z;
+          load_xyz(rb, u, lr, x, y, z);
           sweep_store_key(tile[0], u, x, y, z, sweep_key_w(x, y, z));
         } else {
           sweep_store_key(tile[0], u, 0.f, 0.f, 0.f, pinf);
@@ -304,9 +300,7 @@ chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restric
         for (int p = 0; p < PER; ++p) {
           const int j = t0 + CF_TILE + tid + p * TH;
           if (j < nr) {
-            px[p] = rb[(int64_t)j * 3 + 0];
-            py[p] = rb[(int64_t)j * 3 + 1];
-            pz[p] = rb[(int64_t)j * 3 + 2];
+            load_xyz(rb, j, lr, px[p], py[p], pz[p]);
           } else {
             px[p] = py[p] = pz[p] = 0.f;
           }
@@ -358,16 +352,15 @@ chamfer_fwd_smwide_kernel(const float *__restrict__ xyz1, const float *__restric
 constexpr int SMWIDE_GROUPS = 7;
 
 int launch_smwide(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
-                  float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+                  float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1, XyzLayout l2) {
   const int64_t blocks1 = B * ((N1 + 255) / 256), blocks2 = B * ((N2 + 255) / 256);
   const int64_t total = blocks1 + blocks2;
   const size_t smem = (size_t)SMWIDE_GROUPS * 2 * CF_TILE * sizeof(float4);  // 112 KB
-  TK3D_CUDA(cudaFuncSetAttribute(chamfer_fwd_smwide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
+  TK3D_CUDA(raise_smem_limit((const void *)chamfer_fwd_smwide_kernel<4>, (int)smem));
   const int64_t blocks = (total + SMWIDE_GROUPS - 1) / SMWIDE_GROUPS;
   const int64_t cap = sm_count();
   chamfer_fwd_smwide_kernel<4><<<(unsigned)(blocks < cap ? blocks : cap), 128 * SMWIDE_GROUPS, smem, st>>>(
-      xyz1, xyz2, N1, N2, dist1, idx1, dist2, idx2, sums, (int)blocks1, (int)total);
+      xyz1, xyz2, N1, N2, dist1, idx1, dist2, idx2, sums, (int)blocks1, (int)total, l1, l2);
   return check_launch("chamfer_fwd_smwide_kernel");
 }
 
@@ -394,13 +387,14 @@ const char *chamfer_fwd_f32_kernel_name(int64_t B, int64_t N1, int64_t N2) {
 }
 
 int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_t N1, int64_t N2, float *dist1,
-                         int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st) {
+                         int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1,
+                         XyzLayout l2) {
   // Measured on B200 (B=64, N=M=16384): two queries per thread, six resident blocks per SM and a
   // four-fold unrolled key loop beat four queries per thread by about 10 %.
   switch (chamfer_fwd_f32_plan(B, N1, N2)) {
-    case 0: return launch<1, 1, 2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
-    case 1: return launch_smwide(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
-    default: return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st);
+    case 0: return launch<1, 1, 2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2);
+    case 1: return launch_smwide(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2);
+    default: return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2);
   }
 }
 

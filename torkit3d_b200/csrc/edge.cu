@@ -210,7 +210,7 @@ extern "C" int tk3d_edge_feature_fwd(const void *query_feature, const void *key_
   if (rc) return rc;
   const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
   if (smem > 48 * 1024)
-    TK3D_CUDA(cudaFuncSetAttribute(edge_rows_vec4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TK3D_CUDA(raise_smem_limit((const void *)edge_rows_vec4_kernel, (int)smem));
   dim3 grid((unsigned)((N1 * K + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
   edge_rows_vec4_kernel<<<grid, ROWS_THREADS, smem, st>>>((const float *)scratch, (const float *)query_feature, index,
                                                           (int)C, N2, N1, (int)K, include_query, (float *)out,
@@ -247,8 +247,7 @@ extern "C" int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index,
       TK3D_CUDA(cudaMemsetAsync(scratch, 0, want, st));
       const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
       if (smem > 48 * 1024)
-        TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<1, int64_t>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TK3D_CUDA(raise_smem_limit((const void *)scatter_rows_vec4_kernel<1, int64_t>, (int)smem));
       dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
       scatter_rows_vec4_kernel<1, int64_t><<<grid, ROWS_THREADS, smem, st>>>(
           (const float *)grad_out, index, nullptr, (int)C, N2, E, gstride, (float *)scratch, status);

@@ -365,7 +365,7 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
     const double *p = (const double *)points;
 #define TK3D_FPS64_CASE(PP)                                                                                          \
   {                                                                                                                  \
-    TK3D_CUDA(cudaFuncSetAttribute(fps_resident64_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+    TK3D_CUDA(raise_smem_limit((const void *)fps_resident64_kernel<PP>, \
                                    (int)(FPS_RESIDENT64_MAX_N * 24)));                                               \
     fps_resident64_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,        \
                                                                   (double *)sampled);                                \
@@ -387,7 +387,7 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
     const float *p = (const float *)points;
 #define TK3D_FPS_CASE(PP)                                                                                       \
   {                                                                                                             \
-    TK3D_CUDA(cudaFuncSetAttribute(fps_resident_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)); \
+    TK3D_CUDA(raise_smem_limit((const void *)fps_resident_kernel<PP>, 98304)); \
     fps_resident_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,       \
                                                                 (float *)sampled);                                \
   }
@@ -395,8 +395,7 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
     else if (P <= 4) TK3D_FPS_CASE(2)
     else if (P <= 8) TK3D_FPS_CASE(4)
     else {  // 8193..16384 points: 16 per thread, coordinates stay in shared memory (up to 192 KB)
-      TK3D_CUDA(cudaFuncSetAttribute(fps_resident_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)(FPS_RESIDENT_MAX_N * 12)));
+      TK3D_CUDA(raise_smem_limit((const void *)fps_resident_kernel<8, false>, (int)(FPS_RESIDENT_MAX_N * 12)));
       fps_resident_kernel<8, false><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,
                                                                         (float *)sampled);
     }
@@ -418,6 +417,11 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
 extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index, void *scratch,
                         size_t scratch_bytes, int dtype, void *stream) {
   return fps_impl(points, B, N, S, 0, index, nullptr, scratch, scratch_bytes, dtype, stream);
+}
+
+extern "C" int tk3d_fps_layout(const void *points, int64_t B, int64_t N, int64_t S, int xyz_channel_first,
+                               int64_t *index, void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  return fps_impl(points, B, N, S, xyz_channel_first != 0, index, nullptr, scratch, scratch_bytes, dtype, stream);
 }
 
 extern "C" int tk3d_fps_gather(const void *points, int64_t B, int64_t N, int64_t S, int channel_first,

@@ -300,8 +300,7 @@ extern "C" int tk3d_three_nn_interp_bwd(const void *gout, const int32_t *index32
     if (Nq > 0) {
       const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
       if (smem > 48 * 1024)
-        TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<3, int32_t>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TK3D_CUDA(raise_smem_limit((const void *)scatter_rows_vec4_kernel<3, int32_t>, (int)smem));
       dim3 grid((unsigned)((Nq + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
       scatter_rows_vec4_kernel<3, int32_t><<<grid, ROWS_THREADS, smem, st>>>(
           (const float *)gout, index32, (const float *)weight, (int)C, Nk, Nq, C * Nq, (float *)scratch, status);

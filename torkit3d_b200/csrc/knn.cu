@@ -35,30 +35,20 @@ __device__ __forceinline__ float pinf() { return __int_as_float(0x7f800000); }
 
 // Stage one key tile (padded with points that can only reach the verify path, where they are
 // rejected by index) from registers or global memory.
-__device__ __forceinline__ float4 make_key(const float *__restrict__ rb, int j, int nr) {
+__device__ __forceinline__ float4 make_key(const float *__restrict__ rb, int j, int nr, XyzLayout l) {
   if (j < nr) {
-    const float x = rb[(int64_t)j * 3 + 0], y = rb[(int64_t)j * 3 + 1], z = rb[(int64_t)j * 3 + 2];
-    return make_float4(x, y, z, sweep_key_w(x, y, z));
-  }
-  return make_float4(0.f, 0.f, 0.f, pinf());
-}
-
-__device__ __forceinline__ float4 make_key_strided(const float *__restrict__ rb, int j, int nr, int ps, int cs) {
-  if (j < nr) {
-    const float *r = rb + (int64_t)j * ps;
-    const float x = r[0], y = r[cs], z = r[2 * (int64_t)cs];
+    float x, y, z;
+    load_xyz(rb, j, l, x, y, z);
     return make_float4(x, y, z, sweep_key_w(x, y, z));
   }
   return make_float4(0.f, 0.f, 0.f, pinf());
 }
 
 // ---------------------------------------------------------------------------------------------
-// FUSED (three-nearest-neighbour front end of feature interpolation): coordinates are read
-// through strides (point j, coordinate d at base[j*ps + d*cs], so [N,3] and [3,N] clouds both
-// work), and instead of distances and 64-bit indices the epilogue writes the normalised
-// inverse-distance weights  w_i = (1/max(d_i, eps)) / sum_j (1/max(d_j, eps))  and 32-bit indices.
+// FUSED (three-nearest-neighbour front end of feature interpolation): instead of distances and
+// 64-bit indices the epilogue writes the normalised inverse-distance weights
+// w_i = (1/max(d_i, eps)) / sum_j (1/max(d_j, eps))  and 32-bit indices.
 struct KnnFused {
-  int qps, qcs, kps, kcs;
   float eps;
   float *weight;
   int32_t *index32;
@@ -67,7 +57,7 @@ struct KnnFused {
 template <int K, int Q, bool FUSED = false>
 __global__ void __launch_bounds__(KN_THREADS)
 knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
-                 float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total,
+                 float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl,
                  KnnFused fu = KnnFused()) {
   constexpr int TILE = 512, PER = TILE / KN_THREADS;
   constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
@@ -86,17 +76,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
     for (int s = 0; s < Q; ++s) {
       const int i = i0 + s * KN_THREADS;
       if (i < N1) {
-        if constexpr (FUSED) {
-          const float *q = query + b * 3 * (int64_t)N1 + (int64_t)i * fu.qps;
-          qx[s] = q[0];
-          qy[s] = q[fu.qcs];
-          qz[s] = q[2 * (int64_t)fu.qcs];
-        } else {
-          const float *q = query + (b * N1 + i) * 3;
-          qx[s] = q[0];
-          qy[s] = q[1];
-          qz[s] = q[2];
-        }
+        load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx[s], qy[s], qz[s]);
         thr[s] = pinf();  // accept everything until the list is full
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
@@ -117,9 +97,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll
     for (int p = 0; p < PER; ++p) {
       const int u = tid + p * KN_THREADS;
-      float4 v;
-      if constexpr (FUSED) v = make_key_strided(rb, u, N2, fu.kps, fu.kcs);
-      else v = make_key(rb, u, N2);
+      const float4 v = make_key(rb, u, N2, kl);
       sweep_store_key(tile[0], u, v.x, v.y, v.z, v.w);
     }
     __syncthreads();
@@ -131,10 +109,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
       float4 nxt[PER];
       if (more) {
 #pragma unroll
-        for (int p = 0; p < PER; ++p) {
-          if constexpr (FUSED) nxt[p] = make_key_strided(rb, t0 + TILE + tid + p * KN_THREADS, N2, fu.kps, fu.kcs);
-          else nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2);
-        }
+        for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2, kl);
       }
       const int lim = (min(TILE, N2 - t0) + GK - 1) / GK * GK;
 #pragma unroll 4
@@ -212,11 +187,10 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
           }
         } else {
           float *od = dist + (b * N1 + i) * K;
-          int64_t *oi = index + (b * N1 + i) * K;
 #pragma unroll
           for (int c = 0; c < K; ++c) {
             od[c] = kd[s][c];
-            oi[c] = (int64_t)ki[s][c];
+            index.put((b * N1 + i) * K + c, ki[s][c]);
           }
         }
       }
@@ -228,7 +202,8 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 template <int Q>
 __global__ void __launch_bounds__(KN_THREADS)
 knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
-                    int k, float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
+                    int k, float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql,
+                    XyzLayout kl) {
   constexpr int PER = KN_TILE / KN_THREADS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float4 *tile = reinterpret_cast<float4 *>(smem_raw);                        // [2][KN_TILE]
@@ -247,10 +222,7 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
     for (int s = 0; s < Q; ++s) {
       const int i = i0 + s * KN_THREADS;
       if (i < N1) {
-        const float *q = query + (b * N1 + i) * 3;
-        qx[s] = q[0];
-        qy[s] = q[1];
-        qz[s] = q[2];
+        load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx[s], qy[s], qz[s]);
         thr[s] = qnan();
       } else {
         qx[s] = qy[s] = qz[s] = 0.f;
@@ -266,7 +238,7 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
     const float *rb = key + b * (int64_t)N2 * 3;
     const int ntiles = (N2 + KN_TILE - 1) / KN_TILE;
 #pragma unroll
-    for (int p = 0; p < PER; ++p) tile[tid + p * KN_THREADS] = make_key(rb, tid + p * KN_THREADS, N2);
+    for (int p = 0; p < PER; ++p) tile[tid + p * KN_THREADS] = make_key(rb, tid + p * KN_THREADS, N2, kl);
     __syncthreads();
 
     for (int t = 0; t < ntiles; ++t) {
@@ -276,7 +248,7 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
       float4 nxt[PER];
       if (more) {
 #pragma unroll
-        for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + KN_TILE + tid + p * KN_THREADS, N2);
+        for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + KN_TILE + tid + p * KN_THREADS, N2, kl);
       }
 
       // Drain every candidate buffer of this thread into its sorted lists (tile-local indices).
@@ -349,12 +321,11 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
       const int i = i0 + s * KN_THREADS;
       if (i < N1) {
         float *od = dist + (b * N1 + i) * k;
-        int64_t *oi = index + (b * N1 + i) * k;
         const float *d_s = ld + ((size_t)s * k) * KN_THREADS + tid;
         const int *i_s = li + ((size_t)s * k) * KN_THREADS + tid;
         for (int c = 0; c < k; ++c) {
           od[c] = d_s[c * KN_THREADS];
-          oi[c] = (int64_t)i_s[c * KN_THREADS];
+          index.put((b * N1 + i) * k + c, i_s[c * KN_THREADS]);
         }
       }
     }
@@ -425,7 +396,7 @@ __device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr,
 template <int Q, int KT_NCH, int KT_QCAP, int MINB, int KT_TILE>
 __global__ void __launch_bounds__(KT_THREADS, MINB)
 knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k,
-                   float *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
+                   float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int PER = KT_TILE / KT_THREADS;
   constexpr int CPW = KT_NCH / KT_SPLIT;          // classes per warp: 8, 16 or 32
   constexpr int PPC = KT_TILE / KT_SPLIT / CPW / 2;  // key pairs per class, tile and warp: 4, 2 or 1
@@ -461,12 +432,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       const int i = ibase + s * 32 + lane;
       valid[s] = i < N1;
       qx[s] = qy[s] = qz[s] = 0.f;
-      if (valid[s]) {
-        const float *q = query + (b * N1 + i) * 3;
-        qx[s] = q[0];
-        qy[s] = q[1];
-        qz[s] = q[2];
-      }
+      if (valid[s]) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx[s], qy[s], qz[s]);
       if (part == 0) {
         sq[0][s * 32 + lane] = qx[s];
         sq[1][s * 32 + lane] = qy[s];
@@ -487,7 +453,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     auto fetch = [&](int t0) {
 #pragma unroll
       for (int p = 0; p < PER; ++p) {
-        nxt[p] = make_key(rb, t0 + tid + p * KT_THREADS, N2);
+        nxt[p] = make_key(rb, t0 + tid + p * KT_THREADS, N2, kl);
         if (t0 + tid + p * KT_THREADS < N2) rmax = fmaxf(rmax, fabsf(nxt[p].w));
       }
     };
@@ -618,18 +584,22 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     const bool qvalid = iq < N1;
     const int n = ccnt[col];
     const float cqx = sq[0][col], cqy = sq[1][col], cqz = sq[2][col];
-    if (qvalid && n <= KT_QCAP) {
+    // A list that overflowed, or -- which the bound derivation rules out for finite input, but which
+    // costs nothing to guard -- holds fewer than k candidates, sends its query to the exact scan.
+    const bool listed = n >= k && n <= KT_QCAP;
+    if (qvalid && listed) {
       for (int c = sub; c < n; c += NSUB) {
         const int j = cand[c * QS + col];
-        cd[c * QS + col] =
-            sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], cqx, cqy, cqz);
+        float rx, ry, rz;
+        load_xyz(rb, j, kl, rx, ry, rz);
+        cd[c * QS + col] = sqdist<float>(rx, ry, rz, cqx, cqy, cqz);
       }
     }
     __syncthreads();
     if (qvalid) {
       float *od = dist + (b * N1 + iq) * (int64_t)k;
-      int64_t *oi = index + (b * N1 + iq) * (int64_t)k;
-      if (n <= KT_QCAP) {
+      const int64_t orow = (b * N1 + iq) * (int64_t)k;
+      if (listed) {
         for (int c = sub; c < n; c += NSUB) {
           const float d = cd[c * QS + col];
           const int j = cand[c * QS + col];
@@ -641,7 +611,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
           }
           if (rank < k) {
             od[rank] = d;
-            oi[rank] = (int64_t)j;
+            index.put(orow + rank, j);
           }
         }
       } else if (sub == 0) {
@@ -649,8 +619,9 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
         // column of cd / cand (nobody else touches the column of an overflowed query).
         int nk = 0;
         for (int j = 0; j < N2; ++j) {
-          const float d =
-              sqdist<float>(rb[(int64_t)j * 3 + 0], rb[(int64_t)j * 3 + 1], rb[(int64_t)j * 3 + 2], cqx, cqy, cqz);
+          float rx, ry, rz;
+          load_xyz(rb, j, kl, rx, ry, rz);
+          const float d = sqdist<float>(rx, ry, rz, cqx, cqy, cqz);
           if (nk == k) {
             const float dl = cd[(k - 1) * QS + col];
             if (!(d < dl || (d == dl && j < cand[(k - 1) * QS + col]))) continue;
@@ -669,7 +640,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
         }
         for (int c = 0; c < k; ++c) {
           od[c] = cd[c * QS + col];
-          oi[c] = (int64_t)cand[c * QS + col];
+          index.put(orow + c, cand[c * QS + col]);
         }
       }
     }
@@ -692,18 +663,19 @@ __device__ __forceinline__ bool knn_larger(T v, int64_t jv, T m, int64_t jm) {
   return v > m || (v == m && jv > jm);
 }
 
-// Sift (d, j) down from the root of the max-heap od/oi[0, n).
+// Sift (d, j) down from the root of the max-heap od[0, n) / oi[row, row + n).
 template <typename T>
-__device__ __forceinline__ void knn_sift_down(T *__restrict__ od, int64_t *__restrict__ oi, int64_t n, T d, int64_t j) {
+__device__ __forceinline__ void knn_sift_down(T *__restrict__ od, IndexOut oi, int64_t row, int64_t n, T d,
+                                              int64_t j) {
   int64_t pos = 0;
   while (true) {
     int64_t child = 2 * pos + 1;
     if (child >= n) break;
     T dc = od[child];
-    int64_t jc = oi[child];
+    int64_t jc = oi.get(row + child);
     if (child + 1 < n) {
       const T dr = od[child + 1];
-      const int64_t jr = oi[child + 1];
+      const int64_t jr = oi.get(row + child + 1);
       if (knn_larger<T>(dr, jr, dc, jc)) {
         ++child;
         dc = dr;
@@ -712,11 +684,11 @@ __device__ __forceinline__ void knn_sift_down(T *__restrict__ od, int64_t *__res
     }
     if (!knn_larger<T>(dc, jc, d, j)) break;
     od[pos] = dc;
-    oi[pos] = jc;
+    oi.put(row + pos, jc);
     pos = child;
   }
   od[pos] = d;
-  oi[pos] = j;
+  oi.put(row + pos, j);
 }
 
 // Blocks of 64 threads: the per-query work is long and serial, so many small blocks keep every SM
@@ -725,7 +697,7 @@ constexpr int KG_THREADS = 64;
 template <typename T>
 __global__ void __launch_bounds__(KG_THREADS)
 knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
-                   int64_t k, T *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
+                   int64_t k, T *__restrict__ dist, IndexOut oi, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int TILE = KG_THREADS;
   static_assert((TILE & (TILE - 1)) == 0 && TILE % 8 == 0, "tile indices are masked; batches of eight");
   __shared__ T sx[TILE], sy[TILE], sz[TILE];
@@ -742,24 +714,15 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
     const int64_t i = (blk % chunks) * TILE + tid;
     const bool valid = i < N1;
     T qx = 0, qy = 0, qz = 0;
-    if (valid) {
-      const T *q = query + (b * N1 + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
-    }
+    if (valid) load_xyz(query + b * 3 * N1, i, ql, qx, qy, qz);
     T *od = dist + (b * N1 + (valid ? i : 0)) * k;
-    int64_t *oi = index + (b * N1 + (valid ? i : 0)) * k;
+    const int64_t row = (b * N1 + (valid ? i : 0)) * k;  // offset of this query's index row
     int64_t cnt = 0;
     T root = Exact<T>::inf();  // distance at the heap's root once the heap is full
     const T *rb = key + b * N2 * 3;
     for (int64_t t0 = 0; t0 < N2; t0 += TILE) {
       const int64_t jl = t0 + tid;
-      if (jl < N2) {
-        sx[tid] = rb[jl * 3 + 0];
-        sy[tid] = rb[jl * 3 + 1];
-        sz[tid] = rb[jl * 3 + 2];
-      }
+      if (jl < N2) load_xyz(rb, jl, kl, sx[tid], sy[tid], sz[tid]);
       __syncthreads();
       const int lim = (int)((N2 - t0) < TILE ? (N2 - t0) : TILE);
       if (valid) {
@@ -782,17 +745,19 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
               while (pos > 0) {
                 const int64_t par = (pos - 1) >> 1;
                 const T dp = od[par];
-                const int64_t jp = oi[par];
+                const int64_t jp = oi.get(row + par);
                 if (!knn_larger<T>(d, j, dp, jp)) break;
                 od[pos] = dp;
-                oi[pos] = jp;
+                oi.put(row + pos, jp);
                 pos = par;
               }
               od[pos] = d;
-              oi[pos] = j;
+              oi.put(row + pos, j);
               if (cnt == k) root = od[0];
-            } else if (d < root) {  // false when either is NaN
-              knn_sift_down<T>(od, oi, k, d, j);
+            } else if (d < root || (root != root && d == d)) {
+              // a key enters when it beats the root; a NaN at the root (it orders after every
+              // number) gives way to any real distance
+              knn_sift_down<T>(od, oi, row, k, d, j);
               root = od[0];
             }
           }
@@ -804,53 +769,60 @@ knn_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64
       // heap sort: move the largest to the end, restore the heap on the shorter prefix
       for (int64_t end = cnt - 1; end > 0; --end) {
         const T dl = od[end];
-        const int64_t jl2 = oi[end];
+        const int64_t jl2 = oi.get(row + end);
         od[end] = od[0];
-        oi[end] = oi[0];
-        knn_sift_down<T>(od, oi, end, dl, jl2);
+        oi.put(row + end, oi.get(row));
+        knn_sift_down<T>(od, oi, row, end, dl, jl2);
       }
     }
   }
 }
 
+// Arguments every launcher passes on unchanged: output index tensor (int64 or int32) and the
+// coordinate layouts of the query and key clouds.
+struct KnnIo {
+  IndexOut index;
+  XyzLayout ql, kl;
+};
+
 template <typename T>
-int knn_generic(const T *query, const T *key, int64_t B, int64_t N1, int64_t N2, int64_t k, T *dist,
-                int64_t *index, cudaStream_t st) {
+int knn_generic(const T *query, const T *key, int64_t B, int64_t N1, int64_t N2, int64_t k, T *dist, const KnnIo &io,
+                cudaStream_t st) {
   const int64_t total = B * ((N1 + KG_THREADS - 1) / KG_THREADS);
   if (total == 0) return TK3D_OK;
   const int64_t cap = (int64_t)sm_count() * 256;
   knn_generic_kernel<T><<<(unsigned)(total < cap ? total : cap), KG_THREADS, 0, st>>>(query, key, B, N1, N2, k, dist,
-                                                                                     index, total);
+                                                                                     io.index, total, io.ql, io.kl);
   return check_launch("knn_generic_kernel");
 }
 
 template <int K, int Q>
-int knn_small(const float *query, const float *key, int64_t B, int N1, int N2, float *dist, int64_t *index,
+int knn_small(const float *query, const float *key, int64_t B, int N1, int N2, float *dist, const KnnIo &io,
               cudaStream_t st) {
   const int64_t per = KN_THREADS * Q;
   const int64_t total = B * ((N1 + per - 1) / per);
   const int64_t cap = (int64_t)sm_count() * 256;
   knn_small_kernel<K, Q><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(query, key, B, N1, N2, dist,
-                                                                                      index, total);
+                                                                                      io.index, total, io.ql, io.kl);
   return check_launch("knn_small_kernel");
 }
 
 template <int K>
-int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2, float *dist, int64_t *index,
+int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2, float *dist, const KnnIo &io,
                 cudaStream_t st) {
   const int64_t sms = sm_count();
-  if (B * (int64_t)N1 >= sms * 2 * KN_THREADS * 2) return knn_small<K, 2>(query, key, B, N1, N2, dist, index, st);
-  return knn_small<K, 1>(query, key, B, N1, N2, dist, index, st);
+  if (B * (int64_t)N1 >= sms * 2 * KN_THREADS * 2) return knn_small<K, 2>(query, key, B, N1, N2, dist, io, st);
+  return knn_small<K, 1>(query, key, B, N1, N2, dist, io, st);
 }
 
 template <int Q>
 int three_nn_fused_q(const float *query, const float *key, int64_t B, int N1, int N2, const KnnFused &fu,
-                     cudaStream_t st) {
+                     XyzLayout ql, XyzLayout kl, cudaStream_t st) {
   const int64_t per = KN_THREADS * Q;
   const int64_t total = B * ((N1 + per - 1) / per);
   const int64_t cap = (int64_t)sm_count() * 256;
   knn_small_kernel<3, Q, true><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
-      query, key, B, N1, N2, nullptr, nullptr, total, fu);
+      query, key, B, N1, N2, nullptr, index_out(nullptr, 0), total, ql, kl, fu);
   return check_launch("knn_small_kernel (fused weights)");
 }
 
@@ -860,28 +832,27 @@ size_t buffered_smem(int Q, int k) {
 
 template <int Q>
 int knn_buffered(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist,
-                 int64_t *index, cudaStream_t st) {
+                 const KnnIo &io, cudaStream_t st) {
   const int64_t per = KN_THREADS * Q;
   const int64_t total = B * ((N1 + per - 1) / per);
   const size_t smem = buffered_smem(Q, k);
-  TK3D_CUDA(cudaFuncSetAttribute(knn_buffered_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  TK3D_CUDA(raise_smem_limit((const void *)knn_buffered_kernel<Q>, (int)smem));
   const int64_t cap = (int64_t)sm_count() * 64;
-  knn_buffered_kernel<Q><<<(unsigned)(total < cap ? total : cap), KN_THREADS, smem, st>>>(query, key, B, N1, N2, k,
-                                                                                        dist, index, total);
+  knn_buffered_kernel<Q><<<(unsigned)(total < cap ? total : cap), KN_THREADS, smem, st>>>(
+      query, key, B, N1, N2, k, dist, io.index, total, io.ql, io.kl);
   return check_launch("knn_buffered_kernel");
 }
 
 template <int Q, int NCH, int QCAP, int MINB, int TILE = 256>
-int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, int64_t *index,
+int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, const KnnIo &io,
                 cudaStream_t st) {
   const int64_t total = B * ((N1 + 32 * Q - 1) / (32 * Q));
   const int64_t gcap = (int64_t)sm_count() * 256;
   const size_t smem = kt_smem_bytes<Q, NCH, QCAP, TILE>();
   if (smem + 4096 > 48 * 1024)  // static shared memory of the kernel counts towards the 48 KB default limit
-    TK3D_CUDA(cudaFuncSetAttribute(knn_twopass_kernel<Q, NCH, QCAP, MINB, TILE>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TK3D_CUDA(raise_smem_limit((const void *)knn_twopass_kernel<Q, NCH, QCAP, MINB, TILE>, (int)smem));
   knn_twopass_kernel<Q, NCH, QCAP, MINB, TILE><<<(unsigned)(total < gcap ? total : gcap), KT_THREADS, smem, st>>>(
-      query, key, B, N1, N2, k, dist, index, total);
+      query, key, B, N1, N2, k, dist, io.index, total, io.ql, io.kl);
   return check_launch("knn_twopass_kernel");
 }
 
@@ -892,29 +863,26 @@ int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t 
                        float eps, float *weight, int32_t *index32, cudaStream_t st) {
   if (B * N1 == 0) return TK3D_OK;
   KnnFused fu;
-  fu.qps = channel_first ? 1 : 3;
-  fu.qcs = channel_first ? (int)N1 : 1;
-  fu.kps = channel_first ? 1 : 3;
-  fu.kcs = channel_first ? (int)N2 : 1;
   fu.eps = eps;
   fu.weight = weight;
   fu.index32 = index32;
+  const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
   if (B * N1 >= (int64_t)sm_count() * 2 * KN_THREADS * 2)
-    return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, st);
-  return three_nn_fused_q<1>(query, key, B, (int)N1, (int)N2, fu, st);
+    return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+  return three_nn_fused_q<1>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
 }
 
 }  // namespace tk3d
 
 namespace tk3d {
 bool knn_split_f64(const double *query, const double *key, int64_t B, int64_t N1, int64_t N2, int64_t k, double *dist,
-                   int64_t *index, cudaStream_t st, int *rc);
+                   IndexOut index, XyzLayout ql, XyzLayout kl, cudaStream_t st, int *rc);
 }
 
 using namespace tk3d;
 
-extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
-                        void *distance, int64_t *index, int dtype, void *stream) {
+static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
+                    int channel_first, void *distance, void *index, int index32, int dtype, void *stream) {
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "knn: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0, TK3D_ERR_SHAPE, "knn: negative size");
   TK3D_REQUIRE(k >= 1, TK3D_ERR_K, "knn: k must be >= 1 (got %lld)", (long long)k);
@@ -923,20 +891,24 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
   if (B * N1 == 0) return TK3D_OK;
   TK3D_REQUIRE(query && key && distance && index, TK3D_ERR_NULL, "knn: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
+  KnnIo io;
+  io.index = index_out(index, index32);
+  io.ql = xyz_layout(channel_first, N1);
+  io.kl = xyz_layout(channel_first, N2);
   if (dtype == TK3D_F64) {
     int rc = TK3D_OK;  // few queries and k <= 64: several warps per query group (knn_split.cu)
-    if (knn_split_f64((const double *)query, (const double *)key, B, N1, N2, k, (double *)distance, index, st, &rc))
+    if (knn_split_f64((const double *)query, (const double *)key, B, N1, N2, k, (double *)distance, io.index, io.ql,
+                      io.kl, st, &rc))
       return rc;
-    return knn_generic<double>((const double *)query, (const double *)key, B, N1, N2, k, (double *)distance, index,
-                               st);
+    return knn_generic<double>((const double *)query, (const double *)key, B, N1, N2, k, (double *)distance, io, st);
   }
   const float *q = (const float *)query, *r = (const float *)key;
   float *d = (float *)distance;
   switch (k) {
-    case 1: return knn_small_q<1>(q, r, B, (int)N1, (int)N2, d, index, st);
-    case 2: return knn_small_q<2>(q, r, B, (int)N1, (int)N2, d, index, st);
-    case 3: return knn_small_q<3>(q, r, B, (int)N1, (int)N2, d, index, st);
-    case 4: return knn_small_q<4>(q, r, B, (int)N1, (int)N2, d, index, st);
+    case 1: return knn_small_q<1>(q, r, B, (int)N1, (int)N2, d, io, st);
+    case 2: return knn_small_q<2>(q, r, B, (int)N1, (int)N2, d, io, st);
+    case 3: return knn_small_q<3>(q, r, B, (int)N1, (int)N2, d, io, st);
+    case 4: return knn_small_q<4>(q, r, B, (int)N1, (int)N2, d, io, st);
     default: break;
   }
   // Two-pass selection needs at least two key classes per wanted neighbour to be tight (the class
@@ -944,18 +916,31 @@ extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N
   if (k <= 128 && N2 >= 4 * k && N2 >= (k > 64 ? 512 : 256)) {
     if (k <= 16) {
       if (B * N1 >= (int64_t)sm_count() * 4 * 64)
-        return knn_twopass<2, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
-      return knn_twopass<1, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+        return knn_twopass<2, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
+      return knn_twopass<1, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
     }
-    if (k <= 32) return knn_twopass<1, 64, 104, 5>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
-    if (k <= 64) return knn_twopass<1, 128, 192, 4>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
-    return knn_twopass<1, 256, 384, 2, 512>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+    if (k <= 32) return knn_twopass<1, 64, 104, 5>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
+    if (k <= 64) return knn_twopass<1, 128, 192, 4>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
+    return knn_twopass<1, 256, 384, 2, 512>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
   }
   if (k <= 128) {
     const int64_t sms = sm_count();
     if (k <= 32 && B * N1 >= sms * 2 * KN_THREADS * 2)
-      return knn_buffered<2>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
-    return knn_buffered<1>(q, r, B, (int)N1, (int)N2, (int)k, d, index, st);
+      return knn_buffered<2>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
+    return knn_buffered<1>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
   }
-  return knn_generic<float>(q, r, B, N1, N2, k, d, index, st);
+  return knn_generic<float>(q, r, B, N1, N2, k, d, io, st);
+}
+
+extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
+                        void *distance, int64_t *index, int dtype, void *stream) {
+  return knn_impl(query, key, B, N1, N2, k, 0, distance, index, 0, dtype, stream);
+}
+
+extern "C" int tk3d_knn_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
+                               int xyz_channel_first, void *distance, void *index, int index_dtype, int dtype,
+                               void *stream) {
+  TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "knn: index_dtype %d", index_dtype);
+  return knn_impl(query, key, B, N1, N2, k, xyz_channel_first != 0, distance, index, index_dtype == TK3D_I32, dtype,
+                  stream);
 }

@@ -24,7 +24,7 @@ constexpr int KS_STAGE = 64;  // keys a warp stages at a time
 template <typename T>
 __global__ void __launch_bounds__(256)
 knn_split_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int N1, int N2, int k, int S,
-                 T *__restrict__ dist, int64_t *__restrict__ index, int64_t blocks_total) {
+                 T *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   extern __shared__ __align__(16) unsigned char ks_smem[];
   const int threads = 32 * S;
   T *ld = reinterpret_cast<T *>(ks_smem);                                  // [k][threads]
@@ -41,12 +41,7 @@ knn_split_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t
     const int i = (int)(blk % chunks) * 32 + lane;
     const bool valid = i < N1;
     T qx = 0, qy = 0, qz = 0;
-    if (valid) {
-      const T *q = query + (b * N1 + i) * 3;
-      qx = q[0];
-      qy = q[1];
-      qz = q[2];
-    }
+    if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
     const T *rb = key + b * (int64_t)N2 * 3;
     const int j_begin = min(N2, seg * seglen), j_end = min(N2, j_begin + seglen);
     int cnt = 0;
@@ -88,7 +83,14 @@ knn_split_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t
     for (int j0 = j_begin; j0 < j_end; j0 += KS_STAGE) {
       const int n = min(KS_STAGE, j_end - j0);
       __syncwarp();
-      for (int e = lane; e < n * 3; e += 32) mystage[e] = rb[(int64_t)j0 * 3 + e];
+      if (kl.cs == 1) {  // [N,3]: the stage is one contiguous run
+        for (int e = lane; e < n * 3; e += 32) mystage[e] = rb[(int64_t)j0 * 3 + e];
+      } else {           // [3,N]: three runs, interleaved into the stage
+        for (int e = lane; e < n * 3; e += 32) {
+          const int c = e / n, u = e - c * n;
+          mystage[u * 3 + c] = rb[(int64_t)c * kl.cs + j0 + u];
+        }
+      }
       __syncwarp();
       if (valid) {
         for (int u = 0; u < n; ++u) {
@@ -101,7 +103,9 @@ knn_split_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t
               heaped = true;
               worst = D(0);
             }
-          } else if (d < worst) {  // keys come in ascending index order: an equal distance never enters
+          } else if (d < worst || (worst != worst && d == d)) {
+            // keys come in ascending index order: an equal distance never enters; a NaN at the root
+            // (it orders after every number) gives way to any real distance
             sift(0, k, d, j0 + u);
             worst = D(0);
           }
@@ -123,7 +127,7 @@ knn_split_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t
 
     if (seg == 0 && valid) {
       T *od = dist + (b * N1 + i) * (int64_t)k;
-      int64_t *oi = index + (b * N1 + i) * (int64_t)k;
+      const int64_t orow = (b * N1 + i) * (int64_t)k;
       int pos[8];
 #pragma unroll
       for (int s = 0; s < 8; ++s) pos[s] = 0;
@@ -151,7 +155,7 @@ knn_split_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t
             ++pos[s];
           }
         od[out] = bd;
-        oi[out] = (int64_t)bi;
+        index.put(orow + out, bi);
       }
     }
     __syncthreads();
@@ -168,7 +172,7 @@ static size_t knn_split_smem(int64_t k, int S, size_t elem) {
 
 // Returns true and launches when the split kernel suits the problem; false = caller's own path.
 bool knn_split_f64(const double *query, const double *key, int64_t B, int64_t N1, int64_t N2, int64_t k, double *dist,
-                   int64_t *index, cudaStream_t st, int *rc) {
+                   IndexOut index, XyzLayout ql, XyzLayout kl, cudaStream_t st, int *rc) {
   const int64_t sms = sm_count();
   const int64_t warps = B * ((N1 + 31) / 32);
   if (k > 64 || warps >= sms * 32) return false;  // enough queries to fill the GPU one thread each
@@ -177,14 +181,14 @@ bool knn_split_f64(const double *query, const double *key, int64_t B, int64_t N1
   while (S >= 2 && knn_split_smem(k, S, sizeof(double)) > 200 * 1024) S /= 2;
   if (S < 2) return false;
   const size_t smem = knn_split_smem(k, S, sizeof(double));
-  if (cudaFuncSetAttribute(knn_split_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+  if (raise_smem_limit((const void *)knn_split_kernel<double>, (int)smem) !=
       cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
   const int64_t cap = sms * 16;
   knn_split_kernel<double><<<(unsigned)(warps < cap ? warps : cap), 32 * S, smem, st>>>(
-      query, key, B, (int)N1, (int)N2, (int)k, S, dist, index, warps);
+      query, key, B, (int)N1, (int)N2, (int)k, S, dist, index, warps, ql, kl);
   *rc = check_launch("knn_split_kernel");
   return true;
 }

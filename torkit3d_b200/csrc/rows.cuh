@@ -286,15 +286,14 @@ int gather_rows(const float *in, const IndexT *index, const float *weight, int64
   if (vec) {
     const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
     if (smem > 48 * 1024)
-      TK3D_CUDA(cudaFuncSetAttribute(gather_rows_vec4_kernel<NSRC, IndexT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
+      TK3D_CUDA(raise_smem_limit((const void *)gather_rows_vec4_kernel<NSRC, IndexT>, (int)smem));
     gather_rows_vec4_kernel<NSRC, IndexT><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out,
                                                                     status);
     return check_launch("gather_rows_vec4_kernel");
   }
   const size_t smem = (size_t)C * (ROWS_TE + 1) * sizeof(float);
   if (smem > 48 * 1024)
-    TK3D_CUDA(cudaFuncSetAttribute(gather_rows_kernel<NSRC, IndexT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TK3D_CUDA(raise_smem_limit((const void *)gather_rows_kernel<NSRC, IndexT>, (int)smem));
   gather_rows_kernel<NSRC, IndexT><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out, status);
   return check_launch("gather_rows_kernel");
 }
@@ -308,8 +307,7 @@ int scatter_rows(const float *gout, const int64_t *index, const float *weight, i
   if (E > 0) {
     const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
     if (smem > 48 * 1024)
-      TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<NSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
+      TK3D_CUDA(raise_smem_limit((const void *)scatter_rows_vec4_kernel<NSRC>, (int)smem));
     dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
     scatter_rows_vec4_kernel<NSRC><<<grid, ROWS_THREADS, smem, st>>>(gout, index, weight, (int)C, N1, E, C * E,
                                                                      scratch, status);

@@ -373,7 +373,7 @@ extern "C" int tk3d_sa_group_fwd(const void *points, const void *centroids, cons
                   ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15) == 0;
   const SaSmem sm = sa_smem((int)C, (int)K, vec);
   if (sm.total > 48 * 1024)
-    TK3D_CUDA(cudaFuncSetAttribute(sa_group_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm.total));
+    TK3D_CUDA(raise_smem_limit((const void *)sa_group_fwd_kernel, (int)sm.total));
   const int64_t total = B * ((M + SA_Q - 1) / SA_Q);
   const int64_t cap = (int64_t)sm_count() * 64;
   const float r2 = radius * radius;
@@ -430,8 +430,7 @@ extern "C" int tk3d_sa_group_bwd(const void *gout, const int32_t *index32, int64
       if (E > 0) {
         const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
         if (smem > 48 * 1024)
-          TK3D_CUDA(cudaFuncSetAttribute(scatter_rows_vec4_kernel<1, int32_t>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+          TK3D_CUDA(raise_smem_limit((const void *)scatter_rows_vec4_kernel<1, int32_t>, (int)smem));
         dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
         scatter_rows_vec4_kernel<1, int32_t><<<grid, ROWS_THREADS, smem, st>>>(
             (const float *)gout, index32, nullptr, (int)C, N, E, gstride, (float *)scratch, status);

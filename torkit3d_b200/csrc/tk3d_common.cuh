@@ -35,6 +35,9 @@ inline int check_launch(const char *what) {
 // Number of SMs of the current device (cached per device id; read-only after first use).
 int sm_count();
 
+// Raise a kernel's dynamic shared-memory limit on the current device, once per (kernel, device).
+cudaError_t raise_smem_limit(const void *func, int bytes);
+
 // ---- exact arithmetic ----------------------------------------------------------------------
 // The round-to-nearest intrinsics are never contracted into a fused multiply-add by the compiler,
 // which is what keeps index results bit-reproducible against a CPU evaluation.
@@ -61,6 +64,47 @@ __device__ __forceinline__ T sqdist(T rx, T ry, T rz, T qx, T qy, T qz) {
   using E = Exact<T>;
   T dx = E::sub(rx, qx), dy = E::sub(ry, qy), dz = E::sub(rz, qz);
   return E::add(E::add(E::mul(dx, dx), E::mul(dy, dy)), E::mul(dz, dz));
+}
+
+// ---- coordinate layout and index type of the operator entry points --------------------------
+// A batch of clouds is [B,N,3] (ps = 3, cs = 1: the reference's operator layout) or [B,3,N]
+// (ps = 1, cs = N: the layout its layers pass around).  Cloud b starts at base + b*3*N in both;
+// coordinate c of its point j is cloud[j*ps + c*cs].
+struct XyzLayout {
+  int ps, cs;
+};
+inline XyzLayout xyz_layout(int channel_first, int64_t n) {
+  XyzLayout l;
+  l.ps = channel_first ? 1 : 3;
+  l.cs = channel_first ? (int)n : 1;
+  return l;
+}
+template <typename T>
+__device__ __forceinline__ void load_xyz(const T *__restrict__ cloud, int64_t j, XyzLayout l, T &x, T &y, T &z) {
+  const T *p = cloud + j * l.ps;
+  x = p[0];
+  y = p[l.cs];
+  z = p[2 * (int64_t)l.cs];
+}
+
+// Index tensors are int64 (the reference's type) or, as an opt-in of the *_layout entry points,
+// int32 (half the bytes; every index fits, clouds are limited to 2^30 points).
+struct IndexOut {
+  void *p;
+  int i32;
+  __device__ __forceinline__ void put(int64_t off, int64_t v) const {
+    if (i32) static_cast<int32_t *>(p)[off] = (int32_t)v;
+    else static_cast<int64_t *>(p)[off] = v;
+  }
+  __device__ __forceinline__ int64_t get(int64_t off) const {
+    return i32 ? (int64_t) static_cast<const int32_t *>(p)[off] : static_cast<const int64_t *>(p)[off];
+  }
+};
+inline IndexOut index_out(void *p, int i32) {
+  IndexOut o;
+  o.p = p;
+  o.i32 = i32;
+  return o;
 }
 
 __device__ __forceinline__ double warp_sum(double v) {

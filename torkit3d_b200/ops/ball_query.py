@@ -6,7 +6,8 @@ from ._functions import BallQueryFunction
 __all__ = ["ball_query", "BallQueryFunction"]
 
 
-def ball_query(query: torch.Tensor, key: torch.Tensor, radius, max_neighbors, transpose=True):
+def ball_query(query: torch.Tensor, key: torch.Tensor, radius, max_neighbors, transpose=True, *,
+               index_dtype=torch.int64):
     """First ``max_neighbors`` key indices (ascending) strictly inside ``radius`` of each query.
 
     Args:
@@ -15,10 +16,10 @@ def ball_query(query: torch.Tensor, key: torch.Tensor, radius, max_neighbors, tr
         radius: ball radius (squared in the tensors' dtype after conversion to a C float).
         max_neighbors: K; rows with fewer hits repeat their first hit, rows with none are -1.
         transpose: inputs are channel-first (the default, as in the reference).
+        index_dtype: ``torch.int64`` (the reference's type) or, as an opt-in, ``torch.int32``.
 
     Returns:
-        index [B, N1, K] int64.
+        index [B, N1, K].
     """
-    if transpose:
-        query, key = query.transpose(1, 2), key.transpose(1, 2)
-    return BallQueryFunction.apply(query.contiguous(), key.contiguous(), radius, max_neighbors)
+    # channel-first clouds are read in place (the reference copies them: torkit3d/ops/ball_query.py:32-36)
+    return BallQueryFunction.apply(query, key, radius, max_neighbors, bool(transpose), index_dtype)

@@ -2,7 +2,7 @@
 import torch
 
 from .. import _C
-from ._functions import ChamferDistanceFunction
+from ._functions import ChamferDistanceFunction, pick_layout
 
 __all__ = ["chamfer_distance", "nn_distance", "safe_sqrt", "ChamferDistanceFunction"]
 
@@ -30,9 +30,9 @@ def chamfer_distance(xyz1, xyz2, transpose=False, sqrt=False, eps=1e-12):
         dist1 [B, N1], dist2 [B, N2].  Differentiable w.r.t. both clouds.
     """
     xyz1, xyz2 = _batched(xyz1), _batched(xyz2)
-    if transpose:
-        xyz1, xyz2 = xyz1.transpose(1, 2), xyz2.transpose(1, 2)
-    dist1, dist2 = ChamferDistanceFunction.apply(xyz1, xyz2)
+    # channel-first clouds are read, and their gradients written, in place (the reference transposes
+    # and copies both: torkit3d/ops/chamfer_distance.py:49-52)
+    dist1, dist2 = ChamferDistanceFunction.apply(xyz1, xyz2, bool(transpose))
     if sqrt:
         dist1, dist2 = safe_sqrt(dist1, eps), safe_sqrt(dist2, eps)
     return dist1, dist2
@@ -41,6 +41,5 @@ def chamfer_distance(xyz1, xyz2, transpose=False, sqrt=False, eps=1e-12):
 def nn_distance(xyz1, xyz2, transpose=False):
     """Inference-time variant without autograd: returns [dist1, idx1, dist2, idx2]."""
     xyz1, xyz2 = _batched(xyz1), _batched(xyz2)
-    if transpose:
-        xyz1, xyz2 = xyz1.transpose(1, 2).contiguous(), xyz2.transpose(1, 2).contiguous()
-    return _C.chamfer_distance_forward_cuda(xyz1, xyz2)
+    cf, xyz1, xyz2 = pick_layout(transpose, xyz1, xyz2)
+    return _C.chamfer_distance_forward_cuda(xyz1, xyz2, channel_first=cf)

@@ -7,7 +7,7 @@ __all__ = ["knn_points", "KNNDistanceFunction"]
 
 
 def knn_points(query: torch.Tensor, key: torch.Tensor, k: int, sorted: bool = False, sqrt_distance: bool = False,
-               transpose: bool = False, version: int = 1):
+               transpose: bool = False, version: int = 1, *, index_dtype=torch.int64):
     """For every query point the k nearest key points.
 
     Args:
@@ -19,13 +19,13 @@ def knn_points(query: torch.Tensor, key: torch.Tensor, k: int, sorted: bool = Fa
         sqrt_distance: return Euclidean instead of squared distances.
         transpose: inputs are channel-first.
         version: kernel selector of the reference (0 or 1); both map to the same kernels here.
+        index_dtype: ``torch.int64`` (the reference's type) or, as an opt-in, ``torch.int32``.
 
     Returns:
-        (distance [B, N1, k], index [B, N1, k] int64) -- in this order, as the reference returns them.
+        (distance [B, N1, k], index [B, N1, k]) -- in this order, as the reference returns them.
     """
-    if transpose:
-        query, key = query.transpose(1, 2), key.transpose(1, 2)
-    distance, index = KNNDistanceFunction.apply(query.contiguous(), key.contiguous(), k, version)
+    # channel-first clouds are read in place (the reference copies them: torkit3d/ops/knn_points.py:40-44)
+    distance, index = KNNDistanceFunction.apply(query, key, k, version, bool(transpose), index_dtype)
     if sqrt_distance:
         distance = distance.sqrt()
     return distance, index

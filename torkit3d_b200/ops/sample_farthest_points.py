@@ -14,6 +14,5 @@ def sample_farthest_points(points: torch.Tensor, num_samples, transpose=False):
         num_samples: number of points to pick, 1 <= num_samples <= N.
         transpose: input is channel-first.
     """
-    if transpose:
-        points = points.transpose(1, 2)
-    return SampleFarthestPointsFunction.apply(points.contiguous(), num_samples)
+    # a channel-first cloud is read in place (the reference copies it: torkit3d/ops/sample_farthest_points.py:28-30)
+    return SampleFarthestPointsFunction.apply(points, num_samples, bool(transpose))
