@@ -38,16 +38,20 @@ constexpr int FPS_MAX_THREADS = 1024;
 // with a shared-memory atomicMin.  That costs a second barrier per step but removes the
 // compare-and-two-selects per point of an index-carrying arg-max (0.835 ms against 0.885 ms for
 // 32 clouds of 8192 points).  Points are held two per float2 register pair.
-// The packed add.f32x2 / mul.f32x2 forms of sm_100 are NOT used for the distance: in this loop
-// their results differed in the last bit from the scalar round-to-nearest sequence for about one
-// distance in five (as a fused multiply-add would), even with explicit .rn and -fmad=false, and an
-// exactly tied pair of points in the benchmark data then picked the wrong winner.
+// The distance runs on the packed FP32 instructions of sm_100 (two points per instruction): the
+// step is bound by instruction issue, and eight packed operations per two points replace sixteen
+// scalar ones (0.85 -> 0.70 ms for 32 clouds of 8192 points).  Bit-exactness needs care: a packed
+// add fed by a packed multiply comes out contracted into one fused multiply-add -- with explicit
+// .rn on both, as intrinsics or as inline PTX alike -- which changes the last bit of about one
+// distance in five and flips exactly tied winners.  The sums are therefore written fma(x, one, y)
+// with `one` = 1.0f passed as a kernel argument: round(x * 1 + y) = round(x + y), and an FMA with
+// an unknown multiplier cannot be merged with the multiplies that produced x and y.
 // REG = false (clouds of 8193 to 16384 points, 16 per thread): only the running minima stay in
 // registers, the coordinates are read from the shared-memory copy in every step.
 template <int P2, bool REG = true>
 __global__ void __launch_bounds__(FPS_MAX_THREADS)
 fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__restrict__ index, int ps, int cs,
-                    float *__restrict__ sampled) {
+                    float *__restrict__ sampled, float one) {
   extern __shared__ float sxyz[];  // [3*N] copy of the cloud
   __shared__ unsigned slots[2][32];
   __shared__ int s_idx[2];
@@ -87,25 +91,31 @@ fps_resident_kernel(const float *__restrict__ points, int N, int S, int64_t *__r
 
   int cur = 0;
   if (tid == 0) out[0] = 0;
+  const float2 one2 = make_float2(one, one);
   for (int it = 1; it < S; ++it) {
     const int par = it & 1;
     const float cx = sxyz[3 * cur + 0], cy = sxyz[3 * cur + 1], cz = sxyz[3 * cur + 2];
+    const float2 ncx = make_float2(-cx, -cx), ncy = make_float2(-cy, -cy), ncz = make_float2(-cz, -cz);
     float bm = 0.f;
 #pragma unroll
     for (int i = 0; i < P2; ++i) {
-      float2 d;
+      float2 qx, qy, qz;
       if (REG) {
-        d.x = sqdist<float>(px[i].x, py[i].x, pz[i].x, cx, cy, cz);
-        d.y = sqdist<float>(px[i].y, py[i].y, pz[i].y, cx, cy, cz);
+        qx = px[i], qy = py[i], qz = pz[i];
       } else {
         // beyond N the running minimum is 0 and stays 0 whatever is read (the index is clamped)
         const int j0 = min((2 * i) * T + tid, N - 1), j1 = min((2 * i + 1) * T + tid, N - 1);
-        d.x = sqdist<float>(sxyz[3 * j0], sxyz[3 * j0 + 1], sxyz[3 * j0 + 2], cx, cy, cz);
-        d.y = sqdist<float>(sxyz[3 * j1], sxyz[3 * j1 + 1], sxyz[3 * j1 + 2], cx, cy, cz);
+        qx = make_float2(sxyz[3 * j0], sxyz[3 * j1]);
+        qy = make_float2(sxyz[3 * j0 + 1], sxyz[3 * j1 + 1]);
+        qz = make_float2(sxyz[3 * j0 + 2], sxyz[3 * j1 + 2]);
       }
+      // p - c as p + (-c) (identical in IEEE arithmetic), squares by packed multiplies, the two
+      // sums as fma(x, one, y): see the note above the kernel.
+      const float2 dx = __fadd2_rn(qx, ncx), dy = __fadd2_rn(qy, ncy), dz = __fadd2_rn(qz, ncz);
+      const float2 d = __ffma2_rn(__ffma2_rn(__fmul2_rn(dx, dx), one2, __fmul2_rn(dy, dy)), one2, __fmul2_rn(dz, dz));
       md[i].x = fminf(md[i].x, d.x);
       md[i].y = fminf(md[i].y, d.y);
-      bm = fmaxf(bm, fmaxf(md[i].x, md[i].y));
+      asm("max.f32 %0, %0, %1, %2;" : "+f"(bm) : "f"(md[i].x), "f"(md[i].y));  // three-input maximum
     }
     const unsigned bits = __float_as_uint(bm);
     unsigned gb = __reduce_max_sync(0xffffffffu, bits);
@@ -389,7 +399,7 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
   {                                                                                                             \
     TK3D_CUDA(raise_smem_limit((const void *)fps_resident_kernel<PP>, 98304)); \
     fps_resident_kernel<PP><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,       \
-                                                                (float *)sampled);                                \
+                                                                (float *)sampled, 1.0f);                          \
   }
     if (P <= 2) TK3D_FPS_CASE(1)
     else if (P <= 4) TK3D_FPS_CASE(2)
@@ -397,7 +407,7 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
     else {  // 8193..16384 points: 16 per thread, coordinates stay in shared memory (up to 192 KB)
       TK3D_CUDA(raise_smem_limit((const void *)fps_resident_kernel<8, false>, (int)(FPS_RESIDENT_MAX_N * 12)));
       fps_resident_kernel<8, false><<<(unsigned)B, threads, smem, st>>>(p, (int)N, (int)S, index, (int)ps, (int)cs,
-                                                                        (float *)sampled);
+                                                                        (float *)sampled, 1.0f);
     }
 #undef TK3D_FPS_CASE
     return check_launch("fps_resident_kernel");
