@@ -337,32 +337,43 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 // Two-pass kernel for 4 < k <= 128 (fp32).
 //
 // Pass 1 sweeps all keys with the cheap filter value a (3 FMA per pair) and keeps, per query, the
-// minimum of a over NCH >= 2k interleaved key classes (class = position inside a key tile divided by
-// the keys per class, so every class is spread over the whole cloud whatever the key order).  The k-th smallest class
-// minimum tau bounds the k-th smallest exact distance from above: the k classes below it each
-// hold a distinct key with a <= tau, and for any key
+// minimum of a over NCH >= 2k interleaved key classes.  The k-th smallest class minimum tau bounds
+// the k-th smallest exact distance from above: the k classes at or below it each hold a distinct key
+// with a <= tau, and for any key
 //     d <= (a + 22.2u |r|^2 + 3.1u |q|^2 + |q|^2) (1 + 5.1u)
 // (upper counterpart of the bound derived in sweep.cuh; |r|^2 <= the cloud's maximum).
-// Pass 2 sweeps the keys again and records every key whose filter value admits d <= that bound --
-// typically about 1.4 k candidates -- and the exact top-k by (distance, index) is then selected
-// among the candidates only.  No data-dependent work happens inside the sweeps, so the lanes of a
-// warp stay in step however the insert pattern of a one-pass top-k would look.
+// Pass 2 sweeps the keys again and records every GROUP of eight keys whose smallest filter value
+// admits d <= that bound -- about 1.3 k groups, nearly all holding a single candidate.  The keys of
+// the recorded groups then get their exact distance, the ones below the bound (about 1.35 k) are
+// ranked by (distance, index) among themselves and the first k go straight to the output row.
+// Nothing data dependent happens inside the sweeps: the group append is six predicated
+// straight-line instructions per eight pairs, so the lanes of a warp stay in step whatever the
+// insert pattern of a one-pass top-k would look like.
 //
-// Work split: a block of 4 warps serves 32*Q queries; warp s sweeps the s-th quarter of every key
-// tile for all of them (lane = query), so a cloud of a few thousand queries still fills the GPU.
-// Class minima are merged through shared memory.  Candidates of a query go to ONE list per query
-// (slot claimed with a shared-memory atomic, so the four warps share the space and its order is
-// arbitrary); the final selection ranks every candidate by (distance, index) against all others of
-// its query, which is order independent, and writes it straight to its output position.
-// Shared memory is laid out so that the exact candidate distances reuse the key tiles and class
-// minima (dead by then): 30 KB per block for Q = 2, which keeps seven blocks (28 warps) per SM.
+// Work split: a block of 4 warps serves 32*Q queries (lane = query) and every warp sweeps a quarter
+// of every key tile, so a cloud of a few thousand queries still fills the GPU.  In pass 1 a warp
+// takes the key PAIRS w, w + 4, w + 8, ... of a tile (w = its number rotated by the tile number),
+// in blocks of NCH/4 pairs that are rotated by the tile number as well, and pair c of the p-th
+// block belongs to class (c + p) mod (NCH/4).  Consecutive keys, keys one row apart in a row-major
+// depth image and keys of neighbouring tiles thus land in different warps and classes, which
+// keeps the bound tight for spatially ordered clouds, whose nearest keys sit close to one another
+// in memory (with a plain "position in tile" mapping they share a few classes and the bound
+// degenerates).  In pass 2 a warp takes a contiguous quarter of the tile in groups of eight keys.
+// Class minima are merged through shared memory: for 32 classes every warp sorts its eight minima
+// with a 19-comparator network and one thread per query merges the four sorted runs up to the k-th
+// element; for more classes every value is ranked by counting.
+// Groups of a query go to ONE list per query (slot claimed with a shared-memory atomic, so the four
+// warps share the space and its order is arbitrary).  A group's first candidate replaces the group
+// id in its list slot, further candidates of the same group (rare) go behind the list; the exact
+// candidate distances reuse the key tiles and class minima (dead by then) -- 31 KB of shared memory
+// per block for Q = 2, which keeps seven blocks (28 warps) per SM.
 // If a list overflows (massive ties, adversarial or non-finite input) the query falls back to an
-// exact insertion scan over all keys.
+// exact scan over all keys by one warp (lanes = keys, sorted list in the query's list column).
 constexpr int KT_THREADS = 128;
-constexpr int KT_SPLIT = KT_THREADS / 32;  // key quarters per tile
+constexpr int KT_SPLIT = KT_THREADS / 32;  // warps sharing every tile
 // KT_NCH key classes (32 to 256: at least two per wanted neighbour, i.e. k <= KT_NCH / 2; a warp
-// holds the minima of its KT_NCH / 4 classes in registers) and KT_QCAP candidate slots per query
-// (about 1.4 k candidates are expected) are template parameters of the kernel:
+// holds the minima of its KT_NCH / 4 classes in registers) and KT_QCAP group slots per query are
+// template parameters of the kernel:
 //     k <= 16: 32 classes, 56 slots, one or two queries per lane
 //     k <= 32: 64 classes, 104 slots, one query per lane
 //     k <= 64: 128 classes, 192 slots, one query per lane
@@ -372,10 +383,10 @@ constexpr size_t kt_smem_bytes() {
   return (size_t)2 * KT_TILE * 16 + (size_t)KT_NCH * 32 * Q * 4 + (size_t)KT_QCAP * 32 * Q * 4;
 }
 
-// Predicated append: if !(a >= thr), claim a slot of the query's list and store j there (when the
-// slot exists).  Written in PTX so that it stays five straight-line instructions per pair.
+// Predicated append: if a < thr, claim a slot of the query's list and store v there (when the
+// slot exists).  Written in PTX so that it stays five straight-line instructions.
 template <int STRIDE_BYTES, int KT_QCAP>
-__device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr, unsigned cand_addr, int j) {
+__device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr, unsigned cand_addr, int v) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -388,7 +399,14 @@ __device__ __forceinline__ void kt_append(float a, float thr, unsigned cnt_addr,
       "mad.lo.u32 ad, sl, %6, %3;\n\t"
       "@q st.shared.s32 [ad], %4;\n\t"
       "}" ::"f"(a),
-      "f"(thr), "r"(cnt_addr), "r"(cand_addr), "r"(j), "n"(KT_QCAP), "n"(STRIDE_BYTES));
+      "f"(thr), "r"(cnt_addr), "r"(cand_addr), "r"(v), "n"(KT_QCAP), "n"(STRIDE_BYTES));
+}
+
+// Compare-exchange of a sorting network.
+__device__ __forceinline__ void kt_cx(float &a, float &b) {
+  const float lo = fminf(a, b), hi = fmaxf(a, b);
+  a = lo;
+  b = hi;
 }
 
 // Q = queries per lane (1 or 2): a block serves 32*Q queries.  Two queries per lane halve the
@@ -398,22 +416,28 @@ __global__ void __launch_bounds__(KT_THREADS, MINB)
 knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k,
                    float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int PER = KT_TILE / KT_THREADS;
-  constexpr int CPW = KT_NCH / KT_SPLIT;          // classes per warp: 8, 16 or 32
-  constexpr int PPC = KT_TILE / KT_SPLIT / CPW / 2;  // key pairs per class, tile and warp: 4, 2 or 1
-  constexpr int QS = 32 * Q;              // query slots per block
-  constexpr int NSUB = KT_THREADS / QS;   // threads per query in the selection
+  constexpr int CPW = KT_NCH / KT_SPLIT;          // classes per warp: 8, 16, 32 or 64
+  constexpr int NPAIR = KT_TILE / 2 / KT_SPLIT;   // key pairs per warp and tile: 32 or 64
+  constexpr int PPC = NPAIR / CPW;                // key pairs per class, tile and warp: 4, 2 or 1
+  constexpr int GPP = NPAIR / 4;                  // groups of four pairs (eight keys) per warp and tile
+  constexpr int QS = 32 * Q;                      // query slots per block
+  constexpr int NSUB = KT_THREADS / QS;           // threads per query in the selection
+  constexpr int REGION = 2 * KT_TILE * 16 + KT_NCH * QS * 4;  // bytes of tile + class minima
+  constexpr int FCAP = REGION / (QS * 4);         // exact candidate distances that fit into that region
   extern __shared__ __align__(16) unsigned char kt_smem[];
   float4 *tile = reinterpret_cast<float4 *>(kt_smem);                                  // [2][KT_TILE], pair layout
   float *cm = reinterpret_cast<float *>(kt_smem + 2 * KT_TILE * 16);                   // [KT_NCH][QS] class minima
-  int *cand = reinterpret_cast<int *>(kt_smem + 2 * KT_TILE * 16 + KT_NCH * QS * 4);   // [KT_QCAP][QS]
-  float *cd = reinterpret_cast<float *>(kt_smem);  // [KT_QCAP][QS] exact distances; reuses tile + cm after pass 2
-  static_assert(2 * KT_TILE * 16 + KT_NCH * QS * 4 >= KT_QCAP * QS * 4, "candidate distances fit into tile + cm");
+  int *cand = reinterpret_cast<int *>(kt_smem + REGION);                               // [KT_QCAP][QS] group ids
+  float *cd = reinterpret_cast<float *>(kt_smem);  // [FCAP][QS] exact distances; reuses tile + cm after pass 2
   static_assert(KT_QCAP >= KT_NCH / 2, "the fallback keeps its k <= KT_NCH / 2 list in the query's own column");
-  static_assert(PPC >= 1, "at least one key pair per class, tile and warp");
-  __shared__ int ccnt[QS];
+  static_assert(FCAP >= KT_NCH / 2, "and its distances in the query's column of cd");
+  static_assert(PPC >= 1 && NPAIR % 4 == 0, "whole classes and whole groups per warp and tile");
+  static_assert(FCAP >= KT_QCAP, "a distance slot for every list slot");
+  __shared__ int ccnt[QS];  // groups recorded per query (pass 2); later: "needs the exact scan"
+  __shared__ int fcnt[QS];  // candidates stored behind the group list
+  __shared__ int hcnt[QS];  // candidates found in all
   __shared__ float s_rmax[KT_SPLIT];
-  __shared__ float s_tau[QS];
-  __shared__ float sq[3][QS];
+  __shared__ float s_tau[QS];  // k-th smallest class minimum; after the thresholds are formed, the bound itself
   const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
   const int chunks = (N1 + QS - 1) / QS;
   const float u = 5.9604645e-8f;
@@ -426,18 +450,13 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     float qx[Q], qy[Q], qz[Q], qq[Q];
     float2 mx[Q], my[Q], mz[Q];
     bool valid[Q];
-    __syncthreads();  // the previous iteration's candidate distances alias the tile; sq is rewritten
+    __syncthreads();  // the previous iteration's candidate distances alias the tile
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
       const int i = ibase + s * 32 + lane;
       valid[s] = i < N1;
       qx[s] = qy[s] = qz[s] = 0.f;
       if (valid[s]) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx[s], qy[s], qz[s]);
-      if (part == 0) {
-        sq[0][s * 32 + lane] = qx[s];
-        sq[1][s * 32 + lane] = qy[s];
-        sq[2][s * 32 + lane] = qz[s];
-      }
       mx[s] = make_float2(-2.f * qx[s], -2.f * qx[s]);
       my[s] = make_float2(-2.f * qy[s], -2.f * qy[s]);
       mz[s] = make_float2(-2.f * qz[s], -2.f * qz[s]);
@@ -462,7 +481,7 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * KT_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
     };
 
-    // ---- pass 1: minima of the filter value over this warp's 8 classes
+    // ---- pass 1: minima of the filter value over this warp's classes
     float cmin[Q][CPW];
 #pragma unroll
     for (int s = 0; s < Q; ++s)
@@ -472,19 +491,21 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
     commit(tile);
     __syncthreads();
     for (int t = 0; t < ntiles; ++t) {
-      const float4 *tl = tile + (t & 1) * KT_TILE + part * (KT_TILE / KT_SPLIT);
+      // pair i of this warp sits in float4 slots 2 * (i * KT_SPLIT + w), w = warp rotated by the tile
+      const float4 *tl = tile + (t & 1) * KT_TILE + 2 * ((part + t) & (KT_SPLIT - 1));
       if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
 #pragma unroll
-      for (int c = 0; c < CPW; ++c) {
+      for (int p = 0; p < PPC; ++p) {
+        const float4 *tb = tl + 2 * KT_SPLIT * CPW * ((p + t) % PPC);  // block of CPW pairs, rotated too
 #pragma unroll
-        for (int p = 0; p < PPC; ++p) {
-          const float4 A = tl[c * 2 * PPC + 2 * p], Bv = tl[c * 2 * PPC + 2 * p + 1];
+        for (int c = 0; c < CPW; ++c) {
+          const float4 A = tb[2 * KT_SPLIT * c], Bv = tb[2 * KT_SPLIT * c + 1];
           const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
           const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
 #pragma unroll
           for (int s = 0; s < Q; ++s) {
             const float2 a = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
-            cmin[s][c] = sweep_min3(cmin[s][c], a.x, a.y);
+            cmin[s][(c + p) % CPW] = sweep_min3(cmin[s][(c + p) % CPW], a.x, a.y);
           }
         }
       }
@@ -492,156 +513,300 @@ knn_twopass_kernel(const float *__restrict__ query, const float *__restrict__ ke
       __syncthreads();
     }
 #pragma unroll
-    for (int s = 0; s < Q; ++s)
-#pragma unroll
-      for (int c = 0; c < CPW; ++c) cm[(part * CPW + c) * QS + s * 32 + lane] = cmin[s][c];
-#pragma unroll
     for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
     if (lane == 0) s_rmax[part] = rmax;
     if (tid < QS) s_tau[tid] = pinf();
-    __syncthreads();
-    rmax = fmaxf(fmaxf(s_rmax[0], s_rmax[1]), fmaxf(s_rmax[2], s_rmax[3]));
 
-    // k-th smallest class minimum of each query: rank by counting (ties broken by class number);
-    // each warp ranks its own 8 classes and the one with rank k-1 publishes the value.
+    // ---- k-th smallest class minimum of each query
+    if constexpr (CPW == 8) {
+      // every warp sorts its eight minima (19 compare-exchanges) ...
 #pragma unroll
-    for (int s = 0; s < Q; ++s) {
+      for (int s = 0; s < Q; ++s) {
+        float(&v)[CPW] = cmin[s];
+        kt_cx(v[0], v[1]); kt_cx(v[2], v[3]); kt_cx(v[4], v[5]); kt_cx(v[6], v[7]);
+        kt_cx(v[0], v[2]); kt_cx(v[1], v[3]); kt_cx(v[4], v[6]); kt_cx(v[5], v[7]);
+        kt_cx(v[1], v[2]); kt_cx(v[5], v[6]); kt_cx(v[0], v[4]); kt_cx(v[3], v[7]);
+        kt_cx(v[1], v[5]); kt_cx(v[2], v[6]);
+        kt_cx(v[1], v[4]); kt_cx(v[3], v[6]);
+        kt_cx(v[2], v[4]); kt_cx(v[3], v[5]);
+        kt_cx(v[3], v[4]);
 #pragma unroll
-      for (int c = 0; c < CPW; ++c) {
-        const float v = cmin[s][c];
-        const int cc = part * CPW + c;
-        int rank = 0;
-#pragma unroll 8
-        for (int o = 0; o < KT_NCH; ++o) {
-          const float w = cm[o * QS + s * 32 + lane];
-          rank += (w < v || (w == v && o < cc)) ? 1 : 0;
-        }
-        if (rank == k - 1) s_tau[s * 32 + lane] = v;
+        for (int c = 0; c < CPW; ++c) cm[(part * CPW + c) * QS + s * 32 + lane] = v[c];
       }
+      __syncthreads();
+      // ... and one thread per query merges the four sorted runs up to the k-th element
+      if (tid < QS) {
+        static_assert(KT_SPLIT == 4, "four sorted runs");
+        const float *run = cm + tid;  // element e of run w: run[(w * CPW + e) * QS]
+        int p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+        float h0 = run[0], h1 = run[CPW * QS], h2 = run[2 * CPW * QS], h3 = run[3 * CPW * QS];
+        float v = pinf();
+        for (int r = 0; r < k; ++r) {
+          // the smallest head leaves its run (the first such run on equal values); written without
+          // branches: every head is re-read from its run's current position
+          v = fminf(fminf(h0, h1), fminf(h2, h3));
+          const bool t0 = h0 == v, t1 = !t0 && h1 == v, t2 = !t0 && !t1 && h2 == v, t3 = !t0 && !t1 && !t2 && h3 == v;
+          p0 += t0 ? 1 : 0;
+          p1 += t1 ? 1 : 0;
+          p2 += t2 ? 1 : 0;
+          p3 += t3 ? 1 : 0;
+          const float n0 = run[min(p0, CPW - 1) * QS], n1 = run[(CPW + min(p1, CPW - 1)) * QS];
+          const float n2 = run[(2 * CPW + min(p2, CPW - 1)) * QS], n3 = run[(3 * CPW + min(p3, CPW - 1)) * QS];
+          h0 = p0 < CPW ? n0 : pinf();
+          h1 = p1 < CPW ? n1 : pinf();
+          h2 = p2 < CPW ? n2 : pinf();
+          h3 = p3 < CPW ? n3 : pinf();
+        }
+        s_tau[tid] = v;
+      }
+      __syncthreads();
+    } else {
+#pragma unroll
+      for (int s = 0; s < Q; ++s)
+#pragma unroll
+        for (int c = 0; c < CPW; ++c) cm[(part * CPW + c) * QS + s * 32 + lane] = cmin[s][c];
+      __syncthreads();
+      // rank by counting (ties broken by class number); the value with rank k-1 is published
+#pragma unroll
+      for (int s = 0; s < Q; ++s) {
+#pragma unroll
+        for (int c = 0; c < CPW; ++c) {
+          const float v = cmin[s][c];
+          const int cc = part * CPW + c;
+          int rank = 0;
+#pragma unroll 8
+          for (int o = 0; o < KT_NCH; ++o) {
+            const float w = cm[o * QS + s * 32 + lane];
+            rank += (w < v || (w == v && o < cc)) ? 1 : 0;
+          }
+          if (rank == k - 1) s_tau[s * 32 + lane] = v;
+        }
+      }
+      __syncthreads();
     }
-    __syncthreads();
+    rmax = fmaxf(fmaxf(s_rmax[0], s_rmax[1]), fmaxf(s_rmax[2], s_rmax[3]));
     // Upper bound of the k-th smallest exact distance (constants rounded up generously to cover
     // the roundings of this very computation), then the filter threshold that admits every key
     // at or below it.  Anything non-finite sends the query to the exact fallback: its counter
     // starts beyond the capacity and its threshold admits nothing.
-    float thr[Q];
+    float thr[Q], lim[Q];
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
       const float tau = s_tau[s * 32 + lane];
       const float a_up = tau + 32.f * u * rmax + 8.f * u * qq[s];
       const float d_up = (a_up + qq[s] * (1.f + 8.f * u)) * (1.f + 10.f * u) + 1e-37f;
-      const float lim = __int_as_float(__float_as_int(fmaxf(d_up, 0.f)) + 1);  // next float up
+      lim[s] = __int_as_float(__float_as_int(fmaxf(d_up, 0.f)) + 1);  // next float up
       const bool finite = d_up < 3.0e38f && rmax < 1.0e30f && qq[s] < 1.0e30f;
-      thr[s] = (finite && valid[s]) ? sweep_threshold(lim, qq[s]) : -pinf();
-      if (part == 0) ccnt[s * 32 + lane] = (finite || !valid[s]) ? 0 : KT_QCAP + 1;
+      thr[s] = (finite && valid[s]) ? sweep_threshold(lim[s], qq[s]) : -pinf();
+      if (part == 0) {
+        ccnt[s * 32 + lane] = (finite || !valid[s]) ? 0 : KT_QCAP + 1;
+        fcnt[s * 32 + lane] = 0;
+        hcnt[s * 32 + lane] = 0;
+      }
     }
 
-    // ---- pass 2: collect the candidates (padding keys carry w = +inf and never pass)
+    // ---- pass 2: record the groups of eight consecutive keys (group id = first key / 8) that hold
+    // a candidate; padding keys carry w = +inf and never pass.
     fetch(0);
     commit(tile);
     __syncthreads();
+    if (part == 0) {  // every warp has read s_tau by now: it carries the bound from here on
+#pragma unroll
+      for (int s = 0; s < Q; ++s) s_tau[s * 32 + lane] = lim[s];
+    }
     for (int t = 0; t < ntiles; ++t) {
-      const int t0 = t * KT_TILE + part * (KT_TILE / KT_SPLIT);
       const float4 *tl = tile + (t & 1) * KT_TILE + part * (KT_TILE / KT_SPLIT);
+      const int g0 = (t * KT_TILE + part * (KT_TILE / KT_SPLIT)) >> 3;
       if (t + 1 < ntiles) fetch((t + 1) * KT_TILE);
 #pragma unroll 2
-      for (int u0 = 0; u0 < KT_TILE / KT_SPLIT; u0 += 4) {
-        // Two key pairs (four keys) at a time: one minimum and one compare per query decide
-        // whether any of its four filter values passes; only then are the four appends executed
-        // (about 2 % of the lanes, half of the warps).
-        float2 a[2][Q];
+      for (int g = 0; g < GPP; ++g) {
+        float2 a[4][Q];
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          const float4 A = tl[u0 + 2 * p], Bv = tl[u0 + 2 * p + 1];
+        for (int p = 0; p < 4; ++p) {
+          const float4 A = tl[8 * g + 2 * p], Bv = tl[8 * g + 2 * p + 1];
           const float2 kx = make_float2(A.x, A.y), ky = make_float2(A.z, A.w);
           const float2 kz = make_float2(Bv.x, Bv.y), kw = make_float2(Bv.z, Bv.w);
 #pragma unroll
           for (int s = 0; s < Q; ++s)
             a[p][s] = __ffma2_rn(mx[s], kx, __ffma2_rn(my[s], ky, __ffma2_rn(mz[s], kz, kw)));
         }
-        const int j = t0 + u0;
 #pragma unroll
         for (int s = 0; s < Q; ++s) {
-          const float m = fminf(sweep_min3(a[0][s].x, a[0][s].y, a[1][s].x), a[1][s].y);
-          if (m < thr[s]) {
-            const unsigned ca = cnt_base + 4u * (s * 32 + lane), da = cand_base + 4u * (s * 32 + lane);
-            kt_append<QS * 4, KT_QCAP>(a[0][s].x, thr[s], ca, da, j);
-            kt_append<QS * 4, KT_QCAP>(a[0][s].y, thr[s], ca, da, j + 1);
-            kt_append<QS * 4, KT_QCAP>(a[1][s].x, thr[s], ca, da, j + 2);
-            kt_append<QS * 4, KT_QCAP>(a[1][s].y, thr[s], ca, da, j + 3);
-          }
+          float m = sweep_min3(a[0][s].x, a[0][s].y, a[1][s].x);
+          m = sweep_min3(m, a[1][s].y, a[2][s].x);
+          m = sweep_min3(m, a[2][s].y, a[3][s].x);
+          m = fminf(m, a[3][s].y);
+          kt_append<QS * 4, KT_QCAP>(m, thr[s], cnt_base + 4u * (s * 32 + lane), cand_base + 4u * (s * 32 + lane),
+                                     g0 + g);
         }
       }
       if (t + 1 < ntiles) commit(tile + ((t + 1) & 1) * KT_TILE);
       __syncthreads();
     }
 
-    // ---- exact selection: NSUB threads per query.  First the exact distance of every candidate,
-    // then each candidate's rank by (distance, index) among its query's candidates; ranks below k
-    // go straight to the output row.
+    // ---- exact selection: NSUB threads per query.  The eight keys of every recorded group get
+    // their exact distance (all 24 coordinates are loaded before any is used, so the loads of a
+    // group overlap); keys below the bound are the candidates.  A group's first candidate takes
+    // the group's own list slot (distance in cd, key index in cand; -1 / +inf when the group holds
+    // none), any further ones go behind the list.  Then each candidate is ranked by (distance,
+    // index) among its query's candidates and ranks below k go straight to the output row.
     const int col = tid % QS, sub = tid / QS;
     const int iq = ibase + col;
     const bool qvalid = iq < N1;
     const int n = ccnt[col];
-    const float cqx = sq[0][col], cqy = sq[1][col], cqz = sq[2][col];
-    // A list that overflowed, or -- which the bound derivation rules out for finite input, but which
-    // costs nothing to guard -- holds fewer than k candidates, sends its query to the exact scan.
-    const bool listed = n >= k && n <= KT_QCAP;
-    if (qvalid && listed) {
+    float cqx = 0.f, cqy = 0.f, cqz = 0.f;
+    if (qvalid) load_xyz(query + b * 3 * (int64_t)N1, iq, ql, cqx, cqy, cqz);
+    if (qvalid && n <= KT_QCAP) {
+      const float bound = s_tau[col];
+      int hits = 0;
+      // [N,3] clouds whose rows start on 16-byte boundaries: a whole group is six 16-byte loads
+      const bool vec = kl.cs == 1 && (reinterpret_cast<uintptr_t>(rb) & 15) == 0;
       for (int c = sub; c < n; c += NSUB) {
-        const int j = cand[c * QS + col];
-        float rx, ry, rz;
-        load_xyz(rb, j, kl, rx, ry, rz);
-        cd[c * QS + col] = sqdist<float>(rx, ry, rz, cqx, cqy, cqz);
+        const int j0 = cand[c * QS + col] * 8;
+        float rx[8], ry[8], rz[8];
+        if (vec && j0 + 8 <= N2) {
+          const float4 *g4 = reinterpret_cast<const float4 *>(rb + (int64_t)j0 * 3);
+          const float4 v0 = __ldg(g4), v1 = __ldg(g4 + 1), v2 = __ldg(g4 + 2), v3 = __ldg(g4 + 3), v4 = __ldg(g4 + 4),
+                       v5 = __ldg(g4 + 5);
+          rx[0] = v0.x, ry[0] = v0.y, rz[0] = v0.z, rx[1] = v0.w, ry[1] = v1.x, rz[1] = v1.y;
+          rx[2] = v1.z, ry[2] = v1.w, rz[2] = v2.x, rx[3] = v2.y, ry[3] = v2.z, rz[3] = v2.w;
+          rx[4] = v3.x, ry[4] = v3.y, rz[4] = v3.z, rx[5] = v3.w, ry[5] = v4.x, rz[5] = v4.y;
+          rx[6] = v4.z, ry[6] = v4.w, rz[6] = v5.x, rx[7] = v5.y, ry[7] = v5.z, rz[7] = v5.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) load_xyz(rb, min(j0 + e, N2 - 1), kl, rx[e], ry[e], rz[e]);
+        }
+        int first = -1;
+        float firstd = pinf();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = sqdist<float>(rx[e], ry[e], rz[e], cqx, cqy, cqz);
+          if (j0 + e < N2 && d < bound) {
+            ++hits;
+            if (first < 0) {
+              first = j0 + e;
+              firstd = d;
+            } else {
+              const int row = n + atomicAdd(&fcnt[col], 1);
+              if (row < KT_QCAP) {
+                cd[row * QS + col] = d;
+                cand[row * QS + col] = j0 + e;
+              }
+            }
+          }
+        }
+        cd[c * QS + col] = firstd;
+        cand[c * QS + col] = first;
       }
+      if (hits) atomicAdd(&hcnt[col], hits);
     }
     __syncthreads();
-    if (qvalid) {
+    // A list that overflowed, or -- which the bound derivation rules out for finite input, but which
+    // costs nothing to guard -- holds fewer than k candidates, sends its query to the exact scan.
+    const int rows = n + fcnt[col];
+    const bool listed = n <= KT_QCAP && rows <= KT_QCAP && hcnt[col] >= k;
+    if (qvalid && listed) {
       float *od = dist + (b * N1 + iq) * (int64_t)k;
       const int64_t orow = (b * N1 + iq) * (int64_t)k;
-      if (listed) {
-        for (int c = sub; c < n; c += NSUB) {
-          const float d = cd[c * QS + col];
-          const int j = cand[c * QS + col];
-          int rank = 0;
-          for (int o = 0; o < n; ++o) {
-            const float w = cd[o * QS + col];
-            const int jo = cand[o * QS + col];
-            rank += (w < d || (w == d && jo < j)) ? 1 : 0;
-          }
-          if (rank < k) {
-            od[rank] = d;
-            index.put(orow + rank, j);
-          }
+      for (int f = sub; f < rows; f += NSUB) {
+        const int j = cand[f * QS + col];
+        if (j < 0) continue;
+        const float d = cd[f * QS + col];
+        // rank = candidates with a smaller distance; equal distances (rare) are settled by index
+        int rank = 0, same = 0;
+#pragma unroll 8
+        for (int o = 0; o < rows; ++o) {
+          const float w = cd[o * QS + col];  // empty slots hold +inf
+          rank += w < d ? 1 : 0;
+          same += w == d ? 1 : 0;
         }
-      } else if (sub == 0) {
-        // Exact insertion scan; the sorted list lives in the first k slots of this query's own
-        // column of cd / cand (nobody else touches the column of an overflowed query).
-        int nk = 0;
-        for (int j = 0; j < N2; ++j) {
+        if (same > 1) {
+          for (int o = 0; o < rows; ++o)
+            rank += (cd[o * QS + col] == d && (unsigned)cand[o * QS + col] < (unsigned)j) ? 1 : 0;  // -1 is last
+        }
+        if (rank < k) {
+          od[rank] = d;
+          index.put(orow + rank, j);
+        }
+      }
+    }
+    __syncthreads();  // every thread is done with the lists before an exact scan reuses a column
+    if (sub == 0) ccnt[col] = (qvalid && !listed) ? 1 : 0;
+    __syncthreads();
+
+    // ---- exact scan of the queries flagged above, one warp per query: lanes take 32 consecutive
+    // keys at a time; a key that beats the current k-th entry is inserted into the sorted list kept
+    // in the first k slots of the query's own column of cd / cand (position by counting, entries
+    // behind it moved up by the lanes together).  Keys arrive in ascending index order, so a key
+    // equal to the k-th distance never enters a full list and equal distances stay in index order.
+    // A NaN distance counts as +inf for the ordering.
+    for (int fc = part; fc < QS; fc += KT_SPLIT) {
+      if (ccnt[fc] == 0) continue;  // uniform over the warp
+      const int fq = ibase + fc;
+      float fx, fy, fz;
+      load_xyz(query + b * 3 * (int64_t)N1, fq, ql, fx, fy, fz);
+      int nk = 0;
+      float kth = pinf();
+      for (int base = 0; base < N2; base += 32) {
+        const int j = base + lane;
+        float d = pinf();
+        if (j < N2) {
           float rx, ry, rz;
           load_xyz(rb, j, kl, rx, ry, rz);
-          const float d = sqdist<float>(rx, ry, rz, cqx, cqy, cqz);
-          if (nk == k) {
-            const float dl = cd[(k - 1) * QS + col];
-            if (!(d < dl || (d == dl && j < cand[(k - 1) * QS + col]))) continue;
+          d = sqdist<float>(rx, ry, rz, fx, fy, fz);
+        }
+        const float dv = d == d ? d : pinf();  // ordering value
+        unsigned mask = __ballot_sync(0xffffffffu, j < N2 && (nk < k || dv < kth));
+        while (mask) {
+          const int l = __ffs(mask) - 1;
+          mask &= mask - 1;
+          const float dn = __shfl_sync(0xffffffffu, d, l), dnv = __shfl_sync(0xffffffffu, dv, l);
+          if (nk == k && !(dnv < kth)) continue;  // the k-th entry tightened since the ballot
+          // position: entries ordering at or before the new key (equal distances hold lower indices)
+          int before = 0;
+          for (int r = lane; r < nk; r += 32) {
+            const float w = cd[r * QS + fc];
+            before += ((w == w ? w : pinf()) <= dnv) ? 1 : 0;
           }
-          int pos = nk < k ? nk : k - 1;
-          while (pos > 0) {
-            const float dp = cd[(pos - 1) * QS + col];
-            if (!(d < dp || (d == dp && j < cand[(pos - 1) * QS + col]))) break;
-            cd[pos * QS + col] = dp;
-            cand[pos * QS + col] = cand[(pos - 1) * QS + col];
-            --pos;
+          const int pos = __reduce_add_sync(0xffffffffu, before);
+          const int last = nk < k ? nk : k - 1;  // slot that receives the old entry last - 1
+          // move entries [pos, last) up by one: read them all, then write them all
+          float mv[4];
+          int mj[4];
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int r = lane + 32 * q4;
+            if (r >= pos && r < last) {
+              mv[q4] = cd[r * QS + fc];
+              mj[q4] = cand[r * QS + fc];
+            }
           }
-          cd[pos * QS + col] = d;
-          cand[pos * QS + col] = j;
+          __syncwarp();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int r = lane + 32 * q4;
+            if (r >= pos && r < last) {
+              cd[(r + 1) * QS + fc] = mv[q4];
+              cand[(r + 1) * QS + fc] = mj[q4];
+            }
+          }
+          if (lane == 0) {
+            cd[pos * QS + fc] = dn;
+            cand[pos * QS + fc] = base + l;
+          }
+          __syncwarp();
           if (nk < k) ++nk;
+          if (nk == k) {
+            const float w = cd[(k - 1) * QS + fc];
+            kth = w == w ? w : pinf();
+          }
         }
-        for (int c = 0; c < k; ++c) {
-          od[c] = cd[c * QS + col];
-          index.put(orow + c, cand[c * QS + col]);
-        }
+      }
+      float *od = dist + (b * N1 + fq) * (int64_t)k;
+      const int64_t orow = (b * N1 + fq) * (int64_t)k;
+      for (int c = lane; c < k; c += 32) {
+        od[c] = cd[c * QS + fc];
+        index.put(orow + c, cand[c * QS + fc]);
       }
     }
   }
@@ -944,3 +1109,4 @@ extern "C" int tk3d_knn_layout(const void *query, const void *key, int64_t B, in
   return knn_impl(query, key, B, N1, N2, k, xyz_channel_first != 0, distance, index, index_dtype == TK3D_I32, dtype,
                   stream);
 }
+
