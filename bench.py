@@ -14,12 +14,15 @@ The JSON line also carries:
   roofline      the forward kernel (the dominant launch) against the FP32 FMA rate measured live by
                 a dependent-FFMA kernel; 8 flop per pair (3 sub, 3 mul, 2 add);
   cpu_baseline  the reference's pure-PyTorch brute-force formulation of the same step, timed on the
-                host cores on a bounded sample (rank 0, N=1 only);
+                host cores on a bounded sample (rank 0, N=1 only); extras.cpu_baselines holds the
+                CPU formulations of the other configurations;
+  loss          the global mean chamfer loss of the batch -- the same number for every N;
   e2e           the same metric through the public API with HOST inputs: pinned host -> device
                 copies of both clouds and a device -> host read of the loss inside the timed region;
   extras        the other configurations (KNN, FPS / ball query / grouping, 3-NN interpolation).
 
---impl reference runs the reference's CPU formulation alone (rank 0; other ranks exit);
+--impl reference runs the reference's CPU formulation alone (rank 0; other ranks exit), one whole
+16384 x 16384 cloud pair per step;
 --impl reference-cuda times the reference's own CUDA extension as shipped (default nvcc flags),
 when oracle/_ref/shipped/_C.so has been built.
 """
@@ -173,24 +176,22 @@ def cpu_formulation_rate(sample_rows, repeats=1, threads=None):
 
 
 def run_reference_cpu(args, rank, world):
+    """The reference's CPU formulation alone: every step is the SAME fixed sample (one whole
+    16384 x 16384 cloud pair, forward + backward), so the figure does not depend on a pilot run."""
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    # Size the per-step sample so that warmup+steps stay within about two minutes.
-    rate, dt, _ = cpu_formulation_rate(1024)
-    budget = 120.0 / max(1, args.steps + args.warmup)
-    rows = int(min(C4["N"], max(256, (rate * budget) / (2.0 * C4["M"]))))
-    rows = max(256, (rows // 256) * 256)
-    for _ in range(args.warmup):
-        cpu_formulation_rate(rows)
+    for _ in range(min(args.warmup, 2)):
+        cpu_formulation_rate(C4["N"])
     times = []
     pairs = 0.0
     for _ in range(args.steps):
-        _, dt, pairs = cpu_formulation_rate(rows)
+        _, dt, pairs = cpu_formulation_rate(C4["N"])
         times.append(dt)
     ms = 1e3 * sum(times) / len(times)
     value = pairs / (ms / 1e3)
-    sample = "chamfer fwd+bwd, first %d points of one cloud vs its 16384-point partner, both directions, per step" % rows
+    sample = ("CPU formulation (not the reference's CUDA kernels): chamfer fwd+bwd of one whole 16384 x 16384 "
+              "cloud pair, both directions, per step")
     line = {"impl": "reference", "metric": "chamfer_point_pairs_per_sec", "value": value, "unit": "pairs/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -199,6 +200,64 @@ def run_reference_cpu(args, rank, world):
             "e2e": {"value": value, "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def cpu_config_baselines(budget_s=4.0):
+    """The reference's brute-force CPU formulations of the other configurations, on the host cores.
+
+    Small configurations run whole; the large ones run a stated sample and the rate is what is
+    reported (the sample is named in the result).  Every entry carries its own seconds."""
+    import numpy as np
+
+    from oracle import formulations as F
+    from torkit3d_b200 import workloads
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    out = {"cores": cores}
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        fn()
+        return time.perf_counter() - t0
+
+    # C1: chamfer fwd+bwd, B=2, 1024 x 1024, whole
+    a, b = workloads.c1_chamfer_small()
+    F.chamfer_loss_fwd_bwd(a, b)
+    dt = min(timed(lambda: F.chamfer_loss_fwd_bwd(a, b)) for _ in range(3))
+    out["c1_chamfer_fwd_bwd_ms"] = dt * 1e3
+    # C2: KNN k=16 by cdist + topk (torkit3d/ops/native.py), one cloud at a time, 4 of the 16 clouds
+    q, r = workloads.c2_knn()
+    dt = timed(lambda: [F.knn_cdist_topk(q[i:i + 1], r[i:i + 1], 16) for i in range(4)])
+    out["c2_knn_k16_ms"] = dt * 1e3 * 16 / 4
+    out["c2_knn_sample"] = "4 of 16 clouds, scaled by 4"
+    # C3: FPS (numpy loop of the reference's test), ball query (numpy loop), group (expanded gather)
+    p, feat = workloads.c3_set_abstraction()
+    pn = p.numpy()
+    dt = timed(lambda: F.fps_numpy(pn[:2], 1024))
+    out["c3_fps_ms_per_batch"] = dt * 1e3 * 32 / 2
+    out["c3_fps_sample"] = "2 of 32 clouds, scaled by 16"
+    idx = F.fps_numpy(pn[:1], 1024)
+    cent = np.take_along_axis(pn[:1], idx[:, :, None].repeat(3, 2), 1)
+    dt = timed(lambda: F.ball_query_numpy(cent[:, :256], pn[:1], 0.1, 32))
+    out["c3_ball_query_ms"] = dt * 1e3 * 32 * 4
+    out["c3_ball_query_sample"] = "256 of 1024 centroids of 1 of 32 clouds, scaled by 128"
+    nbr = torch.from_numpy(F.ball_query_numpy(cent, pn[:1], 0.1, 32)).clamp_(min=0)
+    f1 = feat[:1]
+    dt = timed(lambda: F.group_gather(f1, nbr))
+    out["c3_group_fwd_ms"] = dt * 1e3 * 32
+    out["c3_group_fwd_sample"] = "1 of 32 clouds, scaled by 32"
+    # C5: three nearest of 32768 keys by cdist + topk, then the weighted gather: 4096 queries of one cloud
+    qq, rr, ff = workloads.c5_scene_interp(B=1)
+    qs = qq[:, :4096]
+    dt = timed(lambda: F.knn_cdist_topk(qs, rr, 3))
+    out["c5_three_nn_ms"] = dt * 1e3 * 8 * 131072 / 4096
+    d, i = F.knn_cdist_topk(qs, rr, 3)
+    w = F.three_nn_weight(d * d)
+    dt = timed(lambda: F.interpolate_gather(ff, i, w))
+    out["c5_interp_fwd_ms"] = dt * 1e3 * 8 * 131072 / 4096
+    out["c5_sample"] = "4096 of 131072 queries of 1 of 8 clouds, scaled by 256"
+    return out
 
 
 def workload_config(n_gpus, world):
@@ -357,7 +416,7 @@ def run_b200(args, rank, world, local_rank):
     import torch.distributed as dist
 
     from torkit3d_b200 import _lib, workloads
-    from torkit3d_b200.dist import HostCloudPrefetcher, chamfer_loss, shard_range
+    from torkit3d_b200.dist import HostCloudPrefetcher, chamfer_loss, chamfer_step, shard_range
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     torch.cuda.set_device(local_rank)
@@ -374,6 +433,10 @@ def run_b200(args, rank, world, local_rank):
     pairs_local = 2.0 * (b1 - b0) * C4["N"] * C4["M"]
 
     def step():
+        # loss and both gradients in one call; the gradient kernels overlap the scalar all-reduce
+        return chamfer_step(x1, x2, global_batch=C4["B"])
+
+    def step_autograd():
         x1.grad = None
         x2.grad = None
         loss = chamfer_loss(x1, x2, global_batch=C4["B"])
@@ -388,6 +451,9 @@ def run_b200(args, rank, world, local_rank):
     barrier(world)
     ms_step = rank_max(sum(ms) / len(ms), dev, world)
     value = pairs_total / (ms_step * 1e-3)
+    loss_value = float(step()[0])  # identical on every rank and for every number of GPUs
+    ms_auto = time_steps(step_autograd, args.steps, 3, flush)
+    ms_step_autograd = rank_max(sum(ms_auto) / len(ms_auto), dev, world)
 
     # ---- forward kernel alone (the dominant launch), through the C ABI with preallocated outputs
     Bl = b1 - b0
@@ -414,10 +480,11 @@ def run_b200(args, rank, world, local_rank):
                 "peak": peak if peak else nominal, "peak_source": "measured live (dependent FFMA chains)" if peak
                 else "nominal 148 SM x 128 lanes x 2 x 1.965 GHz", "unit": "TFLOP/s",
                 "frac": achieved / (peak if peak else nominal), "nominal_peak": nominal,
-                # DRAM read+write of this kernel from the committed ncu capture (profiles/chamfer_fwd.md:
-                # 9.47 MB at B=24; profiles/chamfer_fwd_smwide.md: 3.17 MB at B=8), scaled to this
-                # launch by the clouds it processes
+                "frac_nominal": achieved / nominal,
+                # DRAM read + write per launch: an ncu capture of this kernel on 24 cloud pairs moved
+                # 9.465 MB (the clouds themselves, read once); scaled by the clouds of this launch
                 "traffic": 9.465e6 * Bl / 24.0, "traffic_unit": "bytes",
+                "traffic_source": "ncu capture at 24 cloud pairs, scaled by cloud count",
                 "flop_per_pair": PAIR_FLOP, "pairs_per_launch": pairs_local, "launch_ms": fwd_ms,
                 "pairs_per_sec": pairs_local / (fwd_ms * 1e-3)}
 
@@ -458,11 +525,8 @@ def run_b200(args, rank, world, local_rank):
             a, b = pf.get()
             if i + 1 < steps:
                 pf.prefetch(x1h, x2h)
-            a = a.detach().requires_grad_(True)
-            b = b.detach().requires_grad_(True)
-            loss = chamfer_loss(a, b, global_batch=C4["B"])
-            loss.backward()
-            loss_host.copy_(loss.detach(), non_blocking=True)
+            loss, _, _ = chamfer_step(a, b, global_batch=C4["B"])
+            loss_host.copy_(loss, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         return float(loss_host)
 
@@ -477,7 +541,7 @@ def run_b200(args, rank, world, local_rank):
     e2e = {"value": pairs_total / e2e_s, "unit": "pairs/s", "ms_per_step": e2e_s * 1e3,
            "h2d_bytes_per_step": int(x1h.numel() * 4 + x2h.numel() * 4), "d2h_bytes_per_step": 4,
            "api": "HostCloudPrefetcher (pinned host clouds, next step's copy on a side stream) + "
-                  "dist.chamfer_loss + backward, loss read back every step"}
+                  "dist.chamfer_step (loss + gradients), loss read back every step"}
 
     ext = extras(dev, rank, world, flush) if not args.no_extras else {}
 
@@ -496,12 +560,16 @@ def run_b200(args, rank, world, local_rank):
                "sample": "reference brute-force PyTorch formulation (difference tensor in 1024-row blocks, min, "
                          "autograd backward) of chamfer fwd+bwd on one 16384 x 16384 cloud pair, repeated %d times" % reps}
 
+        if not args.no_extras:
+            ext["cpu_baselines"] = cpu_config_baselines()
+
     if rank == 0:
         line = {"metric": "chamfer_point_pairs_per_sec", "value": value, "unit": "pairs/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": workload_config(world, world), "clocks": clocks, "e2e": e2e, "gpu_launches": 4,
-                "gpu_launches_detail": "per step: %s, chamfer_mean_loss_kernel, chamfer_bwd_own_kernel, chamfer_bwd_scatter_kernel" % roofline["kernel"],
+                "gpu_launches_detail": "per step: %s, chamfer_bwd_own_kernel, chamfer_bwd_scatter_kernel, chamfer_mean_loss_kernel" % roofline["kernel"],
+                "loss": loss_value, "ms_per_step_autograd": ms_step_autograd,
                 "roofline": roofline, "roofline_backward": bwd, "cpu_baseline": cpu, "extras": ext}
         print(json.dumps(line), flush=True)
     if world > 1:

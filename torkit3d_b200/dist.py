@@ -4,8 +4,9 @@ Every operator of this package is independent per cloud (batch entry) and -- exc
 sampling -- per query point, so a job scales by giving each rank a slice of the batch
 (``batch_shard``) or, for a single huge scene, a slab of the query points (``query_slab``) with the
 key cloud and its features replicated.  No operator needs another rank's data.  The only exchange
-is the scalar chamfer loss: ``chamfer_loss`` produces the local partial sums inside the forward
-kernel's epilogue and all-reduces two float64 numbers (NCCL over NVLink when the tensors are on
+is the scalar chamfer loss: ``chamfer_loss`` (autograd) and ``chamfer_step`` (loss and gradients
+in one call, gradient kernels overlapped with the collective) produce the local partial sums
+inside the forward kernel's epilogue and all-reduce two float64 numbers (NCCL over NVLink when the tensors are on
 GPUs; any ``torch.distributed`` backend works, which is how the CPU ``gloo`` tests exercise the
 host logic with a stand-in for the kernels).
 """
@@ -123,6 +124,68 @@ def chamfer_loss(xyz1, xyz2, global_batch=None, group=None, _forward_fn=None, _b
     return _ChamferLoss.apply(xyz1, xyz2, count1, count2, group, _forward_fn, _backward_fn)
 
 
+_ones = {}
+
+
+def _one(device, dtype):
+    """A cached device scalar 1 (the upstream gradient of a loss); filled once, never written again."""
+    key = (device.type, device.index, dtype)
+    t = _ones.get(key)
+    if t is None:
+        t = torch.ones((), dtype=dtype, device=device)
+        _ones[key] = t
+    return t
+
+
+# ---- training step without autograd ---------------------------------------------------------------
+def chamfer_step(xyz1, xyz2, global_batch=None, group=None):
+    """Mean chamfer loss over a batch sharded across ranks AND its gradients, in one call.
+
+    The loss is linear in the per-point distances, so the gradient kernels need only the counts,
+    not the reduced loss: they are launched right behind the forward kernel while the all-reduce of
+    the two partial sums is in flight (``async_op``), and only the final loss kernel waits for it.
+    Five launches per step (forward, two gradient kernels, the collective, the loss), no
+    element-wise PyTorch kernel, no autograd graph.
+
+    Args:
+        xyz1: [B_local, N1, 3] float32/float64 CUDA tensor, this rank's clouds;  xyz2: [B_local, N2, 3].
+        global_batch, group: as for ``chamfer_loss``.
+
+    Returns:
+        (loss, grad_xyz1, grad_xyz2): the global mean loss (0-dim, identical on every rank) and
+        its gradients w.r.t. this rank's clouds.
+    """
+    from . import _lib
+    from ._C import _dtype, _on, _ptr, _stream
+
+    a, b = xyz1.detach().contiguous(), xyz2.detach().contiguous()
+    lib = _lib.load()
+    world = _world(group)
+    B, n1, n2 = a.size(0), a.size(1), b.size(1)
+    gbatch = int(global_batch) if global_batch is not None else B * world
+    count1, count2 = float(gbatch * n1), float(gbatch * n2)
+    dev, dt = a.device, _dtype(a)
+    with _on(dev):
+        st = _stream(a)
+        d1 = torch.empty((B, n1), dtype=a.dtype, device=dev)
+        d2 = torch.empty((B, n2), dtype=a.dtype, device=dev)
+        i1 = torch.empty((B, n1), dtype=torch.int64, device=dev)
+        i2 = torch.empty((B, n2), dtype=torch.int64, device=dev)
+        ga, gb = torch.empty_like(a), torch.empty_like(b)
+        sums = torch.empty(2, dtype=torch.float64, device=dev)
+        loss = torch.empty((), dtype=a.dtype, device=dev)
+        one = _one(dev, a.dtype)
+        _lib.check(lib.tk3d_chamfer_fwd(_ptr(a), _ptr(b), B, n1, n2, _ptr(d1), _ptr(i1), _ptr(d2), _ptr(i2),
+                                        _ptr(sums), dt, st))
+        work = dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group, async_op=True) if world > 1 else None
+        _lib.check(lib.tk3d_chamfer_bwd_mean(_ptr(one), count1, count2, _ptr(a), _ptr(b), _ptr(i1), _ptr(i2), B, n1,
+                                             n2, _ptr(ga), _ptr(gb), dt, st))
+        if work is not None:
+            work.wait()  # the current stream waits for the collective; the host does not
+        _lib.check(lib.tk3d_chamfer_mean_loss(_ptr(sums), count1, count2, _ptr(loss), dt, st))
+    return loss, ga, gb
+
+
 # ---- training step on host-resident clouds ------------------------------------------------------
 _copy_streams = {}
 
@@ -185,7 +248,7 @@ def chamfer_step_from_host(xyz1_host, xyz2_host, device, global_batch=None, grou
         ga, gbt = torch.empty_like(a), torch.empty_like(b)
         sums = torch.zeros((nch, 2), dtype=torch.float64, device=dev)  # the kernel overwrites its row
         per = (B + nch - 1) // nch if B > 0 else 0
-        one = torch.ones((), dtype=torch.float32, device=dev)  # upstream gradient of the loss
+        one = _one(dev, torch.float32)  # upstream gradient of the loss
         copy.wait_stream(compute)  # the buffers above exist before the side stream writes them
         for t in (a, b):
             t.record_stream(copy)
@@ -207,10 +270,12 @@ def chamfer_step_from_host(xyz1_host, xyz2_host, device, global_batch=None, grou
                                             b[b0:b1].data_ptr(), i1[b0:b1].data_ptr(), i2[b0:b1].data_ptr(),
                                             b1 - b0, n1, n2, ga[b0:b1].data_ptr(), gbt[b0:b1].data_ptr(), _lib.F32,
                                             st))
-        sums = sums.sum(dim=0)
+        sums = sums[0] if nch == 1 else sums.sum(dim=0)
         if world > 1:
             dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
-        loss = (sums[0] / count1 + sums[1] / count2).to(torch.float32)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        check(lib.tk3d_chamfer_mean_loss(sums.data_ptr(), count1, count2, loss.data_ptr(), _lib.F32,
+                                         compute.cuda_stream))
     return loss, ga, gbt
 
 
