@@ -176,7 +176,10 @@ int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, i
  *             returns non-zero and the buffer is given, the features are first transposed into it
  *             ([B,N1,C]) so that every gather reads whole contiguous rows -- several times faster
  *             when the output is much larger than the features.  Without it (NULL) the call gathers
- *             from the native layout.  Results are identical.
+ *             from the native layout.  Results are identical.  The function returns 0 for the
+ *             shapes served by the channel-row kernel (fp32, N1 a multiple of 4 between 256 and
+ *             24576, at least 1024 index entries per cloud), which stages every channel's N1
+ *             features in shared memory and needs no scratch.
  */
 size_t tk3d_group_fwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype);
 int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K,
@@ -257,6 +260,11 @@ int tk3d_fps_layout(const void *points, int64_t B, int64_t N, int64_t num_sample
                     int64_t *index, void *scratch, size_t scratch_bytes, int dtype, void *stream);
 int tk3d_ball_query_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
                            int64_t k, int xyz_channel_first, void *index, int index_dtype, int dtype, void *stream);
+/* tk3d_group_fwd reading an index tensor of `index_dtype` (e.g. the int32 output of the two calls
+ * above); everything else as tk3d_group_fwd. */
+int tk3d_group_fwd_layout(const void *in, const void *index, int index_dtype, int64_t B, int64_t C, int64_t N1,
+                          int64_t N2, int64_t K, void *out, int32_t *status, void *scratch, size_t scratch_bytes,
+                          int dtype, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Fused front ends of the PointNet++ layers that call the operators above.  They replace Python

@@ -77,8 +77,11 @@ def test_argument_errors_need_no_gpu(lib):
     # empty problems succeed without launching anything
     assert lib.tk3d_knn(None, None, 0, 8, 4, 2, None, None, F32, None) == 0
     assert lib.tk3d_group_fwd(None, None, 0, 4, 8, 8, 2, None, None, None, 0, F32, None) == 0
-    # the row-gather path wants scratch only when the output dwarfs the features
-    assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 1024, 32, F32) == 32 * 64 * 8192 * 4
+    # the row-gather path wants scratch only when the output dwarfs the features; shapes the channel-row
+    # kernel serves (N1 a multiple of 4 up to 24576, at least 1024 entries per cloud) need none
+    assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 1024, 32, F32) == 0
+    assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 32768, 4096, 32, F32) == 32 * 64 * 32768 * 4
+    assert lib.tk3d_group_bwd_scratch_bytes(32, 64, 8192, 1024, 32, F32) == 32 * 64 * 8192 * 4
     assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 16, 4, F32) == 0
     assert lib.tk3d_group_fwd_scratch_bytes(32, 64, 8192, 1024, 32, 1) == 0
     assert lib.tk3d_interp_fwd_scratch_bytes(8, 128, 32768, 131072, F32) == 8 * 128 * 32768 * 4

@@ -191,3 +191,18 @@ def test_layout_entry_points_reject_bad_index_dtype():
                                st) == 4
     assert lib.tk3d_ball_query_layout(x.data_ptr(), x.data_ptr(), 1, 8, 8, 0.5, 2, 1, i.data_ptr(), -1, _lib.F32,
                                       st) == 4
+
+
+@pytest.mark.parametrize("B,C,n1,n2,k,dt", [(2, 16, 1024, 256, 16, torch.float32), (3, 7, 333, 50, 5, torch.float32),
+                                            (2, 64, 300, 700, 32, torch.float32), (2, 8, 100, 40, 6, torch.float64)])
+def test_group_points_reads_int32_indices(B, C, n1, n2, k, dt):
+    """ball_query(index_dtype=int32) -> group_points without widening the index: same output as with int64."""
+    from torkit3d_b200 import _C
+
+    g = torch.Generator().manual_seed(n1 + k)
+    f = torch.randn(B, C, n1, generator=g, dtype=dt).to(DEV)
+    idx = torch.randint(0, n1, (B, n2, k), generator=g).to(DEV)
+    out64 = _C.group_points_forward_cuda(f, idx)
+    out32 = _C.group_points_forward_cuda(f, idx.int())
+    assert torch.equal(out64, out32)
+    assert torch.equal(out64, torch.gather(f.unsqueeze(2).expand(B, C, n2, n1), 3, idx.unsqueeze(1).expand(B, C, n2, k)))

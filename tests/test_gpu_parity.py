@@ -545,8 +545,9 @@ def test_group_and_interp_row_gather_path_equals_direct_path(oracle, B, C, n1, n
     idx = torch.randint(0, n1, (B, n2, k), device=DEV)
     idx[0, 0, 0] = -1  # bad index: reads as zero on both paths
     need = lib.tk3d_group_fwd_scratch_bytes(B, C, n1, n2, k, 0)
-    assert need == B * C * n1 * 4
-    scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+    # shapes served by the channel-row kernel (rows staged in shared memory) need no scratch at all
+    assert need in (0, B * C * n1 * 4)
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     o_rows = torch.full((B, C, n2, k), float("nan"), device=DEV)
     o_direct = torch.full((B, C, n2, k), float("nan"), device=DEV)

@@ -172,12 +172,13 @@ def ball_query_cuda(query, key, radius, max_neighbors, *, channel_first=False, i
 
 
 def group_points_forward_cuda(input, index):
-    """input [B,C,N1], index [B,N2,K] -> [B,C,N2,K]."""
+    """input [B,C,N1], index [B,N2,K] (int64, or int32 as an opt-in) -> [B,C,N2,K]."""
     _check_cuda(input=input, index=index)
     _check_eq(input.dim(), 3, "input.dim() == 3")
     _check_eq(index.dim(), 3, "index.dim() == 3")
     _check_eq(input.size(0), index.size(0), "input.size(0) == index.size(0)")
-    _index(index, "index")
+    if index.dtype not in (torch.int64, torch.int32):
+        raise RuntimeError("index must be an int64 tensor.")
     _same_device_dtype(input, index)
     input, index = input.contiguous(), index.contiguous()
     lib = load()
@@ -185,12 +186,17 @@ def group_points_forward_cuda(input, index):
     _, N2, K = index.shape
     with _on(input.device):
         out = torch.empty((B, C, N2, K), dtype=input.dtype, device=input.device)
-        # the row-gather path (transpose into scratch, then gather) pays from about 48 MB of output on
+        # the row-gather path (transpose into scratch, then gather) pays from about 48 MB of output on;
+        # shapes the channel-row kernel serves report a scratch size of 0
         big = out.numel() * out.element_size() >= _ROWS_MIN_OUTPUT_BYTES
         need = _lib.scratch_bytes("tk3d_group_fwd", B, C, N1, N2, K, _dtype(input)) if big else 0
         scratch = torch.empty((need,), dtype=torch.uint8, device=input.device) if need else None
-        check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None,
-                                 _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
+        if index.dtype == torch.int32:
+            check(lib.tk3d_group_fwd_layout(_ptr(input), _ptr(index), _lib.I32, B, C, N1, N2, K, _ptr(out), None,
+                                            _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
+        else:
+            check(lib.tk3d_group_fwd(_ptr(input), _ptr(index), B, C, N1, N2, K, _ptr(out), None,
+                                     _ptr(scratch) if need else None, need, _dtype(input), _stream(input)))
     return out
 
 
