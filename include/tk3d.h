@@ -382,6 +382,17 @@ int tk3d_feature_knn(const void *query, const void *key, int64_t B, int64_t C, i
                      int channel_first, void *distance, int64_t *index, int dtype, void *stream);
 
 /*
+ * Range-checked build.  libtk3d_b200_bounds.so is this library compiled with -DTK3D_BOUNDS: every
+ * coordinate load and every index-tensor access of the operators is checked against the extent of
+ * its tensor, a violation is counted and redirected to element 0.  tk3d_bounds_violations()
+ * synchronises the device and returns the number of violations since the library was loaded; in the
+ * regular build, which carries no checks, it returns -1.  (The reference's only run-time checks on
+ * this path are the device-side asserts of torkit3d/csrc/cuda/group_points_kernel.cu:62 and
+ * interpolate_kernel.cu:40,141, which abort the CUDA context.)
+ */
+long long tk3d_bounds_violations(void);
+
+/*
  * Diagnostic with no counterpart in the reference: launches a kernel of dependent FP32 fused
  * multiply-add chains (`iters` x 64 FMAs per thread, 8 blocks of 256 threads per SM) on `stream`.
  * *flop (a HOST double, optional) receives the number of floating-point operations the launch

@@ -60,6 +60,7 @@ SIGNATURES = {
                                      ctypes.c_size_t, _int, _vp]),
     "tk3d_edge_feature_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp,
                                      ctypes.c_size_t, _int, _vp]),
+    "tk3d_bounds_violations": (ctypes.c_longlong, []),
     "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
     "tk3d_feature_knn": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _int, _vp]),
     "tk3d_chamfer_fwd_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _int]),
@@ -93,6 +94,20 @@ def load():
         fn.restype = res
         fn.argtypes = args
     _lib = lib
+    return lib
+
+
+def load_bounds_checked():
+    """The range-checked build (libtk3d_b200_bounds.so, ``python -m torkit3d_b200.build --bounds``) with the
+    same prototypes attached -- test infrastructure: the operators never load it."""
+    path = os.path.join(_PKG, "libtk3d_b200_bounds.so")
+    if not os.path.exists(path):
+        raise ImportError("libtk3d_b200_bounds.so is not built (python -m torkit3d_b200.build --bounds)")
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
     return lib
 
 

@@ -4,6 +4,8 @@
 
 #include <mutex>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "tk3d_common.cuh"
 
 namespace tk3d {
@@ -70,6 +72,9 @@ cudaError_t raise_smem_limit(const void *func, int bytes) {
   return cudaSuccess;
 }
 
+void nvtx_push(const char *name) { nvtxRangePushA(name); }
+void nvtx_pop() { nvtxRangePop(); }
+
 }  // namespace tk3d
 
 extern "C" {
@@ -91,5 +96,29 @@ const char *tk3d_strerror(int code) {
 }
 
 const char *tk3d_last_error(void) { return tk3d::last_error_buffer(); }
+
+#ifdef TK3D_BOUNDS
+unsigned long long tk3d_bounds_count_ball_query(void);
+unsigned long long tk3d_bounds_count_chamfer(void);
+unsigned long long tk3d_bounds_count_chamfer_fast(void);
+unsigned long long tk3d_bounds_count_diag(void);
+unsigned long long tk3d_bounds_count_edge(void);
+unsigned long long tk3d_bounds_count_feature_knn(void);
+unsigned long long tk3d_bounds_count_fps(void);
+unsigned long long tk3d_bounds_count_group(void);
+unsigned long long tk3d_bounds_count_interp(void);
+unsigned long long tk3d_bounds_count_knn(void);
+unsigned long long tk3d_bounds_count_knn_split(void);
+unsigned long long tk3d_bounds_count_sa_group(void);
+#endif
+
+long long tk3d_bounds_violations(void) {
+#ifdef TK3D_BOUNDS
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  return (long long)(tk3d_bounds_count_ball_query() + tk3d_bounds_count_chamfer() + tk3d_bounds_count_chamfer_fast() + tk3d_bounds_count_diag() + tk3d_bounds_count_edge() + tk3d_bounds_count_feature_knn() + tk3d_bounds_count_fps() + tk3d_bounds_count_group() + tk3d_bounds_count_interp() + tk3d_bounds_count_knn() + tk3d_bounds_count_knn_split() + tk3d_bounds_count_sa_group());
+#else
+  return -1;  // this build carries no range checks
+#endif
+}
 
 }  // extern "C"

@@ -282,7 +282,7 @@ static int ball_query_impl(const void *query, const void *key, int64_t B, int64_
   TK3D_REQUIRE(query && index && (key || N2 == 0), TK3D_ERR_NULL, "ball_query: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
   const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
-  const IndexOut io = index_out(index, index32);
+  const IndexOut io = index_out(index, index32, B * N1 * k);
   if (dtype == TK3D_F32) {
     const float r2 = radius * radius;  // squared in fp32, as the reference does for float tensors
     const int64_t cap = (int64_t)sm_count() * 256;
@@ -308,14 +308,18 @@ static int ball_query_impl(const void *query, const void *key, int64_t B, int64_
 
 extern "C" int tk3d_ball_query(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, float radius,
                                int64_t k, int64_t *index, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_ball_query");
   return ball_query_impl(query, key, B, N1, N2, radius, k, 0, index, 0, dtype, stream);
 }
 
 extern "C" int tk3d_ball_query_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2,
                                       float radius, int64_t k, int xyz_channel_first, void *index, int index_dtype,
                                       int dtype, void *stream) {
+  TK3D_RANGE("tk3d_ball_query_layout");
   TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "ball_query: index_dtype %d",
                index_dtype);
   return ball_query_impl(query, key, B, N1, N2, radius, k, xyz_channel_first != 0, index, index_dtype == TK3D_I32,
                          dtype, stream);
 }
+
+TK3D_BOUNDS_TU(ball_query)

@@ -213,6 +213,7 @@ using namespace tk3d;
 
 extern "C" int tk3d_chamfer_mean_loss(const double *sums, double count1, double count2, void *loss, int dtype,
                                       void *stream) {
+  TK3D_RANGE("tk3d_chamfer_mean_loss");
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "chamfer_mean_loss: dtype %d", dtype);
   TK3D_REQUIRE(sums && loss, TK3D_ERR_NULL, "chamfer_mean_loss: a pointer is NULL");
   TK3D_REQUIRE(count1 > 0 && count2 > 0, TK3D_ERR_SHAPE, "chamfer_mean_loss: counts must be positive");
@@ -246,6 +247,7 @@ static int chamfer_bwd_mean_impl(const void *grad_loss, double count1, double co
 extern "C" int tk3d_chamfer_bwd_mean(const void *grad_loss, double count1, double count2, const void *xyz1,
                                      const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B,
                                      int64_t N1, int64_t N2, void *grad1, void *grad2, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_chamfer_bwd_mean");
   return chamfer_bwd_mean_impl(grad_loss, count1, count2, xyz1, xyz2, idx1, idx2, B, N1, N2, 0, grad1, grad2, dtype,
                                stream);
 }
@@ -254,6 +256,7 @@ extern "C" int tk3d_chamfer_bwd_mean_layout(const void *grad_loss, double count1
                                             const void *xyz2, const int64_t *idx1, const int64_t *idx2, int64_t B,
                                             int64_t N1, int64_t N2, int xyz_channel_first, void *grad1, void *grad2,
                                             int dtype, void *stream) {
+  TK3D_RANGE("tk3d_chamfer_bwd_mean_layout");
   return chamfer_bwd_mean_impl(grad_loss, count1, count2, xyz1, xyz2, idx1, idx2, B, N1, N2, xyz_channel_first != 0,
                                grad1, grad2, dtype, stream);
 }
@@ -288,12 +291,14 @@ static int chamfer_fwd_impl(const void *xyz1, const void *xyz2, int64_t B, int64
 
 extern "C" int tk3d_chamfer_fwd(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2, void *dist1,
                                 int64_t *idx1, void *dist2, int64_t *idx2, double *sums, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_chamfer_fwd");
   return chamfer_fwd_impl(xyz1, xyz2, B, N1, N2, 0, dist1, idx1, dist2, idx2, sums, dtype, stream);
 }
 
 extern "C" int tk3d_chamfer_fwd_layout(const void *xyz1, const void *xyz2, int64_t B, int64_t N1, int64_t N2,
                                        int xyz_channel_first, void *dist1, int64_t *idx1, void *dist2, int64_t *idx2,
                                        double *sums, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_chamfer_fwd_layout");
   return chamfer_fwd_impl(xyz1, xyz2, B, N1, N2, xyz_channel_first != 0, dist1, idx1, dist2, idx2, sums, dtype,
                           stream);
 }
@@ -316,12 +321,16 @@ static int chamfer_bwd_impl(const void *g1, const void *g2, const void *xyz1, co
 extern "C" int tk3d_chamfer_bwd(const void *g1, const void *g2, const void *xyz1, const void *xyz2,
                                 const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
                                 void *grad1, void *grad2, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_chamfer_bwd");
   return chamfer_bwd_impl(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, 0, grad1, grad2, dtype, stream);
 }
 
 extern "C" int tk3d_chamfer_bwd_layout(const void *g1, const void *g2, const void *xyz1, const void *xyz2,
                                        const int64_t *idx1, const int64_t *idx2, int64_t B, int64_t N1, int64_t N2,
                                        int xyz_channel_first, void *grad1, void *grad2, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_chamfer_bwd_layout");
   return chamfer_bwd_impl(g1, g2, xyz1, xyz2, idx1, idx2, B, N1, N2, xyz_channel_first != 0, grad1, grad2, dtype,
                           stream);
 }
+
+TK3D_BOUNDS_TU(chamfer)

@@ -399,3 +399,5 @@ int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_
 }
 
 }  // namespace tk3d
+
+TK3D_BOUNDS_TU(chamfer_fast)

@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(256) ffma_peak_kernel(int64_t iters, float see
 using namespace tk3d;
 
 extern "C" int tk3d_diag_ffma(int64_t iters, float *sink, double *flop, void *stream) {
+  TK3D_RANGE("tk3d_diag_ffma");
   TK3D_REQUIRE(iters > 0, TK3D_ERR_SHAPE, "diag_ffma: iters must be positive");
   TK3D_REQUIRE(sink != nullptr, TK3D_ERR_NULL, "diag_ffma: sink is NULL");
   const int blocks = sm_count() * 8;
@@ -40,3 +41,5 @@ extern "C" int tk3d_diag_ffma(int64_t iters, float *sink, double *flop, void *st
   if (flop) *flop = (double)blocks * 256.0 * (double)iters * 64.0 * 2.0;
   return check_launch("ffma_peak_kernel");
 }
+
+TK3D_BOUNDS_TU(diag)

@@ -189,6 +189,7 @@ extern "C" int tk3d_edge_feature_fwd(const void *query_feature, const void *key_
                                      int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int include_query,
                                      void *out, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
                                      void *stream) {
+  TK3D_RANGE("tk3d_edge_feature_fwd");
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "edge_feature_fwd: dtype %d", dtype);
   TK3D_REQUIRE(edge_shape_ok(B, C, N1, N2, K), TK3D_ERR_SHAPE, "edge_feature_fwd: bad size");
   if (B * C * N1 * K == 0) return TK3D_OK;
@@ -221,6 +222,7 @@ extern "C" int tk3d_edge_feature_fwd(const void *query_feature, const void *key_
 extern "C" int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index, int64_t B, int64_t C, int64_t N1,
                                      int64_t N2, int64_t K, int include_query, void *grad_query, void *grad_key,
                                      int32_t *status, void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_edge_feature_bwd");
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "edge_feature_bwd: dtype %d", dtype);
   TK3D_REQUIRE(edge_shape_ok(B, C, N1, N2, K), TK3D_ERR_SHAPE, "edge_feature_bwd: bad size");
   const int64_t E = N1 * K;
@@ -273,3 +275,5 @@ extern "C" int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index,
   }
   return TK3D_OK;
 }
+
+TK3D_BOUNDS_TU(edge)

@@ -190,6 +190,7 @@ using namespace tk3d;
 
 extern "C" int tk3d_feature_knn(const void *query, const void *key, int64_t B, int64_t C, int64_t N1, int64_t N2,
                                 int64_t k, int channel_first, void *dist, int64_t *index, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_feature_knn");
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "feature_knn: dtype %d", dtype);
   TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_UNSUPPORTED, "feature_knn: float32 only");
   TK3D_REQUIRE(B >= 0 && N1 >= 0 && N2 >= 0 && C >= 1, TK3D_ERR_SHAPE,
@@ -209,3 +210,5 @@ extern "C" int tk3d_feature_knn(const void *query, const void *key, int64_t B, i
   if (k <= 64) return launch<2>(q, r, B, (int)C, (int)N1, (int)N2, (int)k, cf, (float *)dist, index, st);
   return launch<4>(q, r, B, (int)C, (int)N1, (int)N2, (int)k, cf, (float *)dist, index, st);
 }
+
+TK3D_BOUNDS_TU(feature_knn)

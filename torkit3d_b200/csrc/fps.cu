@@ -426,17 +426,20 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
 
 extern "C" int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index, void *scratch,
                         size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_fps");
   return fps_impl(points, B, N, S, 0, index, nullptr, scratch, scratch_bytes, dtype, stream);
 }
 
 extern "C" int tk3d_fps_layout(const void *points, int64_t B, int64_t N, int64_t S, int xyz_channel_first,
                                int64_t *index, void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_fps_layout");
   return fps_impl(points, B, N, S, xyz_channel_first != 0, index, nullptr, scratch, scratch_bytes, dtype, stream);
 }
 
 extern "C" int tk3d_fps_gather(const void *points, int64_t B, int64_t N, int64_t S, int channel_first,
                                int64_t *index, void *sampled, void *scratch, size_t scratch_bytes, int dtype,
                                void *stream) {
+  TK3D_RANGE("tk3d_fps_gather");
   TK3D_REQUIRE(sampled != nullptr || B * S == 0, TK3D_ERR_NULL, "fps_gather: sampled is NULL");
   return fps_impl(points, B, N, S, channel_first, index, sampled, scratch, scratch_bytes, dtype, stream);
 }
@@ -487,6 +490,7 @@ extern "C" size_t tk3d_fps_static_scratch_capacity(void) { return tk3d::FPS_STAT
 
 extern "C" int tk3d_fps_static_scratch(const void *points, int64_t B, int64_t N, int64_t S, int64_t *index,
                                        int dtype, void *stream) {
+  TK3D_RANGE("tk3d_fps_static_scratch");
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "fps_static_scratch: dtype %d", dtype);
   TK3D_REQUIRE(B >= 0 && N >= 0, TK3D_ERR_SHAPE, "fps_static_scratch: negative size");
   TK3D_REQUIRE(S > 0, TK3D_ERR_K, "fps_static_scratch: num_samples must be positive (got %lld)", (long long)S);
@@ -516,3 +520,5 @@ extern "C" int tk3d_fps_static_scratch(const void *points, int64_t B, int64_t N,
                                                                  (double *)scratch);
   return check_launch("fps_streaming_kernel (static scratch)");
 }
+
+TK3D_BOUNDS_TU(fps)

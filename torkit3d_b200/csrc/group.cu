@@ -346,12 +346,14 @@ static int group_fwd_impl(const void *in, const IndexT *index, int64_t B, int64_
 extern "C" int tk3d_group_fwd(const void *in, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
                               int64_t K, void *out, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
                               void *stream) {
+  TK3D_RANGE("tk3d_group_fwd");
   return group_fwd_impl<int64_t>(in, index, B, C, N1, N2, K, out, status, scratch, scratch_bytes, dtype, stream);
 }
 
 extern "C" int tk3d_group_fwd_layout(const void *in, const void *index, int index_dtype, int64_t B, int64_t C,
                                      int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, void *scratch,
                                      size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_group_fwd_layout");
   TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "group_fwd: index_dtype %d",
                index_dtype);
   if (index_dtype == TK3D_I32)
@@ -370,6 +372,7 @@ extern "C" size_t tk3d_group_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1,
 extern "C" int tk3d_group_bwd(const void *gout, const int64_t *index, int64_t B, int64_t C, int64_t N1, int64_t N2,
                               int64_t K, void *gin, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
                               void *stream) {
+  TK3D_RANGE("tk3d_group_bwd");
   int rc = check_group_args("group_bwd", gout, index, gin, B, C, N1, N2, K, dtype);
   if (rc) return rc;
   const int64_t E = N2 * K;
@@ -385,3 +388,5 @@ extern "C" int tk3d_group_bwd(const void *gout, const int64_t *index, int64_t B,
   }
   return group_bwd_t<double>((const double *)gout, index, B, C, N1, E, (double *)gin, status, st);
 }
+
+TK3D_BOUNDS_TU(group)

@@ -157,6 +157,7 @@ extern "C" size_t tk3d_interp_fwd_scratch_bytes(int64_t B, int64_t C, int64_t N1
 extern "C" int tk3d_interp_fwd(const void *in, const int64_t *index, const void *weight, int64_t B, int64_t C,
                                int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, void *scratch,
                                size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_interp_fwd");
   int rc = check_interp_args("interp_fwd", B, C, N1, N2, K, dtype);
   if (rc) return rc;
   if (B * C * N2 == 0) return TK3D_OK;
@@ -181,6 +182,7 @@ extern "C" size_t tk3d_interp_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1
 extern "C" int tk3d_interp_bwd(const void *gout, const int64_t *index, const void *weight, int64_t B, int64_t C,
                                int64_t N1, int64_t N2, int64_t K, void *gin, int32_t *status, void *scratch,
                                size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_interp_bwd");
   int rc = check_interp_args("interp_bwd", B, C, N1, N2, K, dtype);
   if (rc) return rc;
   if (B * C * N1 == 0) return TK3D_OK;
@@ -200,6 +202,7 @@ extern "C" int tk3d_interp_bwd(const void *gout, const int64_t *index, const voi
 
 extern "C" int tk3d_three_nn_weight(const void *distance, int64_t rows, int64_t k, void *weight, int dtype,
                                     void *stream) {
+  TK3D_RANGE("tk3d_three_nn_weight");
   TK3D_REQUIRE(dtype == TK3D_F32 || dtype == TK3D_F64, TK3D_ERR_DTYPE, "three_nn_weight: dtype %d", dtype);
   TK3D_REQUIRE(rows >= 0, TK3D_ERR_SHAPE, "three_nn_weight: negative size");
   TK3D_REQUIRE(k >= 1 && k <= 8, TK3D_ERR_K, "three_nn_weight: k must be in [1,8] (got %lld)", (long long)k);
@@ -264,6 +267,7 @@ extern "C" int tk3d_three_nn_interp_fwd(const void *query_xyz, const void *key_x
                                         int64_t B, int64_t C, int64_t Nq, int64_t Nk, int xyz_channel_first,
                                         float eps, void *out, int32_t *index32, void *weight, int32_t *status,
                                         void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_three_nn_interp_fwd");
   TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "three_nn_interp_fwd: only fp32 has a fused path (dtype %d)", dtype);
   TK3D_REQUIRE(B >= 0 && C >= 0 && Nq >= 0 && Nk >= 0, TK3D_ERR_SHAPE, "three_nn_interp_fwd: negative size");
   TK3D_REQUIRE(Nk >= 3, TK3D_ERR_K, "three_nn_interp_fwd: needs at least 3 key points (got %lld)", (long long)Nk);
@@ -287,6 +291,7 @@ extern "C" int tk3d_three_nn_interp_fwd(const void *query_xyz, const void *key_x
 extern "C" int tk3d_three_nn_interp_bwd(const void *gout, const int32_t *index32, const void *weight, int64_t B,
                                         int64_t C, int64_t Nq, int64_t Nk, void *gfeature, int32_t *status,
                                         void *scratch, size_t scratch_bytes, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_three_nn_interp_bwd");
   TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "three_nn_interp_bwd: only fp32 has a fused path (dtype %d)", dtype);
   TK3D_REQUIRE(fused_interp_shape_ok(B, C, Nq, Nk), TK3D_ERR_SHAPE, "three_nn_interp_bwd: unsupported shape");
   if (B * C * Nk == 0) return TK3D_OK;
@@ -318,3 +323,5 @@ extern "C" int tk3d_three_nn_interp_bwd(const void *gout, const int32_t *index32
       (const float *)gout, index32, (const float *)weight, B, (int)C, Nk, Nq, (float *)gfeature, status);
   return check_launch("interp32_bwd_kernel");
 }
+
+TK3D_BOUNDS_TU(interp)

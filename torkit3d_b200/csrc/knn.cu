@@ -987,7 +987,7 @@ int three_nn_fused_q(const float *query, const float *key, int64_t B, int N1, in
   const int64_t total = B * ((N1 + per - 1) / per);
   const int64_t cap = (int64_t)sm_count() * 256;
   knn_small_kernel<3, Q, true><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
-      query, key, B, N1, N2, nullptr, index_out(nullptr, 0), total, ql, kl, fu);
+      query, key, B, N1, N2, nullptr, index_out(nullptr, 0, 0), total, ql, kl, fu);
   return check_launch("knn_small_kernel (fused weights)");
 }
 
@@ -1057,7 +1057,7 @@ static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, i
   TK3D_REQUIRE(query && key && distance && index, TK3D_ERR_NULL, "knn: a pointer is NULL");
   cudaStream_t st = (cudaStream_t)stream;
   KnnIo io;
-  io.index = index_out(index, index32);
+  io.index = index_out(index, index32, B * N1 * k);
   io.ql = xyz_layout(channel_first, N1);
   io.kl = xyz_layout(channel_first, N2);
   if (dtype == TK3D_F64) {
@@ -1099,14 +1099,17 @@ static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, i
 
 extern "C" int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
                         void *distance, int64_t *index, int dtype, void *stream) {
+  TK3D_RANGE("tk3d_knn");
   return knn_impl(query, key, B, N1, N2, k, 0, distance, index, 0, dtype, stream);
 }
 
 extern "C" int tk3d_knn_layout(const void *query, const void *key, int64_t B, int64_t N1, int64_t N2, int64_t k,
                                int xyz_channel_first, void *distance, void *index, int index_dtype, int dtype,
                                void *stream) {
+  TK3D_RANGE("tk3d_knn_layout");
   TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "knn: index_dtype %d", index_dtype);
   return knn_impl(query, key, B, N1, N2, k, xyz_channel_first != 0, distance, index, index_dtype == TK3D_I32, dtype,
                   stream);
 }
 
+TK3D_BOUNDS_TU(knn)

@@ -194,3 +194,5 @@ bool knn_split_f64(const double *query, const double *key, int64_t B, int64_t N1
 }
 
 }  // namespace tk3d
+
+TK3D_BOUNDS_TU(knn_split)

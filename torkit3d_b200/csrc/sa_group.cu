@@ -349,6 +349,7 @@ extern "C" int tk3d_sa_group_fwd(const void *points, const void *centroids, cons
                                  int64_t N, int64_t M, float radius, int64_t K, int xyz_channel_first, int use_xyz,
                                  void *out, int32_t *index32, int32_t *status, void *scratch, size_t scratch_bytes,
                                  int dtype, void *stream) {
+  TK3D_RANGE("tk3d_sa_group_fwd");
   TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "sa_group_fwd: only fp32 has a fused path (dtype %d)", dtype);
   TK3D_REQUIRE(sa_shape_ok(B, C, N, M, K), TK3D_ERR_SHAPE,
                "sa_group_fwd: unsupported shape B=%lld C=%lld N=%lld M=%lld K=%lld (C <= %d, 1 <= K <= %d)",
@@ -414,6 +415,7 @@ extern "C" int tk3d_sa_group_bwd(const void *gout, const int32_t *index32, int64
                                  int64_t K, int xyz_channel_first, int use_xyz, void *gfeature, void *gpoints,
                                  void *gcentroids, int32_t *status, void *scratch, size_t scratch_bytes, int dtype,
                                  void *stream) {
+  TK3D_RANGE("tk3d_sa_group_bwd");
   TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "sa_group_bwd: only fp32 has a fused path (dtype %d)", dtype);
   TK3D_REQUIRE(sa_shape_ok(B, C, N, M, K), TK3D_ERR_SHAPE, "sa_group_bwd: unsupported shape");
   cudaStream_t st = (cudaStream_t)stream;
@@ -467,3 +469,5 @@ extern "C" int tk3d_sa_group_bwd(const void *gout, const int32_t *index32, int64
   }
   return TK3D_OK;
 }
+
+TK3D_BOUNDS_TU(sa_group)

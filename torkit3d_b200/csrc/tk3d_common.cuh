@@ -38,6 +38,19 @@ int sm_count();
 // Raise a kernel's dynamic shared-memory limit on the current device, once per (kernel, device).
 cudaError_t raise_smem_limit(const void *func, int bytes);
 
+// NVTX range spanning one entry point of the C ABI (host side: argument checks and launches), so
+// that a timeline shows which operator enqueued which kernels.  NVTX binds lazily: without a
+// profiler attached a push / pop is a load and a branch.
+void nvtx_push(const char *name);
+void nvtx_pop();
+struct NvtxRange {
+  explicit NvtxRange(const char *name) { nvtx_push(name); }
+  ~NvtxRange() { nvtx_pop(); }
+  NvtxRange(const NvtxRange &) = delete;
+  NvtxRange &operator=(const NvtxRange &) = delete;
+};
+#define TK3D_RANGE(name) ::tk3d::NvtxRange tk3d_nvtx_range_(name)
+
 // ---- exact arithmetic ----------------------------------------------------------------------
 // The round-to-nearest intrinsics are never contracted into a fused multiply-add by the compiler,
 // which is what keeps index results bit-reproducible against a CPU evaluation.
@@ -70,17 +83,51 @@ __device__ __forceinline__ T sqdist(T rx, T ry, T rz, T qx, T qy, T qz) {
 // A batch of clouds is [B,N,3] (ps = 3, cs = 1: the reference's operator layout) or [B,3,N]
 // (ps = 1, cs = N: the layout its layers pass around).  Cloud b starts at base + b*3*N in both;
 // coordinate c of its point j is cloud[j*ps + c*cs].
+//
+// Range-checked build (-DTK3D_BOUNDS, libtk3d_b200_bounds.so): every coordinate load and every
+// index-tensor access made through the helpers below is checked against the extent of its tensor;
+// a violation is counted (one counter per translation unit, summed by tk3d_bounds_violations())
+// and the access is redirected to element 0, so a logic error shows up as a number instead of a
+// fault.  The regular build carries none of this.
+#ifdef TK3D_BOUNDS
+static __device__ unsigned long long tk3d_oob_count;
+__device__ __forceinline__ int64_t tk3d_checked(int64_t i, int64_t n) {
+  if (i < 0 || i >= n) {
+    atomicAdd(&tk3d_oob_count, 1ull);
+    return 0;
+  }
+  return i;
+}
+#define TK3D_BOUNDS_TU(tag)                                                   \
+  extern "C" unsigned long long tk3d_bounds_count_##tag(void) {               \
+    unsigned long long v = 0;                                                 \
+    cudaMemcpyFromSymbol(&v, tk3d::tk3d_oob_count, sizeof(v));                \
+    return v;                                                                 \
+  }
+#else
+#define TK3D_BOUNDS_TU(tag)
+#endif
+
 struct XyzLayout {
   int ps, cs;
+#ifdef TK3D_BOUNDS
+  int n;  // points per cloud
+#endif
 };
 inline XyzLayout xyz_layout(int channel_first, int64_t n) {
   XyzLayout l;
   l.ps = channel_first ? 1 : 3;
   l.cs = channel_first ? (int)n : 1;
+#ifdef TK3D_BOUNDS
+  l.n = (int)n;
+#endif
   return l;
 }
 template <typename T>
 __device__ __forceinline__ void load_xyz(const T *__restrict__ cloud, int64_t j, XyzLayout l, T &x, T &y, T &z) {
+#ifdef TK3D_BOUNDS
+  j = tk3d_checked(j, l.n);
+#endif
   const T *p = cloud + j * l.ps;
   x = p[0];
   y = p[l.cs];
@@ -92,18 +139,32 @@ __device__ __forceinline__ void load_xyz(const T *__restrict__ cloud, int64_t j,
 struct IndexOut {
   void *p;
   int i32;
+#ifdef TK3D_BOUNDS
+  int64_t count;  // elements of the tensor
+#endif
   __device__ __forceinline__ void put(int64_t off, int64_t v) const {
+#ifdef TK3D_BOUNDS
+    off = tk3d_checked(off, count);
+#endif
     if (i32) static_cast<int32_t *>(p)[off] = (int32_t)v;
     else static_cast<int64_t *>(p)[off] = v;
   }
   __device__ __forceinline__ int64_t get(int64_t off) const {
+#ifdef TK3D_BOUNDS
+    off = tk3d_checked(off, count);
+#endif
     return i32 ? (int64_t) static_cast<const int32_t *>(p)[off] : static_cast<const int64_t *>(p)[off];
   }
 };
-inline IndexOut index_out(void *p, int i32) {
+inline IndexOut index_out(void *p, int i32, int64_t count) {
   IndexOut o;
   o.p = p;
   o.i32 = i32;
+#ifdef TK3D_BOUNDS
+  o.count = count;
+#else
+  (void)count;
+#endif
   return o;
 }
 
