@@ -1,6 +1,6 @@
 """Run one operator on one benchmark configuration a few times (for profilers and quick timings).
 
-    python -m torkit3d_b200.run_case <case> [--iters 3] [--scale-batch B]
+    python run_case.py <case> [--iters 3] [--scale-batch B]
 
 Cases: c1_chamfer, c2_knn, c3_fps, c3_ball, c3_group_fwd, c3_group_bwd, c4_chamfer_fwd,
 c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_bwd, and the layer front ends on the same
@@ -11,11 +11,15 @@ KNN: feature_knn, feature_knn_chain (cdist + topk in PyTorch); knn_f64 (float64 
 size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
 """
 import argparse
+import os
+import sys
 
 import torch
 
-from . import _C, workloads
-from .ops import ball_query, knn_points, sample_farthest_points, three_nn_weight
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from torkit3d_b200 import _C, workloads  # noqa: E402
+from torkit3d_b200.ops import ball_query, knn_points, sample_farthest_points, three_nn_weight  # noqa: E402
 
 
 def build_case(name, batch, dev):
@@ -35,7 +39,7 @@ def build_case(name, batch, dev):
         return lambda: knn_points(q, r, 16)
     if name.startswith("feature_knn"):
         # DGCNN's dynamic graph on 64-channel features: B=32 clouds of 1024 points, k=20
-        from .ops import knn
+        from torkit3d_b200.ops import knn
 
         B = batch or 32
         g = torch.Generator().manual_seed(9)
@@ -48,7 +52,7 @@ def build_case(name, batch, dev):
             return torch.topk(torch.cdist(xt, xt), 20, dim=2, largest=False, sorted=False)
         return knn_chain
     if name.startswith("edge"):
-        from .ops import get_edge_feature, group_points
+        from torkit3d_b200.ops import get_edge_feature, group_points
 
         B = batch or 32
         g = torch.Generator().manual_seed(7)
@@ -68,9 +72,9 @@ def build_case(name, batch, dev):
         if name == "c3_fps":
             return lambda: sample_farthest_points(p, 1024)
         if name in ("c3_fps_gather", "c3_fps_chain", "c3_sa_fused", "c3_sa_chain", "c3_sa_fused_bwd"):
-            from . import _fused
-            from .layers import set_abstraction_group
-            from .ops import group_points
+            from torkit3d_b200 import _fused
+            from torkit3d_b200.layers import set_abstraction_group
+            from torkit3d_b200.ops import group_points
 
             pcf = p.transpose(1, 2).contiguous()  # [B,3,N], the layout the reference's layers pass around
             if name == "c3_fps_gather":
@@ -116,8 +120,8 @@ def build_case(name, batch, dev):
     if name.startswith("c5"):
         q, r, feat = [t.to(dev) for t in workloads.c5_scene_interp(**kw)]
         if name in ("c5_fp_fused", "c5_fp_chain"):
-            from . import _fused
-            from .ops import interpolate_feature
+            from torkit3d_b200 import _fused
+            from torkit3d_b200.ops import interpolate_feature
 
             qcf, rcf = q.transpose(1, 2).contiguous(), r.transpose(1, 2).contiguous()
             if name == "c5_fp_fused":
