@@ -92,7 +92,12 @@ void FN(orc_chamfer_bwd)(const T *g1, const T *g2, const T *xyz1, const T *xyz2,
  * maximum while scanning in ascending index order (torkit3d/csrc/cuda/knn_distance_kernel.cu:65-82
  * with the bounded set of torkit3d/csrc/include/mink.cuh:61-89), so the retained SET is the K
  * smallest under (distance, index) order.  Its slot order is an artefact; this restatement emits
- * each row sorted ascending by (distance, index).  Distances are squared. */
+ * each row sorted ascending by (distance, index).  Distances are squared.  A NaN distance (a NaN
+ * coordinate) orders after every number, so keys with NaN coordinates are returned only when fewer
+ * than K keys have a numeric distance; the reference leaves that case to chance (a NaN in its set
+ * is never displaced, ibid. mink.cuh:70-84, because every comparison with it is false). */
+static int FN(knn_before)(T d, T e) { return d < e || (e != e && d == d); }
+
 void FN(orc_knn)(const T *query, const T *key, int64_t bs, int64_t n1, int64_t n2, int64_t k, T *dist,
                  int64_t *idx) {
   for (int64_t s = 0; s < bs; ++s) {
@@ -104,10 +109,10 @@ void FN(orc_knn)(const T *query, const T *key, int64_t bs, int64_t n1, int64_t n
       int64_t cnt = 0;
       for (int64_t j = 0; j < n2; ++j) {
         T d = FN(sqdist)(q + j * 3, p);
-        if (cnt == k && !(d < od[k - 1])) continue;
+        if (cnt == k && !FN(knn_before)(d, od[k - 1])) continue;
         int64_t pos = (cnt < k) ? cnt : k - 1;
         /* stable: an equal distance with a higher index stays behind */
-        while (pos > 0 && d < od[pos - 1]) {
+        while (pos > 0 && FN(knn_before)(d, od[pos - 1])) {
           od[pos] = od[pos - 1];
           oi[pos] = oi[pos - 1];
           --pos;

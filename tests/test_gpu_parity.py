@@ -248,6 +248,33 @@ def test_knn_ties(oracle, k, dtype):
     np.testing.assert_array_equal(N(d), e)
 
 
+@pytest.mark.parametrize("n1,n2,k,dtype", [(300, 500, 3, np.float32),      # register top-k
+                                           (300, 1200, 16, np.float32),    # two-pass candidate lists
+                                           (300, 2100, 64, np.float32),
+                                           (300, 100, 16, np.float32),     # buffered lists
+                                           (64, 600, 200, np.float32),     # heap in the output row
+                                           (300, 600, 8, np.float64),      # key-split heaps
+                                           (64, 400, 100, np.float64)])
+def test_knn_keys_with_nan_coordinates_order_last(oracle, n1, n2, k, dtype):
+    """A key with a NaN coordinate has a NaN distance to every query; it orders after every number,
+    so with at least k numeric keys it is never returned -- also when it is among the first k keys,
+    where a set maintained with a plain `<` against its maximum would keep it for good (the
+    reference's bounded set does, torkit3d/csrc/include/mink.cuh:70-84)."""
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(n2 + k)
+    q = rng.standard_normal((2, n1, 3)).astype(dtype)
+    r = rng.standard_normal((2, n2, 3)).astype(dtype)
+    bad = rng.random((2, n2)) < 0.1
+    bad[:, [0, 2, 5]] = True
+    r[bad, rng.integers(0, 3, size=int(bad.sum()))] = np.nan
+    d, i = knn_points(T(q), T(r), k, sorted=True)
+    e, j = oracle.knn(q, r, k)
+    assert not np.isnan(e).any() and not bad[np.arange(2)[:, None, None], j].any()
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
 @pytest.mark.parametrize("k", [1, 2, 3, 4])
 def test_knn_small_full_round_of_blocks_bit_exact(oracle, k):
     """Two queries per thread, about one full round of 256-query blocks per SM (1016 blocks), with ties."""
