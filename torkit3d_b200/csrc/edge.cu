@@ -20,45 +20,33 @@ edge_rows_vec4_kernel(const float *__restrict__ keyT, const float *__restrict__ 
                       const int64_t *__restrict__ index, int C, int64_t N2, int64_t N1, int K, int include_query,
                       float *__restrict__ out, int32_t *__restrict__ status) {
   extern __shared__ __align__(16) float tile[];  // [C][ROWS_TE], chunk-swizzled
-  __shared__ int sidx[ROWS_TE];
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ql = lane & 7, el = lane >> 3;
   const int64_t b = blockIdx.y;
   const int64_t E = N1 * K;
   const int64_t e0 = (int64_t)blockIdx.x * ROWS_TE;
   const int n = (int)((E - e0) < ROWS_TE ? (E - e0) : ROWS_TE);  // multiple of 4
   const int L = C >> 2;
 
+  // Four entries per warp and step, as in gather_rows_vec4_kernel: conflict-free scalar stores.
+  const float4 *fb = reinterpret_cast<const float4 *>(keyT + b * N2 * C);
   bool bad = false;
-  for (int t = tid; t < n; t += ROWS_THREADS) {
-    int64_t id = index[b * E + e0 + t];
-    if (id < 0 || id >= N2) {
-      id = -1;
-      bad = true;
+  for (int g = warp; g < (n >> 2); g += ROWS_THREADS / 32) {
+    int id[1];
+    float w[1];
+    rows_load_index<1, int64_t>(index, nullptr, b * E + e0 + 4 * g + el, N2, true, id, w, bad);
+    const float4 *row = fb + (int64_t)(id[0] < 0 ? 0 : id[0]) * L;
+#pragma unroll 4
+    for (int q = ql; q < L; q += 8) {
+      const float4 v = id[0] < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(row + q);
+      float *dst = tile + (4 * q) * ROWS_TE + (((g ^ q) & (ROWS_TE / 4 - 1)) << 2) + el;
+      dst[0] = v.x;
+      dst[ROWS_TE] = v.y;
+      dst[2 * ROWS_TE] = v.z;
+      dst[3 * ROWS_TE] = v.w;
     }
-    sidx[t] = (int)id;
   }
   if (bad && status) atomicOr(status, 1);
-  __syncthreads();
-
-  const float4 *fb = reinterpret_cast<const float4 *>(keyT + b * N2 * C);
-  const int items = n * L;
-  int e = tid / L, q = tid - e * L;
-  const int de = ROWS_THREADS / L, dq = ROWS_THREADS - de * L;
-  for (int t = tid; t < items; t += ROWS_THREADS) {
-    const int id = sidx[e];
-    const float4 v = id < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(fb + (int64_t)id * L + q);
-    float *dst = tile + (4 * q) * ROWS_TE + ((((e >> 2) ^ q) & (ROWS_TE / 4 - 1)) << 2) + (e & 3);
-    dst[0] = v.x;
-    dst[ROWS_TE] = v.y;
-    dst[2 * ROWS_TE] = v.z;
-    dst[3 * ROWS_TE] = v.w;
-    e += de;
-    q += dq;
-    if (q >= L) {
-      q -= L;
-      ++e;
-    }
-  }
   __syncthreads();
 
   // item u = c * 16 + chunk: four consecutive entries of channel c; their query point is (e0+4ch+i)/K
@@ -205,9 +193,7 @@ extern "C" int tk3d_edge_feature_fwd(const void *query_feature, const void *key_
   if (!rows)
     return edge_fwd_direct<float>((const float *)key_feature, (const float *)query_feature, index, B, C, N2, N1, K,
                                   include_query, (float *)out, status, st);
-  dim3 tg((unsigned)((N2 + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)B);
-  transpose_bcn_kernel<<<tg, 256, 0, st>>>((const float *)key_feature, (float *)scratch, (int)C, N2);
-  int rc = check_launch("transpose_bcn_kernel");
+  int rc = transpose_bcn((const float *)key_feature, (float *)scratch, B, C, N2, st);
   if (rc) return rc;
   const size_t smem = (size_t)C * ROWS_TE * sizeof(float);
   if (smem > 48 * 1024)
@@ -255,9 +241,7 @@ extern "C" int tk3d_edge_feature_bwd(const void *grad_out, const int64_t *index,
           (const float *)grad_out, index, nullptr, (int)C, N2, E, gstride, (float *)scratch, status);
       int rc = check_launch("scatter_rows_vec4_kernel");
       if (rc) return rc;
-      dim3 tg((unsigned)((C + 31) / 32), (unsigned)((N2 + 31) / 32), (unsigned)B);
-      transpose_bcn_kernel<<<tg, 256, 0, st>>>((const float *)scratch, (float *)grad_key, (int)N2, C);
-      return check_launch("transpose_bcn_kernel");
+      return transpose_bcn((const float *)scratch, (float *)grad_key, B, N2, C, st);
     }
     TK3D_CUDA(cudaMemsetAsync(grad_key, 0, elem * (size_t)(B * C * N2), st));
     if (E > 0) {

@@ -312,9 +312,7 @@ extern "C" int tk3d_three_nn_interp_bwd(const void *gout, const int32_t *index32
       int rc = check_launch("scatter_rows_vec4_kernel");
       if (rc) return rc;
     }
-    dim3 tg((unsigned)((C + 31) / 32), (unsigned)((Nk + 31) / 32), (unsigned)B);
-    transpose_bcn_kernel<<<tg, 256, 0, st>>>((const float *)scratch, (float *)gfeature, (int)Nk, C);
-    return check_launch("transpose_bcn_kernel");
+    return transpose_bcn((const float *)scratch, (float *)gfeature, B, Nk, C, st);
   }
   TK3D_CUDA(cudaMemsetAsync(gfeature, 0, sizeof(float) * (size_t)(B * C * Nk), st));
   if (Nq == 0) return TK3D_OK;

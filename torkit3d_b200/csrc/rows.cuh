@@ -15,6 +15,7 @@ namespace tk3d {
 constexpr int ROWS_TE = 64;        // entries (index positions) per block
 constexpr int ROWS_THREADS = 256;  // 8 warps
 constexpr int ROWS_MAX_C = 512;
+constexpr int ROWS_GPW = ROWS_TE / 4 / (ROWS_THREADS / 32);  // entry groups (of four) per warp
 
 // in [B][C][N] -> out [B][N][C]
 static __global__ void __launch_bounds__(256) transpose_bcn_kernel(const float *__restrict__ in, float *__restrict__ out,
@@ -39,6 +40,67 @@ static __global__ void __launch_bounds__(256) transpose_bcn_kernel(const float *
     const int c = c0 + tx;
     if (c < C && n < N) dst[n * C + c] = t[tx][ty + 8 * i];
   }
+}
+
+// The same transposition with 16-byte accesses on both sides, for C % 4 == 0, N % 4 == 0 and
+// 16-byte aligned buffers: a block moves a 64 x 64 tile.  Loading, a warp covers four channel rows
+// at a time (lane = 8 * el + ql reads float4 number ql or ql + 8 of row 4g + el) and stores the four
+// values as scalars into a [n][64 c] tile whose 16-byte chunk of channels 4g .. 4g+3 sits at chunk
+// position (g ^ (n >> 2)) & 15: the 32 stores of one instruction fall into 32 different banks.
+// Storing, a lane moves four consecutive channels of one n with a conflict-free 16-byte shared load.
+static __global__ void __launch_bounds__(256) transpose_bcn_vec4_kernel(const float *__restrict__ in,
+                                                                        float *__restrict__ out, int C, int64_t N) {
+  __shared__ __align__(16) float t[64 * 64];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ql = lane & 7, el = lane >> 3;
+  const int64_t b = blockIdx.z;
+  const int64_t n0 = (int64_t)blockIdx.x * 64;
+  const int c0 = blockIdx.y * 64;
+  const float *src = in + b * C * N;
+  float *dst = out + b * N * C;
+#pragma unroll
+  for (int g = warp; g < 16; g += 8) {
+    const int c = c0 + 4 * g + el;
+#pragma unroll
+    for (int q = ql; q < 16; q += 8) {
+      const int64_t n = n0 + 4 * q;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < C && n < N) v = __ldg(reinterpret_cast<const float4 *>(src + (int64_t)c * N + n));
+      float *p = t + (4 * q) * 64 + (((g ^ q) & 15) << 2) + el;
+      p[0] = v.x;
+      p[64] = v.y;
+      p[128] = v.z;
+      p[192] = v.w;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int u = tid; u < 64 * 16; u += 256) {
+    const int nl = u >> 4, ch = u & 15;
+    const int64_t n = n0 + nl;
+    const int c = c0 + 4 * ch;
+    if (n < N && c < C) {
+      const float4 v = *reinterpret_cast<const float4 *>(t + nl * 64 + (((ch ^ (nl >> 2)) & 15) << 2));
+      *reinterpret_cast<float4 *>(dst + n * C + c) = v;
+    }
+  }
+}
+
+// in [B][C][N] -> out [B][N][C] on stream st; picks the 16-byte kernel when sizes and alignment allow.
+inline int transpose_bcn(const float *in, float *out, int64_t B, int64_t C, int64_t N, cudaStream_t st) {
+  if (B <= 0 || C <= 0 || N <= 0) return TK3D_OK;
+  TK3D_REQUIRE(B <= 65535, TK3D_ERR_SHAPE, "transpose: batch too large for this path (B=%lld)", (long long)B);
+  const bool vec = C % 4 == 0 && N % 4 == 0 && C >= 16 && N >= 16 &&
+                   ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (vec && (C + 63) / 64 <= 65535) {
+    dim3 tg((unsigned)((N + 63) / 64), (unsigned)((C + 63) / 64), (unsigned)B);
+    transpose_bcn_vec4_kernel<<<tg, 256, 0, st>>>(in, out, (int)C, N);
+    return check_launch("transpose_bcn_vec4_kernel");
+  }
+  TK3D_REQUIRE((C + 31) / 32 <= 65535, TK3D_ERR_SHAPE, "transpose: size too large for this path");
+  dim3 tg((unsigned)((N + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)B);
+  transpose_bcn_kernel<<<tg, 256, 0, st>>>(in, out, (int)C, N);
+  return check_launch("transpose_bcn_kernel");
 }
 
 // NSRC = 1: out[b,c,e] = featT[b, index[b,e], c]                       (group_points, e = m*K + j)
@@ -99,81 +161,102 @@ gather_rows_kernel(const float *__restrict__ featT, const IndexT *__restrict__ i
   }
 }
 
-// Vectorised variant for C % 4 == 0, E % 4 == 0 and 16-byte aligned buffers: 16-byte global loads
-// (consecutive lanes read consecutive float4 of one row), a [C][64] tile whose 16-byte chunks are
-// XOR-swizzled by the channel group so that the transposing scalar stores are at most 4-way
-// conflicted and the float4 reads of the second phase are conflict-free, and 16-byte streaming
-// stores of four consecutive entries per lane.
+// Vectorised variant for C % 4 == 0, E % 4 == 0 and 16-byte aligned buffers.  The tile is
+// [C][ROWS_TE] floats; the 16-byte chunk holding entries 4g .. 4g+3 of channel c sits at chunk
+// position (g ^ (c >> 2)) & 15 of row c.
+//
+// Phase 1 -- a warp works on four entries at a time: lane = 8 * el + ql reads, for entry 4g + el,
+// the float4 number 8 * qh + ql of its row(s) (eight consecutive lanes cover 128 contiguous
+// bytes) and stores its four channels as scalars.  For one store instruction the bank is
+// 4 * ((g ^ ql) & 7) + el: all 32 lanes hit different banks.  (With one entry per warp, the
+// previous mapping, the 32 stores could only reach the 8 banks congruent to e & 3 -- four
+// wavefronts per store, and the kernel was bound by the shared-memory data path.)  Indices and
+// weights are read straight from global memory, once per group of four entries.
+// Phase 2 -- a lane moves four consecutive entries of one channel: conflict-free 16-byte shared
+// loads, 16-byte streaming stores.
+template <int NSRC, typename IndexT>
+__device__ __forceinline__ void rows_load_index(const IndexT *__restrict__ index, const float *__restrict__ weight,
+                                                int64_t at, int64_t N1, bool live, int (&id)[NSRC], float (&w)[NSRC],
+                                                bool &bad) {
+#pragma unroll
+  for (int i = 0; i < NSRC; ++i) {
+    int64_t v = live ? (int64_t)index[at * NSRC + i] : 0;  // a group beyond the tile reads nothing
+    w[i] = 1.f;
+    if (NSRC > 1) w[i] = live ? weight[at * NSRC + i] : 0.f;
+    if (v < 0 || v >= N1) {
+      v = -1;
+      bad = true;
+    }
+    id[i] = (int)v;
+  }
+}
+
 template <int NSRC, typename IndexT = int64_t>
 __global__ void __launch_bounds__(ROWS_THREADS)
 gather_rows_vec4_kernel(const float *__restrict__ featT, const IndexT *__restrict__ index,
                         const float *__restrict__ weight, int C, int64_t N1, int64_t E, float *__restrict__ out,
                         int32_t *__restrict__ status) {
   extern __shared__ __align__(16) float tile[];  // [C][ROWS_TE], chunk-swizzled
-  __shared__ int sidx[ROWS_TE * NSRC];
-  __shared__ float sw[ROWS_TE * NSRC];
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ql = lane & 7, el = lane >> 3;
   const int64_t b = blockIdx.y;
   const int64_t e0 = (int64_t)blockIdx.x * ROWS_TE;
   const int n = (int)((E - e0) < ROWS_TE ? (E - e0) : ROWS_TE);  // multiple of 4
   const int L = C >> 2;                                           // float4 per row
 
+  const float4 *fb = reinterpret_cast<const float4 *>(featT + b * N1 * C);
   bool bad = false;
-  for (int t = tid; t < n * NSRC; t += ROWS_THREADS) {
-    int64_t id = index[(b * E + e0) * NSRC + t];
-    if (id < 0 || id >= N1) {
-      id = -1;
-      bad = true;
+  // a warp owns the entry groups warp and warp + 8; the indices and weights of both are requested
+  // before the first row load, so the second group does not pay that latency again
+  int ids[ROWS_GPW][NSRC];
+  float ws[ROWS_GPW][NSRC];
+#pragma unroll
+  for (int j = 0; j < ROWS_GPW; ++j) {
+    const int g = warp + j * (ROWS_THREADS / 32);
+    rows_load_index<NSRC, IndexT>(index, weight, b * E + e0 + 4 * g + el, N1, g < (n >> 2), ids[j], ws[j], bad);
+  }
+#pragma unroll
+  for (int j = 0; j < ROWS_GPW; ++j) {
+    const int g = warp + j * (ROWS_THREADS / 32);
+    if (g >= (n >> 2)) break;
+    int (&id)[NSRC] = ids[j];
+    float (&w)[NSRC] = ws[j];
+    const float4 *row[NSRC];
+#pragma unroll
+    for (int i = 0; i < NSRC; ++i) {
+      row[i] = fb + (int64_t)(id[i] < 0 ? 0 : id[i]) * L;
+      if (id[i] < 0) w[i] = 0.f;
     }
-    sidx[t] = (int)id;
-    if (NSRC == 3) sw[t] = weight[(b * E + e0) * NSRC + t];
+#pragma unroll 4
+    for (int q = ql; q < L; q += 8) {
+      float4 v;
+      if (NSRC == 1) {
+        v = id[0] < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(row[0] + q);
+      } else {
+        const float4 f0 = __ldg(row[0] + q);
+        const float4 f1 = __ldg(row[NSRC > 1 ? 1 : 0] + q);
+        const float4 f2 = __ldg(row[NSRC > 2 ? 2 : 0] + q);
+        v.x = f0.x * w[0];
+        v.y = f0.y * w[0];
+        v.z = f0.z * w[0];
+        v.w = f0.w * w[0];
+        v.x += f1.x * w[NSRC > 1 ? 1 : 0];
+        v.y += f1.y * w[NSRC > 1 ? 1 : 0];
+        v.z += f1.z * w[NSRC > 1 ? 1 : 0];
+        v.w += f1.w * w[NSRC > 1 ? 1 : 0];
+        v.x += f2.x * w[NSRC > 2 ? 2 : 0];
+        v.y += f2.y * w[NSRC > 2 ? 2 : 0];
+        v.z += f2.z * w[NSRC > 2 ? 2 : 0];
+        v.w += f2.w * w[NSRC > 2 ? 2 : 0];
+      }
+      float *dst = tile + (4 * q) * ROWS_TE + (((g ^ q) & (ROWS_TE / 4 - 1)) << 2) + el;
+      dst[0] = v.x;
+      dst[ROWS_TE] = v.y;
+      dst[2 * ROWS_TE] = v.z;
+      dst[3 * ROWS_TE] = v.w;
+    }
   }
   if (bad && status) atomicOr(status, 1);
-  __syncthreads();
-
-  // Phase 1: item t = e * L + q  (entry e, float4 q of its row); consecutive threads take
-  // consecutive items, so a warp reads whole contiguous row pieces.
-  const float4 *fb = reinterpret_cast<const float4 *>(featT + b * N1 * C);
-  const int items = n * L;
-  int e = tid / L, q = tid - e * L;
-  const int de = ROWS_THREADS / L, dq = ROWS_THREADS - de * L;
-  for (int t = tid; t < items; t += ROWS_THREADS) {
-    float4 v;
-    if (NSRC == 1) {
-      const int id = sidx[e];
-      v = id < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(fb + (int64_t)id * L + q);
-    } else {
-      const int i0 = sidx[3 * e], i1 = sidx[3 * e + 1], i2 = sidx[3 * e + 2];
-      const float w0 = i0 < 0 ? 0.f : sw[3 * e], w1 = i1 < 0 ? 0.f : sw[3 * e + 1], w2 = i2 < 0 ? 0.f : sw[3 * e + 2];
-      const float4 f0 = __ldg(fb + (int64_t)(i0 < 0 ? 0 : i0) * L + q);
-      const float4 f1 = __ldg(fb + (int64_t)(i1 < 0 ? 0 : i1) * L + q);
-      const float4 f2 = __ldg(fb + (int64_t)(i2 < 0 ? 0 : i2) * L + q);
-      v.x = f0.x * w0;
-      v.y = f0.y * w0;
-      v.z = f0.z * w0;
-      v.w = f0.w * w0;
-      v.x += f1.x * w1;
-      v.y += f1.y * w1;
-      v.z += f1.z * w1;
-      v.w += f1.w * w1;
-      v.x += f2.x * w2;
-      v.y += f2.y * w2;
-      v.z += f2.z * w2;
-      v.w += f2.w * w2;
-    }
-    // channel c = 4q + i lives in row c; entry e sits in chunk ((e >> 2) ^ q) & 15, slot e & 3
-    float *dst = tile + (4 * q) * ROWS_TE + ((((e >> 2) ^ q) & (ROWS_TE / 4 - 1)) << 2) + (e & 3);
-    dst[0] = v.x;
-    dst[ROWS_TE] = v.y;
-    dst[2 * ROWS_TE] = v.z;
-    dst[3 * ROWS_TE] = v.w;
-    e += de;
-    q += dq;
-    if (q >= L) {
-      q -= L;
-      ++e;
-    }
-  }
   __syncthreads();
 
   // Phase 2: item u = c * 16 + chunk; a lane moves four consecutive entries of one channel.
@@ -206,25 +289,12 @@ scatter_rows_vec4_kernel(const float *__restrict__ gout, const IndexT *__restric
                          const float *__restrict__ weight, int C, int64_t N1, int64_t E, int64_t gstride,
                          float *__restrict__ gradT, int32_t *__restrict__ status) {
   extern __shared__ __align__(16) float tile[];  // [C][ROWS_TE], chunk-swizzled
-  __shared__ int sidx[ROWS_TE * NSRC];
-  __shared__ float sw[ROWS_TE * NSRC];
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ql = lane & 7, el = lane >> 3;
   const int64_t b = blockIdx.y;
   const int64_t e0 = (int64_t)blockIdx.x * ROWS_TE;
   const int n = (int)((E - e0) < ROWS_TE ? (E - e0) : ROWS_TE);  // multiple of 4
   const int L = C >> 2;
-
-  bool bad = false;
-  for (int t = tid; t < n * NSRC; t += ROWS_THREADS) {
-    int64_t id = index[(b * E + e0) * NSRC + t];
-    if (id < 0 || id >= N1) {
-      id = -1;
-      bad = true;
-    }
-    sidx[t] = (int)id;
-    if (NSRC == 3) sw[t] = weight[(b * E + e0) * NSRC + t];
-  }
-  if (bad && status) atomicOr(status, 1);
 
   // Phase 1: gout[b, c, e0 + 4*ch ..] -> tile row c, swizzled chunk.
   const int nchunks = n >> 2;
@@ -236,34 +306,37 @@ scatter_rows_vec4_kernel(const float *__restrict__ gout, const IndexT *__restric
       *reinterpret_cast<float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & 15) << 2)) = v;
     }
   }
+  // indices and weights of this warp's two entry groups, requested before the barrier
+  bool bad = false;
+  int ids[ROWS_GPW][NSRC];
+  float ws[ROWS_GPW][NSRC];
+#pragma unroll
+  for (int j = 0; j < ROWS_GPW; ++j) {
+    const int g = warp + j * (ROWS_THREADS / 32);
+    rows_load_index<NSRC, IndexT>(index, weight, b * E + e0 + 4 * g + el, N1, g < nchunks, ids[j], ws[j], bad);
+  }
   __syncthreads();
 
-  // Phase 2: item t = e * L + q -> four channels of entry e, reduced into the row(s) of its index.
+  // Phase 2: the lane mapping of the forward kernel's phase 1 (four entries per warp, conflict-free
+  // scalar reads): four channels of entry 4g + el, reduced into the row(s) of its index.
   float *tb = gradT + b * N1 * C;
-  const int items = n * L;
-  int e = tid / L, q = tid - e * L;
-  const int de = ROWS_THREADS / L, dq = ROWS_THREADS - de * L;
-  for (int t = tid; t < items; t += ROWS_THREADS) {
-    const float *src = tile + (4 * q) * ROWS_TE + ((((e >> 2) ^ q) & (ROWS_TE / 4 - 1)) << 2) + (e & 3);
-    const float vx = src[0], vy = src[ROWS_TE], vz = src[2 * ROWS_TE], vw = src[3 * ROWS_TE];
-    if (NSRC == 1) {
-      const int id = sidx[e];
-      if (id >= 0) red_add4(tb + (int64_t)id * C + 4 * q, vx, vy, vz, vw);
-    } else {
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int id = sidx[3 * e + i];
-        const float w = sw[3 * e + i];
-        if (id >= 0) red_add4(tb + (int64_t)id * C + 4 * q, vx * w, vy * w, vz * w, vw * w);
+  for (int j = 0; j < ROWS_GPW; ++j) {
+    const int g = warp + j * (ROWS_THREADS / 32);
+    if (g >= nchunks) break;
+    int (&id)[NSRC] = ids[j];
+    float (&w)[NSRC] = ws[j];
+#pragma unroll 4
+    for (int q = ql; q < L; q += 8) {
+      const float *src = tile + (4 * q) * ROWS_TE + (((g ^ q) & (ROWS_TE / 4 - 1)) << 2) + el;
+      const float vx = src[0], vy = src[ROWS_TE], vz = src[2 * ROWS_TE], vw = src[3 * ROWS_TE];
+#pragma unroll
+      for (int i = 0; i < NSRC; ++i) {
+        if (id[i] >= 0) red_add4(tb + (int64_t)id[i] * C + 4 * q, vx * w[i], vy * w[i], vz * w[i], vw * w[i]);
       }
     }
-    e += de;
-    q += dq;
-    if (q >= L) {
-      q -= L;
-      ++e;
-    }
   }
+  if (bad && status) atomicOr(status, 1);
 }
 
 inline size_t rows_scratch_bytes(int64_t B, int64_t C, int64_t N1) { return (size_t)B * (size_t)C * (size_t)N1 * 4; }
@@ -277,9 +350,7 @@ template <int NSRC, typename IndexT = int64_t>
 int gather_rows(const float *in, const IndexT *index, const float *weight, int64_t B, int64_t C, int64_t N1,
                 int64_t E, float *out, int32_t *status, float *scratch, cudaStream_t st) {
   TK3D_REQUIRE(B <= 65535, TK3D_ERR_SHAPE, "gather: batch too large for this path (B=%lld)", (long long)B);
-  dim3 tg((unsigned)((N1 + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)B);
-  transpose_bcn_kernel<<<tg, 256, 0, st>>>(in, scratch, (int)C, N1);
-  int rc = check_launch("transpose_bcn_kernel");
+  int rc = transpose_bcn(in, scratch, B, C, N1, st);
   if (rc) return rc;
   dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
   const bool vec = C % 4 == 0 && E % 4 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15) == 0;
@@ -315,9 +386,7 @@ int scatter_rows(const float *gout, const int64_t *index, const float *weight, i
     if (rc) return rc;
   }
   // scratch [B][N1][C] -> gin [B][C][N1]: the same tile transpose with the roles of the axes swapped
-  dim3 tg((unsigned)((C + 31) / 32), (unsigned)((N1 + 31) / 32), (unsigned)B);
-  transpose_bcn_kernel<<<tg, 256, 0, st>>>(scratch, gin, (int)N1, C);
-  return check_launch("transpose_bcn_kernel");
+  return transpose_bcn(scratch, gin, B, N1, C, st);
 }
 
 inline bool rows_vec_ok(int64_t C, int64_t E, const void *a, const void *b) {

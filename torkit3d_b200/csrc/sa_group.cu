@@ -222,29 +222,39 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
         if (vec) {
           const int L = C >> 2;
           const float4 *fb4 = reinterpret_cast<const float4 *>(fb);
-          const int items = n * L;
-          // item t = e * L + q: entry e, 16-byte piece q of its row; four loads in flight per thread
-          for (int t = tid; t < items; t += 4 * SA_THREADS) {
+          // four entries per warp and step (lane = 8 * el + ql), as in gather_rows_vec4_kernel:
+          // the 32 scalar stores of one instruction fall into 32 different banks.  A warp's steps
+          // (entry group, block of eight row pieces) are taken four at a time to keep four loads
+          // in flight per lane.
+          const int ql = lane & 7, el = lane >> 3;
+          constexpr int NW = SA_THREADS / 32;
+          const int QB = (L + 7) >> 3;
+          const int ng = n >> 2;
+          const int steps = ng > part ? ((ng - part + NW - 1) / NW) * QB : 0;
+          int gi = part, qb = 0;
+          for (int t = 0; t < steps; t += 4) {
             float4 v[4];
-            int ee[4], qq[4];
+            int gg[4], qq[4];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-              const int tt = t + w * SA_THREADS;
-              ee[w] = tt / L;
-              qq[w] = tt - ee[w] * L;
+              gg[w] = gi;
+              qq[w] = 8 * qb + ql;
               v[w] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (tt < items) {
-                const int g = s0 + ee[w];
+              if (t + w < steps && qq[w] < L) {
+                const int g = s0 + 4 * gi + el;
                 const int c = g / K;
                 const int id = sidx[c * S1 + (g - c * K)];
                 if (id >= 0) v[w] = __ldg(fb4 + (int64_t)id * L + qq[w]);
               }
+              if (++qb == QB) {
+                qb = 0;
+                gi += NW;
+              }
             }
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-              if (t + w * SA_THREADS < items) {
-                const int e = ee[w], q = qq[w];
-                float *dst = gtile + (4 * q) * SA_TE + ((((e >> 2) ^ q) & (SA_TE / 4 - 1)) << 2) + (e & 3);
+              if (t + w < steps && qq[w] < L) {
+                float *dst = gtile + (4 * qq[w]) * SA_TE + (((gg[w] ^ qq[w]) & (SA_TE / 4 - 1)) << 2) + el;
                 dst[0] = v[w].x;
                 dst[SA_TE] = v[w].y;
                 dst[2 * SA_TE] = v[w].z;
@@ -364,9 +374,7 @@ extern "C" int tk3d_sa_group_fwd(const void *points, const void *centroids, cons
     const size_t want = rows_scratch_bytes(B, C, N);
     TK3D_REQUIRE(scratch != nullptr && scratch_bytes >= want, TK3D_ERR_SCRATCH,
                  "sa_group_fwd: scratch of %zu bytes required (got %zu)", want, scratch_bytes);
-    dim3 tg((unsigned)((N + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)B);
-    transpose_bcn_kernel<<<tg, 256, 0, st>>>((const float *)feature, (float *)scratch, (int)C, N);
-    int rc = check_launch("transpose_bcn_kernel");
+    int rc = transpose_bcn((const float *)feature, (float *)scratch, B, C, N, st);
     if (rc) return rc;
     featT = (const float *)scratch;
   }
@@ -439,9 +447,7 @@ extern "C" int tk3d_sa_group_bwd(const void *gout, const int32_t *index32, int64
         int rc = check_launch("scatter_rows_vec4_kernel");
         if (rc) return rc;
       }
-      dim3 tg((unsigned)((C + 31) / 32), (unsigned)((N + 31) / 32), (unsigned)B);
-      transpose_bcn_kernel<<<tg, 256, 0, st>>>((const float *)scratch, (float *)gfeature, (int)N, C);
-      int rc = check_launch("transpose_bcn_kernel");
+      int rc = transpose_bcn((const float *)scratch, (float *)gfeature, B, N, C, st);
       if (rc) return rc;
     } else {
       TK3D_CUDA(cudaMemsetAsync(gfeature, 0, sizeof(float) * (size_t)(B * C * N), st));
