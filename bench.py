@@ -378,6 +378,12 @@ def extras(dev, rank, world, flush):
     ms = t(lambda: interpolate_feature(ff, i, w), steps=5)
     out["c5_interp_fwd_ms"] = ms
     out["c5_interp_fwd_GBps"] = 708.9e6 / (ms * 1e-3) / 1e9
+    # the same gather from features kept as rows (built once per step, shared by all slabs of a scene)
+    from torkit3d_b200.ops import feature_rows
+    out["c5_feature_rows_ms"] = t(lambda: feature_rows(ff), steps=5)
+    frows = feature_rows(ff)
+    out["c5_interp_fwd_from_rows_ms"] = t(lambda: interpolate_feature(ff, i, w, rows=frows), steps=5)
+    del frows
     ffg = ff.clone().requires_grad_(True)
     o = interpolate_feature(ffg, i, w)
     go = torch.ones_like(o)

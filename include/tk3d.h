@@ -224,6 +224,25 @@ int tk3d_interp_bwd(const void *grad_out, const int64_t *index, const void *weig
                     size_t scratch_bytes, int dtype, void *stream);
 
 /*
+ * Features kept as rows.  The gathers above read rows of a [B,N,C] copy of the features, which they
+ * build in `scratch` on every call.  A caller that gathers from the same features more than once --
+ * query slabs of one scene, several groupings of one cloud, forward passes between two updates of
+ * the features -- builds that copy once with tk3d_feature_rows and hands it to the *_rows forms,
+ * which then launch the gather alone.  No counterpart in the reference, whose kernels read the
+ * [B,C,N] tensor directly (torkit3d/csrc/cuda/group_points_kernel.cu:8-31, interpolate_kernel.cu:8-47).
+ * float32 only, C <= 512, B <= 65535; index_dtype TK3D_I64 or TK3D_I32.
+ *   tk3d_feature_rows:    feature [B,C,N] in;  rows [B,N,C] out (B*N*C*4 bytes)
+ *   tk3d_interp_fwd_rows: rows [B,N1,C], index [B,N2,3], weight [B,N2,3] in;  out [B,C,N2]
+ *   tk3d_group_fwd_rows:  rows [B,N1,C], index [B,N2,K] in;  out [B,C,N2,K]
+ */
+int tk3d_feature_rows(const void *feature, int64_t B, int64_t C, int64_t N, void *rows, int dtype, void *stream);
+int tk3d_interp_fwd_rows(const void *rows, const void *index, int index_dtype, const void *weight, int64_t B,
+                         int64_t C, int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, int dtype,
+                         void *stream);
+int tk3d_group_fwd_rows(const void *rows, const void *index, int index_dtype, int64_t B, int64_t C, int64_t N1,
+                        int64_t N2, int64_t K, void *out, int32_t *status, int dtype, void *stream);
+
+/*
  * Inverse squared-distance weights of the k nearest neighbours:
  * inv = 1 / max(d, 1e-10), weight = inv / sum(inv) over the last axis.
  * Replaces the element-wise PyTorch expressions of FeatureInterpolator.forward

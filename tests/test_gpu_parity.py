@@ -603,6 +603,57 @@ def test_group_and_interp_row_gather_path_equals_direct_path(oracle, B, C, n1, n
         np.testing.assert_allclose(N(i_rows), oracle.interp_fwd(N(f), N(idx3), N(w)), rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("B,C,n1,n2,k", [(2, 64, 300, 700, 32), (2, 33, 129, 100, 9), (1, 512, 64, 40, 16),
+                                         (3, 16, 1000, 222, 4), (2, 128, 4100, 9000, 3)])
+@pytest.mark.parametrize("index_dtype", [torch.int64, torch.int32])
+def test_features_kept_as_rows(oracle, B, C, n1, n2, k, index_dtype):
+    """``feature_rows`` once, then gathers that skip their own transposition: same results as the
+    operators on the [B,C,N1] tensor, for sizes that take the 16-byte kernels and sizes that do not,
+    with both index types, and the same gradient for the features."""
+    from torkit3d_b200 import _C
+    from torkit3d_b200.ops import feature_rows, group_points, interpolate_feature
+
+    g = torch.Generator().manual_seed(C + n2)
+    f = torch.randn(B, C, n1, generator=g).to(DEV)
+    rows = feature_rows(f)
+    assert rows.shape == (B, n1, C) and torch.equal(rows, f.transpose(1, 2).contiguous())
+    idx = torch.randint(0, n1, (B, n2, k), generator=g).to(DEV)
+    out = _C.group_points_forward_rows_cuda(rows, idx.to(index_dtype))
+    np.testing.assert_array_equal(N(out), oracle.group_fwd(N(f), N(idx)))
+    idx3 = torch.randint(0, n1, (B, n2, 3), generator=g).to(DEV)
+    w = torch.rand(B, n2, 3, generator=g).to(DEV)
+    o3 = _C.interpolate_forward_rows_cuda(rows, idx3.to(index_dtype), w)
+    np.testing.assert_allclose(N(o3), oracle.interp_fwd(N(f), N(idx3), N(w)), rtol=1e-5, atol=1e-6)
+    # through the operators, with gradients
+    fa = f.clone().requires_grad_(True)
+    fb = f.clone().requires_grad_(True)
+    ya = interpolate_feature(fa, idx3, w, rows=rows) .sum() + group_points(fa, idx, rows=rows).square().sum()
+    yb = interpolate_feature(fb, idx3, w).sum() + group_points(fb, idx).square().sum()
+    ya.backward()
+    yb.backward()
+    torch.testing.assert_close(ya, yb, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(fa.grad, fb.grad, rtol=1e-5, atol=1e-5)
+
+
+def test_features_kept_as_rows_errors():
+    from torkit3d_b200 import _C
+
+    f = torch.randn(2, 8, 50, device=DEV)
+    rows = _C.feature_rows(f)
+    with pytest.raises(RuntimeError):
+        _C.feature_rows(f.double())
+    with pytest.raises(RuntimeError):
+        _C.feature_rows(f.cpu())
+    with pytest.raises(RuntimeError):
+        _C.group_points_forward_rows_cuda(rows, torch.zeros(3, 4, 5, dtype=torch.int64, device=DEV))
+    with pytest.raises(RuntimeError):
+        _C.interpolate_forward_rows_cuda(rows, torch.zeros(2, 4, 2, dtype=torch.int64, device=DEV),
+                                         torch.zeros(2, 4, 2, device=DEV))
+    # an out-of-range index gathers zeros (and is reported through the C ABI's status word)
+    idx = torch.full((2, 4, 5), 50, dtype=torch.int64, device=DEV)
+    assert float(_C.group_points_forward_rows_cuda(rows, idx).abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("B,C,n1,n2,k", [(3, 64, 700, 300, 16), (2, 128, 512, 2048, 4), (2, 64, 40, 25, 4), (2, 96, 100, 333, 12)])
 def test_group_and_interp_backward_row_path_equals_direct_path(oracle, B, C, n1, n2, k):
     """With scratch the backward accumulates into a transposed buffer with vector atomics; same sums."""

@@ -269,6 +269,69 @@ def interpolate_backward_cuda(grad_output, index, weight, n1):
     return gin
 
 
+def feature_rows(feature):
+    """feature [B,C,N] float32 -> the same values as rows [B,N,C]: the layout the row gathers read.
+    Build it once when several gathers read the same features (query slabs of one scene, several
+    groupings of one cloud) and pass it to the ``*_rows_cuda`` forms below.  No counterpart in the
+    reference."""
+    _check_cuda_contig(feature=feature)
+    _check_eq(feature.dim(), 3, "feature.dim() == 3")
+    if feature.dtype != torch.float32:
+        raise RuntimeError("feature_rows: float32 features only")
+    lib = load()
+    B, C, N = feature.shape
+    with _on(feature.device):
+        rows = torch.empty((B, N, C), dtype=feature.dtype, device=feature.device)
+        check(lib.tk3d_feature_rows(_ptr(feature), B, C, N, _ptr(rows), _lib.F32, _stream(feature)))
+    return rows
+
+
+def _check_rows(rows, index):
+    _check_cuda_contig(rows=rows, index=index)
+    _check_eq(rows.dim(), 3, "rows.dim() == 3")
+    _check_eq(index.dim(), 3, "index.dim() == 3")
+    _check_eq(rows.size(0), index.size(0), "rows.size(0) == index.size(0)")
+    if rows.dtype != torch.float32:
+        raise RuntimeError("rows must be a float32 tensor.")
+    if index.dtype not in (torch.int64, torch.int32):
+        raise RuntimeError("index must be an int64 tensor.")
+    _same_device_dtype(rows, index)
+
+
+def interpolate_forward_rows_cuda(rows, index, weight):
+    """rows [B,N1,C] (``feature_rows`` of the [B,C,N1] features), index/weight [B,N2,3] -> [B,C,N2];
+    the result of ``interpolate_forward_cuda`` on those features, without the per-call transposition."""
+    _check_rows(rows, index)
+    _check_cuda_contig(weight=weight)
+    _check_eq(weight.dim(), 3, "weight.dim() == 3")
+    _check_eq(index.size(1), weight.size(1), "index.size(1) == weight.size(1)")
+    _check_eq(index.size(2), weight.size(2), "index.size(2) == weight.size(2)")
+    if index.size(2) != 3:
+        raise RuntimeError("Only support k=3.")
+    _same_device_dtype(rows, weight, floats=(weight,))
+    lib = load()
+    B, N1, C = rows.shape
+    N2 = index.size(1)
+    with _on(rows.device):
+        out = torch.empty((B, C, N2), dtype=rows.dtype, device=rows.device)
+        check(lib.tk3d_interp_fwd_rows(_ptr(rows), _ptr(index), _index_code(index.dtype), _ptr(weight), B, C, N1, N2,
+                                       3, _ptr(out), None, _lib.F32, _stream(rows)))
+    return out
+
+
+def group_points_forward_rows_cuda(rows, index):
+    """rows [B,N1,C] (``feature_rows`` of the [B,C,N1] features), index [B,N2,K] -> [B,C,N2,K]."""
+    _check_rows(rows, index)
+    lib = load()
+    B, N1, C = rows.shape
+    _, N2, K = index.shape
+    with _on(rows.device):
+        out = torch.empty((B, C, N2, K), dtype=rows.dtype, device=rows.device)
+        check(lib.tk3d_group_fwd_rows(_ptr(rows), _ptr(index), _index_code(index.dtype), B, C, N1, N2, K, _ptr(out),
+                                      None, _lib.F32, _stream(rows)))
+    return out
+
+
 def knn_distance_cuda(query, key, k, version=0, *, channel_first=False, index_dtype=torch.int64):
     """query [B,N1,3], key [B,N2,3] ([B,3,N1], [B,3,N2] with ``channel_first``) ->
     [distance [B,N1,k] (squared), index [B,N1,k]]."""

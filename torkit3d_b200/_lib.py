@@ -72,6 +72,9 @@ SIGNATURES = {
     "tk3d_knn_layout": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _int, _int, _vp]),
     "tk3d_fps_layout": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, ctypes.c_size_t, _int, _vp]),
     "tk3d_ball_query_layout": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _i64, _int, _vp, _int, _int, _vp]),
+    "tk3d_feature_rows": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _vp]),
+    "tk3d_interp_fwd_rows": (_int, [_vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
+    "tk3d_group_fwd_rows": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _int, _vp]),
     "tk3d_group_fwd_layout": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, ctypes.c_size_t, _int,
                                      _vp]),
 }

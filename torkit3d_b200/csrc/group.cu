@@ -363,6 +363,28 @@ extern "C" int tk3d_group_fwd_layout(const void *in, const void *index, int inde
                                  dtype, stream);
 }
 
+extern "C" int tk3d_group_fwd_rows(const void *rows, const void *index, int index_dtype, int64_t B, int64_t C,
+                                   int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status, int dtype,
+                                   void *stream) {
+  TK3D_RANGE("tk3d_group_fwd_rows");
+  int rc = check_group_args("group_fwd_rows", rows, nullptr, out, B, C, N1, N2, K, dtype);
+  if (rc) return rc;
+  TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "group_fwd_rows: float32 only (dtype %d)", dtype);
+  TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "group_fwd_rows: index_dtype %d",
+               index_dtype);
+  TK3D_REQUIRE(C <= ROWS_MAX_C && B <= 65535, TK3D_ERR_SHAPE, "group_fwd_rows: C <= %d and B <= 65535 required",
+               ROWS_MAX_C);
+  const int64_t E = N2 * K;
+  if (B * C * E == 0) return TK3D_OK;
+  TK3D_REQUIRE(index && out && (rows || N1 == 0), TK3D_ERR_NULL, "group_fwd_rows: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (index_dtype == TK3D_I32)
+    return gather_from_rows<1, int32_t>((const float *)rows, (const int32_t *)index, nullptr, B, C, N1, E,
+                                        (float *)out, status, st);
+  return gather_from_rows<1, int64_t>((const float *)rows, (const int64_t *)index, nullptr, B, C, N1, E, (float *)out,
+                                      status, st);
+}
+
 extern "C" size_t tk3d_group_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int64_t K, int dtype) {
   if (dtype != TK3D_F32 || B <= 0 || C <= 0 || N1 <= 0 || N2 <= 0 || K <= 0 || B > 65535) return 0;
   if (C % 4 != 0 || (N2 * K) % 4 != 0 || (N1 + 31) / 32 > 65535) return 0;

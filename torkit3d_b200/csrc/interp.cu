@@ -174,6 +174,38 @@ extern "C" int tk3d_interp_fwd(const void *in, const int64_t *index, const void 
                               st);
 }
 
+extern "C" int tk3d_feature_rows(const void *feature, int64_t B, int64_t C, int64_t N, void *rows, int dtype,
+                                 void *stream) {
+  TK3D_RANGE("tk3d_feature_rows");
+  TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "feature_rows: float32 only (dtype %d)", dtype);
+  TK3D_REQUIRE(B >= 0 && C >= 0 && N >= 0, TK3D_ERR_SHAPE, "feature_rows: negative size");
+  if (B * C * N == 0) return TK3D_OK;
+  TK3D_REQUIRE(feature && rows, TK3D_ERR_NULL, "feature_rows: a pointer is NULL");
+  TK3D_REQUIRE(B <= 65535 && (C + 31) / 32 <= 65535, TK3D_ERR_SHAPE, "feature_rows: size too large");
+  return transpose_bcn((const float *)feature, (float *)rows, B, C, N, (cudaStream_t)stream);
+}
+
+extern "C" int tk3d_interp_fwd_rows(const void *rows, const void *index, int index_dtype, const void *weight, int64_t B,
+                                    int64_t C, int64_t N1, int64_t N2, int64_t K, void *out, int32_t *status,
+                                    int dtype, void *stream) {
+  TK3D_RANGE("tk3d_interp_fwd_rows");
+  int rc = check_interp_args("interp_fwd_rows", B, C, N1, N2, K, dtype);
+  if (rc) return rc;
+  TK3D_REQUIRE(dtype == TK3D_F32, TK3D_ERR_DTYPE, "interp_fwd_rows: float32 only (dtype %d)", dtype);
+  TK3D_REQUIRE(index_dtype == TK3D_I64 || index_dtype == TK3D_I32, TK3D_ERR_DTYPE, "interp_fwd_rows: index_dtype %d",
+               index_dtype);
+  TK3D_REQUIRE(C <= ROWS_MAX_C && B <= 65535, TK3D_ERR_SHAPE, "interp_fwd_rows: C <= %d and B <= 65535 required",
+               ROWS_MAX_C);
+  if (B * C * N2 == 0) return TK3D_OK;
+  TK3D_REQUIRE(index && weight && out && (rows || N1 == 0), TK3D_ERR_NULL, "interp_fwd_rows: a pointer is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (index_dtype == TK3D_I32)
+    return gather_from_rows<3, int32_t>((const float *)rows, (const int32_t *)index, (const float *)weight, B, C, N1,
+                                        N2, (float *)out, status, st);
+  return gather_from_rows<3, int64_t>((const float *)rows, (const int64_t *)index, (const float *)weight, B, C, N1, N2,
+                                      (float *)out, status, st);
+}
+
 extern "C" size_t tk3d_interp_bwd_scratch_bytes(int64_t B, int64_t C, int64_t N1, int64_t N2, int dtype) {
   if (dtype != TK3D_F32 || C % 4 != 0 || N2 % 4 != 0 || (N1 + 31) / 32 > 65535) return 0;
   return tk3d_interp_fwd_scratch_bytes(B, C, N1, N2, dtype);

@@ -346,12 +346,11 @@ inline bool rows_profitable(int64_t C, int64_t N1, int64_t E, int nsrc) {
   return C >= 16 && C <= ROWS_MAX_C && N1 > 0 && E * nsrc >= 2 * N1;
 }
 
+// The gather alone, from features that already lie as rows [B,N1,C].
 template <int NSRC, typename IndexT = int64_t>
-int gather_rows(const float *in, const IndexT *index, const float *weight, int64_t B, int64_t C, int64_t N1,
-                int64_t E, float *out, int32_t *status, float *scratch, cudaStream_t st) {
+int gather_from_rows(const float *scratch, const IndexT *index, const float *weight, int64_t B, int64_t C, int64_t N1,
+                     int64_t E, float *out, int32_t *status, cudaStream_t st) {
   TK3D_REQUIRE(B <= 65535, TK3D_ERR_SHAPE, "gather: batch too large for this path (B=%lld)", (long long)B);
-  int rc = transpose_bcn(in, scratch, B, C, N1, st);
-  if (rc) return rc;
   dim3 grid((unsigned)((E + ROWS_TE - 1) / ROWS_TE), (unsigned)B);
   const bool vec = C % 4 == 0 && E % 4 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15) == 0;
   if (vec) {
@@ -367,6 +366,15 @@ int gather_rows(const float *in, const IndexT *index, const float *weight, int64
     TK3D_CUDA(raise_smem_limit((const void *)gather_rows_kernel<NSRC, IndexT>, (int)smem));
   gather_rows_kernel<NSRC, IndexT><<<grid, ROWS_THREADS, smem, st>>>(scratch, index, weight, (int)C, N1, E, out, status);
   return check_launch("gather_rows_kernel");
+}
+
+// Transposition into caller scratch, then the gather.
+template <int NSRC, typename IndexT = int64_t>
+int gather_rows(const float *in, const IndexT *index, const float *weight, int64_t B, int64_t C, int64_t N1,
+                int64_t E, float *out, int32_t *status, float *scratch, cudaStream_t st) {
+  int rc = transpose_bcn(in, scratch, B, C, N1, st);
+  if (rc) return rc;
+  return gather_from_rows<NSRC, IndexT>(scratch, index, weight, B, C, N1, E, out, status, st);
 }
 
 // Backward through the transposed accumulator; `vec_ok` has been checked by the caller.

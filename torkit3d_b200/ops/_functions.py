@@ -130,16 +130,21 @@ class GroupPointsFunction(torch.autograd.Function):
     Reference: torkit3d/ops/group_points.py:6-19."""
 
     @staticmethod
-    def forward(ctx, points, index):
+    def forward(ctx, points, index, *extra):
+        # extra (an addition to the reference's signature): rows = _C.feature_rows(points), built once
+        # by a caller that groups the same features several times
         ctx.save_for_backward(index)
         ctx.num_points = points.size(2)
+        ctx.n_extra = len(extra)
+        if extra and extra[0] is not None:
+            return _C.group_points_forward_rows_cuda(extra[0], index.contiguous())
         return _C.group_points_forward_cuda(points.contiguous(), index.contiguous())
 
     @staticmethod
     def backward(ctx, *grad_output):
         (index,) = ctx.saved_tensors
         grad_points = _C.group_points_backward_cuda(grad_output[0].contiguous(), index.contiguous(), ctx.num_points)
-        return grad_points, None
+        return (grad_points, None) + _no_grads(ctx.n_extra)
 
 
 class InterpolateFeature(torch.autograd.Function):
@@ -147,9 +152,14 @@ class InterpolateFeature(torch.autograd.Function):
     Reference: torkit3d/ops/interpolate_feature.py:6-24."""
 
     @staticmethod
-    def forward(ctx, feature, index, weight):
+    def forward(ctx, feature, index, weight, *extra):
+        # extra (an addition to the reference's signature): rows = _C.feature_rows(feature), built once
+        # by a caller that interpolates the same features several times (query slabs of one scene)
         ctx.save_for_backward(index, weight)
         ctx.n1 = feature.size(2)
+        ctx.n_extra = len(extra)
+        if extra and extra[0] is not None:
+            return _C.interpolate_forward_rows_cuda(extra[0], index.contiguous(), weight.contiguous())
         return _C.interpolate_forward_cuda(feature.contiguous(), index.contiguous(), weight.contiguous())
 
     @staticmethod
@@ -157,4 +167,4 @@ class InterpolateFeature(torch.autograd.Function):
         index, weight = ctx.saved_tensors
         grad_feature = _C.interpolate_backward_cuda(grad_out[0].contiguous(), index.contiguous(),
                                                     weight.contiguous(), ctx.n1)
-        return grad_feature, None, None
+        return (grad_feature, None, None) + _no_grads(ctx.n_extra)
