@@ -106,22 +106,25 @@ ball_query_fast_kernel(const float *__restrict__ query, const float *__restrict_
 }
 
 // Few queries (B*N1 below a few hundred thousand): one query per thread cannot fill 148 SMs.  Here a
-// block of 4 warps serves 32 queries (lane = query) and warp s sweeps the s-th quarter of every
-// 256-key tile, so four times as many warps are in flight.  Every (quarter, query) keeps its own
-// ascending hit list in shared memory (at most K entries: a quarter can never contribute more than
-// K of the first K hits); at the end the four ascending lists of a query are merged by key index.
+// block of SPLIT warps serves 32 queries (lane = query) and warp s sweeps the s-th slice of every
+// 256-key tile, so SPLIT times as many warps are in flight.  A thread records the hits of its slice
+// as a bit mask (at most 64 keys), the slices' hit counts of the tile are exchanged through shared
+// memory at the tile's barrier, and every thread then knows where its hits belong in the query's
+// row (hits of earlier tiles + hits of lower slices of this tile) and writes them there: rows come
+// out in ascending key order without a merge, for any K.  A query with K hits stops testing, and
+// the block leaves the key loop at the first barrier after all its queries are full.
 constexpr int BS_TILE = 256;
-constexpr int BS_SPLIT = 4;
-constexpr int BS_MAX_K = 64;
 
-__global__ void __launch_bounds__(BQ_THREADS)
+template <int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT)
 ball_query_split_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
                         float r2, int k, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
-  constexpr int PER = BS_TILE / BQ_THREADS;
-  constexpr int QK = BS_TILE / BS_SPLIT;  // keys per warp per tile
+  constexpr int THREADS = 32 * SPLIT;
+  constexpr int PER = BS_TILE / THREADS;
+  constexpr int QK = BS_TILE / SPLIT;  // keys per warp per tile (64 or 32)
+  static_assert(PER >= 1 && QK <= 64 && QK % 8 == 0, "slice must fit a 64-bit hit mask");
   __shared__ float4 tile[2][BS_TILE];
-  extern __shared__ int hits[];           // [BS_SPLIT][k][32]
-  __shared__ int hcount[BS_SPLIT][32];
+  __shared__ int tcount[2][SPLIT][32];
   const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
   const int chunks = (N1 + 31) / 32;
   const float never = __int_as_float(0xff800000);
@@ -134,9 +137,10 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
     if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
     const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
                  mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
-    float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
-    int cnt = 0;
-    int *mine = hits + (part * k) * 32 + lane;
+    const float open_thr = sweep_threshold(r2, sweep_qq(qx, qy, qz));
+    float thr[1] = {valid ? open_thr : never};
+    const int64_t row = (b * N1 + (valid ? i : 0)) * (int64_t)k;
+    int done = 0;  // hits of this query in the tiles swept so far (the same number in every warp)
     const float *rb = key + b * (int64_t)N2 * 3;
     const int ntiles = (N2 + BS_TILE - 1) / BS_TILE;
 
@@ -144,7 +148,7 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
     auto fetch = [&](int t0) {
 #pragma unroll
       for (int p = 0; p < PER; ++p) {
-        const int j = t0 + tid + p * BQ_THREADS;
+        const int j = t0 + tid + p * THREADS;
         float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
         if (j < N2) {
           float x, y, z;
@@ -156,7 +160,7 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
     };
     auto commit = [&](float4 *dst) {
 #pragma unroll
-      for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * BQ_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
+      for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
     };
     fetch(0);
     commit(tile[0]);
@@ -165,62 +169,53 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
       const int t0 = t * BS_TILE + part * QK;
       const float4 *tl = tile[t & 1] + part * QK;
       if (t + 1 < ntiles) fetch((t + 1) * BS_TILE);
+      unsigned long long mask = 0;
+      int cnt = 0;
+      const bool was_full = !valid || done >= k;
 #pragma unroll 2
       for (int u0 = 0; u0 < QK; u0 += 8) {
         float2 a[4];
         if (__builtin_expect(sweep_group2<1, true>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int j = t0 + u0 + u;
             const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
             if (!(av >= thr[0])) {  // padding keys carry +inf; a full row has thr = -inf
               const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {
-                mine[cnt * 32] = j;
-                if (++cnt == k) thr[0] = never;
+                mask |= 1ull << (u0 + u);
+                if (done + ++cnt >= k) thr[0] = never;  // whatever the lower slices found, this row is full
               }
             }
           }
         }
       }
+      tcount[t & 1][part][lane] = cnt;
       if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
-      __syncthreads();
+      // One barrier per tile; it also votes on "every query of this block was full before this tile"
+      // (such a tile recorded no hit anywhere, so nothing is left to write).
+      if (__syncthreads_and(was_full)) break;
+      int before = 0, total = 0;
+#pragma unroll
+      for (int s = 0; s < SPLIT; ++s) {
+        const int c = tcount[t & 1][s][lane];
+        if (s < part) before += c;
+        total += c;
+      }
+      int pos = done + before;
+      while (mask != 0 && pos < k) {
+        const int bit = __ffsll((long long)mask) - 1;
+        mask &= mask - 1;
+        index.put(row + pos, t0 + bit);
+        ++pos;
+      }
+      done += total;
+      if (done >= k) thr[0] = never;
     }
-    hcount[part][lane] = cnt;
-    __syncthreads();
-
-    // Merge: warp 0, lane = query.  Heads of the four ascending lists, smallest key index first.
-    if (part == 0 && valid) {
-      const int64_t row = (b * N1 + i) * (int64_t)k;
-      int pos[BS_SPLIT], n[BS_SPLIT];
-#pragma unroll
-      for (int s = 0; s < BS_SPLIT; ++s) {
-        pos[s] = 0;
-        n[s] = hcount[s][lane];
-      }
-      int out = 0;
-      int64_t first = -1;
-      while (out < k) {
-        int best = 0x7fffffff, bs = -1;
-#pragma unroll
-        for (int s = 0; s < BS_SPLIT; ++s) {
-          if (pos[s] < n[s]) {
-            const int h = hits[(s * k + pos[s]) * 32 + lane];
-            if (h < best) {
-              best = h;
-              bs = s;
-            }
-          }
-        }
-        if (bs < 0) break;
-#pragma unroll
-        for (int s = 0; s < BS_SPLIT; ++s)
-          if (s == bs) ++pos[s];
-        if (out == 0) first = best;
-        index.put(row + out++, best);
-      }
-      for (int c = out; c < k; ++c) index.put(row + c, first);
+    __syncthreads();  // the row's first entry, written by whichever warp found it, is visible now
+    if (valid && done < k) {
+      const int64_t first = done > 0 ? index.get(row) : -1;
+      for (int c = done + part; c < k; c += SPLIT) index.put(row + c, first);
     }
     __syncthreads();
   }
@@ -286,11 +281,15 @@ static int ball_query_impl(const void *query, const void *key, int64_t B, int64_
   if (dtype == TK3D_F32) {
     const float r2 = radius * radius;  // squared in fp32, as the reference does for float tensors
     const int64_t cap = (int64_t)sm_count() * 256;
-    if (k <= BS_MAX_K && B * N1 < (int64_t)sm_count() * 16 * BQ_THREADS) {
+    if (B * N1 < (int64_t)sm_count() * 16 * BQ_THREADS) {
       const int64_t total = B * ((N1 + 31) / 32);
-      const size_t smem = sizeof(int) * BS_SPLIT * (size_t)k * 32;
-      ball_query_split_kernel<<<(unsigned)(total < cap ? total : cap), BQ_THREADS, smem, st>>>(
-          (const float *)query, (const float *)key, B, (int)N1, (int)N2, r2, (int)k, io, total, ql, kl);
+      const unsigned grid = (unsigned)(total < cap ? total : cap);
+      if (total <= 2 * (int64_t)sm_count())  // very few queries: eight warps per 32 queries
+        ball_query_split_kernel<8><<<grid, 256, 0, st>>>((const float *)query, (const float *)key, B, (int)N1, (int)N2,
+                                                         r2, (int)k, io, total, ql, kl);
+      else
+        ball_query_split_kernel<4><<<grid, 128, 0, st>>>((const float *)query, (const float *)key, B, (int)N1, (int)N2,
+                                                         r2, (int)k, io, total, ql, kl);
       return check_launch("ball_query_split_kernel");
     }
     const int64_t total = B * ((N1 + BQ_THREADS - 1) / BQ_THREADS);

@@ -36,16 +36,15 @@ constexpr int SA_MAX_K = 128;
 constexpr int SA_TE = 64;      // entries per gather sub-tile
 
 struct SaSmem {
-  size_t hits, sidx, gtile, total;
+  size_t sidx, gtile, total;
 };
 
-// Dynamic shared memory: [sidx | union(phase A: key tiles + hit lists, phase B: gather tile)].
+// Dynamic shared memory: [sidx | union(phase A: key tiles, phase B: gather tile)].
 inline SaSmem sa_smem(int C, int K, bool vec) {
   SaSmem s;
   s.sidx = sizeof(int) * SA_Q * (size_t)(K + 1);
   s.sidx = (s.sidx + 15) & ~(size_t)15;
-  const size_t phase_a = sizeof(float4) * 2 * SA_TILE + sizeof(int) * SA_SPLIT * (size_t)K * 32;
-  s.hits = sizeof(float4) * 2 * SA_TILE;
+  const size_t phase_a = sizeof(float4) * 2 * SA_TILE;
   s.gtile = sizeof(float) * (size_t)C * (vec ? SA_TE : SA_TE + 1);
   s.total = s.sidx + (phase_a > s.gtile ? phase_a : s.gtile);
   return s;
@@ -57,18 +56,17 @@ __global__ void __launch_bounds__(SA_THREADS)
 sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ centroids,
                     const float *__restrict__ featT, int64_t B, int C, int N, int M, int pps, int pcs, int cps,
                     int cpc, float r2, int K, int use_xyz, int vec, float *__restrict__ out,
-                    int32_t *__restrict__ index32, int32_t *__restrict__ status, int64_t blocks_total,
-                    unsigned hits_off) {
+                    int32_t *__restrict__ index32, int32_t *__restrict__ status, int64_t blocks_total) {
   constexpr int PER = SA_TILE / SA_THREADS;
   constexpr int QK = SA_TILE / SA_SPLIT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ int hcount[SA_SPLIT][SA_Q];
+  static_assert(QK <= 64, "a slice's hits are kept as a 64-bit mask");
+  __shared__ int tcount[2][SA_SPLIT][SA_Q];
   __shared__ float scent[3][SA_Q];
-  const int S1 = K + 1;  // padded row length of the merged lists
+  const int S1 = K + 1;  // padded row length of the hit lists
   int *sidx = reinterpret_cast<int *>(smem_raw);
   unsigned char *uni = smem_raw + (((size_t)sizeof(int) * SA_Q * S1 + 15) & ~(size_t)15);
   float4 *tile0 = reinterpret_cast<float4 *>(uni);
-  int *hits = reinterpret_cast<int *>(uni + hits_off);  // [SA_SPLIT][K][32]
   float *gtile = reinterpret_cast<float *>(uni);
 
   const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
@@ -98,8 +96,8 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
     const float2 mx[1] = {make_float2(-2.f * qx, -2.f * qx)}, my[1] = {make_float2(-2.f * qy, -2.f * qy)},
                  mz[1] = {make_float2(-2.f * qz, -2.f * qz)};
     float thr[1] = {valid ? sweep_threshold(r2, sweep_qq(qx, qy, qz)) : never};
-    int cnt = 0;
-    int *mine = hits + (part * K) * 32 + lane;
+    int done = 0;                   // hits of this centroid in the tiles swept so far (same in every warp)
+    int *row = sidx + lane * S1;    // its hit list, ascending point index
     const float *rb = points + b * 3 * (int64_t)N;
     const int ntiles = (N + SA_TILE - 1) / SA_TILE;
 
@@ -127,66 +125,60 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
       commit(tile0);
     }
     __syncthreads();
+    // Every warp sweeps its slice of the tile and keeps the hits as a bit mask; the slices' counts
+    // are exchanged at the tile's barrier, after which each thread knows where its hits belong in
+    // the centroid's list (hits of earlier tiles + hits of lower slices) and writes them there:
+    // ascending point order without a merge.  The block leaves the loop at the first barrier after
+    // all its lists are full.
     for (int t = 0; t < ntiles; ++t) {
       const int t0 = t * SA_TILE + part * QK;
       const float4 *tl = tile0 + (t & 1) * SA_TILE + part * QK;
       if (t + 1 < ntiles) fetch((t + 1) * SA_TILE);
+      unsigned long long mask = 0;
+      int cnt = 0;
+      const bool was_full = !valid || done >= K;
 #pragma unroll 2
       for (int u0 = 0; u0 < QK; u0 += 8) {
         float2 a[4];
         if (__builtin_expect(sweep_group2<1, true>(tl + u0, mx, my, mz, thr, a), 0)) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int j = t0 + u0 + u;
             const float av = (u & 1) ? a[u >> 1].y : a[u >> 1].x;
             if (!(av >= thr[0])) {  // padding keys carry +inf; a full row has thr = -inf
               const float4 r = sweep_load_key(tl, u0 + u);
               const float d = sqdist<float>(r.x, r.y, r.z, qx, qy, qz);
               if (d < r2) {
-                mine[cnt * 32] = j;
-                if (++cnt == K) thr[0] = never;
+                mask |= 1ull << (u0 + u);
+                if (done + ++cnt >= K) thr[0] = never;
               }
             }
           }
         }
       }
+      tcount[t & 1][part][lane] = cnt;
       if (t + 1 < ntiles) commit(tile0 + ((t + 1) & 1) * SA_TILE);
-      __syncthreads();
+      if (__syncthreads_and(was_full)) break;
+      int before = 0, total = 0;
+#pragma unroll
+      for (int sp = 0; sp < SA_SPLIT; ++sp) {
+        const int c = tcount[t & 1][sp][lane];
+        if (sp < part) before += c;
+        total += c;
+      }
+      int pos = done + before;
+      while (mask != 0 && pos < K) {
+        const int bit = __ffsll((long long)mask) - 1;
+        mask &= mask - 1;
+        row[pos++] = t0 + bit;
+      }
+      done += total;
+      if (done >= K) thr[0] = never;
     }
-    hcount[part][lane] = cnt;
-    __syncthreads();
-
-    // Merge (warp 0, lane = centroid): heads of the four ascending lists, smallest index first.
-    if (part == 0) {
-      int *row = sidx + lane * S1;
-      int pos[SA_SPLIT], n[SA_SPLIT];
-#pragma unroll
-      for (int s = 0; s < SA_SPLIT; ++s) {
-        pos[s] = 0;
-        n[s] = valid ? hcount[s][lane] : 0;
-      }
-      int o = 0, first = -1;
-      while (o < K) {
-        int best = 0x7fffffff, bs = -1;
-#pragma unroll
-        for (int s = 0; s < SA_SPLIT; ++s) {
-          if (pos[s] < n[s]) {
-            const int h = hits[(s * K + pos[s]) * 32 + lane];
-            if (h < best) {
-              best = h;
-              bs = s;
-            }
-          }
-        }
-        if (bs < 0) break;
-#pragma unroll
-        for (int s = 0; s < SA_SPLIT; ++s)
-          if (s == bs) ++pos[s];
-        if (o == 0) first = best;
-        row[o++] = best;
-      }
-      for (int c = o; c < K; ++c) row[c] = first;
-      if (valid && first < 0 && status) atomicOr(status, 1);
+    __syncthreads();  // the lists' first entries are visible to every warp
+    if (done < K) {   // short lists repeat their first hit; empty ones (and padding lanes) hold -1
+      const int first = valid && done > 0 ? row[0] : -1;
+      for (int c = (valid ? done : 0) + part; c < K; c += SA_SPLIT) row[c] = first;
+      if (part == 0 && valid && done == 0 && status) atomicOr(status, 1);
     }
     __syncthreads();  // lists complete; tiles and hit lists are dead from here on
 
@@ -390,7 +382,7 @@ extern "C" int tk3d_sa_group_fwd(const void *points, const void *centroids, cons
   const int cps = xyz_channel_first ? 1 : 3, cpc = xyz_channel_first ? (int)M : 1;
   sa_group_fwd_kernel<<<(unsigned)(total < cap ? total : cap), SA_THREADS, sm.total, st>>>(
       (const float *)points, (const float *)centroids, featT, B, (int)C, (int)N, (int)M, pps, pcs, cps, cpc, r2,
-      (int)K, use_xyz ? 1 : 0, vec, (float *)out, index32, status, total, (unsigned)sm.hits);
+      (int)K, use_xyz ? 1 : 0, vec, (float *)out, index32, status, total);
   return check_launch("sa_group_fwd_kernel");
 }
 
