@@ -221,6 +221,97 @@ ball_query_split_kernel(const float *__restrict__ query, const float *__restrict
   }
 }
 
+// The same scheme with the plain distance test on every key (float64, whose inputs the packed
+// float32 filter cannot serve): SPLIT warps per 32 queries, hit masks, positional writes.
+template <typename T, int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT)
+ball_query_split_exact_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int N1, int N2, T r2,
+                              int k, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
+  constexpr int THREADS = 32 * SPLIT;
+  constexpr int PER = BS_TILE / THREADS;
+  constexpr int QK = BS_TILE / SPLIT;
+  __shared__ T sx[2][BS_TILE], sy[2][BS_TILE], sz[2][BS_TILE];
+  __shared__ int tcount[2][SPLIT][32];
+  const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
+  const int chunks = (N1 + 31) / 32;
+
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int64_t b = blk / chunks;
+    const int i = (int)(blk % chunks) * 32 + lane;
+    const bool valid = i < N1;
+    T qx = 0, qy = 0, qz = 0;
+    if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
+    const int64_t row = (b * N1 + (valid ? i : 0)) * (int64_t)k;
+    int done = 0;
+    const T *rb = key + b * (int64_t)N2 * 3;
+    const int ntiles = (N2 + BS_TILE - 1) / BS_TILE;
+
+    T nx[PER], ny[PER], nz[PER];
+    auto fetch = [&](int t0) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        const int j = t0 + tid + p * THREADS;
+        nx[p] = ny[p] = nz[p] = 0;
+        if (j < N2) load_xyz(rb, j, kl, nx[p], ny[p], nz[p]);
+      }
+    };
+    auto commit = [&](int buf) {
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        sx[buf][tid + p * THREADS] = nx[p];
+        sy[buf][tid + p * THREADS] = ny[p];
+        sz[buf][tid + p * THREADS] = nz[p];
+      }
+    };
+    fetch(0);
+    commit(0);
+    __syncthreads();
+    for (int t = 0; t < ntiles; ++t) {
+      const int buf = t & 1;
+      const int u_lo = part * QK;
+      const int t0 = t * BS_TILE + u_lo;
+      if (t + 1 < ntiles) fetch((t + 1) * BS_TILE);
+      unsigned long long mask = 0;
+      int cnt = 0;
+      const bool was_full = !valid || done >= k;
+      const int lim = min(QK, N2 - t0);  // may be <= 0 in the last tile
+      if (!was_full) {
+        for (int u = 0; u < lim; ++u) {
+          const T d = sqdist<T>(sx[buf][u_lo + u], sy[buf][u_lo + u], sz[buf][u_lo + u], qx, qy, qz);
+          if (d < r2) {
+            mask |= 1ull << u;
+            if (done + ++cnt >= k) break;
+          }
+        }
+      }
+      tcount[buf][part][lane] = cnt;
+      if (t + 1 < ntiles) commit(buf ^ 1);
+      if (__syncthreads_and(was_full)) break;
+      int before = 0, total = 0;
+#pragma unroll
+      for (int s = 0; s < SPLIT; ++s) {
+        const int c = tcount[buf][s][lane];
+        if (s < part) before += c;
+        total += c;
+      }
+      int pos = done + before;
+      while (mask != 0 && pos < k) {
+        const int bit = __ffsll((long long)mask) - 1;
+        mask &= mask - 1;
+        index.put(row + pos, t0 + bit);
+        ++pos;
+      }
+      done += total;
+    }
+    __syncthreads();
+    if (valid && done < k) {
+      const int64_t first = done > 0 ? index.get(row) : -1;
+      for (int c = done + part; c < k; c += SPLIT) index.put(row + c, first);
+    }
+    __syncthreads();
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 ball_query_generic_kernel(const T *__restrict__ query, const T *__restrict__ key, int64_t B, int64_t N1, int64_t N2,
@@ -298,6 +389,13 @@ static int ball_query_impl(const void *query, const void *key, int64_t B, int64_
     return check_launch("ball_query_fast_kernel");
   }
   const double r = (double)radius;
+  if (B * N1 < (int64_t)sm_count() * 8 * 256) {  // too few queries for one thread each
+    const int64_t tot = B * ((N1 + 31) / 32);
+    const int64_t cap4 = (int64_t)sm_count() * 64;
+    ball_query_split_exact_kernel<double, 4><<<(unsigned)(tot < cap4 ? tot : cap4), 128, 0, st>>>(
+        (const double *)query, (const double *)key, B, (int)N1, (int)N2, r * r, (int)k, io, tot, ql, kl);
+    return check_launch("ball_query_split_exact_kernel");
+  }
   const int64_t total = B * ((N1 + 255) / 256);
   const int64_t cap = (int64_t)sm_count() * 64;
   ball_query_generic_kernel<double><<<(unsigned)(total < cap ? total : cap), 256, 0, st>>>(

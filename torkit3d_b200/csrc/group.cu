@@ -39,7 +39,7 @@ group_fwd_direct_kernel(const T *__restrict__ in, const IndexT *__restrict__ ind
     }
   }
   if (bad && status) atomicOr(status, 1);
-  const bool vec_ok = vec && n == GP_VEC;  // host checked: fp32, E % 4 == 0, 16-byte aligned base
+  const bool vec_ok = vec && n == GP_VEC;  // host checked: E % 4 == 0, 16-byte aligned base
   const T *src = in + (b * C + c0) * N1;
   T *dst = out + (b * C + c0) * E + e0;
 #pragma unroll 4
@@ -51,6 +51,12 @@ group_fwd_direct_kernel(const T *__restrict__ in, const IndexT *__restrict__ ind
       if (vec_ok) {
         // streaming store: the output is never re-read by this kernel
         __stcs(reinterpret_cast<float4 *>(dst), make_float4(val[0], val[1], val[2], val[3]));
+        continue;
+      }
+    } else {
+      if (vec_ok) {  // float64: two 16-byte stores instead of four scalar ones
+        __stcs(reinterpret_cast<double2 *>(dst), make_double2(val[0], val[1]));
+        __stcs(reinterpret_cast<double2 *>(dst) + 1, make_double2(val[2], val[3]));
         continue;
       }
     }
@@ -275,7 +281,7 @@ int group_fwd_t(const T *in, const IndexT *index, int64_t B, int64_t C, int64_t 
   TK3D_REQUIRE(tiles < (1LL << 31) && groups <= 65535 && B <= 65535, TK3D_ERR_SHAPE,
                "group_points: grid too large (B=%lld)", (long long)B);
   dim3 grid((unsigned)tiles, (unsigned)groups, (unsigned)B);
-  const int vec = sizeof(T) == 4 && E % GP_VEC == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const int vec = E % GP_VEC == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   group_fwd_direct_kernel<T, IndexT><<<grid, GP_THREADS, 0, st>>>(in, index, C, N1, E, cpb, out, status, vec);
   return check_launch("group_fwd_direct_kernel");
 }

@@ -264,9 +264,11 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
             if (j >= N2) continue;
             const float4 r = tl[u];
             const float d = sqdist<float>(r.x, r.y, r.z, qx[s], qy[s], qz[s]);
-            if (nk[s] == k && !(d < d_s[(k - 1) * KN_THREADS])) continue;
+            // d orders before e: smaller, or a number against a NaN (NaN distances order last)
+            auto before = [](float x, float e) { return x < e || (e != e && x == x); };
+            if (nk[s] == k && !before(d, d_s[(k - 1) * KN_THREADS])) continue;
             int pos = nk[s] < k ? nk[s] : k - 1;
-            while (pos > 0 && d < d_s[(pos - 1) * KN_THREADS]) {
+            while (pos > 0 && before(d, d_s[(pos - 1) * KN_THREADS])) {
               d_s[pos * KN_THREADS] = d_s[(pos - 1) * KN_THREADS];
               i_s[pos * KN_THREADS] = i_s[(pos - 1) * KN_THREADS];
               --pos;
