@@ -341,9 +341,13 @@ scatter_rows_vec4_kernel(const float *__restrict__ gout, const IndexT *__restric
 
 inline size_t rows_scratch_bytes(int64_t B, int64_t C, int64_t N1) { return (size_t)B * (size_t)C * (size_t)N1 * 4; }
 
-// Worth it when the gathered output is at least twice the feature tensor and C fits a tile.
+// Worth it when the output is at least a quarter of the feature tensor and C fits a tile: the
+// transposition moves the features at the HBM copy rate, the row gather then costs about a seventh
+// of the direct gather per output byte (measured on B200: 0.35 us per MB of features + 0.37 us per
+// MB of output against 2.7 us per MB of output).
 inline bool rows_profitable(int64_t C, int64_t N1, int64_t E, int nsrc) {
-  return C >= 16 && C <= ROWS_MAX_C && N1 > 0 && E * nsrc >= 2 * N1;
+  (void)nsrc;
+  return C >= 16 && C <= ROWS_MAX_C && N1 > 0 && 4 * E >= N1;
 }
 
 // The gather alone, from features that already lie as rows [B,N1,C].

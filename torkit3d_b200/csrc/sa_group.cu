@@ -28,9 +28,7 @@ namespace tk3d {
 
 namespace {
 
-constexpr int SA_THREADS = 128;
 constexpr int SA_TILE = 256;   // points per staged tile
-constexpr int SA_SPLIT = 4;    // warps sharing a tile
 constexpr int SA_Q = 32;       // centroids per block
 constexpr int SA_MAX_K = 128;
 constexpr int SA_TE = 64;      // entries per gather sub-tile
@@ -52,16 +50,19 @@ inline SaSmem sa_smem(int C, int K, bool vec) {
 
 // Point j, coordinate d of cloud b lives at base[b*3*N + j*ps + d*cs]: (ps, cs) = (3, 1) for
 // [B,N,3] and (1, N) for [B,3,N].
-__global__ void __launch_bounds__(SA_THREADS)
+template <int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT)
 sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ centroids,
                     const float *__restrict__ featT, int64_t B, int C, int N, int M, int pps, int pcs, int cps,
                     int cpc, float r2, int K, int use_xyz, int vec, float *__restrict__ out,
                     int32_t *__restrict__ index32, int32_t *__restrict__ status, int64_t blocks_total) {
-  constexpr int PER = SA_TILE / SA_THREADS;
-  constexpr int QK = SA_TILE / SA_SPLIT;
+  constexpr int THREADS = 32 * SPLIT;  // SPLIT warps share every tile of points
+  constexpr int PER = SA_TILE / THREADS;
+  constexpr int QK = SA_TILE / SPLIT;
+  static_assert(PER >= 1, "a tile is staged by one pass of the block");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   static_assert(QK <= 64, "a slice's hits are kept as a 64-bit mask");
-  __shared__ int tcount[2][SA_SPLIT][SA_Q];
+  __shared__ int tcount[2][SPLIT][SA_Q];
   __shared__ float scent[3][SA_Q];
   const int S1 = K + 1;  // padded row length of the hit lists
   int *sidx = reinterpret_cast<int *>(smem_raw);
@@ -106,7 +107,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
     auto fetch = [&](int t0) {
 #pragma unroll
       for (int p = 0; p < PER; ++p) {
-        const int j = t0 + tid + p * SA_THREADS;
+        const int j = t0 + tid + p * THREADS;
         float4 v = make_float4(0.f, 0.f, 0.f, __int_as_float(0x7f800000));
         if (j < N) {
           const float *r = rb + (int64_t)j * pps;
@@ -118,7 +119,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
     };
     auto commit = [&](float4 *dst) {
 #pragma unroll
-      for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * SA_THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
+      for (int p = 0; p < PER; ++p) sweep_store_key(dst, tid + p * THREADS, nxt[p].x, nxt[p].y, nxt[p].z, nxt[p].w);
     };
     if (ntiles > 0) {
       fetch(0);
@@ -160,7 +161,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
       if (__syncthreads_and(was_full)) break;
       int before = 0, total = 0;
 #pragma unroll
-      for (int sp = 0; sp < SA_SPLIT; ++sp) {
+      for (int sp = 0; sp < SPLIT; ++sp) {
         const int c = tcount[t & 1][sp][lane];
         if (sp < part) before += c;
         total += c;
@@ -177,7 +178,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
     __syncthreads();  // the lists' first entries are visible to every warp
     if (done < K) {   // short lists repeat their first hit; empty ones (and padding lanes) hold -1
       const int first = valid && done > 0 ? row[0] : -1;
-      for (int c = (valid ? done : 0) + part; c < K; c += SA_SPLIT) row[c] = first;
+      for (int c = (valid ? done : 0) + part; c < K; c += SPLIT) row[c] = first;
       if (part == 0 && valid && done == 0 && status) atomicOr(status, 1);
     }
     __syncthreads();  // lists complete; tiles and hit lists are dead from here on
@@ -188,11 +189,11 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
     float *ob = out + b * ctot * E + e_blk;
     if (index32) {
       int32_t *ip = index32 + b * E + e_blk;
-      for (int e = tid; e < ne; e += SA_THREADS) ip[e] = sidx[(e / K) * S1 + (e % K)];
+      for (int e = tid; e < ne; e += THREADS) ip[e] = sidx[(e / K) * S1 + (e % K)];
     }
     if (use_xyz) {
       float *ox = ob + (int64_t)C * E;
-      for (int e = tid; e < ne; e += SA_THREADS) {
+      for (int e = tid; e < ne; e += THREADS) {
         const int c = e / K;
         const int id = sidx[c * S1 + (e - c * K)];
         float x = 0.f, y = 0.f, z = 0.f;
@@ -219,7 +220,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
           // (entry group, block of eight row pieces) are taken four at a time to keep four loads
           // in flight per lane.
           const int ql = lane & 7, el = lane >> 3;
-          constexpr int NW = SA_THREADS / 32;
+          constexpr int NW = THREADS / 32;
           const int QB = (L + 7) >> 3;
           const int ng = n >> 2;
           const int steps = ng > part ? ((ng - part + NW - 1) / NW) * QB : 0;
@@ -256,7 +257,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
           }
           __syncthreads();
           const int nchunks = n >> 2;
-          for (int u = tid; u < C * (SA_TE / 4); u += SA_THREADS) {
+          for (int u = tid; u < C * (SA_TE / 4); u += THREADS) {
             const int c = u >> 4, ch = u & 15;
             if (ch < nchunks) {
               const float4 v = *reinterpret_cast<const float4 *>(gtile + c * SA_TE + (((ch ^ (c >> 2)) & 15) << 2));
@@ -265,7 +266,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
           }
         } else {
           constexpr int S = SA_TE + 1;
-          for (int e = part; e < n; e += SA_THREADS / 32) {
+          for (int e = part; e < n; e += THREADS / 32) {
             const int g = s0 + e;
             const int c0 = g / K;
             const int id = sidx[c0 * S1 + (g - c0 * K)];
@@ -273,7 +274,7 @@ sa_group_fwd_kernel(const float *__restrict__ points, const float *__restrict__ 
             for (int c = lane; c < C; c += 32) gtile[c * S + e] = id < 0 ? 0.f : __ldg(row + c);
           }
           __syncthreads();
-          for (int c = part; c < C; c += SA_THREADS / 32)
+          for (int c = part; c < C; c += THREADS / 32)
             for (int e = lane; e < n; e += 32) __stcs(ob + (int64_t)c * E + s0 + e, gtile[c * S + e]);
         }
         __syncthreads();
@@ -373,16 +374,24 @@ extern "C" int tk3d_sa_group_fwd(const void *points, const void *centroids, cons
   const int vec = C > 0 && C % 4 == 0 && K % 4 == 0 &&
                   ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15) == 0;
   const SaSmem sm = sa_smem((int)C, (int)K, vec);
-  if (sm.total > 48 * 1024)
-    TK3D_CUDA(raise_smem_limit((const void *)sa_group_fwd_kernel, (int)sm.total));
   const int64_t total = B * ((M + SA_Q - 1) / SA_Q);
+  const bool wide = total <= 2 * (int64_t)sm_count();  // few blocks: eight warps per 32 centroids
+  if (sm.total > 48 * 1024)
+    TK3D_CUDA(raise_smem_limit(wide ? (const void *)sa_group_fwd_kernel<8> : (const void *)sa_group_fwd_kernel<4>,
+                               (int)sm.total));
   const int64_t cap = (int64_t)sm_count() * 64;
   const float r2 = radius * radius;
   const int pps = xyz_channel_first ? 1 : 3, pcs = xyz_channel_first ? (int)N : 1;
   const int cps = xyz_channel_first ? 1 : 3, cpc = xyz_channel_first ? (int)M : 1;
-  sa_group_fwd_kernel<<<(unsigned)(total < cap ? total : cap), SA_THREADS, sm.total, st>>>(
-      (const float *)points, (const float *)centroids, featT, B, (int)C, (int)N, (int)M, pps, pcs, cps, cpc, r2,
-      (int)K, use_xyz ? 1 : 0, vec, (float *)out, index32, status, total);
+  const unsigned grid = (unsigned)(total < cap ? total : cap);
+  if (wide)
+    sa_group_fwd_kernel<8><<<grid, 256, sm.total, st>>>(
+        (const float *)points, (const float *)centroids, featT, B, (int)C, (int)N, (int)M, pps, pcs, cps, cpc, r2,
+        (int)K, use_xyz ? 1 : 0, vec, (float *)out, index32, status, total);
+  else
+    sa_group_fwd_kernel<4><<<grid, 128, sm.total, st>>>(
+        (const float *)points, (const float *)centroids, featT, B, (int)C, (int)N, (int)M, pps, pcs, cps, cpc, r2,
+        (int)K, use_xyz ? 1 : 0, vec, (float *)out, index32, status, total);
   return check_launch("sa_group_fwd_kernel");
 }
 
