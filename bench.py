@@ -521,6 +521,7 @@ def run_b200(args, rank, world, local_rank):
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
 
     pf = HostCloudPrefetcher(dev)
+    step_ws = {}  # output tensors of the step, reused from step to step
 
     def e2e_run(steps):
         # every step's clouds come from pinned host memory; the copy of step i+1 is enqueued on a
@@ -529,9 +530,9 @@ def run_b200(args, rank, world, local_rank):
         pf.prefetch(x1h, x2h)
         for i in range(steps):
             a, b = pf.get()
+            loss, _, _ = chamfer_step(a, b, global_batch=C4["B"], workspace=step_ws)
             if i + 1 < steps:
-                pf.prefetch(x1h, x2h)
-            loss, _, _ = chamfer_step(a, b, global_batch=C4["B"])
+                pf.prefetch(x1h, x2h)  # behind this step's launches; its copy still overlaps them
             loss_host.copy_(loss, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         return float(loss_host)

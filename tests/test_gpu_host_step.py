@@ -57,6 +57,30 @@ def test_prefetcher_double_buffer():
         pf.get()
 
 
+def test_prefetcher_prefetch_behind_the_step_and_workspace():
+    """The next batch may be requested after the current step's kernels were launched (its copy must
+    not overwrite what they still read), and a workspace makes chamfer_step reuse its tensors."""
+    from torkit3d_b200.dist import chamfer_step
+
+    pf = HostCloudPrefetcher(DEV)
+    batches = [workloads.c4_chamfer_large(B=4, N=3000, M=2500, seed=30 + i) for i in range(6)]
+    pinned = [(a.pin_memory(), b.pin_memory()) for a, b in batches]
+    ws = {}
+    losses, ptrs = [], set()
+    pf.prefetch(*pinned[0])
+    for i in range(6):
+        a, b = pf.get()
+        loss, ga, _ = chamfer_step(a, b, workspace=ws)
+        if i + 1 < 6:
+            pf.prefetch(*pinned[i + 1])
+        losses.append(float(loss))          # reads the result before the next call overwrites it
+        ptrs.add(ga.data_ptr())
+    assert len(ptrs) == 1 and len(ws) == 1   # one set of tensors, reused
+    for i in range(6):
+        ref, _, _ = chamfer_step(batches[i][0].to(DEV), batches[i][1].to(DEV))
+        assert abs(losses[i] - float(ref)) <= 1e-6 * abs(float(ref))
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.float64])
 def test_chamfer_step_matches_autograd(dt):
     """dist.chamfer_step (loss + gradients in one call, no autograd graph) against chamfer_loss + backward."""

@@ -138,7 +138,7 @@ def _one(device, dtype):
 
 
 # ---- training step without autograd ---------------------------------------------------------------
-def chamfer_step(xyz1, xyz2, global_batch=None, group=None):
+def chamfer_step(xyz1, xyz2, global_batch=None, group=None, workspace=None):
     """Mean chamfer loss over a batch sharded across ranks AND its gradients, in one call.
 
     The loss is linear in the per-point distances, so the gradient kernels need only the counts,
@@ -150,6 +150,10 @@ def chamfer_step(xyz1, xyz2, global_batch=None, group=None):
     Args:
         xyz1: [B_local, N1, 3] float32/float64 CUDA tensor, this rank's clouds;  xyz2: [B_local, N2, 3].
         global_batch, group: as for ``chamfer_loss``.
+        workspace: optional dict owned by the caller.  The outputs and intermediate tensors of the
+            step are then kept in it and reused by the next call with the same shapes (ten fewer
+            allocations per step, which matters when a step takes less than a millisecond); the
+            tensors returned by one call are overwritten by the next call with that workspace.
 
     Returns:
         (loss, grad_xyz1, grad_xyz2): the global mean loss (0-dim, identical on every rank) and
@@ -167,13 +171,16 @@ def chamfer_step(xyz1, xyz2, global_batch=None, group=None):
     dev, dt = a.device, _dtype(a)
     with _on(dev):
         st = _stream(a)
-        d1 = torch.empty((B, n1), dtype=a.dtype, device=dev)
-        d2 = torch.empty((B, n2), dtype=a.dtype, device=dev)
-        i1 = torch.empty((B, n1), dtype=torch.int64, device=dev)
-        i2 = torch.empty((B, n2), dtype=torch.int64, device=dev)
-        ga, gb = torch.empty_like(a), torch.empty_like(b)
-        sums = torch.empty(2, dtype=torch.float64, device=dev)
-        loss = torch.empty((), dtype=a.dtype, device=dev)
+        key = (B, n1, n2, a.dtype, dev)
+        bufs = workspace.get(key) if workspace is not None else None
+        if bufs is None:
+            bufs = (torch.empty((B, n1), dtype=a.dtype, device=dev), torch.empty((B, n2), dtype=a.dtype, device=dev),
+                    torch.empty((B, n1), dtype=torch.int64, device=dev),
+                    torch.empty((B, n2), dtype=torch.int64, device=dev), torch.empty_like(a), torch.empty_like(b),
+                    torch.empty(2, dtype=torch.float64, device=dev), torch.empty((), dtype=a.dtype, device=dev))
+            if workspace is not None:
+                workspace[key] = bufs
+        d1, d2, i1, i2, ga, gb, sums, loss = bufs
         one = _one(dev, a.dtype)
         _lib.check(lib.tk3d_chamfer_fwd(_ptr(a), _ptr(b), B, n1, n2, _ptr(d1), _ptr(i1), _ptr(d2), _ptr(i2),
                                         _ptr(sums), dt, st))
@@ -286,14 +293,16 @@ class HostCloudPrefetcher:
     ``prefetch(h1, h2)`` enqueues the copies of one batch (pinned float32 CPU tensors [B,N,3]) into
     the free buffer pair; ``get()`` returns the device tensors of the oldest prefetched batch after
     making the current stream wait for its copy.  At most two batches are in flight; a buffer pair
-    is reused only after everything enqueued on the compute stream before the ``prefetch`` call has
-    finished reading it.
+    is reused only after the work that was on the compute stream when the FOLLOWING batch was
+    fetched (the kernels that read the pair) has finished, so ``prefetch`` may be called before or
+    after the current step's kernels are launched and its copy overlaps them either way.
     """
 
     def __init__(self, device):
         self.device = torch.device(device)
         self._slots = [None, None]
         self._events = [None, None]
+        self._release = [None, None]  # per buffer pair: recorded when the other pair was fetched
         self._queue = []
         self._next = 0
 
@@ -312,7 +321,9 @@ class HostCloudPrefetcher:
                 for t in bufs:
                     t.record_stream(copy)
                 self._slots[slot] = bufs
-            copy.wait_stream(compute)  # earlier readers of this buffer pair are done
+                copy.wait_stream(compute)  # fresh memory may have belonged to work still queued there
+            elif self._release[slot] is not None:
+                copy.wait_event(self._release[slot])  # the readers of this buffer pair are done
             with torch.cuda.stream(copy):
                 bufs[0].copy_(h1, non_blocking=True)
                 bufs[1].copy_(h2, non_blocking=True)
@@ -325,5 +336,10 @@ class HostCloudPrefetcher:
         if not self._queue:
             raise RuntimeError("HostCloudPrefetcher: nothing was prefetched")
         slot = self._queue.pop(0)
-        torch.cuda.current_stream(self.device).wait_event(self._events[slot])
+        compute = torch.cuda.current_stream(self.device)
+        # whatever read the other buffer pair has been enqueued by now
+        released = torch.cuda.Event()
+        released.record(compute)
+        self._release[slot ^ 1] = released
+        compute.wait_event(self._events[slot])
         return self._slots[slot]
