@@ -55,9 +55,9 @@ edge_rows_vec4_kernel(const float *__restrict__ keyT, const float *__restrict__ 
   float *ob = out + b * ctot * E + e0;
   const float *qb = qfeat + b * C * N1;
   for (int u = tid; u < C * (ROWS_TE / 4); u += ROWS_THREADS) {
-    const int c = u >> 4, ch = u & 15;
+    const int c = u / ROWS_CH, ch = u % ROWS_CH;
     if (ch < nchunks) {
-      float4 v = *reinterpret_cast<const float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & 15) << 2));
+      float4 v = *reinterpret_cast<const float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & (ROWS_CH - 1)) << 2));
       // query point of each of the four entries: one 32-bit division, then a carry chain
       const unsigned eg = (unsigned)(e0 + 4 * ch);
       unsigned nq = eg / (unsigned)K;

@@ -12,9 +12,10 @@
 
 namespace tk3d {
 
-constexpr int ROWS_TE = 64;        // entries (index positions) per block
-constexpr int ROWS_THREADS = 256;  // 8 warps
+constexpr int ROWS_TE = 32;        // entries (index positions) per block
+constexpr int ROWS_THREADS = 128;  // 4 warps
 constexpr int ROWS_MAX_C = 512;
+constexpr int ROWS_CH = ROWS_TE / 4;   // 16-byte chunks (four entries) per tile row
 constexpr int ROWS_GPW = ROWS_TE / 4 / (ROWS_THREADS / 32);  // entry groups (of four) per warp
 
 // in [B][C][N] -> out [B][N][C]
@@ -192,7 +193,7 @@ __device__ __forceinline__ void rows_load_index(const IndexT *__restrict__ index
 }
 
 template <int NSRC, typename IndexT = int64_t>
-__global__ void __launch_bounds__(ROWS_THREADS)
+__global__ void __launch_bounds__(ROWS_THREADS, 10)
 gather_rows_vec4_kernel(const float *__restrict__ featT, const IndexT *__restrict__ index,
                         const float *__restrict__ weight, int C, int64_t N1, int64_t E, float *__restrict__ out,
                         int32_t *__restrict__ status) {
@@ -227,7 +228,7 @@ gather_rows_vec4_kernel(const float *__restrict__ featT, const IndexT *__restric
       row[i] = fb + (int64_t)(id[i] < 0 ? 0 : id[i]) * L;
       if (id[i] < 0) w[i] = 0.f;
     }
-#pragma unroll 4
+#pragma unroll 2
     for (int q = ql; q < L; q += 8) {
       float4 v;
       if (NSRC == 1) {
@@ -263,9 +264,9 @@ gather_rows_vec4_kernel(const float *__restrict__ featT, const IndexT *__restric
   const int nchunks = n >> 2;
   float *ob = out + b * C * E + e0;
   for (int u = tid; u < C * (ROWS_TE / 4); u += ROWS_THREADS) {
-    const int c = u >> 4, ch = u & 15;
+    const int c = u / ROWS_CH, ch = u % ROWS_CH;
     if (ch < nchunks) {
-      const float4 v = *reinterpret_cast<const float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & 15) << 2));
+      const float4 v = *reinterpret_cast<const float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & (ROWS_CH - 1)) << 2));
       __stcs(reinterpret_cast<float4 *>(ob + (int64_t)c * E + 4 * ch), v);
     }
   }
@@ -300,10 +301,10 @@ scatter_rows_vec4_kernel(const float *__restrict__ gout, const IndexT *__restric
   const int nchunks = n >> 2;
   const float *gb = gout + b * gstride + e0;
   for (int u = tid; u < C * (ROWS_TE / 4); u += ROWS_THREADS) {
-    const int c = u >> 4, ch = u & 15;
+    const int c = u / ROWS_CH, ch = u % ROWS_CH;
     if (ch < nchunks) {
       const float4 v = __ldcs(reinterpret_cast<const float4 *>(gb + (int64_t)c * E + 4 * ch));
-      *reinterpret_cast<float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & 15) << 2)) = v;
+      *reinterpret_cast<float4 *>(tile + c * ROWS_TE + (((ch ^ (c >> 2)) & (ROWS_CH - 1)) << 2)) = v;
     }
   }
   // indices and weights of this warp's two entry groups, requested before the barrier
