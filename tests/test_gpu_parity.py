@@ -203,7 +203,10 @@ KNN_CASES = [(1, 1, 1, 1), (2, 33, 64, 1), (2, 100, 300, 3), (3, 511, 1025, 31),
              (1, 64, 300, 200), (2, 50, 16, 16), (40, 600, 700, 16), (40, 600, 700, 3),
              # two-pass variants with 64 / 128 / 256 key classes (need N2 >= 32 k)
              (2, 300, 2100, 20), (2, 300, 2100, 32), (2, 257, 2200, 64), (1, 100, 3300, 65), (1, 200, 4200, 100),
-             (1, 130, 4100, 128)]
+             (1, 130, 4100, 128),
+             # radix selection: k > 80, or k > 40 on small key clouds; k up to 256, N2 == k
+             (2, 70, 5000, 81), (2, 300, 300, 64), (2, 100, 256, 256), (3, 65, 1500, 256), (1, 33, 700, 41),
+             (1, 40, 20000, 150)]
 
 
 @pytest.mark.parametrize("B,n1,n2,k", KNN_CASES)
@@ -235,7 +238,7 @@ def test_knn_large_k_with_massive_ties(oracle, k):
     np.testing.assert_array_equal(N(d), e)
 
 
-@pytest.mark.parametrize("k", [1, 3, 4, 8, 16, 50, 150])
+@pytest.mark.parametrize("k", [1, 3, 4, 8, 16, 50, 150, 256])
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_knn_ties(oracle, k, dtype):
     from torkit3d_b200.ops import knn_points
@@ -252,7 +255,8 @@ def test_knn_ties(oracle, k, dtype):
                                            (300, 1200, 16, np.float32),    # two-pass candidate lists
                                            (300, 2100, 64, np.float32),
                                            (300, 100, 16, np.float32),     # buffered lists
-                                           (64, 600, 200, np.float32),     # heap in the output row
+                                           (64, 600, 200, np.float32),     # radix selection
+                                           (64, 600, 300, np.float32),     # heap in the output row
                                            (300, 600, 8, np.float64),      # key-split heaps
                                            (64, 400, 100, np.float64)])
 def test_knn_keys_with_nan_coordinates_order_last(oracle, n1, n2, k, dtype):

@@ -1042,6 +1042,10 @@ int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t 
 }  // namespace tk3d
 
 namespace tk3d {
+// Radix selection (knn_select.cu): float32, k <= 256.
+int knn_select_f32(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, IndexOut index,
+                   XyzLayout ql, XyzLayout kl, cudaStream_t st);
+
 bool knn_split_f64(const double *query, const double *key, int64_t B, int64_t N1, int64_t N2, int64_t k, double *dist,
                    IndexOut index, XyzLayout ql, XyzLayout kl, cudaStream_t st, int *rc);
 }
@@ -1080,7 +1084,12 @@ static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, i
   }
   // Two-pass selection needs at least two key classes per wanted neighbour to be tight (the class
   // counts below) and a few keys in every class: N2 >= 4 k, at least 256 (512 for k > 64).
-  if (k <= 128 && N2 >= 4 * k && N2 >= (k > 64 ? 512 : 256)) {
+  // Measured on B200 (16 x 4096 x 4096): the two-pass kernel 0.74 ms at k = 64, 2.04 at 100, 2.52 at
+  // 128; radix selection (knn_select.cu) 1.41 / 1.51 / 1.54 ms, nearly flat in k.
+  // With fewer than 16 keys per wanted neighbour the class minima stop bounding anything for
+  // k > 40 (16 x 4096 x 300, k = 64: 0.47 ms two-pass, 0.26 ms by radix).
+  const bool by_radix = (k > 80 || (k > 40 && N2 < 16 * k)) && k <= 256 && N2 < (1LL << 31);
+  if (!by_radix && k <= 128 && N2 >= 4 * k && N2 >= (k > 64 ? 512 : 256)) {
     if (k <= 16) {
       if (B * N1 >= (int64_t)sm_count() * 4 * 64)
         return knn_twopass<2, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
@@ -1090,12 +1099,16 @@ static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, i
     if (k <= 64) return knn_twopass<1, 128, 192, 4>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
     return knn_twopass<1, 256, 384, 2, 512>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
   }
-  if (k <= 128) {
+  // key clouds too small for the two-pass kernel: buffered lists up to k = 40 (16 x 4096 x 300:
+  // 0.069 ms at k = 16 against 0.195 by radix, 0.47 against 0.26 at k = 64)
+  if (k <= 40) {
     const int64_t sms = sm_count();
     if (k <= 32 && B * N1 >= sms * 2 * KN_THREADS * 2)
       return knn_buffered<2>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
     return knn_buffered<1>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
   }
+  if (k <= 256 && N2 < (1LL << 31))  // large k: selection by radix, no insertions
+    return knn_select_f32(q, r, B, (int)N1, (int)N2, (int)k, d, io.index, io.ql, io.kl, st);
   return knn_generic<float>(q, r, B, N1, N2, k, d, io, st);
 }
 

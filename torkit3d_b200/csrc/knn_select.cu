@@ -1,0 +1,234 @@
+// Brute-force KNN for large k (float32, 32 < k <= 256): selection by radix instead of by insertion.
+//
+// Keeping the k best of a query in a list or heap costs an insertion per accepted key, and with one
+// query per lane every insertion stalls the other 31 lanes of its warp: for k = 200 on 4096 keys the
+// heap kernel spends nearly all of its time there.  Here nothing data dependent happens inside the
+// key sweeps.  A block of four warps serves 32 queries (lane = query; every warp sweeps a quarter of
+// each 256-key tile) and finds the k-th smallest distance of each query EXACTLY by a most-significant-
+// digit radix selection on the bit pattern of the distance (non-negative floats order like their
+// bits): four sweeps, one per byte, each counting the keys whose higher bytes equal the digits found
+// so far into a 256-bin histogram per query in shared memory ([bin][lane]: a lane only ever touches
+// its own bank).  A fifth sweep collects the keys below that distance (in any order) and, by the
+// position scheme of the ball query (hits of a slice as a bit mask, counts exchanged at the tile
+// barrier), the first keys in index order AT that distance, exactly k in all; a bitonic network
+// over (distance bits, index) as one 64-bit word, run by the four warps together on the lists in
+// shared memory, puts them in the (distance, index) order every other path emits.
+//
+// Five sweeps of the plain distance (8 FP32 instructions per pair) are far from the FP32 roofline,
+// but they cost the same for every k, every key order and every tie pattern: 4 x 4096 x 4096 with
+// k = 200 takes a fraction of a millisecond where the heap kernel took 10.8 ms (the reference's
+// bounded-set kernel, torkit3d/csrc/cuda/knn_distance_kernel.cu:102-177 with
+// torkit3d/csrc/include/mink.cuh:61-89, 8.6 ms).  A NaN distance (a NaN coordinate) is given the
+// canonical NaN pattern, which is above +inf as an integer, so such keys order last, by index.
+#include <limits.h>
+
+#include "tk3d_common.cuh"
+
+namespace tk3d {
+namespace {
+
+constexpr int SEL_THREADS = 128;
+constexpr int SEL_SPLIT = SEL_THREADS / 32;
+constexpr int SEL_TILE = 256;
+constexpr int SEL_QK = SEL_TILE / SEL_SPLIT;  // keys per warp per tile: one 64-bit mask
+constexpr int SEL_BINS = 256;
+
+__device__ __forceinline__ unsigned sel_bits(float d) {
+  return d == d ? __float_as_uint(d) : 0x7fc00000u;  // d >= +0 or NaN
+}
+
+// smem: [hist 256 x 32 ints | list n2 x 32 u64] (the list aliases the histogram) + tiles
+__global__ void __launch_bounds__(SEL_THREADS)
+knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k, int n2,
+                  float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
+  extern __shared__ __align__(16) unsigned char sel_smem[];
+  int *hist = reinterpret_cast<int *>(sel_smem);                                // [256][32]
+  unsigned long long *list = reinterpret_cast<unsigned long long *>(sel_smem);  // [n2][32], after the histograms
+  __shared__ float4 tile[2][SEL_TILE];
+  __shared__ int tcount[2][SEL_SPLIT][32];
+  __shared__ int psum[SEL_SPLIT][32];
+  __shared__ int cless[32];
+  const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
+  const int chunks = (N1 + 31) / 32;
+  const int ntiles = (N2 + SEL_TILE - 1) / SEL_TILE;
+
+  for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
+    const int64_t b = blk / chunks;
+    const int i = (int)(blk % chunks) * 32 + lane;
+    const bool valid = i < N1;
+    float qx = 0.f, qy = 0.f, qz = 0.f;
+    if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
+    const float *rb = key + b * (int64_t)N2 * 3;
+
+    // One sweep over the keys: tiles are staged by the whole block (next tile fetched into
+    // registers while the current one is used), `body(u, j, bits)` sees every key of this warp's
+    // slices: position in the slice, index in the cloud, bit pattern of its distance.
+    auto sweep = [&](auto &&body, auto &&tile_end) {
+      float4 nxt[SEL_TILE / SEL_THREADS];
+      auto fetch = [&](int t0) {
+#pragma unroll
+        for (int p = 0; p < SEL_TILE / SEL_THREADS; ++p) {
+          const int j = t0 + tid + p * SEL_THREADS;
+          float x = 0.f, y = 0.f, z = 0.f;
+          if (j < N2) load_xyz(rb, j, kl, x, y, z);
+          nxt[p] = make_float4(x, y, z, 0.f);
+        }
+      };
+      auto commit = [&](float4 *dst) {
+#pragma unroll
+        for (int p = 0; p < SEL_TILE / SEL_THREADS; ++p) dst[tid + p * SEL_THREADS] = nxt[p];
+      };
+      fetch(0);
+      commit(tile[0]);
+      __syncthreads();
+      for (int t = 0; t < ntiles; ++t) {
+        const int t0 = t * SEL_TILE + part * SEL_QK;
+        const float4 *tl = tile[t & 1] + part * SEL_QK;
+        if (t + 1 < ntiles) fetch((t + 1) * SEL_TILE);
+        const int lim = min(SEL_QK, N2 - t0);  // <= 0 for slices beyond the cloud
+#pragma unroll 4
+        for (int u = 0; u < lim; ++u) {
+          const float4 r = tl[u];
+          body(u, t0 + u, sel_bits(sqdist<float>(r.x, r.y, r.z, qx, qy, qz)));
+        }
+        if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
+        tile_end(t, t0);
+      }
+    };
+
+    // ---- the k-th smallest distance, one byte per sweep
+    unsigned prefix = 0;  // digits found so far (the high bytes of the k-th distance)
+    int krem = k;         // rank of the k-th distance among the keys that share those digits
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int e = tid; e < SEL_BINS * 32; e += SEL_THREADS) hist[e] = 0;
+      __syncthreads();
+      sweep(
+          [&](int, int, unsigned bits) {
+            const bool match = pass == 0 || (bits >> (shift + 8)) == prefix;
+            if (match) atomicAdd(&hist[((bits >> shift) & 255u) * 32 + lane], 1);
+          },
+          [&](int, int) { __syncthreads(); });
+      // which bin holds the krem-th key: every warp adds up a quarter of the bins, then all warps
+      // walk the quarter that holds it (the same result in every warp, lane = query)
+      int s = 0;
+      for (int bin = part * 64; bin < part * 64 + 64; ++bin) s += hist[bin * 32 + lane];
+      psum[part][lane] = s;
+      __syncthreads();
+      int before = 0, quarter = 0;
+#pragma unroll
+      for (int w = 0; w < SEL_SPLIT; ++w) {
+        const int c = psum[w][lane];
+        if (quarter == w && before + c < krem && w + 1 < SEL_SPLIT) {
+          before += c;
+          quarter = w + 1;
+        }
+      }
+      int bin = quarter * 64;
+      for (int step = 0; step < 63; ++step) {
+        const int c = hist[bin * 32 + lane];
+        if (before + c >= krem) break;
+        before += c;
+        ++bin;
+      }
+      prefix = (prefix << 8) | (unsigned)bin;
+      krem -= before;
+      __syncthreads();  // the histogram is cleared (or reused as the list) next
+    }
+    const unsigned kth = prefix;  // bit pattern of the k-th smallest distance
+    const int need_eq = krem;     // keys AT that distance that belong to the result (>= 1)
+    const int nless = k - need_eq;
+
+    // ---- collect: everything below kth, and the first need_eq keys (by index) at kth
+    if (part == 0) cless[lane] = 0;
+    for (int e = k * 32 + tid; e < n2 * 32; e += SEL_THREADS) list[e] = ~0ull;  // padding sorts last
+    __syncthreads();
+    unsigned long long mask = 0;
+    int cnt = 0, eq_done = 0;
+    sweep(
+        [&](int u, int j, unsigned bits) {
+          if (bits < kth) {
+            const int slot = atomicAdd(&cless[lane], 1);  // exactly nless keys take this branch
+            list[slot * 32 + lane] = ((unsigned long long)bits << 32) | (unsigned)j;
+          }
+          if (bits == kth) {
+            mask |= 1ull << u;
+            ++cnt;
+          }
+        },
+        [&](int t, int t0) {
+          tcount[t & 1][part][lane] = cnt;
+          __syncthreads();
+          int before = 0, total = 0;
+#pragma unroll
+          for (int w = 0; w < SEL_SPLIT; ++w) {
+            const int c = tcount[t & 1][w][lane];
+            if (w < part) before += c;
+            total += c;
+          }
+          int pos = eq_done + before;
+          while (mask != 0 && pos < need_eq) {
+            const int bit = __ffsll((long long)mask) - 1;
+            mask &= mask - 1;
+            list[(nless + pos) * 32 + lane] = ((unsigned long long)kth << 32) | (unsigned)(t0 + bit);
+            ++pos;
+          }
+          eq_done += total;
+          mask = 0;
+          cnt = 0;
+        });
+    __syncthreads();
+
+    // ---- sort the n2 (k rounded up to a power of two, padded with all-ones) entries of every list
+    // by (distance bits, index): the pairs of each compare-exchange step are dealt to the four warps
+    for (int size = 2; size <= n2; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int p = part; p < (n2 >> 1); p += SEL_SPLIT) {
+          const int lo = ((p & ~(stride - 1)) << 1) | (p & (stride - 1));
+          const int hi = lo | stride;
+          const bool up = (lo & size) == 0;
+          const unsigned long long a = list[lo * 32 + lane], c = list[hi * 32 + lane];
+          if ((a > c) == up) {
+            list[lo * 32 + lane] = c;
+            list[hi * 32 + lane] = a;
+          }
+        }
+        __syncthreads();
+      }
+    }
+    if (valid) {
+      const int64_t row = (b * N1 + i) * (int64_t)k;
+      for (int sl = part; sl < k; sl += SEL_SPLIT) {
+        const unsigned long long e = list[sl * 32 + lane];
+        dist[row + sl] = __uint_as_float((unsigned)(e >> 32));
+        index.put(row + sl, (int64_t)(unsigned)(e & 0xffffffffu));
+      }
+    }
+    __syncthreads();  // the lists become histograms again
+  }
+}
+
+size_t select_smem(int n2) {
+  const size_t h = (size_t)SEL_BINS * 32 * sizeof(int), l = (size_t)n2 * 32 * sizeof(unsigned long long);
+  return h > l ? h : l;
+}
+
+}  // namespace
+
+// k-nearest keys by radix selection; the caller has checked 1 <= k <= 256, k <= N2 < 2^31.
+int knn_select_f32(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, IndexOut index,
+                   XyzLayout ql, XyzLayout kl, cudaStream_t st) {
+  int n2 = 2;
+  while (n2 < k) n2 <<= 1;
+  const size_t smem = select_smem(n2);
+  if (smem + 12 * 1024 > 48 * 1024) TK3D_CUDA(raise_smem_limit((const void *)knn_select_kernel, (int)smem));
+  const int64_t total = B * ((N1 + 31) / 32);
+  const int64_t cap = (int64_t)sm_count() * 32;
+  knn_select_kernel<<<(unsigned)(total < cap ? total : cap), SEL_THREADS, smem, st>>>(query, key, B, N1, N2, k, n2, dist,
+                                                                                    index, total, ql, kl);
+  return check_launch("knn_select_kernel");
+}
+
+}  // namespace tk3d
+
+TK3D_BOUNDS_TU(knn_select)
