@@ -1,13 +1,15 @@
 // Brute-force k nearest neighbours (squared distances, rows sorted ascending by (distance, index)).
 //
-// Four kernels:
+// Four kernels here, two more in files of their own (knn_select.cu: float32 with 64 < k <= 256, or
+// 40 < k with fewer than 16 keys per wanted neighbour, by radix selection; knn_split.cu: float64
+// with few queries):
 //   knn_small_kernel<K,Q>  fp32, k <= 4: per-thread top-K in registers, filter-then-verify sweep
 //                          (sweep.cuh), insertion straight from the verify branch.  With k << N2
 //                          the branch is rare (about k ln(N2/k) times per query).
-//   knn_twopass_kernel     fp32, 4 < k <= 128 (and N2 >= 4 k, at least 256): pass 1 bounds the k-th distance from
+//   knn_twopass_kernel     fp32, 4 < k <= 64 (and N2 >= 4 k, at least 256): pass 1 bounds the k-th distance from
 //                          class minima of the filter value, pass 2 collects the few candidates
 //                          below the bound, exact selection among them (see the kernel's header).
-//   knn_buffered_kernel<Q> fp32, other k <= 128 (small key clouds): same filter, but passing keys are only appended
+//   knn_buffered_kernel<Q> fp32, other k <= 40 (small key clouds): same filter, but passing keys are only appended
 //                          (predicated store, no branch) to a small per-query candidate buffer in
 //                          shared memory; buffers are drained into per-query sorted lists (also in
 //                          shared memory) by the whole warp at once, when any lane's buffer is
@@ -1085,10 +1087,10 @@ static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, i
   // Two-pass selection needs at least two key classes per wanted neighbour to be tight (the class
   // counts below) and a few keys in every class: N2 >= 4 k, at least 256 (512 for k > 64).
   // Measured on B200 (16 x 4096 x 4096): the two-pass kernel 0.74 ms at k = 64, 2.04 at 100, 2.52 at
-  // 128; radix selection (knn_select.cu) 1.41 / 1.51 / 1.54 ms, nearly flat in k.
+  // 128; radix selection (knn_select.cu) 0.82 ms at k = 81, 0.85 at 100, 1.4 at 128 to 240.
   // With fewer than 16 keys per wanted neighbour the class minima stop bounding anything for
   // k > 40 (16 x 4096 x 300, k = 64: 0.47 ms two-pass, 0.26 ms by radix).
-  const bool by_radix = (k > 80 || (k > 40 && N2 < 16 * k)) && k <= 256 && N2 < (1LL << 31);
+  const bool by_radix = (k > 64 || (k > 40 && N2 < 16 * k)) && k <= 256 && N2 < (1LL << 31);
   if (!by_radix && k <= 128 && N2 >= 4 * k && N2 >= (k > 64 ? 512 : 256)) {
     if (k <= 16) {
       if (B * N1 >= (int64_t)sm_count() * 4 * 64)

@@ -3,19 +3,22 @@
 // Keeping the k best of a query in a list or heap costs an insertion per accepted key, and with one
 // query per lane every insertion stalls the other 31 lanes of its warp: for k = 200 on 4096 keys the
 // heap kernel spends nearly all of its time there.  Here nothing data dependent happens inside the
-// key sweeps.  A block of four warps serves 32 queries (lane = query; every warp sweeps a quarter of
+// key sweeps.  A block of eight warps serves 32 queries (lane = query; every warp sweeps an eighth of
 // each 256-key tile) and finds the k-th smallest distance of each query EXACTLY by a most-significant-
 // digit radix selection on the bit pattern of the distance (non-negative floats order like their
-// bits): four sweeps, one per byte, each counting the keys whose higher bytes equal the digits found
+// bits): one sweep per byte, each counting the keys whose higher bytes equal the digits found
 // so far into a 256-bin histogram per query in shared memory ([bin][lane]: a lane only ever touches
-// its own bank).  A fifth sweep collects the keys below that distance (in any order) and, by the
+// its own bank).  Usually two bytes are enough: when the keys up to and including the 16-bit bucket
+// of the k-th distance fit the list of every query of the block, one more sweep collects them and
+// the sort finishes the selection.  Otherwise (massive ties) all four bytes are resolved and a
+// fifth sweep collects the keys below that distance (in any order) and, by the
 // position scheme of the ball query (hits of a slice as a bit mask, counts exchanged at the tile
 // barrier), the first keys in index order AT that distance, exactly k in all; a bitonic network
-// over (distance bits, index) as one 64-bit word, run by the four warps together on the lists in
+// over (distance bits, index) as one 64-bit word, run by the eight warps together on the lists in
 // shared memory, puts them in the (distance, index) order every other path emits.
 //
-// Five sweeps of the plain distance (8 FP32 instructions per pair) are far from the FP32 roofline,
-// but they cost the same for every k, every key order and every tie pattern: 4 x 4096 x 4096 with
+// Three to five sweeps of the plain distance (8 FP32 instructions per pair) are far from the FP32
+// roofline, but they cost nearly the same for every k and every key order: 4 x 4096 x 4096 with
 // k = 200 takes a fraction of a millisecond where the heap kernel took 10.8 ms (the reference's
 // bounded-set kernel, torkit3d/csrc/cuda/knn_distance_kernel.cu:102-177 with
 // torkit3d/csrc/include/mink.cuh:61-89, 8.6 ms).  A NaN distance (a NaN coordinate) is given the
@@ -27,7 +30,7 @@
 namespace tk3d {
 namespace {
 
-constexpr int SEL_THREADS = 128;
+constexpr int SEL_THREADS = 256;
 constexpr int SEL_SPLIT = SEL_THREADS / 32;
 constexpr int SEL_TILE = 256;
 constexpr int SEL_QK = SEL_TILE / SEL_SPLIT;  // keys per warp per tile: one 64-bit mask
@@ -98,6 +101,7 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
 
     // ---- the k-th smallest distance, one byte per sweep
     unsigned prefix = 0;  // digits found so far (the high bytes of the k-th distance)
+    bool short_cut = false;
     int krem = k;         // rank of the k-th distance among the keys that share those digits
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
@@ -109,10 +113,11 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
             if (match) atomicAdd(&hist[((bits >> shift) & 255u) * 32 + lane], 1);
           },
           [&](int, int) { __syncthreads(); });
-      // which bin holds the krem-th key: every warp adds up a quarter of the bins, then all warps
-      // walk the quarter that holds it (the same result in every warp, lane = query)
+      // which bin holds the krem-th key: every warp adds up a share of the bins, then all warps
+      // walk the share that holds it (the same result in every warp, lane = query)
       int s = 0;
-      for (int bin = part * 64; bin < part * 64 + 64; ++bin) s += hist[bin * 32 + lane];
+      constexpr int QB = SEL_BINS / SEL_SPLIT;  // bins per warp
+      for (int bin = part * QB; bin < part * QB + QB; ++bin) s += hist[bin * 32 + lane];
       psum[part][lane] = s;
       __syncthreads();
       int before = 0, quarter = 0;
@@ -124,23 +129,44 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
           quarter = w + 1;
         }
       }
-      int bin = quarter * 64;
-      for (int step = 0; step < 63; ++step) {
-        const int c = hist[bin * 32 + lane];
-        if (before + c >= krem) break;
-        before += c;
+      int bin = quarter * QB;
+      int cbin = hist[bin * 32 + lane];
+      for (int step = 0; step < QB - 1 && before + cbin < krem; ++step) {
+        before += cbin;
         ++bin;
+        cbin = hist[bin * 32 + lane];
       }
       prefix = (prefix << 8) | (unsigned)bin;
       krem -= before;
-      __syncthreads();  // the histogram is cleared (or reused as the list) next
+      // After two bytes the bucket of the k-th distance usually holds a handful of keys: if, for
+      // every query of the block, the keys up to and including that bucket fit the list, they are
+      // collected as they are and the sort below does the rest -- three sweeps instead of five.
+      // (The vote is also the barrier after which the histogram may be cleared or reused.)
+      const bool fits = pass == 1 && (k - krem) + cbin <= n2;
+      if (__syncthreads_and(fits)) {
+        short_cut = true;
+        break;
+      }
     }
+    if (part == 0) cless[lane] = 0;
+    if (short_cut) {
+      // ---- collect every key whose two high bytes do not exceed those of the k-th distance
+      for (int e = tid; e < n2 * 32; e += SEL_THREADS) list[e] = ~0ull;  // unused slots sort last
+      __syncthreads();
+      sweep(
+          [&](int, int j, unsigned bits) {
+            if ((bits >> 16) <= prefix) {
+              const int slot = atomicAdd(&cless[lane], 1);  // at most n2 keys, by the vote above
+              list[slot * 32 + lane] = ((unsigned long long)bits << 32) | (unsigned)j;
+            }
+          },
+          [&](int, int) { __syncthreads(); });
+    } else {
     const unsigned kth = prefix;  // bit pattern of the k-th smallest distance
     const int need_eq = krem;     // keys AT that distance that belong to the result (>= 1)
     const int nless = k - need_eq;
 
     // ---- collect: everything below kth, and the first need_eq keys (by index) at kth
-    if (part == 0) cless[lane] = 0;
     for (int e = k * 32 + tid; e < n2 * 32; e += SEL_THREADS) list[e] = ~0ull;  // padding sorts last
     __syncthreads();
     unsigned long long mask = 0;
@@ -177,10 +203,11 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
           mask = 0;
           cnt = 0;
         });
+    }
     __syncthreads();
 
     // ---- sort the n2 (k rounded up to a power of two, padded with all-ones) entries of every list
-    // by (distance bits, index): the pairs of each compare-exchange step are dealt to the four warps
+    // by (distance bits, index): the pairs of each compare-exchange step are dealt to the warps
     for (int size = 2; size <= n2; size <<= 1) {
       for (int stride = size >> 1; stride > 0; stride >>= 1) {
         for (int p = part; p < (n2 >> 1); p += SEL_SPLIT) {
@@ -218,7 +245,10 @@ size_t select_smem(int n2) {
 // k-nearest keys by radix selection; the caller has checked 1 <= k <= 256, k <= N2 < 2^31.
 int knn_select_f32(const float *query, const float *key, int64_t B, int N1, int N2, int k, float *dist, IndexOut index,
                    XyzLayout ql, XyzLayout kl, cudaStream_t st) {
+  // list length: a power of two with some room above k for the keys that share the 16-bit bucket
+  // of the k-th distance (the short cut of the kernel), at most 256
   int n2 = 2;
+  while (n2 < k + 8 && n2 < 256) n2 <<= 1;
   while (n2 < k) n2 <<= 1;
   const size_t smem = select_smem(n2);
   if (smem + 12 * 1024 > 48 * 1024) TK3D_CUDA(raise_smem_limit((const void *)knn_select_kernel, (int)smem));
