@@ -338,7 +338,7 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 }
 
 // ---------------------------------------------------------------------------------------------
-// Two-pass kernel for 4 < k <= 128 (fp32).
+// Two-pass kernel for 4 < k <= 64 (fp32; larger k: knn_select.cu).
 //
 // Pass 1 sweeps all keys with the cheap filter value a (3 FMA per pair) and keeps, per query, the
 // minimum of a over NCH >= 2k interleaved key classes.  The k-th smallest class minimum tau bounds
@@ -375,13 +375,13 @@ knn_buffered_kernel(const float *__restrict__ query, const float *__restrict__ k
 // exact scan over all keys by one warp (lanes = keys, sorted list in the query's list column).
 constexpr int KT_THREADS = 128;
 constexpr int KT_SPLIT = KT_THREADS / 32;  // warps sharing every tile
-// KT_NCH key classes (32 to 256: at least two per wanted neighbour, i.e. k <= KT_NCH / 2; a warp
+// KT_NCH key classes (32 to 128: at least two per wanted neighbour, i.e. k <= KT_NCH / 2; a warp
 // holds the minima of its KT_NCH / 4 classes in registers) and KT_QCAP group slots per query are
 // template parameters of the kernel:
 //     k <= 16: 32 classes, 56 slots, one or two queries per lane
 //     k <= 32: 64 classes, 104 slots, one query per lane
 //     k <= 64: 128 classes, 192 slots, one query per lane
-//     k <= 128: 256 classes, 384 slots, one query per lane, 512-key tiles (KT_TILE; 256 otherwise)
+// (KT_TILE = keys per tile: 256.)
 template <int Q, int KT_NCH, int KT_QCAP, int KT_TILE>
 constexpr size_t kt_smem_bytes() {
   return (size_t)2 * KT_TILE * 16 + (size_t)KT_NCH * 32 * Q * 4 + (size_t)KT_QCAP * 32 * Q * 4;
@@ -1085,21 +1085,20 @@ static int knn_impl(const void *query, const void *key, int64_t B, int64_t N1, i
     default: break;
   }
   // Two-pass selection needs at least two key classes per wanted neighbour to be tight (the class
-  // counts below) and a few keys in every class: N2 >= 4 k, at least 256 (512 for k > 64).
+  // counts below) and a few keys in every class: N2 >= 4 k, at least 256.
   // Measured on B200 (16 x 4096 x 4096): the two-pass kernel 0.74 ms at k = 64, 2.04 at 100, 2.52 at
   // 128; radix selection (knn_select.cu) 0.82 ms at k = 81, 0.85 at 100, 1.4 at 128 to 240.
   // With fewer than 16 keys per wanted neighbour the class minima stop bounding anything for
   // k > 40 (16 x 4096 x 300, k = 64: 0.47 ms two-pass, 0.26 ms by radix).
   const bool by_radix = (k > 64 || (k > 40 && N2 < 16 * k)) && k <= 256 && N2 < (1LL << 31);
-  if (!by_radix && k <= 128 && N2 >= 4 * k && N2 >= (k > 64 ? 512 : 256)) {
+  if (!by_radix && k <= 64 && N2 >= 4 * k && N2 >= 256) {
     if (k <= 16) {
       if (B * N1 >= (int64_t)sm_count() * 4 * 64)
         return knn_twopass<2, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
       return knn_twopass<1, 32, 56, 7>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
     }
     if (k <= 32) return knn_twopass<1, 64, 104, 5>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
-    if (k <= 64) return knn_twopass<1, 128, 192, 4>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
-    return knn_twopass<1, 256, 384, 2, 512>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
+    return knn_twopass<1, 128, 192, 4>(q, r, B, (int)N1, (int)N2, (int)k, d, io, st);
   }
   // key clouds too small for the two-pass kernel: buffered lists up to k = 40 (16 x 4096 x 300:
   // 0.069 ms at k = 16 against 0.195 by radix, 0.47 against 0.26 at k = 64)
