@@ -7,7 +7,7 @@ c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_fwd_rows, c5_feature_rows,
 inputs in channel-first layout, fused and spelled operator by operator: c3_fps_gather,
 c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain; and the EdgeConv edge
 features of a DGCNN layer (B=32, 1024 points, C=64, K=20): edge_fused, edge_chain; and its feature-space
-KNN: feature_knn, feature_knn_chain (cdist + topk in PyTorch); knn_f64 (float64 KNN, 8 x 2048 x 2048, k=16); knn_k200 (float32, 4 x 4096 x 4096, k=200).  ``--scale-batch`` overrides the batch
+KNN: feature_knn, feature_knn_chain (cdist + topk in PyTorch); knn_f64 (float64 KNN, 8 x 2048 x 2048, k=16); knn_k200 (float32, 4 x 4096 x 4096, k=200); fps_large (4 clouds of 65536 points -> 2048 samples).  ``--scale-batch`` overrides the batch
 size of the configuration (smaller captures for ``ncu``).  Prints the mean CUDA-event time.
 """
 import argparse
@@ -30,6 +30,11 @@ def build_case(name, batch, dev):
     if name == "c2_knn":
         q, r = [t.to(dev) for t in workloads.c2_knn(**kw)]
         return lambda: knn_points(q, r, 16)
+    if name == "fps_large":
+        # clouds beyond one block's registers: 4 clouds of 65536 points -> 2048 samples (a cluster of 8 blocks each)
+        g = torch.Generator().manual_seed(9)
+        p = torch.rand(batch or 4, 65536, 3, generator=g).to(dev)
+        return lambda: sample_farthest_points(p, 2048)
     if name == "knn_k200":
         # large k: the second configuration's clouds (4096 x 4096 per cloud), 4 of them, k=200
         q, r = [t[:(batch or 4)].contiguous().to(dev) for t in workloads.c2_knn()]

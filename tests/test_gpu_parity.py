@@ -401,7 +401,10 @@ def test_feature_knn_golden_wrapper_and_errors(golden):
 
 # ----------------------------------------------------------------------------------------------- fps
 FPS_CASES = [(1, 31, 2), (2, 1024, 128), (3, 1025, 129), (16, 1024, 512), (4, 4096, 300), (2, 8192, 1024),
-             (2, 100, 100), (1, 1, 1), (3, 33, 33), (2, 8193, 200), (1, 20000, 64)]
+             (2, 100, 100), (1, 1, 1), (3, 33, 33), (2, 8193, 200), (1, 20000, 64),
+             # a cluster of 2 / 4 / 8 / 16 blocks per cloud (16385 to 131072 points), then the streaming kernel
+             (2, 16385, 96), (3, 30000, 128), (2, 40961, 70), (1, 65536, 200), (1, 65537, 40), (1, 131072, 33),
+             (1, 131073, 20)]
 
 
 @pytest.mark.parametrize("B,n,s", FPS_CASES)
@@ -414,6 +417,28 @@ def test_fps_bit_exact(oracle, B, n, s):
     np.testing.assert_array_equal(got, oracle.fps(p, s))
     got_t = N(sample_farthest_points(T(p).transpose(1, 2), s, transpose=True))
     np.testing.assert_array_equal(got_t, got)
+
+
+def test_fps_cluster_ties_and_gather(oracle):
+    """Clouds served by a cluster of blocks: exact ties across the blocks' slices (a coarse lattice:
+    the lowest index must win wherever it lives), all points coinciding, and the fused centroid
+    gather in both layouts."""
+    from torkit3d_b200 import _fused
+    from torkit3d_b200.ops import sample_farthest_points
+
+    rng = np.random.default_rng(77)
+    p = (rng.integers(-6, 7, size=(2, 33000, 3)) * 0.5).astype(np.float32)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(p), 300)), oracle.fps(p, 300))
+    same = np.full((1, 17000, 3), 0.25, dtype=np.float32)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(same), 5)), oracle.fps(same, 5))
+    q = rng.random((2, 20000, 3)).astype(np.float32)
+    want = oracle.fps(q, 64)
+    for cf in (False, True):
+        pts = T(q).transpose(1, 2).contiguous() if cf else T(q)
+        idx, cent = _fused.fps_gather(pts, 64, channel_first=cf)
+        np.testing.assert_array_equal(N(idx), want)
+        ref = np.take_along_axis(q, want[..., None], axis=1)
+        np.testing.assert_array_equal(N(cent.transpose(1, 2) if cf else cent), ref)
 
 
 def test_fps_golden_fp64_and_duplicates(oracle, golden):

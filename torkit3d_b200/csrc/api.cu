@@ -105,6 +105,7 @@ unsigned long long tk3d_bounds_count_diag(void);
 unsigned long long tk3d_bounds_count_edge(void);
 unsigned long long tk3d_bounds_count_feature_knn(void);
 unsigned long long tk3d_bounds_count_fps(void);
+unsigned long long tk3d_bounds_count_fps_cluster(void);
 unsigned long long tk3d_bounds_count_group(void);
 unsigned long long tk3d_bounds_count_interp(void);
 unsigned long long tk3d_bounds_count_knn(void);
@@ -116,7 +117,7 @@ unsigned long long tk3d_bounds_count_sa_group(void);
 long long tk3d_bounds_violations(void) {
 #ifdef TK3D_BOUNDS
   if (cudaDeviceSynchronize() != cudaSuccess) return -2;
-  return (long long)(tk3d_bounds_count_ball_query() + tk3d_bounds_count_chamfer() + tk3d_bounds_count_chamfer_fast() + tk3d_bounds_count_diag() + tk3d_bounds_count_edge() + tk3d_bounds_count_feature_knn() + tk3d_bounds_count_fps() + tk3d_bounds_count_group() + tk3d_bounds_count_interp() + tk3d_bounds_count_knn() + tk3d_bounds_count_knn_select() + tk3d_bounds_count_knn_split() + tk3d_bounds_count_sa_group());
+  return (long long)(tk3d_bounds_count_ball_query() + tk3d_bounds_count_chamfer() + tk3d_bounds_count_chamfer_fast() + tk3d_bounds_count_diag() + tk3d_bounds_count_edge() + tk3d_bounds_count_feature_knn() + tk3d_bounds_count_fps() + tk3d_bounds_count_fps_cluster() + tk3d_bounds_count_group() + tk3d_bounds_count_interp() + tk3d_bounds_count_knn() + tk3d_bounds_count_knn_select() + tk3d_bounds_count_knn_split() + tk3d_bounds_count_sa_group());
 #else
   return -1;  // this build carries no range checks
 #endif

@@ -16,6 +16,7 @@
 //    the cluster barrier costs more per step than the divided arithmetic saves.)
 //  * fp64, N <= 8192: the same persistent structure with the coordinates in shared memory and up to
 //    8 running minima per thread; the block maximum is taken on the 64-bit pattern in two REDUX steps.
+//  * fp32, 16385 to 131072 points: a thread-block cluster per cloud, fps_cluster.cu.
 //  * any other case ("streaming" kernel): points are re-read from global memory (L1/L2 resident)
 //    and the running minimum lives in a caller-provided global scratch array.
 //
@@ -344,6 +345,11 @@ int threads_for(int64_t N) {
 
 }  // namespace tk3d
 
+namespace tk3d {
+bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                     float *sampled, cudaStream_t st, int *rc);
+}
+
 using namespace tk3d;
 
 extern "C" size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype) {
@@ -411,6 +417,10 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
     }
 #undef TK3D_FPS_CASE
     return check_launch("fps_resident_kernel");
+  }
+  if (dtype == TK3D_F32) {  // 16385 to 131072 points: a cluster of blocks per cloud (fps_cluster.cu), no scratch
+    int rc = TK3D_OK;
+    if (fps_cluster_f32((const float *)points, B, N, S, (int)ps, cs, index, (float *)sampled, st, &rc)) return rc;
   }
   TK3D_REQUIRE(scratch != nullptr && scratch_bytes >= need, TK3D_ERR_SCRATCH,
                "fps: scratch of %zu bytes required, %zu given", need, scratch ? scratch_bytes : (size_t)0);

@@ -1,0 +1,215 @@
+// Farthest point sampling of large float32 clouds (16385 to 131072 points) on a thread-block cluster.
+//
+// The resident kernel of fps.cu keeps a cloud in the registers of ONE block, which ends at 16384
+// points; beyond that the streaming kernel re-reads the cloud and its running minima from L2 in
+// every step, still with one block per cloud (4 clouds of 65536 points: 4 busy SMs, 19 us per
+// step).  Here a cluster of 2, 4, 8 or 16 blocks shares a cloud: every block keeps a contiguous slice
+// of up to 8192 points and their running minima in registers, exactly like the resident kernel,
+// and finds its own farthest point (two block barriers); then each block writes its candidate --
+// (distance bits, index, coordinates), 32 bytes -- into the shared memory of every block of the
+// cluster (distributed shared memory), one cluster barrier makes the candidates visible, and
+// every block picks the same winner from its local copy: highest distance, lowest index.  The
+// candidate slots are double buffered by the step's parity, so one cluster barrier per step is
+// enough (a block can only be one step ahead of the slowest one).
+//
+// For clouds that fit one block the cluster barrier costs more than the divided arithmetic saves
+// (measured: 1.07 ms against 0.88 ms for 32 clouds of 8192 points), which is why this kernel only
+// takes the clouds the resident kernel cannot hold.
+// Arithmetic, tie rule and padding are those of fps_resident_kernel; the reference's kernel is
+// torkit3d/csrc/cuda/sample_farthest_points_kernel.cu:33-103 (one block per cloud, any size).
+#include <cooperative_groups.h>
+
+#include "tk3d_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace tk3d {
+namespace {
+
+constexpr int FC_THREADS = 1024;
+constexpr int FC_P2 = 4;                               // float2 pairs per thread: 8 points
+constexpr int FC_SLICE = FC_THREADS * 2 * FC_P2;       // 8192 points per block
+constexpr int FC_MAX_CL = 16;                          // 8 is the portable cluster size; 16 needs an opt-in
+
+struct __align__(16) FcCandidate {
+  unsigned bits;  // running-minimum distance of the block's farthest point
+  int idx;        // its index in the cloud
+  float x, y, z;
+  int pad[3];
+};
+
+__global__ void __launch_bounds__(FC_THREADS)
+fps_cluster_kernel(const float *__restrict__ points, int N, int NL, int S, int64_t *__restrict__ index, int ps, int cs,
+                   float *__restrict__ sampled, float one) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CL = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  const int cloud = blockIdx.x / CL;
+  extern __shared__ float sxyz[];  // [3*NL]: this block's slice of the cloud
+  __shared__ FcCandidate cand[2][FC_MAX_CL];
+  __shared__ unsigned slots[2][32];
+  __shared__ int s_idx[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int T = FC_THREADS, nwarps = FC_THREADS / 32;
+  const float *pts = points + (int64_t)cloud * N * 3;
+  int64_t *out = index + (int64_t)cloud * S;
+  const int base = rank * NL;
+  const int nloc = max(0, min(NL, N - base));
+
+  // Point j, coordinate d sits at pts[j*ps + d*cs]: (3, 1) for [N,3] clouds, (1, N) for [3,N].
+  for (int e = tid; e < 3 * nloc; e += T) {
+    const int j = e / 3, d = e - 3 * j;
+    sxyz[e] = pts[(int64_t)(base + j) * ps + (int64_t)d * cs];
+  }
+  if (tid < 2) s_idx[tid] = 0x7fffffff;
+  __syncthreads();
+
+  // Point (i, h) of this thread is local j = (2*i + h) * T + tid: ascending in (i, h).
+  float2 px[FC_P2], py[FC_P2], pz[FC_P2], md[FC_P2];
+  const float qnan = __int_as_float(0x7fc00000), pinf = __int_as_float(0x7f800000);
+#pragma unroll
+  for (int i = 0; i < FC_P2; ++i) {
+    const int j0 = (2 * i) * T + tid, j1 = (2 * i + 1) * T + tid;
+    px[i].x = j0 < nloc ? sxyz[3 * j0 + 0] : qnan;
+    py[i].x = j0 < nloc ? sxyz[3 * j0 + 1] : qnan;
+    pz[i].x = j0 < nloc ? sxyz[3 * j0 + 2] : qnan;
+    px[i].y = j1 < nloc ? sxyz[3 * j1 + 0] : qnan;
+    py[i].y = j1 < nloc ? sxyz[3 * j1 + 1] : qnan;
+    pz[i].y = j1 < nloc ? sxyz[3 * j1 + 2] : qnan;
+    md[i].x = j0 < nloc ? pinf : 0.f;  // padding: distance 0, NaN coordinates keep it there
+    md[i].y = j1 < nloc ? pinf : 0.f;
+  }
+
+  // the first sample is point 0 of the cloud
+  float cx = pts[0], cy = pts[cs], cz = pts[2 * (int64_t)cs];
+  const bool writer = rank == 0 && tid == 0;
+  const int sps = cs == 1 ? 3 : 1, scs = cs == 1 ? 1 : S;  // layout of `sampled`: that of the input
+  float *sm = sampled ? sampled + (int64_t)cloud * S * 3 : nullptr;
+  if (writer) {
+    out[0] = 0;
+    if (sm) {
+      sm[0] = cx;
+      sm[scs] = cy;
+      sm[2 * (int64_t)scs] = cz;
+    }
+  }
+  cluster.sync();  // every block of the cluster is running: its shared memory may be written from now on
+
+  const float2 one2 = make_float2(one, one);
+  for (int it = 1; it < S; ++it) {
+    const int par = it & 1;
+    const float2 ncx = make_float2(-cx, -cx), ncy = make_float2(-cy, -cy), ncz = make_float2(-cz, -cz);
+    float bm = 0.f;
+#pragma unroll
+    for (int i = 0; i < FC_P2; ++i) {
+      // p - c as p + (-c), squares by packed multiplies, the sums as fma(x, one, y) with one = 1.0
+      // from a kernel argument: exact, and it keeps the compiler from contracting multiply and add
+      const float2 dx = __fadd2_rn(px[i], ncx), dy = __fadd2_rn(py[i], ncy), dz = __fadd2_rn(pz[i], ncz);
+      const float2 d = __ffma2_rn(__ffma2_rn(__fmul2_rn(dx, dx), one2, __fmul2_rn(dy, dy)), one2, __fmul2_rn(dz, dz));
+      md[i].x = fminf(md[i].x, d.x);
+      md[i].y = fminf(md[i].y, d.y);
+      asm("max.f32 %0, %0, %1, %2;" : "+f"(bm) : "f"(md[i].x), "f"(md[i].y));
+    }
+    const unsigned bits = __float_as_uint(bm);
+    unsigned gb = __reduce_max_sync(0xffffffffu, bits);
+    if (lane == 0) slots[par][warp] = gb;
+    __syncthreads();
+    gb = __reduce_max_sync(0xffffffffu, lane < nwarps ? slots[par][lane] : 0u);
+    if (tid == 0) s_idx[par ^ 1] = 0x7fffffff;  // re-arm the other slot: its readers are past the barrier above
+    if (bits == gb) {
+      int mine = 0x7fffffff;
+#pragma unroll
+      for (int i = FC_P2 - 1; i >= 0; --i) {
+        if (md[i].y == bm) mine = (2 * i + 1) * T + tid;
+        if (md[i].x == bm) mine = (2 * i) * T + tid;
+      }
+      atomicMin(&s_idx[par], mine);
+    }
+    __syncthreads();
+    // this block's candidate goes to every block of the cluster (thread r writes to block r)
+    if (tid < CL) {
+      const int loc = s_idx[par];
+      FcCandidate c;
+      c.bits = gb;
+      c.idx = base + loc;  // beyond N for a padding slot, which can only win against other padding
+      const bool real = loc < nloc;
+      c.x = real ? sxyz[3 * loc + 0] : 0.f;
+      c.y = real ? sxyz[3 * loc + 1] : 0.f;
+      c.z = real ? sxyz[3 * loc + 2] : 0.f;
+      c.pad[0] = c.pad[1] = c.pad[2] = 0;
+      FcCandidate *remote = cluster.map_shared_rank(&cand[par][rank], tid);
+      *remote = c;
+    }
+    cluster.sync();
+    // every block picks the same winner: highest distance, lowest index
+    unsigned wb = cand[par][0].bits;
+    int wi = cand[par][0].idx, wr = 0;
+    for (int r = 1; r < CL; ++r) {
+      const unsigned b = cand[par][r].bits;
+      const int ix = cand[par][r].idx;
+      if (b > wb || (b == wb && ix < wi)) {
+        wb = b;
+        wi = ix;
+        wr = r;
+      }
+    }
+    cx = cand[par][wr].x;
+    cy = cand[par][wr].y;
+    cz = cand[par][wr].z;
+    if (writer) {
+      out[it] = wi;
+      if (sm) {
+        sm[(int64_t)it * sps] = cx;
+        sm[(int64_t)it * sps + scs] = cy;
+        sm[(int64_t)it * sps + 2 * (int64_t)scs] = cz;
+      }
+    }
+  }
+  cluster.sync();  // no block leaves while another may still write into its shared memory
+}
+
+}  // namespace
+
+// Launches the cluster kernel when the clouds suit it (float32, 16384 < N <= 131072); returns false
+// when they do not or when the device refuses the cluster launch (the caller then takes its own
+// path), true with *rc set otherwise.
+bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                     float *sampled, cudaStream_t st, int *rc) {
+  if (N <= 16384 || N > (int64_t)FC_MAX_CL * FC_SLICE || B * FC_MAX_CL >= (1LL << 31)) return false;
+  int CL = 2;
+  while ((int64_t)CL * FC_SLICE < N) CL <<= 1;
+  const int NL = (int)((N + CL - 1) / CL);
+  const size_t smem = (size_t)NL * 12;
+  if (raise_smem_limit((const void *)fps_cluster_kernel, 98304) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  if (CL > 8 && cudaFuncSetAttribute((const void *)fps_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed,
+                                     1) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(B * CL));
+  cfg.blockDim = dim3(FC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fps_cluster_kernel, points, (int)N, NL, (int)S, index, ps, (int)cs,
+                                           sampled, 1.0f);
+  if (e != cudaSuccess) {  // e.g. a device partition without room for the cluster
+    (void)cudaGetLastError();
+    return false;
+  }
+  *rc = check_launch("fps_cluster_kernel");
+  return true;
+}
+
+}  // namespace tk3d
+
+TK3D_BOUNDS_TU(fps_cluster)
