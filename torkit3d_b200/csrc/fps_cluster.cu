@@ -140,21 +140,17 @@ fps_cluster_kernel(const float *__restrict__ points, int N, int NL, int S, int64
       *remote = c;
     }
     cluster.sync();
-    // every block picks the same winner: highest distance, lowest index
-    unsigned wb = cand[par][0].bits;
-    int wi = cand[par][0].idx, wr = 0;
-    for (int r = 1; r < CL; ++r) {
-      const unsigned b = cand[par][r].bits;
-      const int ix = cand[par][r].idx;
-      if (b > wb || (b == wb && ix < wi)) {
-        wb = b;
-        wi = ix;
-        wr = r;
-      }
-    }
-    cx = cand[par][wr].x;
-    cy = cand[par][wr].y;
-    cz = cand[par][wr].z;
+    // every block (every warp: lane r looks at candidate r) picks the same winner: highest
+    // distance, lowest index
+    const bool has = lane < CL;
+    const unsigned cb = has ? cand[par][lane].bits : 0u;
+    const int ci = has ? cand[par][lane].idx : 0x7fffffff;
+    const unsigned wb = __reduce_max_sync(0xffffffffu, cb);
+    const int wi = __reduce_min_sync(0xffffffffu, (has && cb == wb) ? ci : 0x7fffffff);
+    const int src = __ffs(__ballot_sync(0xffffffffu, has && cb == wb && ci == wi)) - 1;
+    cx = __shfl_sync(0xffffffffu, has ? cand[par][lane].x : 0.f, src);
+    cy = __shfl_sync(0xffffffffu, has ? cand[par][lane].y : 0.f, src);
+    cz = __shfl_sync(0xffffffffu, has ? cand[par][lane].z : 0.f, src);
     if (writer) {
       out[it] = wi;
       if (sm) {
