@@ -123,7 +123,9 @@ int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t 
  *   index  [B,S]     out
  *   scratch          device buffer of at least tk3d_fps_scratch_bytes(B,N,dtype) bytes (the running
  *                    minimum distance of clouds too large to keep on chip); may be NULL when that
- *                    function returns 0.  Contents on entry are ignored.
+ *                    function returns 0.  Contents on entry are ignored.  (float32 clouds of 16385
+ *                    to 131072 points run on a thread-block cluster and leave it untouched; it is
+ *                    what the call falls back on when the device refuses the cluster launch.)
  */
 size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype);
 int tk3d_fps(const void *points, int64_t B, int64_t N, int64_t num_samples, int64_t *index, void *scratch,
