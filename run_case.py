@@ -3,7 +3,7 @@
     python run_case.py <case> [--iters 3] [--scale-batch B]
 
 Cases: c1_chamfer, c2_knn, c3_fps, c3_ball, c3_group_fwd, c3_group_bwd, c4_chamfer_fwd,
-c4_chamfer_bwd, c5_three_nn, c5_interp_fwd, c5_interp_fwd_rows, c5_feature_rows, c5_interp_bwd, and the layer front ends on the same
+c4_chamfer_bwd, c5_three_nn, c5_three_nn_slab8, c5_interp_fwd, c5_interp_fwd_rows, c5_feature_rows, c5_interp_bwd, and the layer front ends on the same
 inputs in channel-first layout, fused and spelled operator by operator: c3_fps_gather,
 c3_fps_chain, c3_sa_fused, c3_sa_chain, c3_sa_fused_bwd, c5_fp_fused, c5_fp_chain; and the EdgeConv edge
 features of a DGCNN layer (B=32, 1024 points, C=64, K=20): edge_fused, edge_chain; and its feature-space
@@ -144,6 +144,9 @@ def build_case(name, batch, dev):
             return fp_chain
         if name == "c5_three_nn":
             return lambda: knn_points(q, r, 3)
+        if name == "c5_three_nn_slab8":  # one rank's query slab of an 8-GPU run, keys replicated
+            qs = q[:, :q.size(1) // 8].contiguous()
+            return lambda: knn_points(qs, r, 3)
         d, i = knn_points(q, r, 3)
         w = three_nn_weight(d)
         if name == "c5_interp_fwd":
