@@ -1,11 +1,12 @@
 // Ball query: first k key indices (ascending) whose squared distance is < radius^2.
 //
-// fp32 fast path: the filter-then-verify sweep of sweep.cuh (pair layout, packed FMAs) with a
-// constant bound (radius^2).  A
-// verified hit is written straight to the output row; a query stops testing once it has k hits
-// (its threshold becomes -inf) and the block leaves the key loop as soon as all its queries are
-// full -- the reference keeps scanning to the end of the cloud.  Short rows are padded with the
-// first hit, rows without a hit are filled with -1, so every output element is written here.
+// fp32: the filter-then-verify sweep of sweep.cuh (pair layout, packed FMAs) with a constant
+// bound (radius^2).  With many queries one thread serves a query and writes verified hits straight
+// to the output row; with few, several warps share 32 queries and place their hits by counting
+// (ball_query_split_kernel below).  A query stops testing once it has k hits (its threshold becomes
+// -inf) and a block leaves the key loop as soon as all its queries are full -- the reference keeps
+// scanning to the end of the cloud.  Short rows are padded with the first hit, rows without a hit
+// are filled with -1, so every output element is written here.
 #include "sweep.cuh"
 
 namespace tk3d {

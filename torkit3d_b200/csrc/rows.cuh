@@ -164,7 +164,9 @@ gather_rows_kernel(const float *__restrict__ featT, const IndexT *__restrict__ i
 
 // Vectorised variant for C % 4 == 0, E % 4 == 0 and 16-byte aligned buffers.  The tile is
 // [C][ROWS_TE] floats; the 16-byte chunk holding entries 4g .. 4g+3 of channel c sits at chunk
-// position (g ^ (c >> 2)) & 15 of row c.
+// position (g ^ (c >> 2)) & (ROWS_TE / 4 - 1) of row c.  Tiles are small (32 entries, four warps):
+// a barrier then holds few warps and ten blocks fit an SM, which measured 10 % faster than 64
+// entries with eight warps on the interpolation gather.
 //
 // Phase 1 -- a warp works on four entries at a time: lane = 8 * el + ql reads, for entry 4g + el,
 // the float4 number 8 * qh + ql of its row(s) (eight consecutive lanes cover 128 contiguous
@@ -207,7 +209,7 @@ gather_rows_vec4_kernel(const float *__restrict__ featT, const IndexT *__restric
 
   const float4 *fb = reinterpret_cast<const float4 *>(featT + b * N1 * C);
   bool bad = false;
-  // a warp owns the entry groups warp and warp + 8; the indices and weights of both are requested
+  // a warp owns the entry groups warp and warp + 4; the indices and weights of both are requested
   // before the first row load, so the second group does not pay that latency again
   int ids[ROWS_GPW][NSRC];
   float ws[ROWS_GPW][NSRC];
