@@ -156,3 +156,48 @@ def test_knn_largest_shape_of_the_reference_tests(ref):
     cd, ci = canon(td, ti)
     np.testing.assert_array_equal(mi.cpu().numpy(), ci)
     np.testing.assert_array_equal(md.cpu().numpy(), cd)
+
+
+def test_random_shapes(ref):
+    """Seeded random shapes, sizes and point distributions (uniform, normal, a coarse lattice with
+    massive ties, a nearly flat slab) through every kernel choice of the KNN, ball-query and FPS
+    dispatch -- among them radix selection for large k, the hit-mask ball query for few queries and
+    the cluster FPS for large clouds -- against the reference's kernels."""
+    import random
+
+    from torkit3d_b200 import _C
+
+    rnd = random.Random(1234)
+    g = torch.Generator().manual_seed(5)
+
+    def cloud(B, n, kind):
+        if kind == 0:
+            return torch.rand(B, n, 3, generator=g)
+        if kind == 1:
+            return torch.randn(B, n, 3, generator=g)
+        if kind == 2:
+            return torch.randint(-4, 5, (B, n, 3), generator=g) * 0.25
+        return torch.rand(B, n, 3, generator=g) * torch.tensor([10.0, 10.0, 0.01])
+
+    for _ in range(40):
+        kind = rnd.randrange(4)
+        B = rnd.choice([1, 2, 3, 5])
+        n1 = rnd.choice([1, 17, 100, 333, 1000, 2500])
+        n2 = rnd.choice([40, 257, 300, 1000, 3000, 9000])
+        k = min(n2, rnd.choice([1, 3, 5, 16, 31, 41, 64, 65, 100, 130, 200, 256]))
+        q, r = cloud(B, n1, kind).to(DEV), cloud(B, n2, kind).to(DEV)
+        md, mi = _C.knn_distance_cuda(q, r, k, 0)
+        cd, ci = canon(*ref.knn_distance_cuda(q, r, k, 0))
+        np.testing.assert_array_equal(md.cpu().numpy(), cd, err_msg="knn %s" % ((kind, B, n1, n2, k),))
+        if kind != 2:  # among exactly tied distances the reference's retained set is not the lowest indices
+            np.testing.assert_array_equal(mi.cpu().numpy(), ci, err_msg="knn %s" % ((kind, B, n1, n2, k),))
+        radius, K = rnd.choice([0.05, 0.2, 0.5, 1.5]), rnd.choice([1, 8, 32, 64, 128, 300])
+        assert torch.equal(_C.ball_query_cuda(q, r, radius, K), ref.ball_query_cuda(q, r, radius, K)), \
+            "ball query %s" % ((kind, B, n1, n2, radius, K),)
+    for _ in range(8):
+        kind = rnd.choice([0, 1, 3])  # exact ties are broken differently by the reference (lowest thread)
+        B, n = rnd.choice([1, 2, 3]), rnd.choice([16385, 20000, 33333, 65536, 70000, 131072])
+        s = rnd.choice([1, 7, 64, 200])
+        p = cloud(B, n, kind).to(DEV)
+        assert torch.equal(_C.sample_farthest_points_cuda(p, s), ref.sample_farthest_points_cuda(p, s)), \
+            "fps %s" % ((kind, B, n, s),)
