@@ -415,6 +415,29 @@ def extras(dev, rank, world, flush):
     out["feature_knn_pair_channels_per_sec"] = x.size(0) * 1024 * 1024 * 64 / (ms * 1e-3)
     xt = x.transpose(1, 2)
     out["feature_knn_cdist_topk_ms"] = t(lambda: torch.topk(torch.cdist(xt, xt), 20, dim=2, largest=False), steps=10)
+    del x, xt, pts, ind
+    # beyond the five configurations: large k (radix selection) and clouds beyond one block (cluster FPS)
+    q4, r4 = [batch_shard(v[:8], rank, world).to(dev) for v in workloads.c2_knn()]
+    out["knn_k200_ms"] = t(lambda: knn_points(q4, r4, 200), steps=5)
+    gen = torch.Generator().manual_seed(9)
+    big = batch_shard(torch.rand(8, 65536, 3, generator=gen), rank, world).to(dev)
+    out["fps_65536_to_2048_ms"] = t(lambda: sample_farthest_points(big, 2048), steps=3)
+    del q4, r4, big
+    if world > 1:
+        # hardware check of the query-slab sharding: every rank interpolates its slab of a small
+        # scene, the slabs are gathered and compared with the unsharded result on every rank
+        qs, rs, fs = [v.to(dev) for v in workloads.c5_scene_interp(B=2, NQ=2048 * world, NR=4096, C=16, seed=11)]
+        d, i = knn_points(qs, rs, 3)
+        whole = interpolate_feature(fs, i, three_nn_weight(d))
+        mine_q = query_slab(qs, rank, world).contiguous()
+        dm, im = knn_points(mine_q, rs, 3)
+        part = interpolate_feature(fs, im, three_nn_weight(dm)).contiguous()
+        parts = [torch.empty_like(part) for _ in range(world)]
+        idxs = [torch.empty_like(im) for _ in range(world)]
+        dist.all_gather(parts, part)
+        dist.all_gather(idxs, im)
+        out["c5_slabs_equal_unsharded"] = bool(torch.equal(torch.cat(idxs, 1), i)
+                                               and torch.allclose(torch.cat(parts, 2), whole, rtol=1e-5, atol=1e-6))
     return out
 
 
