@@ -17,8 +17,8 @@
 // over (distance bits, index) as one 64-bit word, run by the eight warps together on the lists in
 // shared memory, puts them in the (distance, index) order every other path emits.
 //
-// Three to five sweeps of the plain distance (8 FP32 instructions per pair) are far from the FP32
-// roofline, but they cost nearly the same for every k and every key order: 4 x 4096 x 4096 with
+// Three to five sweeps of the plain distance (two keys per packed FP32 instruction) are far from the
+// FP32 roofline, but they cost nearly the same for every k and every key order: 4 x 4096 x 4096 with
 // k = 200 takes a fraction of a millisecond where the heap kernel took 10.8 ms (the reference's
 // bounded-set kernel, torkit3d/csrc/cuda/knn_distance_kernel.cu:102-177 with
 // torkit3d/csrc/include/mink.cuh:61-89, 8.6 ms).  A NaN distance (a NaN coordinate) is given the
@@ -43,11 +43,11 @@ __device__ __forceinline__ unsigned sel_bits(float d) {
 // smem: [hist 256 x 32 ints | list n2 x 32 u64] (the list aliases the histogram) + tiles
 __global__ void __launch_bounds__(SEL_THREADS)
 knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2, int k, int n2,
-                  float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
+                  float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl, float one) {
   extern __shared__ __align__(16) unsigned char sel_smem[];
   int *hist = reinterpret_cast<int *>(sel_smem);                                // [256][32]
   unsigned long long *list = reinterpret_cast<unsigned long long *>(sel_smem);  // [n2][32], after the histograms
-  __shared__ float4 tile[2][SEL_TILE];
+  __shared__ float4 tile[2][SEL_TILE];  // key pair p: [2p] = (x0, x1, y0, y1), [2p+1] = (z0, z1, -, -)
   __shared__ int tcount[2][SEL_SPLIT][32];
   __shared__ int psum[SEL_SPLIT][32];
   __shared__ int cless[32];
@@ -62,6 +62,12 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
     float qx = 0.f, qy = 0.f, qz = 0.f;
     if (valid) load_xyz(query + b * 3 * (int64_t)N1, i, ql, qx, qy, qz);
     const float *rb = key + b * (int64_t)N2 * 3;
+    // The distance of TWO keys per instruction on the packed FP32 pipe: key - query as key + (-query),
+    // packed squares, and the two sums as fma(x, one, y) with `one` = 1.0f from a kernel argument --
+    // round(x * 1 + y) = round(x + y), and a multiplier the compiler cannot see keeps it from fusing
+    // the squares into the sums (see the note in fps.cu).  Bit for bit ((dx*dx + dy*dy) + dz*dz).
+    const float2 nqx = make_float2(-qx, -qx), nqy = make_float2(-qy, -qy), nqz = make_float2(-qz, -qz);
+    const float2 one2 = make_float2(one, one);
 
     // One sweep over the keys: tiles are staged by the whole block (next tile fetched into
     // registers while the current one is used), `body(u, j, bits)` sees every key of this warp's
@@ -79,7 +85,13 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
       };
       auto commit = [&](float4 *dst) {
 #pragma unroll
-        for (int p = 0; p < SEL_TILE / SEL_THREADS; ++p) dst[tid + p * SEL_THREADS] = nxt[p];
+        for (int p = 0; p < SEL_TILE / SEL_THREADS; ++p) {
+          const int u = tid + p * SEL_THREADS;
+          float *f = reinterpret_cast<float *>(dst) + (u >> 1) * 8 + (u & 1);
+          f[0] = nxt[p].x;
+          f[2] = nxt[p].y;
+          f[4] = nxt[p].z;
+        }
       };
       fetch(0);
       commit(tile[0]);
@@ -90,9 +102,15 @@ knn_select_kernel(const float *__restrict__ query, const float *__restrict__ key
         if (t + 1 < ntiles) fetch((t + 1) * SEL_TILE);
         const int lim = min(SEL_QK, N2 - t0);  // <= 0 for slices beyond the cloud
 #pragma unroll 4
-        for (int u = 0; u < lim; ++u) {
-          const float4 r = tl[u];
-          body(u, t0 + u, sel_bits(sqdist<float>(r.x, r.y, r.z, qx, qy, qz)));
+        for (int u = 0; u < lim; u += 2) {
+          const float4 A = tl[u];
+          const float2 kz = *reinterpret_cast<const float2 *>(tl + u + 1);
+          const float2 dx = __fadd2_rn(make_float2(A.x, A.y), nqx), dy = __fadd2_rn(make_float2(A.z, A.w), nqy);
+          const float2 dz = __fadd2_rn(kz, nqz);
+          const float2 d =
+              __ffma2_rn(__ffma2_rn(__fmul2_rn(dx, dx), one2, __fmul2_rn(dy, dy)), one2, __fmul2_rn(dz, dz));
+          body(u, t0 + u, sel_bits(d.x));
+          if (u + 1 < lim) body(u + 1, t0 + u + 1, sel_bits(d.y));
         }
         if (t + 1 < ntiles) commit(tile[(t + 1) & 1]);
         tile_end(t, t0);
@@ -255,7 +273,7 @@ int knn_select_f32(const float *query, const float *key, int64_t B, int N1, int 
   const int64_t total = B * ((N1 + 31) / 32);
   const int64_t cap = (int64_t)sm_count() * 32;
   knn_select_kernel<<<(unsigned)(total < cap ? total : cap), SEL_THREADS, smem, st>>>(query, key, B, N1, N2, k, n2, dist,
-                                                                                    index, total, ql, kl);
+                                                                                    index, total, ql, kl, 1.0f);
   return check_launch("knn_select_kernel");
 }
 
