@@ -74,3 +74,36 @@ def test_graph_set_abstraction_front_end():
     want = chain()
     assert torch.equal(got[0], want[0])
     assert torch.equal(got[1], want[1])
+
+
+def test_graph_large_k_small_ball_and_large_cloud_fps():
+    """The kernels with several phases or a cluster launch inside one call -- radix-selection KNN
+    (histogram sweeps, vote, collect, sort), the hit-mask ball query for few queries and the
+    cluster FPS of a cloud beyond one block -- captured WITHOUT a warm-up call of these shapes
+    before the capture (the first call of a kernel may raise its shared-memory limit or opt into
+    the large cluster size while capturing), then replayed on new values."""
+    gen = torch.Generator().manual_seed(321)
+    q = torch.randn(2, 300, 3, generator=gen).to(DEV)
+    r = torch.randn(2, 3000, 3, generator=gen).to(DEV)
+    big = torch.rand(1, 70000, 3, generator=gen).to(DEV)
+
+    def chain():
+        d, i = _C.knn_distance_cuda(q, r, 150, 0)
+        bq = _C.ball_query_cuda(q, r, 0.6, 100)
+        fp = _C.sample_farthest_points_cuda(big, 40)
+        return d, i, bq, fp
+
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = chain()
+    for _ in range(2):
+        q.copy_(torch.randn(q.shape, generator=gen))
+        r.copy_(torch.randn(r.shape, generator=gen))
+        big.copy_(torch.rand(big.shape, generator=gen))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = [o.clone() for o in outs]
+        want = chain()
+        for g, w in zip(got, want):
+            assert torch.equal(g, w)
