@@ -69,4 +69,33 @@ def test_bounds_build_counts_no_violation_and_matches_the_regular_build():
             both(knn)
             both(ball)
             both(chamfer)
+    # farthest point sampling: one block per cloud (registers / shared memory), a cluster of blocks
+    # per cloud, the streaming kernel; ball query with more neighbours than one tile can give
+    for (B, n, s, dt) in ((3, 1025, 129, torch.float32), (2, 9000, 100, torch.float32), (2, 20000, 60, torch.float32),
+                          (1, 70001, 30, torch.float32), (1, 140000, 12, torch.float32), (2, 3000, 70, torch.float64)):
+        code = _lib.F32 if dt == torch.float32 else _lib.F64
+        p = torch.rand(B, n, 3, generator=g, dtype=dt).to(DEV)
+        for cf in (0, 1):
+            pp = p.transpose(1, 2).contiguous() if cf else p
+
+            def fps(lib):
+                need = lib.tk3d_fps_scratch_bytes(B, n, code)
+                scr = torch.empty(max(need, 1), dtype=torch.uint8, device=DEV)
+                i = torch.empty(B, s, dtype=torch.int64, device=DEV)
+                c = torch.empty((B, 3, s) if cf else (B, s, 3), dtype=dt, device=DEV)
+                assert lib.tk3d_fps_gather(pp.data_ptr(), B, n, s, cf, i.data_ptr(), c.data_ptr(),
+                                           scr.data_ptr() if need else None, need, code, st) == 0
+                return i, c
+
+            both(fps)
+    q = torch.rand(2, 100, 3, generator=g).to(DEV)
+    r = torch.rand(2, 2000, 3, generator=g).to(DEV)
+
+    def wide_ball(lib):
+        i = torch.empty(2, 100, 300, dtype=torch.int32, device=DEV)
+        assert lib.tk3d_ball_query_layout(q.data_ptr(), r.data_ptr(), 2, 100, 2000, 0.5, 300, 0, i.data_ptr(), _lib.I32,
+                                          _lib.F32, st) == 0
+        return (i,)
+
+    both(wide_ball)
     assert chk.tk3d_bounds_violations() == 0
