@@ -153,3 +153,27 @@ def test_group_and_interpolate(B, C, n1, n2, k):
                       (scrb, "group bwd scratch", False), (o3, "interp out", True), (scr3, "interp scratch", False),
                       (gi3, "interp grad", True), (scr3b, "interp bwd scratch", False)):
         t.check(nm, written=wr)
+
+
+@pytest.mark.parametrize("B,C,n1,n2,k", [(2, 64, 1024, 256, 16), (3, 7, 333, 50, 5), (2, 128, 4100, 9000, 3), (1, 512, 64, 40, 16)])
+@pytest.mark.parametrize("i32", [0, 1])
+def test_features_kept_as_rows(B, C, n1, n2, k, i32):
+    L, lib = _lib()
+    f = torch.randn(B, C, n1, device=DEV)
+    rows = Banded((B, n1, C), torch.float32)
+    assert lib.tk3d_feature_rows(f.data_ptr(), B, C, n1, rows.ptr(), L.F32, _st()) == 0
+    it = torch.int32 if i32 else torch.int64
+    code = L.I32 if i32 else L.I64
+    idx = torch.randint(0, n1, (B, n2, k), device=DEV).to(it)
+    out = Banded((B, C, n2, k), torch.float32)
+    assert lib.tk3d_group_fwd_rows(rows.ptr(), idx.data_ptr(), code, B, C, n1, n2, k, out.ptr(), None, L.F32, _st()) == 0
+    idx3 = torch.randint(0, n1, (B, n2, 3), device=DEV).to(it)
+    w = torch.rand(B, n2, 3, device=DEV)
+    o3 = Banded((B, C, n2), torch.float32)
+    assert lib.tk3d_interp_fwd_rows(rows.ptr(), idx3.data_ptr(), code, w.data_ptr(), B, C, n1, n2, 3, o3.ptr(), None,
+                                    L.F32, _st()) == 0
+    torch.cuda.synchronize()
+    rows.check("rows")
+    out.check("group out")
+    o3.check("interp out")
+    assert torch.equal(rows.view, f.transpose(1, 2).contiguous())
