@@ -180,9 +180,10 @@ def weights_np(d, eps):
     return (inv / s[..., None]).astype(np.float32)
 
 
-# (1, 260000, 1500, 4): about one full round of 256-query blocks per SM
+# (1, 260000, 1500, 4): about one full round of 256-query blocks per SM; (2, 60000, 900, 4): less than
+# one round, where two lanes share a query
 @pytest.mark.parametrize("B,nq,nk,C", [(2, 1000, 300, 64), (2, 1001, 257, 6), (1, 4096, 1024, 256), (3, 50, 3, 16),
-                                       (1, 260000, 1500, 4)])
+                                       (1, 260000, 1500, 4), (2, 60000, 900, 4)])
 @pytest.mark.parametrize("channel_first", [True, False])
 def test_three_nn_interp_forward(oracle, B, nq, nk, C, channel_first):
     g = torch.Generator().manual_seed(61)

@@ -280,6 +280,29 @@ def test_knn_keys_with_nan_coordinates_order_last(oracle, n1, n2, k, dtype):
 
 
 @pytest.mark.parametrize("k", [1, 2, 3, 4])
+@pytest.mark.parametrize("n2", [700, 3001])
+def test_knn_small_two_lanes_per_query_bit_exact(oracle, k, n2):
+    """Less than one round of 256-query blocks (here 100000 queries: about 2.6 blocks per SM): two
+    lanes share a query, sweep alternate key groups and merge their lists; a lattice gives exact
+    ties across the two lanes' groups, which must still resolve to the lowest index."""
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(70 + k)
+    q = (rng.integers(-30, 31, size=(2, 50000, 3)) / 8).astype(np.float32)
+    r = (rng.integers(-30, 31, size=(2, n2, 3)) / 8).astype(np.float32)
+    d, i = knn_points(T(q), T(r), k, sorted=True)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+    q2 = rng.standard_normal((1, 90001, 3)).astype(np.float32)
+    r2 = rng.standard_normal((1, 1234, 3)).astype(np.float32)
+    d, i = knn_points(T(q2), T(r2), k, sorted=True)
+    e, j = oracle.knn(q2, r2, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
+@pytest.mark.parametrize("k", [1, 2, 3, 4])
 def test_knn_small_full_round_of_blocks_bit_exact(oracle, k):
     """Two queries per thread, about one full round of 256-query blocks per SM (1016 blocks), with ties."""
     from torkit3d_b200.ops import knn_points
