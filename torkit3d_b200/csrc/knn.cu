@@ -1057,9 +1057,11 @@ int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2,
                 cudaStream_t st) {
   const int64_t sms = sm_count();
   const int64_t nq = B * (int64_t)N1;
-  // Less than one round of 256-query tasks (seven per SM): two lanes per query, i.e. twice the
-  // warps (C5's query slab of an 8-GPU run, 8 x 16384 x 32768: 1.16 -> 1.07 ms).
-  if (nq >= sms * 2 * KN_THREADS * 2 && nq < sms * 7 * KN_THREADS * 2)
+  // At most half a round of 256-query tasks (seven per SM make a round): two lanes per query, i.e.
+  // twice the warps and still one round (C5's query slab of an 8-GPU run, 8 x 16384 x 32768: 1.16 ->
+  // 1.07 ms; 16 x 8192 x 8192, k = 1: 0.29 -> 0.25 ms).  Closer to a full round the doubled tasks spill
+  // into a second one (8 x 32000 x 32768, k = 3: 1.81 -> 2.03 ms), so those stay as they are.
+  if (nq >= sms * 2 * KN_THREADS * 2 && 2 * nq <= sms * 7 * KN_THREADS * 2)
     return knn_small<K, 2, true>(query, key, B, N1, N2, dist, io, st);
   if (nq >= sms * 2 * KN_THREADS * 2) return knn_small<K, 2>(query, key, B, N1, N2, dist, io, st);
   return knn_small<K, 1>(query, key, B, N1, N2, dist, io, st);
@@ -1118,7 +1120,7 @@ int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t 
   fu.index32 = index32;
   const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
   const int64_t sms = sm_count();
-  if (B * N1 >= sms * 2 * KN_THREADS * 2 && B * N1 < sms * 7 * KN_THREADS * 2)  // less than one round: two lanes per query
+  if (B * N1 >= sms * 2 * KN_THREADS * 2 && 2 * B * N1 <= sms * 7 * KN_THREADS * 2)  // at most half a round: two lanes per query
     return three_nn_fused_q<2, true>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
   if (B * N1 >= sms * 2 * KN_THREADS * 2)
     return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
