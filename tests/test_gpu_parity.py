@@ -302,6 +302,23 @@ def test_knn_small_two_lanes_per_query_bit_exact(oracle, k, n2):
     np.testing.assert_array_equal(N(d), e)
 
 
+@pytest.mark.parametrize("k", [1, 3, 4])
+@pytest.mark.parametrize("B,n1,n2", [(2, 20000, 1500), (2, 5000, 2600), (1, 1500, 5000), (1, 77, 9000)])
+def test_knn_small_several_lanes_per_query_bit_exact(oracle, k, B, n1, n2):
+    """Few queries: 2, 4 or 8 lanes share a query (40000, 10000, 1500 and 77 queries here), sweep
+    every 2nd / 4th / 8th key group and merge their lists in butterfly steps; lattice clouds give
+    exact ties across the lanes' groups, which must resolve to the lowest index."""
+    from torkit3d_b200.ops import knn_points
+
+    rng = np.random.default_rng(90 + k + n1)
+    q = (rng.integers(-20, 21, size=(B, n1, 3)) / 4).astype(np.float32)
+    r = (rng.integers(-20, 21, size=(B, n2, 3)) / 4).astype(np.float32)
+    d, i = knn_points(T(q), T(r), k, sorted=True)
+    e, j = oracle.knn(q, r, k)
+    np.testing.assert_array_equal(N(i), j)
+    np.testing.assert_array_equal(N(d), e)
+
+
 @pytest.mark.parametrize("k", [1, 2, 3, 4])
 def test_knn_small_full_round_of_blocks_bit_exact(oracle, k):
     """Two queries per thread, about one full round of 256-query blocks per SM (1016 blocks), with ties."""

@@ -56,13 +56,14 @@ struct KnnFused {
   int32_t *index32;
 };
 
-// HALF: two lanes per query.  Lanes l and l + 16 of a warp hold the same Q queries and sweep
-// alternate key groups of every tile, each into its own sorted list; once per tile they exchange
-// their thresholds (the partner's k-th distance bounds the query's k-th distance as well as the
-// lane's own), and at the end the two lists are merged by (distance, index).  Same pairs per
-// shared-memory load, same staging, but twice the warps for a given number of queries: for launches
-// of less than one round of tasks, whose time is the critical path of a single warp.
-template <int K, int Q, bool FUSED = false, bool HALF = false>
+// LANES > 1: several lanes per query.  The LANES lanes l, l + 32/LANES, ... of a warp hold the same
+// Q queries and sweep every LANES-th key group of each tile, each into its own sorted list; once
+// per tile they exchange the smallest of their k-th distances (any lane's k-th distance bounds the
+// query's k-th distance as well as its own), and at the end the lists are merged by (distance,
+// index) in log2(LANES) butterfly steps.  Same pairs per shared-memory load, same staging, but
+// LANES times the warps for a given number of queries: for launches that cannot fill the GPU with
+// one lane per query, whose time is the critical path of a single warp.
+template <int K, int Q, bool FUSED = false, int LANES = 1>
 __global__ void __launch_bounds__(KN_THREADS)
 knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
                  float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl,
@@ -71,20 +72,22 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
   constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
   __shared__ float4 tile[2][TILE];  // pair layout of sweep.cuh
   const int tid = threadIdx.x;
-  constexpr int QPB = HALF ? KN_THREADS * Q / 2 : KN_THREADS * Q;  // queries per block
+  constexpr bool HALF = LANES > 1;
+  constexpr int QL = 32 / LANES;                      // distinct queries (per s) in a warp
+  constexpr int QPB = KN_THREADS * Q / LANES;         // queries per block
   const int chunks = (N1 + QPB - 1) / QPB;
-  const int half = HALF ? (tid >> 4) & 1 : 0;  // which of the two lanes of a query this is
+  const int half = (tid & 31) / QL;                   // which of a query's LANES lanes this is
 
   for (int64_t blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
     const int64_t b = blk / chunks;
     const int i0 = (int)(blk % chunks) * QPB;
     // query s of this thread
     auto qindex = [&](int s) {
-      if (HALF) return i0 + (tid >> 5) * (16 * Q) + s * 16 + (tid & 15);
+      if (HALF) return i0 + (tid >> 5) * (QL * Q) + s * QL + (tid & (QL - 1));
       return i0 + tid + s * KN_THREADS;
     };
     float qx[Q], qy[Q], qz[Q], thr[Q];
-    float pthr[Q];  // HALF: the partner lane's threshold at the last exchange
+    float pthr[Q];  // LANES > 1: threshold from the other lanes' k-th distances at the last exchange
     float2 mx[Q], my[Q], mz[Q];
     float kd[Q][K];
     int ki[Q][K];
@@ -128,16 +131,18 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
 #pragma unroll
         for (int p = 0; p < PER; ++p) nxt[p] = make_key(rb, t0 + TILE + tid + p * KN_THREADS, N2, kl);
       }
-      constexpr int STEP = HALF ? 2 * GK : GK;  // HALF: the two lanes of a query take alternate groups
+      constexpr int STEP = LANES * GK;  // the lanes of a query take every LANES-th group
       const int lim = (min(TILE, N2 - t0) + STEP - 1) / STEP * STEP;
-      // HALF: the partner's k-th entry bounds this query's k-th entry too.  A key of this lane's
-      // groups AT the partner's k-th distance may still precede it by index, so the bound is taken
-      // one ulp above that distance: the filter guarantees a pass for d < bound only.  Once per
-      // tile: exchanging four times per tile measured 20 % slower (it breaks up the unrolled loop).
+      // LANES > 1: another lane's k-th entry bounds this query's k-th entry too.  A key of this
+      // lane's groups AT that distance may still precede it by index, so the bound is taken one
+      // ulp above it: the filter guarantees a pass for d < bound only.  Once per tile: exchanging
+      // four times per tile measured 20 % slower (it breaks up the unrolled loop).
       auto exchange = [&]() {
 #pragma unroll
         for (int s = 0; s < Q; ++s) {
-          const float pk = __shfl_xor_sync(0xffffffffu, kd[s][K - 1], 16);
+          float pk = kd[s][K - 1];  // smallest k-th distance among the query's lanes (a NaN is never smaller)
+#pragma unroll
+          for (int o = QL; o < 32; o <<= 1) pk = fminf(pk, __shfl_xor_sync(0xffffffffu, pk, o));
           const float up = pk < pinf() ? __uint_as_float(__float_as_uint(pk) + 1u) : pk;  // pk >= +0 or NaN
           pthr[s] = pk == pk ? sweep_threshold(up, sweep_qq(qx[s], qy[s], qz[s])) : pinf();
           thr[s] = fminf(thr[s], pthr[s]);
@@ -202,15 +207,18 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
     }
 
     if constexpr (HALF) {
-      // merge the two lanes' sorted lists by (distance, index); both lanes end up with the result
+      // merge the lanes' sorted lists by (distance, index) in butterfly steps; every lane ends up
+      // with the result
+#pragma unroll
+      for (int o = QL; o < 32; o <<= 1) {
 #pragma unroll
       for (int s = 0; s < Q; ++s) {
         float od_[K];
         int oi_[K];
 #pragma unroll
         for (int c = 0; c < K; ++c) {
-          od_[c] = __shfl_xor_sync(0xffffffffu, kd[s][c], 16);
-          oi_[c] = __shfl_xor_sync(0xffffffffu, ki[s][c], 16);
+          od_[c] = __shfl_xor_sync(0xffffffffu, kd[s][c], o);
+          oi_[c] = __shfl_xor_sync(0xffffffffu, ki[s][c], o);
         }
         float rd[K];
         int ri[K];
@@ -242,6 +250,7 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
           kd[s][c] = rd[c];
           ki[s][c] = ri[c];
         }
+      }
       }
     }
 
@@ -1041,15 +1050,33 @@ int knn_generic(const T *query, const T *key, int64_t B, int64_t N1, int64_t N2,
   return check_launch("knn_generic_kernel");
 }
 
-template <int K, int Q, bool HALF = false>
+template <int K, int Q, int LANES = 1>
 int knn_small(const float *query, const float *key, int64_t B, int N1, int N2, float *dist, const KnnIo &io,
               cudaStream_t st) {
-  const int64_t per = HALF ? KN_THREADS * Q / 2 : KN_THREADS * Q;
+  const int64_t per = KN_THREADS * Q / LANES;
   const int64_t total = B * ((N1 + per - 1) / per);
   const int64_t cap = (int64_t)sm_count() * 256;
-  knn_small_kernel<K, Q, false, HALF><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
+  knn_small_kernel<K, Q, false, LANES><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
       query, key, B, N1, N2, dist, io.index, total, io.ql, io.kl, KnnFused{});
   return check_launch("knn_small_kernel");
+}
+
+// Lanes per query for launches with one query per thread (fewer than about 75 000 queries).  Measured
+// on B200 (148 SMs), k = 1 / k = 3, in ms:
+//   queries   1 lane        2 lanes       4 lanes       8 lanes        (queries x keys)
+//   65536     0.34 / 0.47   0.31 / 0.47   0.57 / 0.67                  4 x 16384 x 16384
+//   40000     0.029/ 0.057  0.027/ 0.049  0.028/ 0.055  0.040/ 0.063   4 x 10000 x 512
+//   32768     0.039/ 0.079  0.033/ 0.067  0.030/ 0.055  0.053/ 0.078   32 x 1024 x 1024
+//   16384     0.055/ 0.112  0.040/ 0.081  0.034/ 0.061  0.046/ 0.061   8 x 2048 x 2048
+//    8192     0.43 / 0.64   0.28 / 0.35   0.21 / 0.27   0.33 / 0.35    2 x 4096 x 32768
+//    2048     0.159/ 0.276  0.108/ 0.169  0.071/ 0.116  0.053/ 0.089   4 x 512 x 10000
+//    1000     1.16 / 1.58   0.76 / 0.78   0.51 / 0.57   0.40 / 0.46    1 x 1000 x 100000
+inline int lanes_per_query(int64_t nq) {
+  const int64_t sms = sm_count();
+  if (nq * 3 > sms * 1000) return 1;   // above about 49 000 queries on 148 SMs
+  if (nq * 6 > sms * 1000) return 2;   // above about 24 600
+  if (nq * 48 > sms * 1000) return 4;  // above about 3 000
+  return 8;
 }
 
 template <int K>
@@ -1062,18 +1089,23 @@ int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2,
   // 1.07 ms; 16 x 8192 x 8192, k = 1: 0.29 -> 0.25 ms).  Closer to a full round the doubled tasks spill
   // into a second one (8 x 32000 x 32768, k = 3: 1.81 -> 2.03 ms), so those stay as they are.
   if (nq >= sms * 2 * KN_THREADS * 2 && 2 * nq <= sms * 7 * KN_THREADS * 2)
-    return knn_small<K, 2, true>(query, key, B, N1, N2, dist, io, st);
+    return knn_small<K, 2, 2>(query, key, B, N1, N2, dist, io, st);
   if (nq >= sms * 2 * KN_THREADS * 2) return knn_small<K, 2>(query, key, B, N1, N2, dist, io, st);
-  return knn_small<K, 1>(query, key, B, N1, N2, dist, io, st);
+  switch (lanes_per_query(nq)) {
+    case 8: return knn_small<K, 1, 8>(query, key, B, N1, N2, dist, io, st);
+    case 4: return knn_small<K, 1, 4>(query, key, B, N1, N2, dist, io, st);
+    case 2: return knn_small<K, 1, 2>(query, key, B, N1, N2, dist, io, st);
+    default: return knn_small<K, 1>(query, key, B, N1, N2, dist, io, st);
+  }
 }
 
-template <int Q, bool HALF = false>
+template <int Q, int LANES = 1>
 int three_nn_fused_q(const float *query, const float *key, int64_t B, int N1, int N2, const KnnFused &fu,
                      XyzLayout ql, XyzLayout kl, cudaStream_t st) {
-  const int64_t per = HALF ? KN_THREADS * Q / 2 : KN_THREADS * Q;
+  const int64_t per = KN_THREADS * Q / LANES;
   const int64_t total = B * ((N1 + per - 1) / per);
   const int64_t cap = (int64_t)sm_count() * 256;
-  knn_small_kernel<3, Q, true, HALF><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
+  knn_small_kernel<3, Q, true, LANES><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
       query, key, B, N1, N2, nullptr, index_out(nullptr, 0, 0), total, ql, kl, fu);
   return check_launch("knn_small_kernel (fused weights)");
 }
@@ -1121,10 +1153,15 @@ int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t 
   const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
   const int64_t sms = sm_count();
   if (B * N1 >= sms * 2 * KN_THREADS * 2 && 2 * B * N1 <= sms * 7 * KN_THREADS * 2)  // at most half a round: two lanes per query
-    return three_nn_fused_q<2, true>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+    return three_nn_fused_q<2, 2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
   if (B * N1 >= sms * 2 * KN_THREADS * 2)
     return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
-  return three_nn_fused_q<1>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+  switch (lanes_per_query(B * N1)) {
+    case 8: return three_nn_fused_q<1, 8>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+    case 4: return three_nn_fused_q<1, 4>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+    case 2: return three_nn_fused_q<1, 2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+    default: return three_nn_fused_q<1>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+  }
 }
 
 }  // namespace tk3d
