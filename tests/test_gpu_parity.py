@@ -50,6 +50,29 @@ def test_chamfer_forward_bit_exact(oracle, B, n1, n2, dtype):
     np.testing.assert_array_equal(d2, e2)
 
 
+# Few queries: 2, 4 or 8 lanes share a query; clouds of very different sizes: one launch per
+# direction, each with its own shape.  Lattice clouds give exact ties across the lanes' key groups.
+@pytest.mark.parametrize("B,n1,n2", [(2, 1024, 1024), (4, 4096, 4096), (6, 1000, 3000), (1, 300, 50000), (2, 30000, 777),
+                                     (1, 17, 9000), (3, 9000, 2), (2, 70000, 1000), (1, 8192, 8192)])
+@pytest.mark.parametrize("lattice", [False, True])
+def test_chamfer_forward_few_queries_and_unequal_clouds(oracle, B, n1, n2, lattice):
+    from torkit3d_b200.ops import nn_distance
+
+    rng = np.random.default_rng(B * 77 + n1 + n2)
+    if lattice:
+        a = (rng.integers(-12, 13, size=(B, n1, 3)) / 4).astype(np.float32)
+        b = (rng.integers(-12, 13, size=(B, n2, 3)) / 4).astype(np.float32)
+    else:
+        a = rng.standard_normal((B, n1, 3)).astype(np.float32)
+        b = rng.standard_normal((B, n2, 3)).astype(np.float32)
+    d1, i1, d2, i2 = [N(t) for t in nn_distance(T(a), T(b))]
+    e1, j1, e2, j2 = oracle.chamfer_fwd(a, b)
+    np.testing.assert_array_equal(i1, j1)
+    np.testing.assert_array_equal(i2, j2)
+    np.testing.assert_array_equal(d1, e1)
+    np.testing.assert_array_equal(d2, e2)
+
+
 # At least 148 * 512 queries but no more than two rounds of 256-query tasks per SM: the launcher
 # runs these as one 896-thread block per SM (seven independent 128-thread groups).
 SM_WIDE_SHAPES = [(3, 20001, 9999), (1, 100000, 3), (2, 70000, 0), (8, 16384, 16384), (16, 4097, 5003),

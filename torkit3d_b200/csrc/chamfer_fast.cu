@@ -60,7 +60,14 @@ __device__ __forceinline__ void chamfer_verify(const float4 *tl, int u0, int t0,
   }
 }
 
-template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128>
+// LANES > 1: several lanes per query, for launches that cannot fill the GPU with one lane per query
+// (their time is the critical path of a single warp).  The LANES lanes l, l + 32/LANES, ... of a
+// warp hold the same Q queries and sweep every LANES-th key group of each tile; once per tile they
+// exchange the smallest of their best distances -- any lane's best bounds the query's nearest
+// distance; taken one ulp higher, because a key AT that distance with a lower index must still pass
+// this lane's filter -- and at the end the best (distance, index) of all lanes is kept.  Same pairs
+// per shared-memory load, LANES times the warps.
+template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128, int LANES = 1>
 __global__ void __launch_bounds__(CF_THREADS, MINB)
 chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict__ xyz2, int64_t B, int N1, int N2,
                         float *__restrict__ dist1, int64_t *__restrict__ idx1, float *__restrict__ dist2,
@@ -82,16 +89,25 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
     const int nq = dir ? N2 : N1;
     const int nr = dir ? N1 : N2;
     const XyzLayout lq = dir ? l2 : l1, lr = dir ? l1 : l2;
-    const int chunks = (nq + CF_THREADS * Q - 1) / (CF_THREADS * Q);
+    constexpr int QL = 32 / LANES;                 // distinct queries (per s) in a warp
+    constexpr int QPB = CF_THREADS * Q / LANES;    // queries per block
+    const int chunks = (nq + QPB - 1) / QPB;
     const int64_t b = id / chunks;
-    const int i0 = (int)(id % chunks) * (CF_THREADS * Q) + tid;
+    const int i0 = (int)(id % chunks) * QPB;
+    const int part = (tid & 31) / QL;              // which of a query's LANES lanes this is
+    auto qindex = [&](int s) {
+      if (LANES > 1) return i0 + (tid >> 5) * (QL * Q) + s * QL + (tid & (QL - 1));
+      return i0 + tid + s * CF_THREADS;
+    };
 
     float qx[Q], qy[Q], qz[Q], thr[Q], best[Q];
+    float pthr[Q];  // LANES > 1: threshold from the lanes' best distances at the last exchange
     float2 mx[Q], my[Q], mz[Q];
     int arg[Q];
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
-      const int i = i0 + s * CF_THREADS;
+      const int i = qindex(s);
+      pthr[s] = pinf;
       best[s] = pinf;
       arg[s] = -1;
       if (i < nq) {
@@ -145,15 +161,33 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
         }
       }
 
-      const int lim = (cnt + GK - 1) / GK * GK;
+      constexpr int STEP = LANES * GK;  // the lanes of a query take every LANES-th group
+      const int lim = (cnt + STEP - 1) / STEP * STEP;
 #pragma unroll UNR
-      for (int u0 = 0; u0 < lim; u0 += GK) {
+      for (int u0 = part * GK; u0 < lim; u0 += STEP) {
         float2 a[4];
         float m[2];
         bool any;
         if constexpr (Q == 2) any = sweep_group2_gated(tl + u0, mx, my, mz, thr, a, m);
         else any = sweep_group2<Q, true>(tl + u0, mx, my, mz, thr, a);
-        if (__builtin_expect(any, 0)) chamfer_verify<Q>(tl, u0, t0, a, m, qx, qy, qz, thr, best, arg);
+        if (__builtin_expect(any, 0)) {
+          chamfer_verify<Q>(tl, u0, t0, a, m, qx, qy, qz, thr, best, arg);
+          if constexpr (LANES > 1) {
+#pragma unroll
+            for (int s = 0; s < Q; ++s) thr[s] = fminf(thr[s], pthr[s]);
+          }
+        }
+      }
+      if constexpr (LANES > 1) {
+#pragma unroll
+        for (int s = 0; s < Q; ++s) {
+          float pk = best[s];  // smallest best distance among the query's lanes (a NaN is never smaller)
+#pragma unroll
+          for (int o = QL; o < 32; o <<= 1) pk = fminf(pk, __shfl_xor_sync(0xffffffffu, pk, o));
+          const float up = pk < pinf ? __uint_as_float(__float_as_uint(pk) + 1u) : pk;  // pk >= +0
+          pthr[s] = sweep_threshold(up, sweep_qq(qx[s], qy[s], qz[s]));
+          thr[s] = fminf(thr[s], pthr[s]);
+        }
       }
 
       if (more) {
@@ -170,21 +204,35 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
       __syncthreads();
     }
 
+    if constexpr (LANES > 1) {  // the best (distance, index) over the lanes, in butterfly steps
+#pragma unroll
+      for (int o = QL; o < 32; o <<= 1) {
+#pragma unroll
+        for (int s = 0; s < Q; ++s) {
+          const float od = __shfl_xor_sync(0xffffffffu, best[s], o);
+          const int oi = __shfl_xor_sync(0xffffffffu, arg[s], o);
+          if (oi >= 0 && (arg[s] < 0 || od < best[s] || (od == best[s] && oi < arg[s]))) {
+            best[s] = od;
+            arg[s] = oi;
+          }
+        }
+      }
+    }
     float *dist = dir ? dist2 : dist1;
     int64_t *idx = dir ? idx2 : idx1;
-    double part = 0.0;
+    double psum = 0.0;
 #pragma unroll
     for (int s = 0; s < Q; ++s) {
-      const int i = i0 + s * CF_THREADS;
-      if (i < nq) {
+      const int i = qindex(s);
+      if (i < nq && part == 0) {
         dist[b * nq + i] = best[s];
         idx[b * nq + i] = (int64_t)arg[s];
-        part += (double)best[s];
+        psum += (double)best[s];
       }
     }
     if (sums != nullptr) {
-      part = warp_sum(part);
-      if ((tid & 31) == 0) ssum[tid >> 5] = part;
+      psum = warp_sum(psum);
+      if ((tid & 31) == 0) ssum[tid >> 5] = psum;
       __syncthreads();
       if (tid == 0) {
         double tot = 0;
@@ -197,16 +245,18 @@ chamfer_fwd_fast_kernel(const float *__restrict__ xyz1, const float *__restrict_
   }
 }
 
-template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128>
+template <int Q, int MINB = 1, int UNR = 2, int CF_THREADS = 128, int LANES = 1>
 int launch(const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1, int64_t *idx1,
-           float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1, XyzLayout l2) {
-  const int64_t per = CF_THREADS * Q;
-  const int64_t blocks1 = B * ((N1 + per - 1) / per), blocks2 = B * ((N2 + per - 1) / per);
+           float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1, XyzLayout l2, int only_dir = -1) {
+  // only_dir: -1 = both directions in this launch, 0 = cloud 1 -> cloud 2 only, 1 = the other one
+  const int64_t per = CF_THREADS * Q / LANES;
+  const int64_t blocks1 = only_dir == 1 ? 0 : B * ((N1 + per - 1) / per);
+  const int64_t blocks2 = only_dir == 0 ? 0 : B * ((N2 + per - 1) / per);
   const int64_t total = blocks1 + blocks2;
   if (total == 0) return TK3D_OK;
   const int64_t cap = (int64_t)sm_count() * 256;
   const unsigned grid = (unsigned)(total < cap ? total : cap);
-  chamfer_fwd_fast_kernel<Q, MINB, UNR, CF_THREADS><<<grid, CF_THREADS, 0, st>>>(
+  chamfer_fwd_fast_kernel<Q, MINB, UNR, CF_THREADS, LANES><<<grid, CF_THREADS, 0, st>>>(
       xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums, blocks1, total, l1, l2);
   return check_launch("chamfer_fwd_fast_kernel");
 }
@@ -386,13 +436,56 @@ const char *chamfer_fwd_f32_kernel_name(int64_t B, int64_t N1, int64_t N2) {
   return names[chamfer_fwd_f32_plan(B, N1, N2)];
 }
 
+// Lanes per query for launches with one query per thread; `nq` counts the queries of both
+// directions of a symmetric problem.  Measured on B200 (148 SMs), forward of both directions, ms:
+//   queries  1 lane   2 lanes  4 lanes  8 lanes    (clouds)
+//   65536    0.062    0.076    0.106    0.177      16 x 2048 x 2048
+//   32768    0.082    0.064    0.098    0.171      4 x 4096 x 4096
+//   24096    0.141    0.091    0.075    0.107      2 x 2048 x 10000
+//   16384    0.035    0.027    0.025    0.034      8 x 1024 x 1024
+//    4096    0.034    0.024    0.024    0.024      2 x 1024 x 1024
+static int chamfer_lanes(int64_t nq) {
+  const int64_t sms = sm_count();
+  if (nq * 3 > sms * 1000) return 1;   // above about 49 000 queries on 148 SMs
+  if (nq * 6 > sms * 1000) return 2;   // above about 24 600
+  if (nq * 48 > sms * 1000) return 4;  // above about 3 000
+  return 8;
+}
+
+// One direction (or both) with one query per thread and the lane count that suits `nq` queries.
+static int launch_lanes(int64_t nq, const float *xyz1, const float *xyz2, int64_t B, int N1, int N2, float *dist1,
+                        int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1,
+                        XyzLayout l2, int only_dir) {
+  switch (chamfer_lanes(nq)) {
+    case 8: return launch<1, 1, 2, 128, 8>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, only_dir);
+    case 4: return launch<1, 1, 2, 128, 4>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, only_dir);
+    case 2: return launch<1, 1, 2, 128, 2>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, only_dir);
+    default: return launch<1, 1, 2>(xyz1, xyz2, B, N1, N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, only_dir);
+  }
+}
+
 int chamfer_fwd_f32_fast(const float *xyz1, const float *xyz2, int64_t B, int64_t N1, int64_t N2, float *dist1,
                          int64_t *idx1, float *dist2, int64_t *idx2, double *sums, cudaStream_t st, XyzLayout l1,
                          XyzLayout l2) {
+  const int64_t sms = sm_count();
+  const int64_t small = B * (N1 < N2 ? N1 : N2), large = B * (N1 < N2 ? N2 : N1);
+  // Clouds of very different sizes: the direction with few queries sweeps the large cloud and is
+  // the critical path, the other one is many queries against few keys.  Each gets its own launch
+  // and its own shape (1 x 300 x 50000: 0.54 -> 0.19 ms).
+  if (small > 0 && large >= 4 * small && 2 * small < sms * 2 * 128 * 2) {
+    const int few = N1 < N2 ? 0 : 1;  // the direction whose queries are the small cloud
+    int rc = launch_lanes(2 * small, xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, few);
+    if (rc) return rc;
+    if (2 * large < sms * 2 * 128 * 2)
+      return launch_lanes(2 * large, xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2,
+                          1 - few);
+    return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, 1 - few);
+  }
   // Measured on B200 (B=64, N=M=16384): two queries per thread, six resident blocks per SM and a
   // four-fold unrolled key loop beat four queries per thread by about 10 %.
   switch (chamfer_fwd_f32_plan(B, N1, N2)) {
-    case 0: return launch<1, 1, 2>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2);
+    case 0:
+      return launch_lanes(B * (N1 + N2), xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2, -1);
     case 1: return launch_smwide(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2);
     default: return launch<2, 6, 4>(xyz1, xyz2, B, (int)N1, (int)N2, dist1, idx1, dist2, idx2, sums, st, l1, l2);
   }
