@@ -1087,8 +1087,10 @@ int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2,
   // At most half a round of 256-query tasks (seven per SM make a round): two lanes per query, i.e.
   // twice the warps and still one round (C5's query slab of an 8-GPU run, 8 x 16384 x 32768: 1.16 ->
   // 1.07 ms; 16 x 8192 x 8192, k = 1: 0.29 -> 0.25 ms).  Closer to a full round the doubled tasks spill
-  // into a second one (8 x 32000 x 32768, k = 3: 1.81 -> 2.03 ms), so those stay as they are.
-  if (nq >= sms * 2 * KN_THREADS * 2 && 2 * nq <= sms * 7 * KN_THREADS * 2)
+  // into a second one (8 x 32000 x 32768, k = 3: 1.81 -> 2.03 ms), so those stay as they are.  With k = 4
+  // the two-lane variant needs 79 registers, six blocks per SM instead of seven, and loses (the same
+  // slab: 1.64 ms with one lane, 2.34 with two; 1.83 with two capped at 72 registers).
+  if (K <= 3 && nq >= sms * 2 * KN_THREADS * 2 && 2 * nq <= sms * 7 * KN_THREADS * 2)
     return knn_small<K, 2, 2>(query, key, B, N1, N2, dist, io, st);
   if (nq >= sms * 2 * KN_THREADS * 2) return knn_small<K, 2>(query, key, B, N1, N2, dist, io, st);
   switch (lanes_per_query(nq)) {
@@ -1152,8 +1154,9 @@ int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t 
   fu.index32 = index32;
   const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
   const int64_t sms = sm_count();
-  if (B * N1 >= sms * 2 * KN_THREADS * 2 && 2 * B * N1 <= sms * 7 * KN_THREADS * 2)  // at most half a round: two lanes per query
-    return three_nn_fused_q<2, 2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
+  // Two queries per thread always run one lane per query here: with the weights fused in, the
+  // two-lane variant needs 79 registers (six blocks per SM, not seven) and is slower (8 x 16384 x
+  // 32768: 1.24 ms against 1.39, or 1.33 when capped at 72 registers).
   if (B * N1 >= sms * 2 * KN_THREADS * 2)
     return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
   switch (lanes_per_query(B * N1)) {
