@@ -561,7 +561,7 @@ def test_ball_query_golden_and_boundary(oracle, golden):
 
 # ------------------------------------------------------------------------------- group / interpolate
 @pytest.mark.parametrize("B,C,n1,n2,k", [(2, 3, 512, 128, 32), (5, 64, 513, 129, 33), (1, 1, 1, 1, 1), (3, 7, 100, 50, 5),
-                                        (4, 32, 2048, 512, 16)])
+                                        (4, 32, 2048, 512, 16), (2, 5, 260, 37, 31), (1, 4, 12288, 64, 32)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 def test_group_points(oracle, B, C, n1, n2, k, dtype):
     from torkit3d_b200.ops import group_points

@@ -101,10 +101,16 @@ class _NoSwitch:
 _NO_SWITCH = _NoSwitch()
 
 
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _on(device):
     """Context that makes ``device`` current; free when it already is (the usual case: the small
-    operators are dominated by host time, and torch.cuda.device() costs several microseconds)."""
-    if device.index is None or device.index == torch.cuda.current_device():
+    operators are dominated by host time, and torch.cuda.device() costs several microseconds).
+    The tensors at hand are CUDA tensors, so the runtime is initialised and the raw getter (a
+    quarter of the cost of torch.cuda.current_device()) may be asked directly."""
+    index = device.index
+    if index is None or index == (_raw_device() if _raw_device is not None else torch.cuda.current_device()):
         return _NO_SWITCH
     return torch.cuda.device(device)
 
@@ -414,16 +420,21 @@ def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None, *, channel_first=False)
     ``sums`` (optional, a float64 CUDA tensor of 2 elements) receives sum(dist1), sum(dist2); it has
     no counterpart in the reference and is what the multi-GPU loss helper reduces.
     """
-    _check_cuda_contig(xyz1=xyz1, xyz2=xyz2)
-    _check_eq(xyz1.dim(), 3, "xyz1.dim() == 3")
-    _check_eq(xyz2.dim(), 3, "xyz2.dim() == 3")
-    _check_eq(xyz1.size(0), xyz2.size(0), "xyz1.size(0) == xyz2.size(0)")
     pdim, cdim = _xyz_dims(channel_first)
-    _check_eq(xyz1.size(cdim), 3, "xyz1.size(%d) == 3" % cdim)
-    _check_eq(xyz2.size(cdim), 3, "xyz2.size(%d) == 3" % cdim)
-    _same_device_dtype(xyz1, xyz2, floats=(xyz2,))
+    s1, s2 = xyz1.shape, xyz2.shape
+    # one combined test for the usual case; the ordered checks only run to name what is wrong
+    if not (xyz1.is_cuda and xyz2.is_cuda and len(s1) == 3 and len(s2) == 3 and s1[0] == s2[0] and s1[cdim] == 3
+            and s2[cdim] == 3 and xyz1.dtype is xyz2.dtype and xyz1.device == xyz2.device and xyz1.is_contiguous()
+            and xyz2.is_contiguous()):
+        _check_cuda_contig(xyz1=xyz1, xyz2=xyz2)
+        _check_eq(xyz1.dim(), 3, "xyz1.dim() == 3")
+        _check_eq(xyz2.dim(), 3, "xyz2.dim() == 3")
+        _check_eq(xyz1.size(0), xyz2.size(0), "xyz1.size(0) == xyz2.size(0)")
+        _check_eq(xyz1.size(cdim), 3, "xyz1.size(%d) == 3" % cdim)
+        _check_eq(xyz2.size(cdim), 3, "xyz2.size(%d) == 3" % cdim)
+        _same_device_dtype(xyz1, xyz2, floats=(xyz2,))
     lib = load()
-    B, N1, N2 = xyz1.size(0), xyz1.size(pdim), xyz2.size(pdim)
+    B, N1, N2 = s1[0], s1[pdim], s2[pdim]
     dev = xyz1.device
     with _on(dev):
         dist1 = torch.empty((B, N1), dtype=xyz1.dtype, device=dev)
@@ -444,14 +455,12 @@ def chamfer_distance_forward_cuda(xyz1, xyz2, sums=None, *, channel_first=False)
     return [dist1, idx1, dist2, idx2]
 
 
-def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, *, channel_first=False):
-    """-> [grad_xyz1 [B,N1,3], grad_xyz2 [B,N2,3]] (the clouds' own layout: [B,3,N] with ``channel_first``)."""
+def _chamfer_backward_checks(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, pdim, cdim):
     _check_cuda_contig(grad_dist1=grad_dist1, grad_dist2=grad_dist2, xyz1=xyz1, xyz2=xyz2, idx1=idx1, idx2=idx2)
     bs, n1, n2 = grad_dist1.size(0), grad_dist1.size(1), grad_dist2.size(1)
     _check_eq(grad_dist2.size(0), bs, "grad_dist2.size(0) == bs")
     _check_eq(xyz1.size(0), bs, "xyz1.size(0) == bs")
     _check_eq(xyz2.size(0), bs, "xyz2.size(0) == bs")
-    pdim, cdim = _xyz_dims(channel_first)
     _check_eq(xyz1.size(pdim), n1, "xyz1.size(%d) == n1" % pdim)
     _check_eq(xyz2.size(pdim), n2, "xyz2.size(%d) == n2" % pdim)
     _check_eq(xyz1.size(cdim), 3, "xyz1.size(%d) == 3" % cdim)
@@ -463,6 +472,22 @@ def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx
     _index(idx1, "idx1")
     _index(idx2, "idx2")
     _same_device_dtype(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, floats=(grad_dist2, xyz1, xyz2))
+
+
+def chamfer_distance_backward_cuda(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, *, channel_first=False):
+    """-> [grad_xyz1 [B,N1,3], grad_xyz2 [B,N2,3]] (the clouds' own layout: [B,3,N] with ``channel_first``)."""
+    pdim, cdim = _xyz_dims(channel_first)
+    sg1, sg2, s1, s2 = grad_dist1.shape, grad_dist2.shape, xyz1.shape, xyz2.shape
+    ok = (len(sg1) == 2 and len(sg2) == 2 and len(s1) == 3 and len(s2) == 3 and idx1.shape == sg1 and idx2.shape == sg2
+          and sg1[0] == sg2[0] == s1[0] == s2[0] and s1[pdim] == sg1[1] and s2[pdim] == sg2[1] and s1[cdim] == 3
+          and s2[cdim] == 3 and idx1.dtype is torch.int64 and idx2.dtype is torch.int64
+          and grad_dist1.dtype is grad_dist2.dtype is xyz1.dtype is xyz2.dtype
+          and grad_dist1.is_cuda and grad_dist1.device == grad_dist2.device == xyz1.device == xyz2.device == idx1.device
+          == idx2.device and grad_dist1.is_contiguous() and grad_dist2.is_contiguous() and xyz1.is_contiguous()
+          and xyz2.is_contiguous() and idx1.is_contiguous() and idx2.is_contiguous())
+    if not ok:  # the ordered checks name what is wrong, in the reference's words
+        _chamfer_backward_checks(grad_dist1, grad_dist2, xyz1, xyz2, idx1, idx2, pdim, cdim)
+    bs, n1, n2 = sg1[0], sg1[1], sg2[1]
     lib = load()
     dev = grad_dist1.device
     with _on(dev):

@@ -129,7 +129,7 @@ group_bwd_kernel(const T *__restrict__ gout, const int64_t *__restrict__ index, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Channel-row forward kernel (fp32, clouds whose N1 floats fit shared memory twice): no transposed
+// Channel-row forward kernel (clouds whose N1 features fit shared memory twice): no transposed
 // copy of the features, no scratch.  (The mirror image for the backward -- gradient rows
 // accumulated with shared-memory reductions -- was measured slower than the vector reductions
 // into a transposed accumulator, 0.18 against 0.12 ms on 32 x 64 x 8192 <- 32768 entries: a
@@ -156,11 +156,13 @@ __device__ __forceinline__ void cr_cp_wait() {
 }
 
 // R rounds of four consecutive entries per thread: a block covers CR_THREADS * 4 * R entries.
-template <typename IndexT, int R, bool VEC>
+template <typename T, typename IndexT, int R, bool VEC>
 __global__ void __launch_bounds__(CR_THREADS)
-group_fwd_chanrow_kernel(const float *__restrict__ in, const IndexT *__restrict__ index, int C, int N1, int64_t E,
-                         int cg, float *__restrict__ out, int32_t *__restrict__ status) {
-  extern __shared__ __align__(16) float cr_rows[];  // [2][N1 + 4]; slots N1..N1+3 of each hold 0
+group_fwd_chanrow_kernel(const T *__restrict__ in, const IndexT *__restrict__ index, int C, int N1, int64_t E,
+                         int cg, T *__restrict__ out, int32_t *__restrict__ status) {
+  extern __shared__ __align__(16) unsigned char cr_raw[];
+  T *cr_rows = reinterpret_cast<T *>(cr_raw);  // [2][N1 + 4]; slots N1..N1+3 of each hold 0
+  constexpr int PER16 = 16 / (int)sizeof(T);   // elements per 16-byte copy
   const int tid = threadIdx.x;
   const int64_t b = blockIdx.z;
   const int c0 = blockIdx.y * cg, c1 = min(C, c0 + cg);
@@ -183,13 +185,13 @@ group_fwd_chanrow_kernel(const float *__restrict__ in, const IndexT *__restrict_
     }
   }
   if (bad && status) atomicOr(status, 1);
-  if (tid < 8) cr_rows[(tid >> 2) * stride + N1 + (tid & 3)] = 0.f;
+  if (tid < 8) cr_rows[(tid >> 2) * stride + N1 + (tid & 3)] = (T)0;
 
-  const float *src = in + (b * C + c0) * (int64_t)N1;
+  const T *src = in + (b * C + c0) * (int64_t)N1;
   auto stage = [&](int c, int buf) {
-    const float *g = src + (int64_t)(c - c0) * N1;
-    float *d = cr_rows + buf * stride;
-    for (int q = tid; q < N1 / 4; q += CR_THREADS) cr_cp_async16(d + 4 * q, g + 4 * q);
+    const T *g = src + (int64_t)(c - c0) * N1;
+    T *d = cr_rows + buf * stride;
+    for (int q = tid; q < N1 / PER16; q += CR_THREADS) cr_cp_async16(d + PER16 * q, g + PER16 * q);
     cr_cp_commit();
   };
   stage(c0, 0);
@@ -202,36 +204,42 @@ group_fwd_chanrow_kernel(const float *__restrict__ in, const IndexT *__restrict_
       cr_cp_wait<0>();
     }
     __syncthreads();
-    const float *row = cr_rows + buf * stride;
-    float *o = out + (b * C + c) * E;
+    const T *row = cr_rows + buf * stride;
+    T *o = out + (b * C + c) * E;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int64_t e = e0 + (int64_t)(r * CR_THREADS + tid) * 4;
       if (e >= E) break;
-      const float4 v = make_float4(row[id[r][0]], row[id[r][1]], row[id[r][2]], row[id[r][3]]);
+      const T v0 = row[id[r][0]], v1 = row[id[r][1]], v2 = row[id[r][2]], v3 = row[id[r][3]];
       if (VEC) {
-        __stcs(reinterpret_cast<float4 *>(o + e), v);
+        if constexpr (sizeof(T) == 4) {
+          __stcs(reinterpret_cast<float4 *>(o + e), make_float4(v0, v1, v2, v3));
+        } else {
+          __stcs(reinterpret_cast<double2 *>(o + e), make_double2(v0, v1));
+          __stcs(reinterpret_cast<double2 *>(o + e) + 1, make_double2(v2, v3));
+        }
       } else {
-        o[e] = v.x;
-        if (e + 1 < E) o[e + 1] = v.y;
-        if (e + 2 < E) o[e + 2] = v.z;
-        if (e + 3 < E) o[e + 3] = v.w;
+        o[e] = v0;
+        if (e + 1 < E) o[e + 1] = v1;
+        if (e + 2 < E) o[e + 2] = v2;
+        if (e + 3 < E) o[e + 3] = v3;
       }
     }
     __syncthreads();
   }
 }
 
-// Largest cloud the channel-row kernels take: two rows (forward) must fit the 227 KB of an SM.
-constexpr int64_t CR_MAX_N1 = 24576;
+// Largest cloud the channel-row kernels take: two rows (forward) must fit the 227 KB of an SM
+// (24576 floats or 12288 doubles).
+constexpr int64_t CR_MAX_ROW_BYTES = 24576 * 4;
 
-inline bool chanrow_ok(const void *in, int64_t B, int64_t C, int64_t N1, int64_t E) {
-  return N1 >= 256 && N1 % 4 == 0 && N1 <= CR_MAX_N1 && E >= 1024 && B <= 65535 && C <= 65535 &&
+inline bool chanrow_ok(const void *in, int64_t B, int64_t C, int64_t N1, int64_t E, int64_t elem = 4) {
+  return N1 >= 256 && N1 % 4 == 0 && N1 * elem <= CR_MAX_ROW_BYTES && E >= 1024 && B <= 65535 && C <= 65535 &&
          (reinterpret_cast<uintptr_t>(in) & 15) == 0;
 }
 
-template <typename IndexT>
-int group_fwd_chanrow(const float *in, const IndexT *index, int64_t B, int64_t C, int64_t N1, int64_t E, float *out,
+template <typename T, typename IndexT>
+int group_fwd_chanrow(const T *in, const IndexT *index, int64_t B, int64_t C, int64_t N1, int64_t E, T *out,
                       int32_t *status, cudaStream_t st) {
   // entries per block: 8192 when that still leaves enough blocks, else 4096
   const int64_t sms = sm_count();
@@ -244,14 +252,14 @@ int group_fwd_chanrow(const float *in, const IndexT *index, int64_t B, int64_t C
   const int cg = (int)((C + groups - 1) / groups);
   groups = (C + cg - 1) / cg;
   TK3D_REQUIRE(chunks < (1LL << 31), TK3D_ERR_SHAPE, "group_points: too many entries");
-  const size_t smem = (size_t)2 * (N1 + 4) * sizeof(float);
+  const size_t smem = (size_t)2 * (N1 + 4) * sizeof(T);
   dim3 grid((unsigned)chunks, (unsigned)groups, (unsigned)B);
   const bool vec = E % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
 #define TK3D_CR_LAUNCH(RR, VV)                                                                                   \
   {                                                                                                              \
-    TK3D_CUDA(raise_smem_limit((const void *)group_fwd_chanrow_kernel<IndexT, RR, VV>, (int)smem));             \
-    group_fwd_chanrow_kernel<IndexT, RR, VV><<<grid, CR_THREADS, smem, st>>>(in, index, (int)C, (int)N1, E, cg, \
-                                                                             out, status);                       \
+    TK3D_CUDA(raise_smem_limit((const void *)group_fwd_chanrow_kernel<T, IndexT, RR, VV>, (int)smem));             \
+    group_fwd_chanrow_kernel<T, IndexT, RR, VV><<<grid, CR_THREADS, smem, st>>>(in, index, (int)C, (int)N1, E, cg, \
+                                                                                out, status);                       \
   }
   if (big) {
     if (vec) TK3D_CR_LAUNCH(8, true) else TK3D_CR_LAUNCH(8, false)
@@ -264,8 +272,8 @@ int group_fwd_chanrow(const float *in, const IndexT *index, int64_t B, int64_t C
 
 // How many channels one block walks: enough blocks to fill the GPU a few times over, but as few
 // channel groups as possible so the indices are read once per group.
-int64_t channels_per_block(int64_t tiles, int64_t B, int64_t C) {
-  const int64_t want = (int64_t)sm_count() * 8;
+int64_t channels_per_block(int64_t tiles, int64_t B, int64_t C, int mult = 8) {
+  const int64_t want = (int64_t)sm_count() * mult;
   int64_t groups = (want + tiles * B - 1) / (tiles * B);
   if (groups < 1) groups = 1;
   if (groups > C) groups = C;
@@ -292,7 +300,8 @@ int group_bwd_t(const T *gout, const int64_t *index, int64_t B, int64_t C, int64
   TK3D_CUDA(cudaMemsetAsync(gin, 0, sizeof(T) * (size_t)(B * C * N1), st));
   if (E == 0) return TK3D_OK;
   const int64_t tiles = (E + GP_TILE - 1) / GP_TILE;
-  const int64_t cpb = channels_per_block(tiles, B, C);
+  // many small blocks suit the atomics (float64, 8 x 64 x 1024 <- 512 x 32: 0.059 -> 0.053 ms)
+  const int64_t cpb = channels_per_block(tiles, B, C, 128);
   const int64_t groups = (C + cpb - 1) / cpb;
   TK3D_REQUIRE(tiles < (1LL << 31) && groups <= 65535 && B <= 65535, TK3D_ERR_SHAPE,
                "group_points: grid too large (B=%lld)", (long long)B);
@@ -337,7 +346,7 @@ static int group_fwd_impl(const void *in, const IndexT *index, int64_t B, int64_
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == TK3D_F32) {
     if (chanrow_ok(in, B, C, N1, E))
-      return group_fwd_chanrow<IndexT>((const float *)in, index, B, C, N1, E, (float *)out, status, st);
+      return group_fwd_chanrow<float, IndexT>((const float *)in, index, B, C, N1, E, (float *)out, status, st);
     const size_t want = tk3d_group_fwd_scratch_bytes(B, C, N1, N2, K, dtype);
     const size_t rows = rows_profitable(C, N1, E, 1) && B <= 65535 ? rows_scratch_bytes(B, C, N1) : 0;
     (void)want;
@@ -346,6 +355,8 @@ static int group_fwd_impl(const void *in, const IndexT *index, int64_t B, int64_
                                     (float *)scratch, st);
     return group_fwd_t<float, IndexT>((const float *)in, index, B, C, N1, E, (float *)out, status, st);
   }
+  if (chanrow_ok(in, B, C, N1, E, 8))
+    return group_fwd_chanrow<double, IndexT>((const double *)in, index, B, C, N1, E, (double *)out, status, st);
   return group_fwd_t<double, IndexT>((const double *)in, index, B, C, N1, E, (double *)out, status, st);
 }
 
