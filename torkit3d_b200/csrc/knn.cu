@@ -46,28 +46,17 @@ __device__ __forceinline__ float4 make_key(const float *__restrict__ rb, int j, 
   return make_float4(0.f, 0.f, 0.f, pinf());
 }
 
-// ---------------------------------------------------------------------------------------------
-// FUSED (three-nearest-neighbour front end of feature interpolation): instead of distances and
-// 64-bit indices the epilogue writes the normalised inverse-distance weights
-// w_i = (1/max(d_i, eps)) / sum_j (1/max(d_j, eps))  and 32-bit indices.
-struct KnnFused {
-  float eps;
-  float *weight;
-  int32_t *index32;
-};
-
 // LANES > 1: several lanes per query.  The LANES lanes l, l + 32/LANES, ... of a warp hold the same
 // Q queries and sweep every LANES-th key group of each tile, each into its own sorted list; once
-// per tile they exchange the smallest of their k-th distances (any lane's k-th distance bounds the
-// query's k-th distance as well as its own), and at the end the lists are merged by (distance,
-// index) in log2(LANES) butterfly steps.  Same pairs per shared-memory load, same staging, but
+// per tile they exchange their lists' distances and continue with the k-th smallest of the union
+// as the bound (the lists hold disjoint keys, so that bounds the query's k-th distance), and at the
+// end the lists are merged by (distance, index) in log2(LANES) butterfly steps.  Same pairs per shared-memory load, same staging, but
 // LANES times the warps for a given number of queries: for launches that cannot fill the GPU with
 // one lane per query, whose time is the critical path of a single warp.
-template <int K, int Q, bool FUSED = false, int LANES = 1>
+template <int K, int Q, int LANES = 1>
 __global__ void __launch_bounds__(KN_THREADS)
 knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key, int64_t B, int N1, int N2,
-                 float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl,
-                 KnnFused fu = KnnFused()) {
+                 float *__restrict__ dist, IndexOut index, int64_t blocks_total, XyzLayout ql, XyzLayout kl) {
   constexpr int TILE = 512, PER = TILE / KN_THREADS;
   constexpr int GK = 8 / Q;  // keys per filter group: eight (key, query) pairs share one branch
   __shared__ float4 tile[2][TILE];  // pair layout of sweep.cuh
@@ -140,9 +129,33 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
       auto exchange = [&]() {
 #pragma unroll
         for (int s = 0; s < Q; ++s) {
-          float pk = kd[s][K - 1];  // smallest k-th distance among the query's lanes (a NaN is never smaller)
+          // k-th smallest distance of the UNION of the lanes' lists (they hold disjoint keys): the
+          // k smallest of two ascending lists a, b are min(a[c], b[K-1-c]), c = 0..K-1
+          float e[K];
 #pragma unroll
-          for (int o = QL; o < 32; o <<= 1) pk = fminf(pk, __shfl_xor_sync(0xffffffffu, pk, o));
+          for (int c = 0; c < K; ++c) e[c] = kd[s][c];
+#pragma unroll
+          for (int o = QL; o < 32; o <<= 1) {
+            float pe[K];
+#pragma unroll
+            for (int c = 0; c < K; ++c) pe[c] = __shfl_xor_sync(0xffffffffu, e[c], o);
+#pragma unroll
+            for (int c = 0; c < K; ++c) e[c] = fminf(e[c], pe[K - 1 - c]);
+            if (2 * o < 32) {  // another step follows: it needs the list in ascending order again
+#pragma unroll
+              for (int a_ = 0; a_ < K - 1; ++a_) {
+#pragma unroll
+                for (int c = 0; c < K - 1 - a_; ++c) {
+                  const float lo = fminf(e[c], e[c + 1]), hi = fmaxf(e[c], e[c + 1]);
+                  e[c] = lo;
+                  e[c + 1] = hi;
+                }
+              }
+            }
+          }
+          float pk = e[0];
+#pragma unroll
+          for (int c = 1; c < K; ++c) pk = fmaxf(pk, e[c]);
           const float up = pk < pinf() ? __uint_as_float(__float_as_uint(pk) + 1u) : pk;  // pk >= +0 or NaN
           pthr[s] = pk == pk ? sweep_threshold(up, sweep_qq(qx[s], qy[s], qz[s])) : pinf();
           thr[s] = fminf(thr[s], pthr[s]);
@@ -258,27 +271,11 @@ knn_small_kernel(const float *__restrict__ query, const float *__restrict__ key,
     for (int s = 0; s < Q; ++s) {
       const int i = qindex(s);
       if (i < N1 && half == 0) {
-        if constexpr (FUSED) {
-          float inv[K], sum = 0.f;
+        float *od = dist + (b * N1 + i) * K;
 #pragma unroll
-          for (int c = 0; c < K; ++c) {
-            inv[c] = __fdiv_rn(1.0f, fmaxf(kd[s][c], fu.eps));
-            sum = c == 0 ? inv[0] : __fadd_rn(sum, inv[c]);
-          }
-          float *ow = fu.weight + (b * N1 + i) * K;
-          int32_t *oi = fu.index32 + (b * N1 + i) * K;
-#pragma unroll
-          for (int c = 0; c < K; ++c) {
-            ow[c] = __fdiv_rn(inv[c], sum);
-            oi[c] = ki[s][c];
-          }
-        } else {
-          float *od = dist + (b * N1 + i) * K;
-#pragma unroll
-          for (int c = 0; c < K; ++c) {
-            od[c] = kd[s][c];
-            index.put((b * N1 + i) * K + c, ki[s][c]);
-          }
+        for (int c = 0; c < K; ++c) {
+          od[c] = kd[s][c];
+          index.put((b * N1 + i) * K + c, ki[s][c]);
         }
       }
     }
@@ -1056,25 +1053,27 @@ int knn_small(const float *query, const float *key, int64_t B, int N1, int N2, f
   const int64_t per = KN_THREADS * Q / LANES;
   const int64_t total = B * ((N1 + per - 1) / per);
   const int64_t cap = (int64_t)sm_count() * 256;
-  knn_small_kernel<K, Q, false, LANES><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
-      query, key, B, N1, N2, dist, io.index, total, io.ql, io.kl, KnnFused{});
+  knn_small_kernel<K, Q, LANES><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
+      query, key, B, N1, N2, dist, io.index, total, io.ql, io.kl);
   return check_launch("knn_small_kernel");
 }
 
 // Lanes per query for launches with one query per thread (fewer than about 75 000 queries).  Measured
 // on B200 (148 SMs), k = 1 / k = 3, in ms:
 //   queries   1 lane        2 lanes       4 lanes       8 lanes        (queries x keys)
-//   65536     0.34 / 0.47   0.31 / 0.47   0.57 / 0.67                  4 x 16384 x 16384
-//   40000     0.029/ 0.057  0.027/ 0.049  0.028/ 0.055  0.040/ 0.063   4 x 10000 x 512
-//   32768     0.039/ 0.079  0.033/ 0.067  0.030/ 0.055  0.053/ 0.078   32 x 1024 x 1024
-//   16384     0.055/ 0.112  0.040/ 0.081  0.034/ 0.061  0.046/ 0.061   8 x 2048 x 2048
-//    8192     0.43 / 0.64   0.28 / 0.35   0.21 / 0.27   0.33 / 0.35    2 x 4096 x 32768
-//    2048     0.159/ 0.276  0.108/ 0.169  0.071/ 0.116  0.053/ 0.089   4 x 512 x 10000
-//    1000     1.16 / 1.58   0.76 / 0.78   0.51 / 0.57   0.40 / 0.46    1 x 1000 x 100000
+//   65536     0.35 / 0.48   0.31 / 0.44   0.57 / 0.64   1.13 / 1.18    4 x 16384 x 16384
+//   65536     0.109/ 0.192  0.096/ 0.200  0.166/ 0.220  0.304/ 0.352   1 x 65536 x 4096
+//   40000     0.029/ 0.057  0.029/ 0.049  0.028/ 0.056  0.040/ 0.063   4 x 10000 x 512
+//   32768     0.039/ 0.079  0.033/ 0.067  0.031/ 0.053  0.054/ 0.074   32 x 1024 x 1024
+//   32768                   0.118/ 0.202  0.151/ 0.185  0.291/ 0.319   16 x 2048 x 8192
+//   16384     0.055/ 0.112  0.041/ 0.077  0.034/ 0.055  0.046/ 0.057   8 x 2048 x 2048
+//    8192     0.43 / 0.64   0.28 / 0.32   0.21 / 0.24   0.33 / 0.35    2 x 4096 x 32768
+//    4096                   0.52 / 0.54   0.34 / 0.37   0.38 / 0.39    1 x 4096 x 65536
+//    2048     0.159/ 0.276  0.108/ 0.156  0.071/ 0.100  0.054/ 0.072   4 x 512 x 10000
+//    1000     1.16 / 1.58   0.76 / 0.74   0.51 / 0.52   0.40 / 0.43    1 x 1000 x 100000
 inline int lanes_per_query(int64_t nq) {
   const int64_t sms = sm_count();
-  if (nq * 3 > sms * 1000) return 1;   // above about 49 000 queries on 148 SMs
-  if (nq * 6 > sms * 1000) return 2;   // above about 24 600
+  if (nq * 6 > sms * 1000) return 2;   // above about 24 600 queries on 148 SMs
   if (nq * 48 > sms * 1000) return 4;  // above about 3 000
   return 8;
 }
@@ -1099,17 +1098,6 @@ int knn_small_q(const float *query, const float *key, int64_t B, int N1, int N2,
     case 2: return knn_small<K, 1, 2>(query, key, B, N1, N2, dist, io, st);
     default: return knn_small<K, 1>(query, key, B, N1, N2, dist, io, st);
   }
-}
-
-template <int Q, int LANES = 1>
-int three_nn_fused_q(const float *query, const float *key, int64_t B, int N1, int N2, const KnnFused &fu,
-                     XyzLayout ql, XyzLayout kl, cudaStream_t st) {
-  const int64_t per = KN_THREADS * Q / LANES;
-  const int64_t total = B * ((N1 + per - 1) / per);
-  const int64_t cap = (int64_t)sm_count() * 256;
-  knn_small_kernel<3, Q, true, LANES><<<(unsigned)(total < cap ? total : cap), KN_THREADS, 0, st>>>(
-      query, key, B, N1, N2, nullptr, index_out(nullptr, 0, 0), total, ql, kl, fu);
-  return check_launch("knn_small_kernel (fused weights)");
 }
 
 size_t buffered_smem(int Q, int k) {
@@ -1144,27 +1132,40 @@ int knn_twopass(const float *query, const float *key, int64_t B, int N1, int N2,
 
 }  // namespace
 
-// Three nearest keys of every query with inverse-distance weights (see KnnFused); N2 >= 3.
+// Three nearest keys of every query with inverse-distance weights, the front end of feature
+// interpolation: w_i = (1/max(d_i, eps)) / sum_j (1/max(d_j, eps)) and 32-bit indices; N2 >= 3.
+// The sweep writes the squared distances into `weight` and a second, tiny kernel turns every row
+// into weights in place (0.01 ms for 524288 queries).  Computing the weights in the sweep's own
+// epilogue saved that launch but left the sweep's two-lane variant with 79 registers, six blocks
+// per SM, i.e. out of reach for the half-filled launches that need it (8 x 16384 x 32768 with the
+// gather that follows: 1.24 -> 1.11 ms; 8 x 65536 x 32768: 6.80 -> 6.77).
+__global__ void __launch_bounds__(256)
+three_nn_weight_inplace_kernel(float *__restrict__ weight, int64_t rows, float eps) {
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r < rows; r += (int64_t)gridDim.x * blockDim.x) {
+    float *w = weight + r * 3;
+    float inv[3], sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      inv[c] = __fdiv_rn(1.0f, fmaxf(w[c], eps));
+      sum = c == 0 ? inv[0] : __fadd_rn(sum, inv[c]);
+    }
+#pragma unroll
+    for (int c = 0; c < 3; ++c) w[c] = __fdiv_rn(inv[c], sum);
+  }
+}
+
 int three_nn_fused_f32(const float *query, const float *key, int64_t B, int64_t N1, int64_t N2, int channel_first,
                        float eps, float *weight, int32_t *index32, cudaStream_t st) {
   if (B * N1 == 0) return TK3D_OK;
-  KnnFused fu;
-  fu.eps = eps;
-  fu.weight = weight;
-  fu.index32 = index32;
-  const XyzLayout ql = xyz_layout(channel_first, N1), kl = xyz_layout(channel_first, N2);
-  const int64_t sms = sm_count();
-  // Two queries per thread always run one lane per query here: with the weights fused in, the
-  // two-lane variant needs 79 registers (six blocks per SM, not seven) and is slower (8 x 16384 x
-  // 32768: 1.24 ms against 1.39, or 1.33 when capped at 72 registers).
-  if (B * N1 >= sms * 2 * KN_THREADS * 2)
-    return three_nn_fused_q<2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
-  switch (lanes_per_query(B * N1)) {
-    case 8: return three_nn_fused_q<1, 8>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
-    case 4: return three_nn_fused_q<1, 4>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
-    case 2: return three_nn_fused_q<1, 2>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
-    default: return three_nn_fused_q<1>(query, key, B, (int)N1, (int)N2, fu, ql, kl, st);
-  }
+  KnnIo io;
+  io.index = index_out(index32, 1, B * N1 * 3);
+  io.ql = xyz_layout(channel_first, N1);
+  io.kl = xyz_layout(channel_first, N2);
+  int rc = knn_small_q<3>(query, key, B, (int)N1, (int)N2, weight, io, st);
+  if (rc) return rc;
+  const int64_t rows = B * N1, blocks = (rows + 255) / 256, cap = (int64_t)sm_count() * 8;
+  three_nn_weight_inplace_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(weight, rows, eps);
+  return check_launch("three_nn_weight_inplace_kernel");
 }
 
 }  // namespace tk3d
