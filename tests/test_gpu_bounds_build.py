@@ -71,7 +71,8 @@ def test_bounds_build_counts_no_violation_and_matches_the_regular_build():
             both(chamfer)
     # farthest point sampling: one block per cloud (registers / shared memory), a cluster of blocks
     # per cloud, the streaming kernel; ball query with more neighbours than one tile can give
-    for (B, n, s, dt) in ((3, 1025, 129, torch.float32), (2, 9000, 100, torch.float32), (2, 20000, 60, torch.float32),
+    for (B, n, s, dt) in ((3, 1025, 129, torch.float32), (2, 6000, 50, torch.float32), (2, 9000, 100, torch.float32),
+                          (2, 20000, 60, torch.float32),
                           (1, 70001, 30, torch.float32), (1, 140000, 12, torch.float32), (2, 3000, 70, torch.float64)):
         code = _lib.F32 if dt == torch.float32 else _lib.F64
         p = torch.rand(B, n, 3, generator=g, dtype=dt).to(DEV)

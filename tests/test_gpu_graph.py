@@ -86,12 +86,14 @@ def test_graph_large_k_small_ball_and_large_cloud_fps():
     q = torch.randn(2, 300, 3, generator=gen).to(DEV)
     r = torch.randn(2, 3000, 3, generator=gen).to(DEV)
     big = torch.rand(1, 70000, 3, generator=gen).to(DEV)
+    mid = torch.rand(2, 7000, 3, generator=gen).to(DEV)  # clusters of eight small blocks, mbarriers in shared memory
 
     def chain():
         d, i = _C.knn_distance_cuda(q, r, 150, 0)
         bq = _C.ball_query_cuda(q, r, 0.6, 100)
         fp = _C.sample_farthest_points_cuda(big, 40)
-        return d, i, bq, fp
+        fm = _C.sample_farthest_points_cuda(mid, 90)
+        return d, i, bq, fp, fm
 
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
@@ -101,6 +103,7 @@ def test_graph_large_k_small_ball_and_large_cloud_fps():
         q.copy_(torch.randn(q.shape, generator=gen))
         r.copy_(torch.randn(r.shape, generator=gen))
         big.copy_(torch.rand(big.shape, generator=gen))
+        mid.copy_(torch.rand(mid.shape, generator=gen))
         graph.replay()
         torch.cuda.synchronize()
         got = [o.clone() for o in outs]

@@ -465,6 +465,9 @@ def test_feature_knn_golden_wrapper_and_errors(golden):
 # ----------------------------------------------------------------------------------------------- fps
 FPS_CASES = [(1, 31, 2), (2, 1024, 128), (3, 1025, 129), (16, 1024, 512), (4, 4096, 300), (2, 8192, 1024),
              (2, 100, 100), (1, 1, 1), (3, 33, 33), (2, 8193, 200), (1, 20000, 64),
+             # few clouds of 4097 to 16384 points: clusters of eight small blocks without barriers in the step;
+             # many such clouds: one block per cloud again
+             (2, 4097, 50), (3, 5000, 300), (1, 16384, 128), (40, 6000, 64), (3, 12345, 2000), (90, 4500, 32),
              # a cluster of 2 / 4 / 8 / 16 blocks per cloud (16385 to 131072 points), then the streaming kernel
              (2, 16385, 96), (3, 30000, 128), (2, 40961, 70), (1, 65536, 200), (1, 65537, 40), (1, 131072, 33),
              (1, 131073, 20)]
@@ -494,14 +497,23 @@ def test_fps_cluster_ties_and_gather(oracle):
     np.testing.assert_array_equal(N(sample_farthest_points(T(p), 300)), oracle.fps(p, 300))
     same = np.full((1, 17000, 3), 0.25, dtype=np.float32)
     np.testing.assert_array_equal(N(sample_farthest_points(T(same), 5)), oracle.fps(same, 5))
-    q = rng.random((2, 20000, 3)).astype(np.float32)
-    want = oracle.fps(q, 64)
-    for cf in (False, True):
-        pts = T(q).transpose(1, 2).contiguous() if cf else T(q)
-        idx, cent = _fused.fps_gather(pts, 64, channel_first=cf)
-        np.testing.assert_array_equal(N(idx), want)
-        ref = np.take_along_axis(q, want[..., None], axis=1)
-        np.testing.assert_array_equal(N(cent.transpose(1, 2) if cf else cent), ref)
+    for n in (20000, 7000, 9001):  # 1024-thread blocks with a cluster barrier; eight blocks of 64 / 128 threads
+        q = rng.random((2, n, 3)).astype(np.float32)
+        want = oracle.fps(q, 64)
+        for cf in (False, True):
+            pts = T(q).transpose(1, 2).contiguous() if cf else T(q)
+            idx, cent = _fused.fps_gather(pts, 64, channel_first=cf)
+            np.testing.assert_array_equal(N(idx), want)
+            ref = np.take_along_axis(q, want[..., None], axis=1)
+            np.testing.assert_array_equal(N(cent.transpose(1, 2) if cf else cent), ref)
+    # the same ties and coinciding points on the barrier-free kernel's sizes
+    p = (rng.integers(-4, 5, size=(3, 8000, 3)) * 0.5).astype(np.float32)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(p), 400)), oracle.fps(p, 400))
+    same = np.full((2, 10000, 3), -1.5, dtype=np.float32)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(same), 7)), oracle.fps(same, 7))
+    dup = rng.random((1, 3000, 3)).astype(np.float32)
+    dup = np.concatenate([dup, dup, dup[:, :500]], axis=1)  # every point twice or three times
+    np.testing.assert_array_equal(N(sample_farthest_points(T(dup), 3200)), oracle.fps(dup, 3200))
 
 
 def test_fps_golden_fp64_and_duplicates(oracle, golden):

@@ -393,6 +393,12 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
 #undef TK3D_FPS64_CASE
     return check_launch("fps_resident64_kernel");
   }
+  if (dtype == TK3D_F32 && N > 4096) {
+    // a cluster of blocks per cloud (fps_cluster.cu): few clouds of 4097 to 16384 points, and every
+    // cloud of 16385 to 131072 points; no scratch.  Declines (false) what the kernels below do better.
+    int rc = TK3D_OK;
+    if (fps_cluster_f32((const float *)points, B, N, S, (int)ps, cs, index, (float *)sampled, st, &rc)) return rc;
+  }
   if (need == 0) {
     // Up to 8 points per thread in registers (16 with the coordinates left in shared memory); at
     // least 4 warps so that every SM sub-partition has work.
@@ -417,10 +423,6 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
     }
 #undef TK3D_FPS_CASE
     return check_launch("fps_resident_kernel");
-  }
-  if (dtype == TK3D_F32) {  // 16385 to 131072 points: a cluster of blocks per cloud (fps_cluster.cu), no scratch
-    int rc = TK3D_OK;
-    if (fps_cluster_f32((const float *)points, B, N, S, (int)ps, cs, index, (float *)sampled, st, &rc)) return rc;
   }
   TK3D_REQUIRE(scratch != nullptr && scratch_bytes >= need, TK3D_ERR_SCRATCH,
                "fps: scratch of %zu bytes required, %zu given", need, scratch ? scratch_bytes : (size_t)0);

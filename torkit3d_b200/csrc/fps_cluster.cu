@@ -1,20 +1,23 @@
-// Farthest point sampling of large float32 clouds (16385 to 131072 points) on a thread-block cluster.
+// Farthest point sampling of float32 clouds on thread-block clusters: two kernels.
 //
-// The resident kernel of fps.cu keeps a cloud in the registers of ONE block, which ends at 16384
-// points; beyond that the streaming kernel re-reads the cloud and its running minima from L2 in
-// every step, still with one block per cloud (4 clouds of 65536 points: 4 busy SMs, 19 us per
-// step).  Here a cluster of 2, 4, 8 or 16 blocks shares a cloud: every block keeps a contiguous slice
-// of up to 8192 points and their running minima in registers, exactly like the resident kernel,
-// and finds its own farthest point (two block barriers); then each block writes its candidate --
-// (distance bits, index, coordinates), 32 bytes -- into the shared memory of every block of the
-// cluster (distributed shared memory), one cluster barrier makes the candidates visible, and
-// every block picks the same winner from its local copy: highest distance, lowest index.  The
-// candidate slots are double buffered by the step's parity, so one cluster barrier per step is
-// enough (a block can only be one step ahead of the slowest one).
+// fps_cluster_kernel (16385 to 131072 points).  The resident kernel of fps.cu keeps a cloud in the
+// registers of ONE block, which ends at 16384 points; beyond that the streaming kernel re-reads the
+// cloud and its running minima from L2 in every step, still with one block per cloud (4 clouds of
+// 65536 points: 4 busy SMs, 19 us per step).  Here a cluster of 2, 4, 8 or 16 blocks shares a
+// cloud: every block keeps a contiguous slice of up to 8192 points and their running minima in
+// registers, exactly like the resident kernel, and finds its own farthest point (two block
+// barriers); then each block writes its candidate -- (distance bits, index, coordinates), 32 bytes
+// -- into the shared memory of every block of the cluster (distributed shared memory), one cluster
+// barrier makes the candidates visible, and every block picks the same winner from its local copy:
+// highest distance, lowest index.  The candidate slots are double buffered by the step's parity,
+// so one cluster barrier per step is enough (a block can only be one step ahead of the slowest one).
+// With 1024-thread blocks that barrier costs more than the divided arithmetic saves on clouds that
+// fit one block (32 clouds of 8192 points, 1024 samples: 0.78 to 1.2 ms for clusters of 2 to 16
+// blocks of 1024 to 128 threads, against 0.70 ms for one block).
 //
-// For clouds that fit one block the cluster barrier costs more than the divided arithmetic saves
-// (measured: 1.07 ms against 0.88 ms for 32 clouds of 8192 points), which is why this kernel only
-// takes the clouds the resident kernel cannot hold.
+// fps_warpcast_kernel (4097 to 16384 points, few clouds) has no block or cluster barrier in its
+// step at all: see the comment in front of it.  32 clouds of 8192 points, 1024 samples: 0.53 ms.
+//
 // Arithmetic, tie rule and padding are those of fps_resident_kernel; the reference's kernel is
 // torkit3d/csrc/cuda/sample_farthest_points_kernel.cu:33-103 (one block per cloud, any size).
 #include <cooperative_groups.h>
@@ -26,9 +29,7 @@ namespace cg = cooperative_groups;
 namespace tk3d {
 namespace {
 
-constexpr int FC_THREADS = 1024;
-constexpr int FC_P2 = 4;                               // float2 pairs per thread: 8 points
-constexpr int FC_SLICE = FC_THREADS * 2 * FC_P2;       // 8192 points per block
+constexpr int FC_SLICE = 1024 * 2 * 4;                 // 8192 points per block: 1024 threads, 4 float2 pairs each
 constexpr int FC_MAX_CL = 16;                          // 8 is the portable cluster size; 16 needs an opt-in
 
 struct __align__(16) FcCandidate {
@@ -38,6 +39,7 @@ struct __align__(16) FcCandidate {
   int pad[3];
 };
 
+template <int FC_THREADS, int FC_P2>
 __global__ void __launch_bounds__(FC_THREADS)
 fps_cluster_kernel(const float *__restrict__ points, int N, int NL, int S, int64_t *__restrict__ index, int ps, int cs,
                    float *__restrict__ sampled, float one) {
@@ -165,28 +167,217 @@ fps_cluster_kernel(const float *__restrict__ points, int N, int NL, int S, int64
 
 }  // namespace
 
-// Launches the cluster kernel when the clouds suit it (float32, 16384 < N <= 131072); returns false
-// when they do not or when the device refuses the cluster launch (the caller then takes its own
-// path), true with *rc set otherwise.
-bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
-                     float *sampled, cudaStream_t st, int *rc) {
-  if (N <= 16384 || N > (int64_t)FC_MAX_CL * FC_SLICE || B * FC_MAX_CL >= (1LL << 31)) return false;
-  int CL = 2;
-  while ((int64_t)CL * FC_SLICE < N) CL <<= 1;
+// ---------------------------------------------------------------------------------------------
+// Variant without block or cluster barriers in the step (clouds of up to 32 warps x 32 lanes x
+// 2*P2 points).  Every WARP finds its own farthest point (two REDUX) and sends it -- 20 bytes:
+// distance bits, index, coordinates -- straight into the shared memory of every block of the
+// cluster with st.async, which also counts the bytes on an mbarrier of the receiving block.  A warp
+// then waits on its own block's mbarrier until the candidates of all warps of the cluster have
+// landed, and lane l looks at candidate l: two more REDUX pick the winner.  The candidate slots
+// and mbarriers are double buffered by the step's parity: a warp can send for step i+2 only after
+// it has seen every warp's candidate of step i+1, which those warps send after they have read
+// step i.  Every wait has an iteration limit; a warp that runs into it marks the rest of its
+// cloud's output with -1 and leaves.
+struct __align__(16) FwCandidate {
+  unsigned bits;
+  int idx;
+  float x, y;
+  float z;
+  int pad[3];
+};
+constexpr unsigned FW_CAND_BYTES = 20;
+
+__device__ __forceinline__ unsigned fw_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned fw_mapa(unsigned addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ unsigned fw_try_wait(unsigned bar, unsigned phase) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(phase)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ unsigned long long fw_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <int FW_THREADS, int FW_P2>
+__global__ void __launch_bounds__(FW_THREADS)
+fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int64_t *__restrict__ index, int ps, int cs,
+                    float *__restrict__ sampled, float one) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CL = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  const int cloud = blockIdx.x / CL;
+  extern __shared__ float sxyz[];  // [3*NL]: this block's slice of the cloud
+  __shared__ FwCandidate cand[2][32];
+  __shared__ __align__(8) unsigned long long mbar[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int T = FW_THREADS, W = FW_THREADS / 32;
+  const int nw = CL * W;           // warps of the cluster, at most 32
+  const int gw = rank * W + warp;  // this warp's candidate slot
+  const float *pts = points + (int64_t)cloud * N * 3;
+  int64_t *out = index + (int64_t)cloud * S;
+  const int base = rank * NL;
+  const int nloc = max(0, min(NL, N - base));
+
+  for (int e = tid; e < 3 * nloc; e += T) {
+    const int j = e / 3, d = e - 3 * j;
+    sxyz[e] = pts[(int64_t)(base + j) * ps + (int64_t)d * cs];
+  }
+  const unsigned bar0 = fw_smem(&mbar[0]), bar1 = fw_smem(&mbar[1]);
+  const unsigned expect = (unsigned)nw * FW_CAND_BYTES;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // steps 1 and 2 use barrier 1 and barrier 0
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar1), "r"(expect) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar0), "r"(expect) : "memory");
+  }
+  __syncthreads();
+
+  float2 px[FW_P2], py[FW_P2], pz[FW_P2], md[FW_P2];
+  const float qnan = __int_as_float(0x7fc00000), pinf = __int_as_float(0x7f800000);
+#pragma unroll
+  for (int i = 0; i < FW_P2; ++i) {
+    const int j0 = (2 * i) * T + tid, j1 = (2 * i + 1) * T + tid;
+    px[i].x = j0 < nloc ? sxyz[3 * j0 + 0] : qnan;
+    py[i].x = j0 < nloc ? sxyz[3 * j0 + 1] : qnan;
+    pz[i].x = j0 < nloc ? sxyz[3 * j0 + 2] : qnan;
+    px[i].y = j1 < nloc ? sxyz[3 * j1 + 0] : qnan;
+    py[i].y = j1 < nloc ? sxyz[3 * j1 + 1] : qnan;
+    pz[i].y = j1 < nloc ? sxyz[3 * j1 + 2] : qnan;
+    md[i].x = j0 < nloc ? pinf : 0.f;
+    md[i].y = j1 < nloc ? pinf : 0.f;
+  }
+
+  float cx = pts[0], cy = pts[cs], cz = pts[2 * (int64_t)cs];
+  const bool writer = rank == 0 && tid == 0;
+  const int sps = cs == 1 ? 3 : 1, scs = cs == 1 ? 1 : S;
+  float *sm = sampled ? sampled + (int64_t)cloud * S * 3 : nullptr;
+  if (writer) {
+    out[0] = 0;
+    if (sm) {
+      sm[0] = cx;
+      sm[scs] = cy;
+      sm[2 * (int64_t)scs] = cz;
+    }
+  }
+  cluster.sync();  // every block's mbarriers are initialised and armed: candidates may be sent
+
+  // this lane's target block when it sends (lanes 0..CL-1 of every warp)
+  const unsigned tgt = (unsigned)(lane < CL ? lane : 0);
+  const unsigned rcand0 = fw_mapa(fw_smem(&cand[0][gw]), tgt), rcand1 = fw_mapa(fw_smem(&cand[1][gw]), tgt);
+  const unsigned rbar0 = fw_mapa(bar0, tgt), rbar1 = fw_mapa(bar1, tgt);
+
+  const float2 one2 = make_float2(one, one);
+  bool failed = false;
+  int it = 1;
+  for (; it < S; ++it) {
+    const int par = it & 1;
+    const float2 ncx = make_float2(-cx, -cx), ncy = make_float2(-cy, -cy), ncz = make_float2(-cz, -cz);
+    float bm = 0.f;
+#pragma unroll
+    for (int i = 0; i < FW_P2; ++i) {
+      const float2 dx = __fadd2_rn(px[i], ncx), dy = __fadd2_rn(py[i], ncy), dz = __fadd2_rn(pz[i], ncz);
+      const float2 d = __ffma2_rn(__ffma2_rn(__fmul2_rn(dx, dx), one2, __fmul2_rn(dy, dy)), one2, __fmul2_rn(dz, dz));
+      md[i].x = fminf(md[i].x, d.x);
+      md[i].y = fminf(md[i].y, d.y);
+      asm("max.f32 %0, %0, %1, %2;" : "+f"(bm) : "f"(md[i].x), "f"(md[i].y));
+    }
+    const unsigned bits = __float_as_uint(bm);
+    const unsigned gb = __reduce_max_sync(0xffffffffu, bits);
+    int mine = 0x7fffffff;
+    if (bits == gb) {
+#pragma unroll
+      for (int i = FW_P2 - 1; i >= 0; --i) {
+        if (md[i].y == bm) mine = (2 * i + 1) * T + tid;
+        if (md[i].x == bm) mine = (2 * i) * T + tid;
+      }
+    }
+    const int loc = __reduce_min_sync(0xffffffffu, mine);  // lowest local index holding the warp's maximum
+    if (lane < CL) {
+      const bool real = loc < nloc;
+      const float x = real ? sxyz[3 * loc + 0] : 0.f, y = real ? sxyz[3 * loc + 1] : 0.f,
+                  z = real ? sxyz[3 * loc + 2] : 0.f;
+      const unsigned rc = par ? rcand1 : rcand0, rb = par ? rbar1 : rbar0;
+      asm volatile(
+          "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(rc),
+          "r"(gb), "r"(base + loc), "r"(__float_as_uint(x)), "r"(__float_as_uint(y)), "r"(rb)
+          : "memory");
+      asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(rc + 16),
+                   "r"(__float_as_uint(z)), "r"(rb)
+                   : "memory");
+    }
+    // wait until the candidates of all warps of the cluster have landed in this block
+    const unsigned lb = par ? bar1 : bar0, phase = (unsigned)((it - 1) >> 1) & 1u;
+    unsigned ok = fw_try_wait(lb, phase);
+    if (!ok) {  // bounded by time (one second) and by count
+      const unsigned long long t0 = fw_now();
+      for (int spin = 0; spin < (1 << 24) && !ok; ++spin) {
+        ok = fw_try_wait(lb, phase);
+        if (!ok && fw_now() - t0 > 1000000000ull) break;
+      }
+    }
+    if (!__all_sync(0xffffffffu, ok != 0)) {
+      failed = true;
+      break;
+    }
+    // the barrier just completed is used again two steps on
+    if (tid == 0 && it + 2 < S)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(lb), "r"(expect) : "memory");
+    const bool has = lane < nw;
+    const unsigned cb = has ? cand[par][lane].bits : 0u;
+    const int ci = has ? cand[par][lane].idx : 0x7fffffff;
+    const unsigned wb = __reduce_max_sync(0xffffffffu, cb);
+    const int wi = __reduce_min_sync(0xffffffffu, (has && cb == wb) ? ci : 0x7fffffff);
+    const int src = __ffs(__ballot_sync(0xffffffffu, has && cb == wb && ci == wi)) - 1;
+    cx = cand[par][src].x;
+    cy = cand[par][src].y;
+    cz = cand[par][src].z;
+    if (writer) {
+      out[it] = wi;
+      if (sm) {
+        sm[(int64_t)it * sps] = cx;
+        sm[(int64_t)it * sps + scs] = cy;
+        sm[(int64_t)it * sps + 2 * (int64_t)scs] = cz;
+      }
+    }
+  }
+  if (failed && rank == 0 && warp == 0 && lane == 0)
+    for (int r = it; r < S; ++r) out[r] = -1;  // a wait ran into its limit: the rest of the row is marked
+  cluster.sync();  // no block leaves while a candidate may still be on its way into its shared memory
+}
+
+using FpsClusterKernel = void (*)(const float *, int, int, int, int64_t *, int, int, float *, float);
+
+static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const float *points, int64_t B, int64_t N,
+                                      int64_t S, int ps, int64_t cs, int64_t *index, float *sampled, cudaStream_t st,
+                                      int *rc, int CL) {
   const int NL = (int)((N + CL - 1) / CL);
   const size_t smem = (size_t)NL * 12;
-  if (raise_smem_limit((const void *)fps_cluster_kernel, 98304) != cudaSuccess) {
+  if (raise_smem_limit((const void *)kern, 98304) != cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
-  if (CL > 8 && cudaFuncSetAttribute((const void *)fps_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed,
-                                     1) != cudaSuccess) {
+  if (CL > 8 && cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+                    cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(B * CL));
-  cfg.blockDim = dim3(FC_THREADS);
+  cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -196,14 +387,54 @@ bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int p
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, fps_cluster_kernel, points, (int)N, NL, (int)S, index, ps, (int)cs,
-                                           sampled, 1.0f);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, points, (int)N, NL, (int)S, index, ps, (int)cs, sampled, 1.0f);
   if (e != cudaSuccess) {  // e.g. a device partition without room for the cluster
     (void)cudaGetLastError();
     return false;
   }
   *rc = check_launch("fps_cluster_kernel");
   return true;
+}
+
+template <int THREADS, int P2>
+static bool fps_cluster_launch(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                               float *sampled, cudaStream_t st, int *rc, int CL) {
+  return fps_cluster_launch_kernel(fps_cluster_kernel<THREADS, P2>, THREADS, points, B, N, S, ps, cs, index, sampled, st,
+                                   rc, CL);
+}
+
+template <int THREADS, int P2>
+static bool fps_warpcast_launch(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                                float *sampled, cudaStream_t st, int *rc, int CL) {
+  return fps_cluster_launch_kernel(fps_warpcast_kernel<THREADS, P2>, THREADS, points, B, N, S, ps, cs, index, sampled,
+                                   st, rc, CL);
+}
+
+// Launches a cluster kernel when the clouds suit one (float32, 4096 < N <= 131072); returns false
+// when they do not or when the device refuses the cluster launch (the caller then takes its own
+// path), true with *rc set otherwise.
+//
+// 4097 to 16384 points and few clouds: the barrier-free kernel on clusters of eight small blocks
+// (two warps each up to 8192 points, four beyond; 16 points per thread).  Measured on B200, 512
+// samples, against one 1024-thread block per cloud (fps_resident_kernel), in ms:
+//   clouds            1      16     37     64     96
+//   N =  8192  here   0.253  0.269  0.286  0.300  0.358     one block  0.356
+//   N = 16384  here   0.303  0.336  0.374  0.448  0.762     one block  0.699
+// (four blocks of 256 threads: 0.261 / 0.264 / 0.320 / 0.325 / 0.404 at N = 8192).  Beyond about
+// half a cloud per SM the blocks of several clusters share SMs and the one-block kernel is as fast;
+// up to 4096 points its step (0.43 us) is shorter than the exchange over distributed shared
+// memory (0.5 us).
+bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                     float *sampled, cudaStream_t st, int *rc) {
+  if (N > 4096 && N <= 16384) {
+    if (B * 15 > (int64_t)sm_count() * 8) return false;
+    if (N <= 8192) return fps_warpcast_launch<64, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8);
+    return fps_warpcast_launch<128, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8);
+  }
+  if (N <= 16384 || N > (int64_t)FC_MAX_CL * FC_SLICE || B * FC_MAX_CL >= (1LL << 31)) return false;
+  int CL = 2;
+  while ((int64_t)CL * FC_SLICE < N) CL <<= 1;
+  return fps_cluster_launch<1024, 4>(points, B, N, S, ps, cs, index, sampled, st, rc, CL);
 }
 
 }  // namespace tk3d
