@@ -414,6 +414,28 @@ int tk3d_feature_knn(const void *query, const void *key, int64_t B, int64_t C, i
 long long tk3d_bounds_violations(void);
 
 /*
+ * Bounded waits.  One kernel waits for other thread blocks: farthest point sampling of float32
+ * clouds of 4097 to 131072 points runs on a thread-block cluster whose warps wait, in every step,
+ * for the candidates of all other warps of the cluster (an mbarrier in shared memory).  Every such
+ * wait gives up after one second; the warp then stops, which makes the other warps of its cluster
+ * give up as well, index[b][i..] of that cloud is set to -1 from the first step that was not
+ * completed, and the kernel ends normally: the CUDA context stays usable.
+ * tk3d_fps_expired_waits() synchronises nothing itself beyond a 4-byte copy from the device and
+ * returns the number of waits that gave up on the current device since the library was loaded
+ * (0 in normal operation; -1 if the counter cannot be read).
+ *
+ * tk3d_diag_fps_wait_limit() is a diagnostic with no counterpart in the reference, for testing
+ * that path without a fault: it runs the cluster kernel on points [B,N,3] (float32, 4096 < N <=
+ * 131072) with the waits limited to limit_ms (1..1000) and with one warp of every cluster sending
+ * nothing in step drop_step (>= 1; -1: every warp sends, i.e. a normal run), so that every wait of
+ * that step runs out.  index [B,num_samples] then holds the regular result up to drop_step - 1
+ * and -1 from drop_step on.
+ */
+long long tk3d_fps_expired_waits(void);
+int tk3d_diag_fps_wait_limit(const void *points, int64_t B, int64_t N, int64_t num_samples, int64_t *index,
+                             int64_t limit_ms, int64_t drop_step, void *stream);
+
+/*
  * Diagnostic with no counterpart in the reference: launches a kernel of dependent FP32 fused
  * multiply-add chains (`iters` x 64 FMAs per thread, 8 blocks of 256 threads per SM) on `stream`.
  * *flop (a HOST double, optional) receives the number of floating-point operations the launch

@@ -61,6 +61,8 @@ SIGNATURES = {
     "tk3d_edge_feature_bwd": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp,
                                      ctypes.c_size_t, _int, _vp]),
     "tk3d_bounds_violations": (ctypes.c_longlong, []),
+    "tk3d_fps_expired_waits": (ctypes.c_longlong, []),
+    "tk3d_diag_fps_wait_limit": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp]),
     "tk3d_diag_ffma": (_int, [_i64, _vp, ctypes.POINTER(ctypes.c_double), _vp]),
     "tk3d_feature_knn": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _int, _vp]),
     "tk3d_chamfer_fwd_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _int]),

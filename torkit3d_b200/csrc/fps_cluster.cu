@@ -72,10 +72,14 @@ __device__ __forceinline__ unsigned long long fw_now() {
   return t;
 }
 
+// Waits that ran into their limit since the library was loaded (per device); read by
+// tk3d_fps_expired_waits().
+__device__ unsigned int fw_expired_waits = 0;
+
 template <int FW_THREADS, int FW_P2, int FW_SLOTS>
 __global__ void __launch_bounds__(FW_THREADS)
 fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int64_t *__restrict__ index, int ps, int cs,
-                    float *__restrict__ sampled, float one) {
+                    float *__restrict__ sampled, float one, unsigned long long limit_ns, int drop_step) {
   cg::cluster_group cluster = cg::this_cluster();
   const int CL = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   const int cloud = blockIdx.x / CL;
@@ -167,7 +171,7 @@ fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int6
       }
     }
     const int loc = __reduce_min_sync(0xffffffffu, mine);  // lowest local index holding the warp's maximum
-    if (lane < CL) {
+    if (lane < CL && !(it == drop_step && gw == 0)) {  // drop_step: diagnostic only, -1 otherwise
       const bool real = loc < nloc;
       const float x = real ? sxyz[3 * loc + 0] : 0.f, y = real ? sxyz[3 * loc + 1] : 0.f,
                   z = real ? sxyz[3 * loc + 2] : 0.f;
@@ -183,11 +187,11 @@ fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int6
     // wait until the candidates of all warps of the cluster have landed in this block
     const unsigned lb = par ? bar1 : bar0, phase = (unsigned)((it - 1) >> 1) & 1u;
     unsigned ok = fw_try_wait(lb, phase);
-    if (!ok) {  // bounded by time (one second) and by count
+    if (!ok) {  // bounded by time (limit_ns: one second) and by count
       const unsigned long long t0 = fw_now();
       for (int spin = 0; spin < (1 << 24) && !ok; ++spin) {
         ok = fw_try_wait(lb, phase);
-        if (!ok && fw_now() - t0 > 1000000000ull) break;
+        if (!ok && fw_now() - t0 > limit_ns) break;
       }
     }
     if (!__all_sync(0xffffffffu, ok != 0)) {
@@ -231,16 +235,23 @@ fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int6
       }
     }
   }
+  if (failed && lane == 0) atomicAdd(&fw_expired_waits, 1u);
   if (failed && rank == 0 && warp == 0 && lane == 0)
     for (int r = it; r < S; ++r) out[r] = -1;  // a wait ran into its limit: the rest of the row is marked
   cluster.sync();  // no block leaves while a candidate may still be on its way into its shared memory
 }
 
-using FpsClusterKernel = void (*)(const float *, int, int, int, int64_t *, int, int, float *, float);
+using FpsClusterKernel = void (*)(const float *, int, int, int, int64_t *, int, int, float *, float,
+                                  unsigned long long, int);
+
+struct FwWait {
+  unsigned long long limit_ns;  // every wait for the other warps' candidates gives up after this long
+  int drop_step;                // diagnostic: the step in which one warp per cluster sends nothing; -1: none
+};
 
 static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const float *points, int64_t B, int64_t N,
                                       int64_t S, int ps, int64_t cs, int64_t *index, float *sampled, cudaStream_t st,
-                                      int *rc, int CL) {
+                                      int *rc, int CL, FwWait wt) {
   const int NL = (int)((N + CL - 1) / CL);
   const size_t smem = (size_t)NL * 12;
   if (raise_smem_limit((const void *)kern, 98304) != cudaSuccess) {
@@ -264,7 +275,8 @@ static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, points, (int)N, NL, (int)S, index, ps, (int)cs, sampled, 1.0f);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, points, (int)N, NL, (int)S, index, ps, (int)cs, sampled, 1.0f,
+                                           wt.limit_ns, wt.drop_step);
   if (e != cudaSuccess) {  // e.g. a device partition without room for the cluster
     (void)cudaGetLastError();
     return false;
@@ -275,12 +287,12 @@ static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const 
 
 template <int THREADS, int P2>
 static bool fps_warpcast_launch(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
-                                float *sampled, cudaStream_t st, int *rc, int CL) {
+                                float *sampled, cudaStream_t st, int *rc, int CL, FwWait wt) {
   if (CL * (THREADS / 32) <= 32)
     return fps_cluster_launch_kernel(fps_warpcast_kernel<THREADS, P2, 32>, THREADS, points, B, N, S, ps, cs, index,
-                                     sampled, st, rc, CL);
+                                     sampled, st, rc, CL, wt);
   return fps_cluster_launch_kernel(fps_warpcast_kernel<THREADS, P2, 512>, THREADS, points, B, N, S, ps, cs, index,
-                                   sampled, st, rc, CL);
+                                   sampled, st, rc, CL, wt);
 }
 
 // Launches a cluster kernel when the clouds suit one (float32, 4096 < N <= 131072); returns false
@@ -297,21 +309,51 @@ static bool fps_warpcast_launch(const float *points, int64_t B, int64_t N, int64
 // half a cloud per SM the blocks of several clusters share SMs and the one-block kernel is as fast;
 // up to 4096 points its step (0.43 us) is shorter than the exchange over distributed shared
 // memory (0.5 us).
-bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
-                     float *sampled, cudaStream_t st, int *rc) {
+static bool fps_cluster_dispatch(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs,
+                                 int64_t *index, float *sampled, cudaStream_t st, int *rc, FwWait wt, bool force) {
   if (N > 4096 && N <= 16384) {
-    if (B * 15 > (int64_t)sm_count() * 8) return false;
-    if (N <= 8192) return fps_warpcast_launch<64, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8);
-    return fps_warpcast_launch<128, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8);
+    if (!force && B * 15 > (int64_t)sm_count() * 8) return false;
+    if (N <= 8192) return fps_warpcast_launch<64, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
+    return fps_warpcast_launch<128, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
   }
   if (N <= 16384 || N > 131072 || B * FC_MAX_CL >= (1LL << 31)) return false;
   // larger clouds: 32 points per thread, so that a cluster has at most 128 warps (4 clouds, 512 samples:
   // 32768 points 0.375 ms, 0.48 with 16 points per thread and twice the warps; 65536 points 0.51 / 0.60)
-  if (N <= 32768) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 8);
-  if (N <= 65536) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 16);
-  return fps_warpcast_launch<256, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 16);
+  if (N <= 32768) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
+  if (N <= 65536) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 16, wt);
+  return fps_warpcast_launch<256, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 16, wt);
+}
+
+bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                     float *sampled, cudaStream_t st, int *rc) {
+  return fps_cluster_dispatch(points, B, N, S, ps, cs, index, sampled, st, rc, FwWait{1000000000ull, -1}, false);
 }
 
 }  // namespace tk3d
+
+using namespace tk3d;
+
+extern "C" long long tk3d_fps_expired_waits(void) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, fw_expired_waits, sizeof(v)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return (long long)v;
+}
+
+extern "C" int tk3d_diag_fps_wait_limit(const void *points, int64_t B, int64_t N, int64_t num_samples, int64_t *index,
+                                        int64_t limit_ms, int64_t drop_step, void *stream) {
+  TK3D_REQUIRE(points && index, TK3D_ERR_NULL, "diag_fps_wait_limit: a pointer is NULL");
+  TK3D_REQUIRE(B > 0 && N > 4096 && N <= 131072 && num_samples > 0 && num_samples <= N, TK3D_ERR_SHAPE,
+               "diag_fps_wait_limit: needs 4096 < N <= 131072 and 0 < num_samples <= N");
+  TK3D_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, TK3D_ERR_SHAPE, "diag_fps_wait_limit: limit of 1 to 1000 ms");
+  int rc = TK3D_OK;
+  const FwWait wt{(unsigned long long)limit_ms * 1000000ull, (int)drop_step};
+  if (!fps_cluster_dispatch((const float *)points, B, N, num_samples, 3, 1, index, nullptr, (cudaStream_t)stream, &rc, wt,
+                            true))
+    return fail(TK3D_ERR_CUDA, "diag_fps_wait_limit: the device refused the cluster launch");
+  return rc;
+}
 
 TK3D_BOUNDS_TU(fps_cluster)
