@@ -468,9 +468,10 @@ FPS_CASES = [(1, 31, 2), (2, 1024, 128), (3, 1025, 129), (16, 1024, 512), (4, 40
              # few clouds of 4097 to 16384 points: clusters of eight small blocks without barriers in the step;
              # many such clouds: one block per cloud again
              (2, 4097, 50), (3, 5000, 300), (1, 16384, 128), (40, 6000, 64), (3, 12345, 2000), (90, 4500, 32),
-             # a cluster of 2 / 4 / 8 / 16 blocks per cloud (16385 to 131072 points), then the streaming kernel
+             # a cluster of 8 / 16 blocks per cloud (16385 to 262144 points; beyond 131072 the coordinates stay in
+             # shared memory), then the streaming kernel
              (2, 16385, 96), (3, 30000, 128), (2, 40961, 70), (1, 65536, 200), (1, 65537, 40), (1, 131072, 33),
-             (1, 131073, 20)]
+             (1, 131073, 20), (2, 200000, 30), (1, 262144, 16), (1, 262145, 8)]
 
 
 @pytest.mark.parametrize("B,n,s", FPS_CASES)

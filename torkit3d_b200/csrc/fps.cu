@@ -10,13 +10,12 @@
 //    coordinates from the shared-memory copy (192 KB at most) in every step.
 //    A step is: P exact distance updates per thread, a block-wide maximum of the running minima
 //    (REDUX, one shared-memory exchange, REDUX), and the lowest index holding that maximum.
-//    (A variant that spreads one cloud over a thread-block cluster of 2-8 CTAs, exchanging the
-//    per-warp candidates through distributed shared memory with one cluster barrier per step, was
-//    measured slower on B200 -- 1.07 ms against 0.88 ms for 32 clouds of 8192 points -- because
-//    the cluster barrier costs more per step than the divided arithmetic saves.)
+//    Clouds of up to 4096 points, and large batches of clouds up to 16384 points (more than about
+//    half a cloud per SM).
 //  * fp64, N <= 8192: the same persistent structure with the coordinates in shared memory and up to
 //    8 running minima per thread; the block maximum is taken on the 64-bit pattern in two REDUX steps.
-//  * fp32, 16385 to 131072 points: a thread-block cluster per cloud, fps_cluster.cu.
+//  * fp32, 16385 to 262144 points (and few clouds of 4097 to 16384): a thread-block cluster per cloud,
+//    fps_cluster.cu.
 //  * any other case ("streaming" kernel): points are re-read from global memory (L1/L2 resident)
 //    and the running minimum lives in a caller-provided global scratch array.
 //
@@ -395,7 +394,7 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
   }
   if (dtype == TK3D_F32 && N > 4096) {
     // a cluster of blocks per cloud (fps_cluster.cu): few clouds of 4097 to 16384 points, and every
-    // cloud of 16385 to 131072 points; no scratch.  Declines (false) what the kernels below do better.
+    // cloud of 16385 to 262144 points; no scratch.  Declines (false) what the kernels below do better.
     int rc = TK3D_OK;
     if (fps_cluster_f32((const float *)points, B, N, S, (int)ps, cs, index, (float *)sampled, st, &rc)) return rc;
   }

@@ -1,4 +1,4 @@
-// Farthest point sampling of float32 clouds on thread-block clusters (4097 to 131072 points).
+// Farthest point sampling of float32 clouds on thread-block clusters (4097 to 262144 points).
 //
 // The resident kernel of fps.cu keeps a cloud in the registers of ONE block: its step is a chain of
 // two block barriers over 32 warps and two block reductions (0.69 us at 8192 points), it ends at
@@ -76,7 +76,9 @@ __device__ __forceinline__ unsigned long long fw_now() {
 // tk3d_fps_expired_waits().
 __device__ unsigned int fw_expired_waits = 0;
 
-template <int FW_THREADS, int FW_P2, int FW_SLOTS>
+// FW_REGS false (clouds beyond 131072 points): the coordinates stay in shared memory, which then
+// holds FW_THREADS * 2 * FW_P2 points, and only the running minima live in registers.
+template <int FW_THREADS, int FW_P2, int FW_SLOTS, bool FW_REGS = true>
 __global__ void __launch_bounds__(FW_THREADS)
 fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int64_t *__restrict__ index, int ps, int cs,
                     float *__restrict__ sampled, float one, unsigned long long limit_ns, int drop_step) {
@@ -111,17 +113,25 @@ fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int6
   }
   __syncthreads();
 
-  float2 px[FW_P2], py[FW_P2], pz[FW_P2], md[FW_P2];
+  constexpr int FW_PREG = FW_REGS ? FW_P2 : 1;
+  float2 px[FW_PREG], py[FW_PREG], pz[FW_PREG], md[FW_P2];
   const float qnan = __int_as_float(0x7fc00000), pinf = __int_as_float(0x7f800000);
+  if constexpr (!FW_REGS) {
+    // padding slots of the shared-memory copy: NaN coordinates keep their distance of 0
+    for (int e = 3 * nloc + tid; e < 3 * T * 2 * FW_P2; e += T) sxyz[e] = qnan;
+    __syncthreads();
+  }
 #pragma unroll
   for (int i = 0; i < FW_P2; ++i) {
     const int j0 = (2 * i) * T + tid, j1 = (2 * i + 1) * T + tid;
-    px[i].x = j0 < nloc ? sxyz[3 * j0 + 0] : qnan;
-    py[i].x = j0 < nloc ? sxyz[3 * j0 + 1] : qnan;
-    pz[i].x = j0 < nloc ? sxyz[3 * j0 + 2] : qnan;
-    px[i].y = j1 < nloc ? sxyz[3 * j1 + 0] : qnan;
-    py[i].y = j1 < nloc ? sxyz[3 * j1 + 1] : qnan;
-    pz[i].y = j1 < nloc ? sxyz[3 * j1 + 2] : qnan;
+    if constexpr (FW_REGS) {
+      px[i].x = j0 < nloc ? sxyz[3 * j0 + 0] : qnan;
+      py[i].x = j0 < nloc ? sxyz[3 * j0 + 1] : qnan;
+      pz[i].x = j0 < nloc ? sxyz[3 * j0 + 2] : qnan;
+      px[i].y = j1 < nloc ? sxyz[3 * j1 + 0] : qnan;
+      py[i].y = j1 < nloc ? sxyz[3 * j1 + 1] : qnan;
+      pz[i].y = j1 < nloc ? sxyz[3 * j1 + 2] : qnan;
+    }
     md[i].x = j0 < nloc ? pinf : 0.f;
     md[i].y = j1 < nloc ? pinf : 0.f;
   }
@@ -154,7 +164,18 @@ fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int6
     float bm = 0.f;
 #pragma unroll
     for (int i = 0; i < FW_P2; ++i) {
-      const float2 dx = __fadd2_rn(px[i], ncx), dy = __fadd2_rn(py[i], ncy), dz = __fadd2_rn(pz[i], ncz);
+      float2 qx_, qy_, qz_;
+      if constexpr (FW_REGS) {
+        qx_ = px[i];
+        qy_ = py[i];
+        qz_ = pz[i];
+      } else {
+        const float *a0 = sxyz + 3 * ((2 * i) * T + tid), *a1 = sxyz + 3 * ((2 * i + 1) * T + tid);
+        qx_ = make_float2(a0[0], a1[0]);
+        qy_ = make_float2(a0[1], a1[1]);
+        qz_ = make_float2(a0[2], a1[2]);
+      }
+      const float2 dx = __fadd2_rn(qx_, ncx), dy = __fadd2_rn(qy_, ncy), dz = __fadd2_rn(qz_, ncz);
       const float2 d = __ffma2_rn(__ffma2_rn(__fmul2_rn(dx, dx), one2, __fmul2_rn(dy, dy)), one2, __fmul2_rn(dz, dz));
       md[i].x = fminf(md[i].x, d.x);
       md[i].y = fminf(md[i].y, d.y);
@@ -251,10 +272,10 @@ struct FwWait {
 
 static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const float *points, int64_t B, int64_t N,
                                       int64_t S, int ps, int64_t cs, int64_t *index, float *sampled, cudaStream_t st,
-                                      int *rc, int CL, FwWait wt) {
+                                      int *rc, int CL, FwWait wt, size_t smem_fixed = 0) {
   const int NL = (int)((N + CL - 1) / CL);
-  const size_t smem = (size_t)NL * 12;
-  if (raise_smem_limit((const void *)kern, 98304) != cudaSuccess) {
+  const size_t smem = smem_fixed ? smem_fixed : (size_t)NL * 12;
+  if (raise_smem_limit((const void *)kern, smem_fixed ? (int)smem_fixed : 98304) != cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
@@ -295,7 +316,7 @@ static bool fps_warpcast_launch(const float *points, int64_t B, int64_t N, int64
                                    sampled, st, rc, CL, wt);
 }
 
-// Launches a cluster kernel when the clouds suit one (float32, 4096 < N <= 131072); returns false
+// Launches a cluster kernel when the clouds suit one (float32, 4096 < N <= 262144); returns false
 // when they do not or when the device refuses the cluster launch (the caller then takes its own
 // path), true with *rc set otherwise.
 //
@@ -316,7 +337,10 @@ static bool fps_cluster_dispatch(const float *points, int64_t B, int64_t N, int6
     if (N <= 8192) return fps_warpcast_launch<64, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
     return fps_warpcast_launch<128, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
   }
-  if (N <= 16384 || N > 131072 || B * FC_MAX_CL >= (1LL << 31)) return false;
+  if (N <= 16384 || N > 262144 || B * FC_MAX_CL >= (1LL << 31)) return false;
+  if (N > 131072)  // 64 points per thread: running minima in registers, coordinates in 192 KB of shared memory
+    return fps_cluster_launch_kernel(fps_warpcast_kernel<256, 32, 128, false>, 256, points, B, N, S, ps, cs, index,
+                                     sampled, st, rc, 16, wt, (size_t)256 * 64 * 12);
   // larger clouds: 32 points per thread, so that a cluster has at most 128 warps (4 clouds, 512 samples:
   // 32768 points 0.375 ms, 0.48 with 16 points per thread and twice the warps; 65536 points 0.51 / 0.60)
   if (N <= 32768) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
