@@ -124,7 +124,8 @@ int tk3d_knn(const void *query, const void *key, int64_t B, int64_t N1, int64_t 
  *   scratch          device buffer of at least tk3d_fps_scratch_bytes(B,N,dtype) bytes (the running
  *                    minimum distance of clouds too large to keep on chip); may be NULL when that
  *                    function returns 0.  Contents on entry are ignored.  (float32 clouds of 16385
- *                    to 262144 points run on a thread-block cluster and leave it untouched; it is
+ *                    to 262144 points and float64 clouds of 8193 to 131072 points run on a
+ *                    thread-block cluster and leave it untouched; it is
  *                    what the call falls back on when the device refuses the cluster launch.)
  */
 size_t tk3d_fps_scratch_bytes(int64_t B, int64_t N, int dtype);
@@ -414,8 +415,9 @@ int tk3d_feature_knn(const void *query, const void *key, int64_t B, int64_t C, i
 long long tk3d_bounds_violations(void);
 
 /*
- * Bounded waits.  One kernel waits for other thread blocks: farthest point sampling of float32
- * clouds of 4097 to 262144 points runs on a thread-block cluster whose warps wait, in every step,
+ * Bounded waits.  One kind of kernel waits for other thread blocks: farthest point sampling of
+ * float32 clouds of 4097 to 262144 points (float64: 2049 to 131072) runs on a thread-block cluster
+ * whose warps wait, in every step,
  * for the candidates of all other warps of the cluster (an mbarrier in shared memory).  Every such
  * wait gives up after one second; the warp then stops, which makes the other warps of its cluster
  * give up as well, index[b][i..] of that cloud is set to -1 from the first step that was not

@@ -517,6 +517,39 @@ def test_fps_cluster_ties_and_gather(oracle):
     np.testing.assert_array_equal(N(sample_farthest_points(T(dup), 3200)), oracle.fps(dup, 3200))
 
 
+@pytest.mark.parametrize("B,n,s", [(2, 3000, 60), (1, 4097, 40), (2, 8192, 50), (3, 9000, 30), (1, 20000, 40),
+                                   (1, 40000, 20), (1, 70000, 16), (1, 131072, 10), (1, 131073, 6), (90, 2500, 16)])
+def test_fps_float64_clusters_bit_exact(oracle, B, n, s):
+    """float64 clouds on thread-block clusters (few clouds of 2049 to 8192 points, every cloud of 8193 to
+    131072 points), the streaming kernel beyond, one block per cloud for large batches; both layouts."""
+    from torkit3d_b200.ops import sample_farthest_points
+
+    rng = np.random.default_rng(n + s)
+    p = rng.random((B, n, 3))
+    want = oracle.fps(p, s)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(p), s)), want)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(p).transpose(1, 2), s, transpose=True)), want)
+
+
+def test_fps_float64_cluster_ties_and_gather(oracle):
+    from torkit3d_b200 import _fused
+    from torkit3d_b200.ops import sample_farthest_points
+
+    rng = np.random.default_rng(78)
+    p = rng.integers(-5, 6, size=(2, 6000, 3)) * 0.5  # a coarse lattice: exact ties across the blocks' slices
+    np.testing.assert_array_equal(N(sample_farthest_points(T(p), 300)), oracle.fps(p, 300))
+    same = np.full((1, 9000, 3), 0.25)
+    np.testing.assert_array_equal(N(sample_farthest_points(T(same), 5)), oracle.fps(same, 5))
+    q = rng.random((2, 12000, 3))
+    want = oracle.fps(q, 48)
+    for cf in (False, True):
+        pts = T(q).transpose(1, 2).contiguous() if cf else T(q)
+        idx, cent = _fused.fps_gather(pts, 48, channel_first=cf)
+        np.testing.assert_array_equal(N(idx), want)
+        ref = np.take_along_axis(q, want[..., None], axis=1)
+        np.testing.assert_array_equal(N(cent.transpose(1, 2) if cf else cent), ref)
+
+
 def test_fps_golden_fp64_and_duplicates(oracle, golden):
     from torkit3d_b200.ops import sample_farthest_points
 

@@ -14,6 +14,7 @@
 //    half a cloud per SM).
 //  * fp64, N <= 8192: the same persistent structure with the coordinates in shared memory and up to
 //    8 running minima per thread; the block maximum is taken on the 64-bit pattern in two REDUX steps.
+//    (Few clouds of 2049 to 8192 points and every cloud of 8193 to 131072 points: clusters, fps_cluster.cu.)
 //  * fp32, 16385 to 262144 points (and few clouds of 4097 to 16384): a thread-block cluster per cloud,
 //    fps_cluster.cu.
 //  * any other case ("streaming" kernel): points are re-read from global memory (L1/L2 resident)
@@ -347,6 +348,8 @@ int threads_for(int64_t N) {
 namespace tk3d {
 bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
                      float *sampled, cudaStream_t st, int *rc);
+bool fps_cluster_f64(const double *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                     double *sampled, cudaStream_t st, int *rc);
 }
 
 using namespace tk3d;
@@ -372,6 +375,12 @@ static int fps_impl(const void *points, int64_t B, int64_t N, int64_t S, int cha
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t ps = channel_first ? 1 : 3, cs = channel_first ? N : 1;
   const size_t need = tk3d_fps_scratch_bytes(B, N, dtype);
+  if (dtype == TK3D_F64 && N > 2048) {
+    // a cluster of blocks per cloud (fps_cluster.cu): few clouds of 2049 to 8192 points, every cloud of
+    // 8193 to 131072 points; no scratch.  Declines (false) what the kernels below do better.
+    int rc = TK3D_OK;
+    if (fps_cluster_f64((const double *)points, B, N, S, (int)ps, cs, index, (double *)sampled, st, &rc)) return rc;
+  }
   if (need == 0 && dtype == TK3D_F64) {
     int threads = threads_for((N + 7) / 8);
     if (threads < 128) threads = 128;

@@ -1,4 +1,5 @@
-// Farthest point sampling of float32 clouds on thread-block clusters (4097 to 262144 points).
+// Farthest point sampling on thread-block clusters: float32 clouds of 4097 to 262144 points, float64
+// clouds of 2049 to 131072 points.
 //
 // The resident kernel of fps.cu keeps a cloud in the registers of ONE block: its step is a chain of
 // two block barriers over 32 warps and two block reductions (0.69 us at 8192 points), it ends at
@@ -262,25 +263,185 @@ fps_warpcast_kernel(const float *__restrict__ points, int N, int NL, int S, int6
   cluster.sync();  // no block leaves while a candidate may still be on its way into its shared memory
 }
 
-using FpsClusterKernel = void (*)(const float *, int, int, int, int64_t *, int, int, float *, float,
-                                  unsigned long long, int);
+// ---------------------------------------------------------------------------------------------
+// float64: the same step on doubles.  The coordinates stay in the block's shared-memory copy (24
+// bytes per point), the running minima live in registers (P per thread); a candidate is 40 bytes
+// (64-bit distance pattern, index, three doubles), the maxima are taken on the 64-bit pattern in
+// two REDUX steps.  Arithmetic as in fps_resident64_kernel: ((dx*dx + dy*dy) + dz*dz) with
+// individually rounded operations.
+struct __align__(16) FwCandidate64 {
+  unsigned long long bits;
+  int idx;
+  int pad;
+  double x, y;
+  double z;
+  double pad2;
+};
+constexpr unsigned FW_CAND64_BYTES = 40;
+
+__device__ __forceinline__ unsigned long long fw_warp_max64(unsigned long long v) {
+  const unsigned hi = (unsigned)(v >> 32), lo = (unsigned)v;
+  const unsigned whi = __reduce_max_sync(0xffffffffu, hi);
+  const unsigned wlo = __reduce_max_sync(0xffffffffu, hi == whi ? lo : 0u);
+  return ((unsigned long long)whi << 32) | wlo;
+}
+
+template <int FW_THREADS, int FW_P, int FW_SLOTS>
+__global__ void __launch_bounds__(FW_THREADS)
+fps_warpcast64_kernel(const double *__restrict__ points, int N, int NL, int S, int64_t *__restrict__ index, int ps,
+                      int cs, double *__restrict__ sampled, unsigned long long limit_ns, int drop_step) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CL = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  const int cloud = blockIdx.x / CL;
+  extern __shared__ double dxyz[];  // [3 * FW_THREADS * FW_P]: this block's slice, padded with NaN
+  __shared__ FwCandidate64 cand[2][FW_SLOTS];
+  __shared__ __align__(8) unsigned long long mbar[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int T = FW_THREADS, W = FW_THREADS / 32;
+  const int nw = CL * W, gw = rank * W + warp;
+  const double *pts = points + (int64_t)cloud * N * 3;
+  int64_t *out = index + (int64_t)cloud * S;
+  const int base = rank * NL;
+  const int nloc = max(0, min(NL, N - base));
+  const double qnan = __longlong_as_double(0x7ff8000000000000LL);
+
+  for (int e = tid; e < 3 * T * FW_P; e += T) {
+    const int j = e / 3, d = e - 3 * j;
+    dxyz[e] = j < nloc ? pts[(int64_t)(base + j) * ps + (int64_t)d * cs] : qnan;
+  }
+  const unsigned bar0 = fw_smem(&mbar[0]), bar1 = fw_smem(&mbar[1]);
+  const unsigned expect = (unsigned)nw * FW_CAND64_BYTES;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar1), "r"(expect) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar0), "r"(expect) : "memory");
+  }
+  __syncthreads();
+
+  // Point i of this thread is local j = i * T + tid; padding keeps a running minimum of 0.
+  double md[FW_P];
+#pragma unroll
+  for (int i = 0; i < FW_P; ++i) md[i] = (i * T + tid) < nloc ? Exact<double>::inf() : 0.0;
+
+  double cx = pts[0], cy = pts[cs], cz = pts[2 * (int64_t)cs];
+  const bool writer = rank == 0 && tid == 0;
+  const int sps = cs == 1 ? 3 : 1, scs = cs == 1 ? 1 : S;
+  double *sm = sampled ? sampled + (int64_t)cloud * S * 3 : nullptr;
+  if (writer) {
+    out[0] = 0;
+    if (sm) {
+      sm[0] = cx;
+      sm[scs] = cy;
+      sm[2 * (int64_t)scs] = cz;
+    }
+  }
+  cluster.sync();
+
+  const unsigned tgt = (unsigned)(lane < CL ? lane : 0);
+  const unsigned rcand0 = fw_mapa(fw_smem(&cand[0][gw]), tgt), rcand1 = fw_mapa(fw_smem(&cand[1][gw]), tgt);
+  const unsigned rbar0 = fw_mapa(bar0, tgt), rbar1 = fw_mapa(bar1, tgt);
+
+  bool failed = false;
+  int it = 1;
+  for (; it < S; ++it) {
+    const int par = it & 1;
+    double bm = 0.0;
+#pragma unroll
+    for (int i = 0; i < FW_P; ++i) {
+      const double *a = dxyz + 3 * (i * T + tid);
+      const double d = sqdist<double>(a[0], a[1], a[2], cx, cy, cz);
+      md[i] = fmin(md[i], d);
+      bm = fmax(bm, md[i]);
+    }
+    const unsigned long long bits = (unsigned long long)__double_as_longlong(bm);
+    const unsigned long long gb = fw_warp_max64(bits);
+    int mine = 0x7fffffff;
+    if (bits == gb) {
+#pragma unroll
+      for (int i = FW_P - 1; i >= 0; --i)
+        if (md[i] == bm) mine = i * T + tid;
+    }
+    const int loc = __reduce_min_sync(0xffffffffu, mine);
+    if (lane < CL && !(it == drop_step && gw == 0)) {
+      const bool real = loc < nloc;
+      const double x = real ? dxyz[3 * loc + 0] : 0.0, y = real ? dxyz[3 * loc + 1] : 0.0,
+                   z = real ? dxyz[3 * loc + 2] : 0.0;
+      const unsigned rc = par ? rcand1 : rcand0, rb = par ? rbar1 : rbar0;
+      asm volatile(
+          "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(rc),
+          "r"((unsigned)gb), "r"((unsigned)(gb >> 32)), "r"(base + loc), "r"(0), "r"(rb)
+          : "memory");
+      asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b64 [%0], {%1, %2}, [%3];" ::"r"(rc + 16),
+                   "l"(__double_as_longlong(x)), "l"(__double_as_longlong(y)), "r"(rb)
+                   : "memory");
+      asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b64 [%0], %1, [%2];" ::"r"(rc + 32),
+                   "l"(__double_as_longlong(z)), "r"(rb)
+                   : "memory");
+    }
+    const unsigned lb = par ? bar1 : bar0, phase = (unsigned)((it - 1) >> 1) & 1u;
+    unsigned ok = fw_try_wait(lb, phase);
+    if (!ok) {
+      const unsigned long long t0 = fw_now();
+      for (int spin = 0; spin < (1 << 24) && !ok; ++spin) {
+        ok = fw_try_wait(lb, phase);
+        if (!ok && fw_now() - t0 > limit_ns) break;
+      }
+    }
+    if (!__all_sync(0xffffffffu, ok != 0)) {
+      failed = true;
+      break;
+    }
+    if (tid == 0 && it + 2 < S)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(lb), "r"(expect) : "memory");
+    const bool has = lane < nw;
+    unsigned long long cb = 0ull;
+    int ci = 0x7fffffff, slot = lane;
+    for (int sl = lane; sl < nw; sl += 32) {
+      const unsigned long long b_ = cand[par][sl].bits;
+      const int i_ = cand[par][sl].idx;
+      if (b_ > cb || (b_ == cb && i_ < ci)) {
+        cb = b_;
+        ci = i_;
+        slot = sl;
+      }
+    }
+    const unsigned long long wb = fw_warp_max64(has ? cb : 0ull);
+    const int wi = __reduce_min_sync(0xffffffffu, (has && cb == wb) ? ci : 0x7fffffff);
+    int src = __ffs(__ballot_sync(0xffffffffu, has && cb == wb && ci == wi)) - 1;
+    src = __shfl_sync(0xffffffffu, slot, src);
+    cx = cand[par][src].x;
+    cy = cand[par][src].y;
+    cz = cand[par][src].z;
+    if (writer) {
+      out[it] = wi;
+      if (sm) {
+        sm[(int64_t)it * sps] = cx;
+        sm[(int64_t)it * sps + scs] = cy;
+        sm[(int64_t)it * sps + 2 * (int64_t)scs] = cz;
+      }
+    }
+  }
+  if (failed && lane == 0) atomicAdd(&fw_expired_waits, 1u);
+  if (failed && rank == 0 && warp == 0 && lane == 0)
+    for (int r = it; r < S; ++r) out[r] = -1;
+  cluster.sync();
+}
 
 struct FwWait {
   unsigned long long limit_ns;  // every wait for the other warps' candidates gives up after this long
   int drop_step;                // diagnostic: the step in which one warp per cluster sends nothing; -1: none
 };
 
-static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const float *points, int64_t B, int64_t N,
-                                      int64_t S, int ps, int64_t cs, int64_t *index, float *sampled, cudaStream_t st,
-                                      int *rc, int CL, FwWait wt, size_t smem_fixed = 0) {
-  const int NL = (int)((N + CL - 1) / CL);
-  const size_t smem = smem_fixed ? smem_fixed : (size_t)NL * 12;
-  if (raise_smem_limit((const void *)kern, smem_fixed ? (int)smem_fixed : 98304) != cudaSuccess) {
+// Cluster launch shared by the float32 and float64 kernels; `args` are the kernel's arguments.
+static bool fps_cluster_launch_any(const void *kern, int THREADS, int64_t B, size_t smem, size_t smem_limit,
+                                   cudaStream_t st, int *rc, int CL, void **args) {
+  if (raise_smem_limit(kern, (int)smem_limit) != cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
-  if (CL > 8 && cudaFuncSetAttribute((const void *)kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
-                    cudaSuccess) {
+  if (CL > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
     (void)cudaGetLastError();
     return false;
   }
@@ -296,8 +457,7 @@ static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, points, (int)N, NL, (int)S, index, ps, (int)cs, sampled, 1.0f,
-                                           wt.limit_ns, wt.drop_step);
+  const cudaError_t e = cudaLaunchKernelExC(&cfg, kern, args);
   if (e != cudaSuccess) {  // e.g. a device partition without room for the cluster
     (void)cudaGetLastError();
     return false;
@@ -306,9 +466,34 @@ static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const 
   return true;
 }
 
+using FpsClusterKernel = void (*)(const float *, int, int, int, int64_t *, int, int, float *, float,
+                                  unsigned long long, int);
+
+static bool fps_cluster_launch_kernel(FpsClusterKernel kern, int THREADS, const float *points, int64_t B, int64_t N,
+                                      int64_t S, int ps, int64_t cs, int64_t *index, float *sampled, cudaStream_t st,
+                                      int *rc, int CL, FwWait wt, size_t smem_fixed = 0) {
+  int n = (int)N, NL = (int)((N + CL - 1) / CL), s_ = (int)S, cs_ = (int)cs;
+  float one = 1.0f;
+  const size_t smem = smem_fixed ? smem_fixed : (size_t)NL * 12;
+  void *args[] = {&points, &n, &NL, &s_, &index, &ps, &cs_, &sampled, &one, &wt.limit_ns, &wt.drop_step};
+  return fps_cluster_launch_any((const void *)kern, THREADS, B, smem, smem_fixed ? smem_fixed : 98304, st, rc, CL, args);
+}
+
+template <int THREADS, int P, int SLOTS>
+static bool fps_warpcast64_launch(const double *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs,
+                                  int64_t *index, double *sampled, cudaStream_t st, int *rc, int CL, FwWait wt) {
+  if (CL * (THREADS / 32) > SLOTS || (int64_t)CL * THREADS * P < N) return false;  // a slot per warp, a register per point
+  int n = (int)N, NL = (int)((N + CL - 1) / CL), s_ = (int)S, cs_ = (int)cs;
+  const size_t smem = (size_t)THREADS * P * 24;
+  void *args[] = {&points, &n, &NL, &s_, &index, &ps, &cs_, &sampled, &wt.limit_ns, &wt.drop_step};
+  return fps_cluster_launch_any((const void *)fps_warpcast64_kernel<THREADS, P, SLOTS>, THREADS, B, smem, smem, st, rc,
+                                CL, args);
+}
+
 template <int THREADS, int P2>
 static bool fps_warpcast_launch(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
                                 float *sampled, cudaStream_t st, int *rc, int CL, FwWait wt) {
+  if (CL * (THREADS / 32) > 512 || (int64_t)CL * THREADS * 2 * P2 < N) return false;  // a slot per warp, a register per point
   if (CL * (THREADS / 32) <= 32)
     return fps_cluster_launch_kernel(fps_warpcast_kernel<THREADS, P2, 32>, THREADS, points, B, N, S, ps, cs, index,
                                      sampled, st, rc, CL, wt);
@@ -346,6 +531,27 @@ static bool fps_cluster_dispatch(const float *points, int64_t B, int64_t N, int6
   if (N <= 32768) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
   if (N <= 65536) return fps_warpcast_launch<128, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 16, wt);
   return fps_warpcast_launch<256, 16>(points, B, N, S, ps, cs, index, sampled, st, rc, 16, wt);
+}
+
+// float64: few clouds of 2049 to 8192 points (the one-block kernel's step is 1.1 us at 4096 points),
+// every cloud of 8193 to 131072 points (the streaming kernel otherwise).
+bool fps_cluster_f64(const double *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
+                     double *sampled, cudaStream_t st, int *rc) {
+  const FwWait wt{1000000000ull, -1};
+  if (N <= 2048 || N > 131072 || B * FC_MAX_CL >= (1LL << 31)) return false;
+  // Double-precision arithmetic makes the distance updates the longer part of the step, so the
+  // clouds are spread over more threads than in float32 (4 to 32 points per thread).  Measured, 256
+  // samples of 4 / 32 clouds, in ms: 4096 points 0.20 / 0.23 (one block per cloud 0.29), 8192 points
+  // 0.26 / 0.32 (0.46), 16384 points 0.29 / 0.38 (streaming kernel 2.2), 65536 points 0.57 / 1.8 (6.6).
+  if (N <= 8192) {
+    if (B * 15 > (int64_t)sm_count() * 8) return false;
+    if (N <= 4096) return fps_warpcast64_launch<128, 4, 32>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
+    return fps_warpcast64_launch<256, 4, 128>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
+  }
+  if (N <= 16384) return fps_warpcast64_launch<256, 8, 128>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
+  if (N <= 32768) return fps_warpcast64_launch<256, 16, 128>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
+  if (N <= 65536) return fps_warpcast64_launch<256, 16, 128>(points, B, N, S, ps, cs, index, sampled, st, rc, 16, wt);
+  return fps_warpcast64_launch<256, 32, 128>(points, B, N, S, ps, cs, index, sampled, st, rc, 16, wt);
 }
 
 bool fps_cluster_f32(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs, int64_t *index,
