@@ -6,8 +6,8 @@
 // 16384 points, and beyond that the streaming kernel re-reads the cloud and its running minima from
 // L2 in every step (4 clouds of 65536 points: 19 us per step).  Here a cluster of 8 or 16 small
 // blocks shares a cloud: every block keeps a contiguous slice of the points and their running
-// minima in registers (16 or 32 points per thread), and the step has no block or cluster barrier at
-// all -- see fps_warpcast_kernel.  32 clouds of 8192 points, 1024 samples: 0.53 ms against 0.70 ms;
+// minima in registers (8 to 32 points per thread), and the step has no block or cluster barrier at
+// all -- see fps_warpcast_kernel.  32 clouds of 8192 points, 1024 samples: 0.56 ms against 0.70 ms;
 // 4 clouds of 65536 points, 2048 samples: 2.0 ms against 39.9 ms for the streaming kernel.
 //
 // Measured and dropped: the same clusters with 1024-thread blocks that reduce inside the block
@@ -505,21 +505,24 @@ static bool fps_warpcast_launch(const float *points, int64_t B, int64_t N, int64
 // when they do not or when the device refuses the cluster launch (the caller then takes its own
 // path), true with *rc set otherwise.
 //
-// 4097 to 16384 points and few clouds: the barrier-free kernel on clusters of eight small blocks
-// (two warps each up to 8192 points, four beyond; 16 points per thread).  Measured on B200, 512
-// samples, against one 1024-thread block per cloud (fps_resident_kernel), in ms:
-//   clouds            1      16     37     64     96
-//   N =  8192  here   0.253  0.269  0.286  0.300  0.358     one block  0.356
-//   N = 16384  here   0.303  0.336  0.374  0.448  0.762     one block  0.699
-// (four blocks of 256 threads: 0.261 / 0.264 / 0.320 / 0.325 / 0.404 at N = 8192).  Beyond about
-// half a cloud per SM the blocks of several clusters share SMs and the one-block kernel is as fast;
-// up to 4096 points its step (0.43 us) is shorter than the exchange over distributed shared
-// memory (0.5 us).
+// 4097 to 16384 points and few clouds: up to 8192 points clusters of four blocks of 256 threads (8
+// points per thread), beyond that eight blocks of 128 threads (16 points per thread).  Measured on
+// two B200s, 512 samples, against one 1024-thread block per cloud (fps_resident_kernel), in ms:
+//   clouds                      4      32     64     96
+//   N =  8192  4 x 256 threads  0.26-0.27  0.28  0.33   0.40     one block  0.356
+//              8 x  64 threads  0.25-0.29  0.27-0.31  0.30-0.33  0.36   (faster on one GPU, slower on the other)
+//   N = 16384  8 x 128 threads  0.30   0.34-0.37  0.45   0.76     one block  0.699
+// Beyond about half a cloud per SM the blocks of several clusters share SMs and the one-block
+// kernel is as fast; up to 4096 points its step (0.43 us) is shorter than the exchange over
+// distributed shared memory (0.45 to 0.5 us).
 static bool fps_cluster_dispatch(const float *points, int64_t B, int64_t N, int64_t S, int ps, int64_t cs,
                                  int64_t *index, float *sampled, cudaStream_t st, int *rc, FwWait wt, bool force) {
   if (N > 4096 && N <= 16384) {
+    if (N <= 8192) {
+      if (!force && B * 15 > (int64_t)sm_count() * 7) return false;
+      return fps_warpcast_launch<256, 4>(points, B, N, S, ps, cs, index, sampled, st, rc, 4, wt);
+    }
     if (!force && B * 15 > (int64_t)sm_count() * 8) return false;
-    if (N <= 8192) return fps_warpcast_launch<64, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
     return fps_warpcast_launch<128, 8>(points, B, N, S, ps, cs, index, sampled, st, rc, 8, wt);
   }
   if (N <= 16384 || N > 262144 || B * FC_MAX_CL >= (1LL << 31)) return false;
