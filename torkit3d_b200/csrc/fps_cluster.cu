@@ -4,7 +4,7 @@
 // The resident kernel of fps.cu keeps a cloud in the registers of ONE block: its step is a chain of
 // two block barriers over 32 warps and two block reductions (0.69 us at 8192 points), it ends at
 // 16384 points, and beyond that the streaming kernel re-reads the cloud and its running minima from
-// L2 in every step (4 clouds of 65536 points: 19 us per step).  Here a cluster of 8 or 16 small
+// L2 in every step (4 clouds of 65536 points: 19 us per step).  Here a cluster of 4, 8 or 16 small
 // blocks shares a cloud: every block keeps a contiguous slice of the points and their running
 // minima in registers (8 to 32 points per thread), and the step has no block or cluster barrier at
 // all -- see fps_warpcast_kernel.  32 clouds of 8192 points, 1024 samples: 0.56 ms against 0.70 ms;
