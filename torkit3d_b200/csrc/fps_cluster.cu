@@ -37,9 +37,10 @@ constexpr int FC_MAX_CL = 16;  // 8 is the portable cluster size; 16 needs an op
 // and mbarriers are double buffered by the step's parity: a warp can send for step i+2 only after
 // it has seen every warp's candidate of step i+1, which those warps send after they have read
 // step i.  The fewer warps a cluster has the shorter the step (its floor is the exchange over
-// distributed shared memory, about 0.45 us), hence 16 or 32 points per thread.  Every wait is
-// limited to one second; a warp that runs into the limit marks the rest of its cloud's output
-// with -1 and leaves.
+// distributed shared memory, about 0.45 us), hence up to 32 points per thread.  Every wait is
+// limited (limit_ns: one second in regular calls); a warp that runs into the limit stops, the
+// rest of its cloud's index row is set to -1, fw_expired_waits counts it, and every block still
+// leaves through the final cluster barrier.
 struct __align__(16) FwCandidate {
   unsigned bits;
   int idx;
